@@ -1,0 +1,701 @@
+// C ABI of the library (include/ckb200.h): argument validation, tensor-map construction and
+// kernel launches.  There is no CPU path in this file: every *_run either launches the sm_100a
+// kernels or returns an error.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/ckb200.h"
+#include "ckb_launch.cuh"
+
+namespace {
+
+using namespace ckb;
+
+thread_local std::string t_last_error;
+std::atomic<uint64_t> g_launches{0};
+
+// Device status word read by the kernels through KernelParams::status.
+__device__ uint32_t g_status_word;
+
+int fail(int code, const char* fmt, ...)
+{
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    t_last_error = buf;
+    return code;
+}
+
+#define CKB_CUDA(expr)                                                                          \
+    do                                                                                          \
+    {                                                                                           \
+        cudaError_t e__ = (expr);                                                               \
+        if(e__ != cudaSuccess)                                                                  \
+            return fail(CKB_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e__));         \
+    } while(0)
+
+// ---- driver entry points for tensor-map encoding (no link-time libcuda dependency) -------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+typedef CUresult (*EncodeIm2colFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const int*, const int*,
+                                   cuuint32_t, cuuint32_t, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+
+EncodeTiledFn g_encode_tiled   = nullptr;
+EncodeIm2colFn g_encode_im2col = nullptr;
+std::once_flag g_entry_once;
+int g_driver_version = 0;
+
+void load_entry_points()
+{
+    std::call_once(g_entry_once, [] {
+        void* fn                            = nullptr;
+        cudaDriverEntryPointQueryResult qres = cudaDriverEntryPointSymbolNotFound;
+        if(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) ==
+               cudaSuccess &&
+           qres == cudaDriverEntryPointSuccess)
+            g_encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
+        fn = nullptr;
+        if(cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &fn, cudaEnableDefault, &qres) ==
+               cudaSuccess &&
+           qres == cudaDriverEntryPointSuccess)
+            g_encode_im2col = reinterpret_cast<EncodeIm2colFn>(fn);
+        cudaDriverGetVersion(&g_driver_version);
+    });
+}
+
+struct DeviceInfo
+{
+    int sm_count = 0;
+    int cc_major = 0, cc_minor = 0;
+    uint32_t* status = nullptr;
+    bool ready       = false;
+};
+DeviceInfo g_dev[64];
+std::mutex g_dev_mutex;
+
+int current_device(DeviceInfo** out)
+{
+    int dev = 0;
+    CKB_CUDA(cudaGetDevice(&dev));
+    if(dev < 0 || dev >= 64)
+        return fail(CKB_ERR_INVALID, "device ordinal %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    DeviceInfo& d = g_dev[dev];
+    if(!d.ready)
+    {
+        cudaDeviceProp prop;
+        CKB_CUDA(cudaGetDeviceProperties(&prop, dev));
+        d.sm_count = prop.multiProcessorCount;
+        d.cc_major = prop.major;
+        d.cc_minor = prop.minor;
+        if(prop.major != 10)
+            return fail(CKB_ERR_UNSUPPORTED,
+                        "device '%s' is compute capability %d.%d; this library holds sm_100a code only",
+                        prop.name, prop.major, prop.minor);
+        void* sym = nullptr;
+        CKB_CUDA(cudaGetSymbolAddress(&sym, g_status_word));
+        d.status = static_cast<uint32_t*>(sym);
+        CKB_CUDA(cudaMemset(d.status, 0, sizeof(uint32_t)));
+        d.ready = true;
+    }
+    *out = &d;
+    return CKB_OK;
+}
+
+uint64_t wait_limit_ns()
+{
+    static uint64_t v = [] {
+        const char* s = getenv("CKB_WAIT_LIMIT_MS");
+        double ms     = s ? atof(s) : 2000.0;
+        if(ms <= 0)
+            ms = 2000.0;
+        return static_cast<uint64_t>(ms * 1e6);
+    }();
+    return v;
+}
+
+int forced_bn()
+{
+    const char* s = getenv("CKB_FORCE_BN");
+    return s ? atoi(s) : 0;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int elem_bytes(int dtype) { return dtype == CKB_I8 ? 1 : 2; }
+
+CUtensorMapDataType tm_dtype(int dtype)
+{
+    return dtype == CKB_I8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                           : dtype == CKB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                               : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+}
+
+// K-major matrix [rows][k] with row pitch `ld` elements -> 2-D map, box = 128 bytes x box_rows.
+int encode_kmajor_2d(CUtensorMap* tm, int dtype, const void* ptr, int64_t rows, int64_t k,
+                     int64_t ld, int box_rows)
+{
+    load_entry_points();
+    if(!g_encode_tiled)
+        return fail(CKB_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+    const int eb          = elem_bytes(dtype);
+    cuuint64_t dims[2]    = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * eb};
+    cuuint32_t box[2]     = {static_cast<cuuint32_t>(BK_BYTES / eb), static_cast<cuuint32_t>(box_rows)};
+    cuuint32_t estr[2]    = {1, 1};
+    CUresult r            = g_encode_tiled(tm, tm_dtype(dtype), 2, const_cast<void*>(ptr), dims, strides,
+                                box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if(r != CUDA_SUCCESS)
+        return fail(CKB_ERR_CUDA, "cuTensorMapEncodeTiled failed (CUresult %d) rows=%lld k=%lld ld=%lld",
+                    static_cast<int>(r), (long long)rows, (long long)k, (long long)ld);
+    return CKB_OK;
+}
+
+int pick_bn(int64_t M, int64_t N, int sm_count)
+{
+    const int f = forced_bn();
+    if(f == 256 || f == 128 || f == 64)
+        return f;
+    if(N <= 64)
+        return 64;
+    if(N <= 128)
+        return 128;
+    // Prefer the 256-wide tile (lowest shared-memory traffic per flop) unless it leaves most of
+    // the machine idle.
+    const int64_t tiles256 = ((M + BM - 1) / BM) * ((N + 255) / 256);
+    if(tiles256 < sm_count / 2)
+        return 128;
+    return 256;
+}
+
+bool epilogue_valid_for(int epi, int ab_dtype)
+{
+    if(epi < 0 || epi >= CKB_EPI_COUNT_)
+        return false;
+    if(ab_dtype == CKB_I8)
+        return epi == CKB_EPI_PASSTHROUGH || epi == CKB_EPI_RELU ||
+               epi == CKB_EPI_REQUANT_RELU_REQUANT || epi == CKB_EPI_REQUANT_RELU_REQUANT_RNE;
+    return epi != CKB_EPI_REQUANT_RELU_REQUANT && epi != CKB_EPI_REQUANT_RELU_REQUANT_RNE;
+}
+
+// Shared validation of one GEMM problem.  `why` receives the reason on failure.
+int check_gemm(const ckb_gemm_desc* d, bool need_pointers)
+{
+    if(!d)
+        return fail(CKB_ERR_INVALID, "null descriptor");
+    if(d->ab_dtype != CKB_F16 && d->ab_dtype != CKB_I8)
+        return fail(CKB_ERR_UNSUPPORTED, "A/B dtype %d not supported (f16 and int8 are)", d->ab_dtype);
+    if(d->e_dtype != d->ab_dtype)
+        return fail(CKB_ERR_UNSUPPORTED, "E dtype must equal the A/B dtype (f16->f16, int8->int8)");
+    if(d->a_layout != CKB_ROW_MAJOR || d->b_layout != CKB_COL_MAJOR || d->e_layout != CKB_ROW_MAJOR)
+        return fail(CKB_ERR_UNSUPPORTED,
+                    "only A row-major, B column-major, E row-major (both operands K-contiguous) is supported");
+    if(!epilogue_valid_for(d->epilogue, d->ab_dtype))
+        return fail(CKB_ERR_UNSUPPORTED, "epilogue %d not available for dtype %d", d->epilogue, d->ab_dtype);
+    if(d->n_ds != epi_num_d(d->epilogue))
+        return fail(CKB_ERR_INVALID, "epilogue %d reads %d D tensors, descriptor gives %d", d->epilogue,
+                    epi_num_d(d->epilogue), d->n_ds);
+    if(d->M < 1 || d->N < 1 || d->K < 1)
+        return fail(CKB_ERR_UNSUPPORTED, "M, N, K must be positive");
+    if(d->M > 0x7FFFFF00ll || d->N > 0x7FFFFF00ll || d->K > 0x7FFFFF00ll)
+        return fail(CKB_ERR_UNSUPPORTED, "M, N, K must fit in int32");
+    const int eb = elem_bytes(d->ab_dtype);
+    if(d->lda < d->K || d->ldb < d->K || d->lde < d->N)
+        return fail(CKB_ERR_INVALID, "leading dimension smaller than the row length");
+    if((d->lda * eb) % 16 != 0 || (d->ldb * eb) % 16 != 0)
+        return fail(CKB_ERR_UNSUPPORTED, "lda and ldb must be multiples of 16 bytes (TMA row pitch)");
+    for(int i = 0; i < d->n_ds; ++i)
+        if(d->ldd[i] != 0 && d->ldd[i] < d->N)
+            return fail(CKB_ERR_INVALID, "ldd[%d] smaller than N", i);
+    if(need_pointers)
+    {
+        if(!d->p_a || !d->p_b || !d->p_e)
+            return fail(CKB_ERR_INVALID, "null tensor pointer");
+        if(!aligned16(d->p_a) || !aligned16(d->p_b))
+            return fail(CKB_ERR_UNSUPPORTED, "A and B must be 16-byte aligned");
+        for(int i = 0; i < d->n_ds; ++i)
+            if(!d->p_ds[i])
+                return fail(CKB_ERR_INVALID, "null D%d pointer", i);
+    }
+    return CKB_OK;
+}
+
+bool gemm_vec_ok(const ckb_gemm_desc* d)
+{
+    const int per16 = 16 / elem_bytes(d->ab_dtype);
+    bool ok         = aligned16(d->p_e) && d->lde % per16 == 0;
+    for(int i = 0; i < d->n_ds; ++i)
+        ok = ok && aligned16(d->p_ds[i]) && d->ldd[i] % per16 == 0;
+    return ok;
+}
+
+void fill_epilogue(EpilogueArgs& ea, const ckb_gemm_desc* d)
+{
+    ea.kind   = d->epilogue;
+    ea.out_i8 = d->ab_dtype == CKB_I8;
+    ea.bf16   = d->ab_dtype == CKB_BF16;
+    ea.pad_   = 0;
+    memcpy(ea.p, d->epi_params, sizeof(ea.p));
+    ea.e    = d->p_e;
+    ea.d0   = d->n_ds > 0 ? d->p_ds[0] : nullptr;
+    ea.d1   = d->n_ds > 1 ? d->p_ds[1] : nullptr;
+    ea.lde  = d->lde;
+    ea.ldd0 = d->n_ds > 0 ? d->ldd[0] : 0;
+    ea.ldd1 = d->n_ds > 1 ? d->ldd[1] : 0;
+}
+
+typedef cudaError_t (*LaunchFn)(int, const KernelParams&, int, cudaStream_t);
+
+// One launch, or the reference timing protocol (kernel_launch.hpp:12-74): a warm-up launch, then
+// n_rep launches between two events.
+int run_timed(LaunchFn fn, int bn, const KernelParams& p, int grid, cudaStream_t stream, int n_rep,
+              float* avg_ms)
+{
+    if(avg_ms)
+        *avg_ms = 0.f;
+    if(n_rep <= 0)
+    {
+        CKB_CUDA(fn(bn, p, grid, stream));
+        g_launches.fetch_add(1);
+        return CKB_OK;
+    }
+    CKB_CUDA(fn(bn, p, grid, stream)); // warm-up
+    g_launches.fetch_add(1);
+    cudaEvent_t start, stop;
+    CKB_CUDA(cudaEventCreate(&start));
+    CKB_CUDA(cudaEventCreate(&stop));
+    CKB_CUDA(cudaDeviceSynchronize());
+    CKB_CUDA(cudaEventRecord(start, stream));
+    for(int i = 0; i < n_rep; ++i)
+    {
+        cudaError_t e = fn(bn, p, grid, stream);
+        if(e != cudaSuccess)
+        {
+            cudaEventDestroy(start);
+            cudaEventDestroy(stop);
+            return fail(CKB_ERR_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
+        }
+    }
+    g_launches.fetch_add(n_rep);
+    CKB_CUDA(cudaEventRecord(stop, stream));
+    CKB_CUDA(cudaEventSynchronize(stop));
+    float total = 0.f;
+    CKB_CUDA(cudaEventElapsedTime(&total, start, stop));
+    cudaEventDestroy(start);
+    cudaEventDestroy(stop);
+    if(avg_ms)
+        *avg_ms = total / n_rep;
+    return CKB_OK;
+}
+
+} // namespace
+
+extern "C" {
+
+int ckb_abi_version(void) { return CKB_ABI_VERSION; }
+
+const char* ckb_last_error(void) { return t_last_error.c_str(); }
+
+uint64_t ckb_launch_count(void) { return g_launches.load(); }
+
+int ckb_device_info(char* name, size_t name_bytes, int* sm_count, int* cc_major, int* cc_minor)
+{
+    int dev = 0;
+    CKB_CUDA(cudaGetDevice(&dev));
+    cudaDeviceProp prop;
+    CKB_CUDA(cudaGetDeviceProperties(&prop, dev));
+    if(name && name_bytes)
+    {
+        strncpy(name, prop.name, name_bytes - 1);
+        name[name_bytes - 1] = 0;
+    }
+    if(sm_count)
+        *sm_count = prop.multiProcessorCount;
+    if(cc_major)
+        *cc_major = prop.major;
+    if(cc_minor)
+        *cc_minor = prop.minor;
+    return CKB_OK;
+}
+
+int ckb_device_status(uint32_t* word)
+{
+    DeviceInfo* dev = nullptr;
+    int rc          = current_device(&dev);
+    if(rc)
+        return rc;
+    CKB_CUDA(cudaDeviceSynchronize());
+    uint32_t w = 0;
+    CKB_CUDA(cudaMemcpy(&w, dev->status, sizeof(w), cudaMemcpyDeviceToHost));
+    if(w != 0)
+        CKB_CUDA(cudaMemset(dev->status, 0, sizeof(w)));
+    if(word)
+        *word = w;
+    if(w != 0)
+        return fail(CKB_ERR_DEVICE, "kernel wait timed out: code %u in block %u", w >> 24, w & 0xFFFFFFu);
+    return CKB_OK;
+}
+
+// ---- memory helpers -----------------------------------------------------------------------------
+int ckb_malloc(void** dev_ptr, size_t bytes)
+{
+    if(!dev_ptr)
+        return fail(CKB_ERR_INVALID, "null output pointer");
+    CKB_CUDA(cudaMalloc(dev_ptr, bytes));
+    return CKB_OK;
+}
+int ckb_free(void* dev_ptr)
+{
+    CKB_CUDA(cudaFree(dev_ptr));
+    return CKB_OK;
+}
+int ckb_memcpy_h2d(void* dev_dst, const void* host_src, size_t bytes)
+{
+    CKB_CUDA(cudaMemcpy(dev_dst, host_src, bytes, cudaMemcpyHostToDevice));
+    return CKB_OK;
+}
+int ckb_memcpy_d2h(void* host_dst, const void* dev_src, size_t bytes)
+{
+    CKB_CUDA(cudaMemcpy(host_dst, dev_src, bytes, cudaMemcpyDeviceToHost));
+    return CKB_OK;
+}
+int ckb_memset(void* dev_ptr, int value, size_t bytes)
+{
+    CKB_CUDA(cudaMemset(dev_ptr, value, bytes));
+    return CKB_OK;
+}
+int ckb_device_synchronize(void)
+{
+    CKB_CUDA(cudaDeviceSynchronize());
+    return CKB_OK;
+}
+
+// ---- GEMM ---------------------------------------------------------------------------------------
+int ckb_gemm_supported(const ckb_gemm_desc* desc) { return check_gemm(desc, false); }
+
+int ckb_gemm_run(const ckb_gemm_desc* d, void* stream, int n_rep, float* avg_ms)
+{
+    int rc = check_gemm(d, true);
+    if(rc)
+        return rc;
+    DeviceInfo* dev = nullptr;
+    rc              = current_device(&dev);
+    if(rc)
+        return rc;
+    const int bn = pick_bn(d->M, d->N, dev->sm_count);
+    const int eb = elem_bytes(d->ab_dtype);
+    KernelParams p;
+    memset(&p, 0, sizeof(p));
+    rc = encode_kmajor_2d(&p.tm_a, d->ab_dtype, d->p_a, d->M, d->K, d->lda, BM);
+    if(rc)
+        return rc;
+    rc = encode_kmajor_2d(&p.tm_b, d->ab_dtype, d->p_b, d->N, d->K, d->ldb, bn);
+    if(rc)
+        return rc;
+    fill_epilogue(p.epi, d);
+    const int64_t tiles_m = (d->M + BM - 1) / BM;
+    const int64_t tiles_n = (d->N + bn - 1) / bn;
+    if(tiles_m * tiles_n > 0x7FFFFFFFll)
+        return fail(CKB_ERR_UNSUPPORTED, "too many tiles");
+    p.total_tiles   = static_cast<int32_t>(tiles_m * tiles_n);
+    p.M             = static_cast<int32_t>(d->M);
+    p.N             = static_cast<int32_t>(d->N);
+    p.tiles_n       = static_cast<int32_t>(tiles_n);
+    const int bk    = BK_BYTES / eb;
+    p.num_kb        = static_cast<int32_t>((d->K + bk - 1) / bk);
+    p.vec_ok        = gemm_vec_ok(d) ? 1 : 0;
+    p.wait_limit_ns = wait_limit_ns();
+    p.status        = dev->status;
+    const int grid  = p.total_tiles < dev->sm_count ? p.total_tiles : dev->sm_count;
+    LaunchFn fn     = d->ab_dtype == CKB_I8 ? launch_gemm_i8 : launch_gemm_f16;
+    return run_timed(fn, bn, p, grid, static_cast<cudaStream_t>(stream), n_rep, avg_ms);
+}
+
+// ---- grouped GEMM -------------------------------------------------------------------------------
+static int check_grouped(const ckb_grouped_gemm_desc* g, bool need_pointers)
+{
+    if(!g || g->group_count < 1 || !g->groups)
+        return fail(CKB_ERR_INVALID, "grouped descriptor needs at least one group");
+    const ckb_gemm_desc& g0 = g->groups[0];
+    for(int i = 0; i < g->group_count; ++i)
+    {
+        const ckb_gemm_desc& gi = g->groups[i];
+        int rc                  = check_gemm(&gi, need_pointers);
+        if(rc)
+        {
+            std::string msg = "group " + std::to_string(i) + ": " + t_last_error;
+            t_last_error    = msg;
+            return rc;
+        }
+        if(gi.ab_dtype != g0.ab_dtype || gi.epilogue != g0.epilogue || gi.n_ds != g0.n_ds ||
+           memcmp(gi.epi_params, g0.epi_params, sizeof(g0.epi_params)) != 0)
+            return fail(CKB_ERR_UNSUPPORTED, "group %d: dtype / epilogue differ from group 0", i);
+    }
+    return CKB_OK;
+}
+
+int ckb_grouped_gemm_supported(const ckb_grouped_gemm_desc* desc) { return check_grouped(desc, false); }
+
+int ckb_grouped_gemm_workspace_size(const ckb_grouped_gemm_desc* desc, size_t* bytes)
+{
+    if(!desc || !bytes || desc->group_count < 1)
+        return fail(CKB_ERR_INVALID, "bad arguments");
+    *bytes = static_cast<size_t>(desc->group_count) * sizeof(GroupEntry) + 128; // + alignment slack
+    return CKB_OK;
+}
+
+int ckb_grouped_gemm_run(const ckb_grouped_gemm_desc* g, void* workspace, size_t workspace_bytes,
+                         void* stream_, int n_rep, float* avg_ms)
+{
+    int rc = check_grouped(g, true);
+    if(rc)
+        return rc;
+    size_t need = 0;
+    ckb_grouped_gemm_workspace_size(g, &need);
+    if(!workspace || workspace_bytes < need)
+        return fail(CKB_ERR_WORKSPACE, "grouped GEMM needs %zu bytes of device workspace, got %zu", need,
+                    workspace ? workspace_bytes : 0);
+    DeviceInfo* dev = nullptr;
+    rc              = current_device(&dev);
+    if(rc)
+        return rc;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    const int dtype     = g->groups[0].ab_dtype;
+    const int eb        = elem_bytes(dtype);
+    const int bk        = BK_BYTES / eb;
+    int64_t max_n = 0, sum_m = 0;
+    for(int i = 0; i < g->group_count; ++i)
+    {
+        max_n = max_n > g->groups[i].N ? max_n : g->groups[i].N;
+        sum_m += g->groups[i].M;
+    }
+    const int bn = pick_bn(sum_m, max_n, dev->sm_count);
+
+    std::vector<GroupEntry> table(g->group_count);
+    int64_t tile_start = 0;
+    for(int i = 0; i < g->group_count; ++i)
+    {
+        const ckb_gemm_desc& d = g->groups[i];
+        GroupEntry& ge         = table[i];
+        memset(&ge, 0, sizeof(ge));
+        rc = encode_kmajor_2d(&ge.tm_a, dtype, d.p_a, d.M, d.K, d.lda, BM);
+        if(rc)
+            return rc;
+        rc = encode_kmajor_2d(&ge.tm_b, dtype, d.p_b, d.N, d.K, d.ldb, bn);
+        if(rc)
+            return rc;
+        const int64_t tm = (d.M + BM - 1) / BM, tn = (d.N + bn - 1) / bn;
+        ge.M          = static_cast<int32_t>(d.M);
+        ge.N          = static_cast<int32_t>(d.N);
+        ge.K          = static_cast<int32_t>(d.K);
+        ge.tiles_n    = static_cast<int32_t>(tn);
+        ge.tile_start = static_cast<int32_t>(tile_start);
+        ge.num_kb     = static_cast<int32_t>((d.K + bk - 1) / bk);
+        ge.vec_ok     = gemm_vec_ok(&d) ? 1 : 0;
+        ge.e          = d.p_e;
+        ge.d0         = d.n_ds > 0 ? d.p_ds[0] : nullptr;
+        ge.d1         = d.n_ds > 1 ? d.p_ds[1] : nullptr;
+        ge.lde        = d.lde;
+        ge.ldd0       = d.n_ds > 0 ? d.ldd[0] : 0;
+        ge.ldd1       = d.n_ds > 1 ? d.ldd[1] : 0;
+        tile_start += tm * tn;
+        if(tile_start > 0x7FFFFFFFll)
+            return fail(CKB_ERR_UNSUPPORTED, "too many tiles");
+    }
+    uintptr_t ws_addr = (reinterpret_cast<uintptr_t>(workspace) + 127u) & ~static_cast<uintptr_t>(127u);
+    GroupEntry* d_table = reinterpret_cast<GroupEntry*>(ws_addr);
+    // Pageable source: the runtime stages the bytes before returning, so `table` may go out of scope.
+    CKB_CUDA(cudaMemcpyAsync(d_table, table.data(), table.size() * sizeof(GroupEntry),
+                             cudaMemcpyHostToDevice, stream));
+
+    KernelParams p;
+    memset(&p, 0, sizeof(p));
+    fill_epilogue(p.epi, &g->groups[0]);
+    p.groups        = d_table;
+    p.group_count   = g->group_count;
+    p.total_tiles   = static_cast<int32_t>(tile_start);
+    p.wait_limit_ns = wait_limit_ns();
+    p.status        = dev->status;
+    const int grid  = p.total_tiles < dev->sm_count ? p.total_tiles : dev->sm_count;
+    LaunchFn fn     = dtype == CKB_I8 ? launch_grouped_i8 : launch_grouped_f16;
+    return run_timed(fn, bn, p, grid, stream, n_rep, avg_ms);
+}
+
+// ---- conv2d forward -------------------------------------------------------------------------------
+static int check_conv(const ckb_conv2d_fwd_desc* d, bool need_pointers)
+{
+    if(!d)
+        return fail(CKB_ERR_INVALID, "null descriptor");
+    if(d->dtype != CKB_F16)
+        return fail(CKB_ERR_UNSUPPORTED, "conv2d forward supports f16 only");
+    const int e = d->epilogue;
+    if(!(e == CKB_EPI_PASSTHROUGH || e == CKB_EPI_RELU || e == CKB_EPI_ADD_RELU ||
+         e == CKB_EPI_ADD_HARDSWISH || e == CKB_EPI_ADD_RELU_ADD || e == CKB_EPI_ADD))
+        return fail(CKB_ERR_UNSUPPORTED, "epilogue %d not available for conv2d forward", e);
+    if(d->N < 1 || d->K < 1 || d->C < 1 || d->Hi < 1 || d->Wi < 1 || d->Y < 1 || d->X < 1)
+        return fail(CKB_ERR_UNSUPPORTED, "all extents must be positive");
+    if(d->stride_h < 1 || d->stride_w < 1 || d->dilation_h < 1 || d->dilation_w < 1 || d->pad_h < 0 ||
+       d->pad_w < 0 || d->pad_h_right < 0 || d->pad_w_right < 0)
+        return fail(CKB_ERR_INVALID, "strides and dilations must be >= 1, pads >= 0");
+    const int ho = (d->Hi + d->pad_h + d->pad_h_right - ((d->Y - 1) * d->dilation_h + 1)) / d->stride_h + 1;
+    const int wo = (d->Wi + d->pad_w + d->pad_w_right - ((d->X - 1) * d->dilation_w + 1)) / d->stride_w + 1;
+    if(ho != d->Ho || wo != d->Wo || ho < 1 || wo < 1)
+        return fail(CKB_ERR_INVALID, "Ho/Wo (%d,%d) do not match the convolution geometry (%d,%d)", d->Ho,
+                    d->Wo, ho, wo);
+    if(d->C % 8 != 0)
+        return fail(CKB_ERR_UNSUPPORTED, "C must be a multiple of 8 (16-byte pixel pitch for TMA)");
+    // Limits of the im2col tensor map: traversal stride <= 8, box corners within [-128, 127].
+    if(d->stride_h > 8 || d->stride_w > 8)
+        return fail(CKB_ERR_UNSUPPORTED, "convolution stride > 8 not supported");
+    const int up_h = d->pad_h_right - (d->Y - 1) * d->dilation_h;
+    const int up_w = d->pad_w_right - (d->X - 1) * d->dilation_w;
+    if(d->pad_h > 128 || d->pad_w > 128 || up_h < -128 || up_w < -128 || up_h > 127 || up_w > 127)
+        return fail(CKB_ERR_UNSUPPORTED, "padding / filter extent beyond the im2col box-corner range");
+    if((d->Y - 1) * d->dilation_h > 65535 || (d->X - 1) * d->dilation_w > 65535)
+        return fail(CKB_ERR_UNSUPPORTED, "filter offset beyond 16 bits");
+    const int64_t gm = static_cast<int64_t>(d->N) * d->Ho * d->Wo;
+    if(gm > 0x7FFFFF00ll)
+        return fail(CKB_ERR_UNSUPPORTED, "N*Ho*Wo must fit in int32");
+    // 2 GB per-tensor limit of the reference (device_convnd_fwd_xdl_nhwc_kyxc_nhwk.hpp:884-892)
+    const int64_t two_gb = int64_t(1) << 31;
+    if(static_cast<int64_t>(d->N) * d->Hi * d->Wi * d->C * 2 > two_gb || gm * d->K * 2 > two_gb)
+        return fail(CKB_ERR_UNSUPPORTED, "tensor larger than 2 GB");
+    const int nd = epi_num_d(e);
+    if(need_pointers)
+    {
+        if(!d->p_in || !d->p_wei || !d->p_out)
+            return fail(CKB_ERR_INVALID, "null tensor pointer");
+        if(!aligned16(d->p_in) || !aligned16(d->p_wei))
+            return fail(CKB_ERR_UNSUPPORTED, "input and weights must be 16-byte aligned");
+        if(nd >= 1 && !d->p_bias)
+            return fail(CKB_ERR_INVALID, "epilogue needs a bias pointer");
+        if(nd >= 2 && !d->p_resi)
+            return fail(CKB_ERR_INVALID, "epilogue needs a residual pointer");
+    }
+    return CKB_OK;
+}
+
+int ckb_conv2d_fwd_supported(const ckb_conv2d_fwd_desc* desc) { return check_conv(desc, false); }
+
+int ckb_conv2d_fwd_run(const ckb_conv2d_fwd_desc* d, void* stream, int n_rep, float* avg_ms)
+{
+    int rc = check_conv(d, true);
+    if(rc)
+        return rc;
+    DeviceInfo* dev = nullptr;
+    rc              = current_device(&dev);
+    if(rc)
+        return rc;
+    load_entry_points();
+    if(!g_encode_im2col || !g_encode_tiled)
+        return fail(CKB_ERR_CUDA, "tensor-map entry points not available");
+    const int64_t gm = static_cast<int64_t>(d->N) * d->Ho * d->Wo;
+    const int bn     = pick_bn(gm, d->K, dev->sm_count);
+    const int bk     = BK_BYTES / 2; // channels per stage
+
+    KernelParams p;
+    memset(&p, 0, sizeof(p));
+    {
+        // Input as (C, W, H, N); the column of 128 output pixels is walked by the TMA unit.
+        cuuint64_t dims[4]    = {static_cast<cuuint64_t>(d->C), static_cast<cuuint64_t>(d->Wi),
+                              static_cast<cuuint64_t>(d->Hi), static_cast<cuuint64_t>(d->N)};
+        cuuint64_t strides[3] = {static_cast<cuuint64_t>(d->C) * 2,
+                                 static_cast<cuuint64_t>(d->Wi) * d->C * 2,
+                                 static_cast<cuuint64_t>(d->Hi) * d->Wi * d->C * 2};
+        int lower[2]          = {-d->pad_w, -d->pad_h};
+        int upper[2]          = {d->pad_w_right - (d->X - 1) * d->dilation_w,
+                        d->pad_h_right - (d->Y - 1) * d->dilation_h};
+        cuuint32_t estr[4]    = {1, static_cast<cuuint32_t>(d->stride_w),
+                              static_cast<cuuint32_t>(d->stride_h), 1};
+        CUresult r = g_encode_im2col(&p.tm_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                                     const_cast<void*>(d->p_in), dims, strides, lower, upper,
+                                     static_cast<cuuint32_t>(bk), static_cast<cuuint32_t>(BM), estr,
+                                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if(r != CUDA_SUCCESS)
+            return fail(CKB_ERR_CUDA, "cuTensorMapEncodeIm2col failed (CUresult %d)", static_cast<int>(r));
+        // Drivers up to CUDA 13.1 mis-encode im2col maps of tensors smaller than 128 KiB; the
+        // published remedy (CUTLASS, cute/atom/copy_traits_sm90_im2col.hpp) clears bit 21 of the
+        // descriptor's second 64-bit word.
+        const int64_t in_bytes = static_cast<int64_t>(d->N) * d->Hi * d->Wi * d->C * 2;
+        if(g_driver_version <= 13010 && in_bytes < 131072)
+            reinterpret_cast<uint64_t*>(&p.tm_a)[1] &= ~(1ull << 21);
+    }
+    {
+        // Weights KYXC as (C, Y*X, K): a box never crosses a filter tap, channels beyond C read 0.
+        cuuint64_t dims[3]    = {static_cast<cuuint64_t>(d->C), static_cast<cuuint64_t>(d->Y) * d->X,
+                              static_cast<cuuint64_t>(d->K)};
+        cuuint64_t strides[2] = {static_cast<cuuint64_t>(d->C) * 2,
+                                 static_cast<cuuint64_t>(d->Y) * d->X * d->C * 2};
+        cuuint32_t box[3]     = {static_cast<cuuint32_t>(bk), 1, static_cast<cuuint32_t>(bn)};
+        cuuint32_t estr[3]    = {1, 1, 1};
+        CUresult r = g_encode_tiled(&p.tm_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                                    const_cast<void*>(d->p_wei), dims, strides, box, estr,
+                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if(r != CUDA_SUCCESS)
+            return fail(CKB_ERR_CUDA, "cuTensorMapEncodeTiled (weights) failed (CUresult %d)",
+                        static_cast<int>(r));
+    }
+    const int nd = epi_num_d(d->epilogue);
+    p.epi.kind   = d->epilogue;
+    memcpy(p.epi.p, d->epi_params, sizeof(p.epi.p));
+    p.epi.e    = d->p_out;
+    p.epi.lde  = d->K;
+    p.epi.d0   = nd >= 1 ? d->p_bias : nullptr;
+    p.epi.ldd0 = 0;
+    p.epi.d1   = nd >= 2 ? d->p_resi : nullptr;
+    p.epi.ldd1 = d->K;
+    bool vec   = aligned16(d->p_out) && d->K % 8 == 0;
+    if(nd >= 1)
+        vec = vec && aligned16(d->p_bias);
+    if(nd >= 2)
+        vec = vec && aligned16(d->p_resi);
+    const int64_t tiles_m = (gm + BM - 1) / BM;
+    const int64_t tiles_n = (d->K + bn - 1) / bn;
+    if(tiles_m * tiles_n > 0x7FFFFFFFll)
+        return fail(CKB_ERR_UNSUPPORTED, "too many tiles");
+    p.total_tiles   = static_cast<int32_t>(tiles_m * tiles_n);
+    p.M             = static_cast<int32_t>(gm);
+    p.N             = d->K;
+    p.tiles_n       = static_cast<int32_t>(tiles_n);
+    p.conv.Ho       = d->Ho;
+    p.conv.Wo       = d->Wo;
+    p.conv.HoWo     = d->Ho * d->Wo;
+    p.conv.Y        = d->Y;
+    p.conv.X        = d->X;
+    p.conv.c_blocks = (d->C + bk - 1) / bk;
+    p.conv.stride_h = d->stride_h;
+    p.conv.stride_w = d->stride_w;
+    p.conv.dil_h    = d->dilation_h;
+    p.conv.dil_w    = d->dilation_w;
+    p.conv.pad_h    = d->pad_h;
+    p.conv.pad_w    = d->pad_w;
+    p.num_kb        = d->Y * d->X * p.conv.c_blocks;
+    p.vec_ok        = vec ? 1 : 0;
+    p.wait_limit_ns = wait_limit_ns();
+    p.status        = dev->status;
+    const int grid  = p.total_tiles < dev->sm_count ? p.total_tiles : dev->sm_count;
+    return run_timed(launch_conv_f16, bn, p, grid, static_cast<cudaStream_t>(stream), n_rep, avg_ms);
+}
+
+} // extern "C"

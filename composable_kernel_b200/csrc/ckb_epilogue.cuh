@@ -1,0 +1,221 @@
+// Device-side fused epilogues.  Each function is the device twin of a Composable Kernel
+// element-wise functor (citations in include/ckb200.h next to the CKB_EPI_* ids) and is
+// written operation by operation like the host functor: fp32 arithmetic without fused
+// multiply-add (the library is compiled with -fmad=false), binary16 arithmetic through the
+// correctly rounded __hadd, one final rounding to the output type.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#include "../../include/ckb200.h"
+
+namespace ckb {
+
+struct EpilogueArgs
+{
+    int32_t kind;   // CKB_EPI_*
+    int32_t out_i8; // 1: E is int8 (accumulator is int32), 0: E is 16-bit float
+    int32_t bf16;   // 1: 16-bit float type is bfloat16
+    int32_t pad_;
+    float p[4];
+    void* e;
+    const void* d0;
+    const void* d1;
+    int64_t lde, ldd0, ldd1; // row strides in elements (ldd = 0: broadcast row)
+};
+
+__host__ __device__ constexpr int epi_num_d(int kind)
+{
+    return (kind == CKB_EPI_ADD || kind == CKB_EPI_ADD_RELU_F16 || kind == CKB_EPI_BILINEAR ||
+            kind == CKB_EPI_ADD_RELU || kind == CKB_EPI_ADD_HARDSWISH)
+               ? 1
+               : (kind == CKB_EPI_ADD_ADD_FASTGELU || kind == CKB_EPI_ADD_RELU_ADD) ? 2 : 0;
+}
+
+__device__ __forceinline__ float fast_gelu_dev(float x)
+{
+    const float u   = 2.0f * x * (0.035677f * x * x + 0.797885f);
+    const float emu = expf(-u);
+    const float cdf = 0.5f + 0.5f * (2.0f / (1.0f + emu) - 1.0f);
+    return x * cdf;
+}
+
+// 16-bit float helpers (T = __half or __nv_bfloat16)
+template <typename T>
+__device__ __forceinline__ T from_f32(float x);
+template <>
+__device__ __forceinline__ __half from_f32<__half>(float x)
+{
+    return __float2half_rn(x);
+}
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x)
+{
+    return __float2bfloat16_rn(x);
+}
+__device__ __forceinline__ float to_f32(__half x) { return __half2float(x); }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+// One output element, 16-bit float output.
+template <int EPI, typename T>
+__device__ __forceinline__ T epi_apply_f(float c, T d0, T d1, const float* p)
+{
+    if constexpr(EPI == CKB_EPI_PASSTHROUGH)
+        return from_f32<T>(c);
+    else if constexpr(EPI == CKB_EPI_SCALE)
+        return from_f32<T>(p[0] * c);
+    else if constexpr(EPI == CKB_EPI_RELU)
+        return from_f32<T>(c > 0.0f ? c : 0.0f);
+    else if constexpr(EPI == CKB_EPI_FASTGELU)
+        return from_f32<T>(fast_gelu_dev(c));
+    else if constexpr(EPI == CKB_EPI_ADD)
+        return __hadd(from_f32<T>(c), d0);
+    else if constexpr(EPI == CKB_EPI_ADD_RELU_F16)
+    {
+        const T x = __hadd(from_f32<T>(c), d0);
+        return to_f32(x) > 0.0f ? x : from_f32<T>(0.0f);
+    }
+    else if constexpr(EPI == CKB_EPI_BILINEAR)
+        return from_f32<T>(p[0] * c + p[1] * to_f32(d0));
+    else if constexpr(EPI == CKB_EPI_ADD_ADD_FASTGELU)
+        return from_f32<T>(fast_gelu_dev(c + to_f32(d0) + to_f32(d1)));
+    else if constexpr(EPI == CKB_EPI_ADD_RELU_ADD)
+    {
+        const float a = c + to_f32(d0);
+        const float b = a > 0.0f ? a : 0.0f;
+        return from_f32<T>(b + to_f32(d1));
+    }
+    else if constexpr(EPI == CKB_EPI_ADD_RELU)
+    {
+        const float a = c + to_f32(d0);
+        return from_f32<T>(a > 0.0f ? a : 0.0f);
+    }
+    else if constexpr(EPI == CKB_EPI_ADD_HARDSWISH)
+    {
+        const float a = c + to_f32(d0);
+        const float b = a + 3.0f;
+        const float y = (b > 0.0f ? 1.0f : 0.0f) * (b > 6.0f ? 6.0f : b) * a * 0.166667f;
+        return from_f32<T>(y);
+    }
+    else
+        return from_f32<T>(c);
+}
+
+// One output element, int8 output, int32 accumulator.
+template <int EPI>
+__device__ __forceinline__ int32_t epi_apply_i8(int32_t acc, const float* p)
+{
+    if constexpr(EPI == CKB_EPI_REQUANT_RELU_REQUANT)
+    {
+        const float c            = __int2float_rn(acc);
+        const float gemm_requant = __fmul_rn(p[0], c);
+        const float relu         = gemm_requant > 0.0f ? gemm_requant : 0.0f;
+        const float relu_requant = __fmul_rn(p[1], relu);
+        const float y =
+            relu_requant > 127.0f ? 127.0f : relu_requant < -128.0f ? -128.0f : relu_requant;
+        return __float2int_rz(y); // static_cast<int8_t>(float): toward zero
+    }
+    else if constexpr(EPI == CKB_EPI_REQUANT_RELU_REQUANT_RNE)
+    {
+        const float c  = __int2float_rn(acc);
+        const float q0 = rintf(__fmul_rn(p[0], c)); // round-to-nearest-even
+        const float r  = q0 > 0.0f ? q0 : 0.0f;
+        const float q1 = rintf(__fmul_rn(p[1], r));
+        const float y  = q1 > 127.0f ? 127.0f : q1 < -128.0f ? -128.0f : q1;
+        return __float2int_rz(y);
+    }
+    else if constexpr(EPI == CKB_EPI_RELU)
+    {
+        const float c = __int2float_rn(acc);
+        return __float2int_rz(c > 0.0f ? c : 0.0f);
+    }
+    else
+        return acc; // PassThrough: the store keeps the low 8 bits (static_cast<int8_t>(int32))
+}
+
+// Stores one row segment of `ncols` (<= 32) outputs starting at column n0 of row m.
+// v[] holds the accumulator bits of 32 consecutive columns.
+template <int EPI, typename T>
+__device__ __forceinline__ void epi_store_row_f(const uint32_t (&v)[32], const EpilogueArgs& ea,
+                                                int64_t m, int64_t n0, int ncols, bool vec_ok)
+{
+    constexpr int ND = epi_num_d(EPI);
+    T* e_row         = static_cast<T*>(ea.e) + m * ea.lde + n0;
+    const T* d0_row  = ND >= 1 ? static_cast<const T*>(ea.d0) + m * ea.ldd0 + n0 : nullptr;
+    const T* d1_row  = ND >= 2 ? static_cast<const T*>(ea.d1) + m * ea.ldd1 + n0 : nullptr;
+    if(ncols == 32 && vec_ok)
+    {
+#pragma unroll
+        for(int j = 0; j < 4; ++j) // 4 x 8 elements = 4 x 128-bit
+        {
+            uint4 q0 = make_uint4(0, 0, 0, 0), q1 = make_uint4(0, 0, 0, 0);
+            if constexpr(ND >= 1)
+                q0 = __ldg(reinterpret_cast<const uint4*>(d0_row) + j);
+            if constexpr(ND >= 2)
+                q1 = __ldg(reinterpret_cast<const uint4*>(d1_row) + j);
+            const T* h0 = reinterpret_cast<const T*>(&q0);
+            const T* h1 = reinterpret_cast<const T*>(&q1);
+            uint4 out;
+            T* ho = reinterpret_cast<T*>(&out);
+#pragma unroll
+            for(int i = 0; i < 8; ++i)
+                ho[i] = epi_apply_f<EPI, T>(__uint_as_float(v[j * 8 + i]), h0[i], h1[i], ea.p);
+            reinterpret_cast<uint4*>(e_row)[j] = out;
+        }
+    }
+    else
+    {
+#pragma unroll
+        for(int i = 0; i < 32; ++i)
+        {
+            if(i < ncols)
+            {
+                T a = from_f32<T>(0.0f), b = from_f32<T>(0.0f);
+                if constexpr(ND >= 1)
+                    a = d0_row[i];
+                if constexpr(ND >= 2)
+                    b = d1_row[i];
+                e_row[i] = epi_apply_f<EPI, T>(__uint_as_float(v[i]), a, b, ea.p);
+            }
+        }
+    }
+}
+
+template <int EPI>
+__device__ __forceinline__ void epi_store_row_i8(const uint32_t (&v)[32], const EpilogueArgs& ea,
+                                                 int64_t m, int64_t n0, int ncols, bool vec_ok)
+{
+    int8_t* e_row = static_cast<int8_t*>(ea.e) + m * ea.lde + n0;
+    if(ncols == 32 && vec_ok)
+    {
+#pragma unroll
+        for(int j = 0; j < 2; ++j) // 2 x 16 elements = 2 x 128-bit
+        {
+            uint32_t w[4];
+#pragma unroll
+            for(int k = 0; k < 4; ++k)
+            {
+                uint32_t packed = 0;
+#pragma unroll
+                for(int i = 0; i < 4; ++i)
+                {
+                    const int32_t r =
+                        epi_apply_i8<EPI>(static_cast<int32_t>(v[j * 16 + k * 4 + i]), ea.p);
+                    packed |= (static_cast<uint32_t>(r) & 0xFFu) << (8 * i);
+                }
+                w[k] = packed;
+            }
+            reinterpret_cast<uint4*>(e_row)[j] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+    }
+    else
+    {
+#pragma unroll
+        for(int i = 0; i < 32; ++i)
+            if(i < ncols)
+                e_row[i] = static_cast<int8_t>(epi_apply_i8<EPI>(static_cast<int32_t>(v[i]), ea.p));
+    }
+}
+
+} // namespace ckb

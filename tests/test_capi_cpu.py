@@ -1,0 +1,116 @@
+"""CPU tests of the C-ABI boundary: the library loads, exports every symbol the header declares,
+its structs have the layout the Python binding assumes, and argument validation (the
+IsSupportedArgument side) works without a GPU.  No compute call is made here."""
+import ctypes
+import os
+import re
+import subprocess
+import tempfile
+
+import pytest
+
+import composable_kernel_b200 as ck
+from composable_kernel_b200 import capi
+from oracle import ck_oracle as oracle
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "ckb200.h")
+
+
+def _declared_symbols():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(ckb_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    L = capi.lib()
+    names = _declared_symbols()
+    assert len(names) >= 18
+    for n in names:
+        assert hasattr(L, n), f"{n} declared in ckb200.h but not exported"
+        assert n in capi.SYMBOLS, f"{n} has no ctypes prototype"
+    assert L.ckb_abi_version() == 1
+
+
+def test_struct_layout_matches_header():
+    src = r'''
+    #include "ckb200.h"
+    #include <stdio.h>
+    #include <stddef.h>
+    int main(){ printf("%zu %zu %zu %zu %zu %zu\n", sizeof(ckb_gemm_desc), sizeof(ckb_conv2d_fwd_desc),
+      sizeof(ckb_grouped_gemm_desc), offsetof(ckb_gemm_desc, p_e), offsetof(ckb_gemm_desc, epi_params),
+      offsetof(ckb_conv2d_fwd_desc, p_in)); return 0; }'''
+    with tempfile.TemporaryDirectory() as td:
+        c = os.path.join(td, "t.c")
+        open(c, "w").write(src)
+        exe = os.path.join(td, "t")
+        subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), c, "-o", exe], check=True)
+        out = subprocess.run([exe], capture_output=True, text=True, check=True).stdout.split()
+    want = [ctypes.sizeof(capi.GemmDesc), ctypes.sizeof(capi.Conv2dFwdDesc), ctypes.sizeof(capi.GroupedGemmDesc),
+            capi.GemmDesc.p_e.offset, capi.GemmDesc.epi_params.offset, capi.Conv2dFwdDesc.p_in.offset]
+    assert [int(x) for x in out] == want
+
+
+def test_epilogue_ids_agree_between_header_binding_and_oracle():
+    text = open(HEADER).read()
+    for name, value in re.findall(r"(CKB_EPI_[A-Z0-9_]+)\s*=\s*(\d+)", text):
+        if name.endswith("COUNT_"):
+            continue
+        assert getattr(capi, name) == int(value)
+        assert getattr(oracle, name.replace("CKB_", "")) == int(value)
+
+
+def test_gemm_supported_rules():
+    op = ck.DeviceGemm()
+    ok = op.MakeArgument(0x1000, 0x2000, 0x3000, 3840, 4096, 4096, 4096, 4096, 4096)
+    assert op.IsSupportedArgument(ok)
+    # ragged sizes are fine (TMA zero-fills), as long as rows are 16-byte pitched
+    assert op.IsSupportedArgument(op.MakeArgument(0x1000, 0x2000, 0x3000, 100, 37, 72, 72, 72, 37))
+    assert not op.IsSupportedArgument(op.MakeArgument(0x1000, 0x2000, 0x3000, 100, 37, 70, 70, 70, 37))
+    assert "16 bytes" in capi.last_error()
+    assert not op.IsSupportedArgument(op.MakeArgument(0x1000, 0x2000, 0x3000, 0, 8, 8, 8, 8, 8))
+    # non-PassThrough A/B element ops cannot be applied by TMA
+    assert not op.IsSupportedArgument(op.MakeArgument(0x1000, 0x2000, 0x3000, 8, 8, 8, 8, 8, 8, ck.Scale(2.0)))
+    # layouts other than row x col
+    assert not ck.DeviceGemm(capi.CKB_F16, capi.CKB_COL_MAJOR, capi.CKB_COL_MAJOR).IsSupportedArgument(
+        ck.DeviceGemm(capi.CKB_F16, capi.CKB_COL_MAJOR, capi.CKB_COL_MAJOR).MakeArgument(
+            0x1000, 0x2000, 0x3000, 8, 8, 8, 8, 8, 8))
+    # int8 epilogues are int8-only
+    assert not op.IsSupportedArgument(op.MakeArgument(0x1000, 0x2000, 0x3000, 8, 8, 8, 8, 8, 8, None, None,
+                                                      ck.RequantReluRequant(0.03, 1.0)))
+    i8 = ck.DeviceGemm(capi.CKB_I8)
+    assert i8.IsSupportedArgument(i8.MakeArgument(0x1000, 0x2000, 0x3000, 3840, 4096, 4096, 4096, 4096, 4096,
+                                                  None, None, ck.RequantReluRequant(0.03, 1.0)))
+    # Run on an unsupported argument throws like the reference (device_gemm_xdl_cshuffle.hpp:475-481)
+    bad = op.MakeArgument(0x1000, 0x2000, 0x3000, 100, 37, 70, 70, 70, 37)
+    with pytest.raises(RuntimeError, match="invalid setting"):
+        op.MakeInvoker().Run(bad)
+
+
+def test_multiple_d_and_grouped_validation():
+    md = ck.DeviceGemmMultipleD()
+    arg = md.MakeArgument(0x1000, 0x2000, [0x4000, 0x5000], 0x3000, 3840, 4096, 4096, 4096, 4096, [0, 4096], 4096,
+                          None, None, ck.AddAddFastGelu())
+    assert md.IsSupportedArgument(arg)
+    arg = md.MakeArgument(0x1000, 0x2000, [0x4000], 0x3000, 3840, 4096, 4096, 4096, 4096, [0], 4096,
+                          None, None, ck.AddAddFastGelu())
+    assert not md.IsSupportedArgument(arg)  # functor reads two D tensors
+    g = ck.DeviceGroupedGemm()
+    descs = [ck.GemmDescHost(256 * (1 + i % 16), 4096, 4096, 4096, 4096, 4096) for i in range(64)]
+    ga = g.MakeArgument([0x1000] * 64, [0x2000] * 64, [], [0x3000] * 64, descs)
+    assert g.IsSupportedArgument(ga)
+    assert g.GetWorkSpaceSize(ga) >= 64 * 256
+    with pytest.raises(RuntimeError, match="group_count"):
+        g.MakeArgument([0x1000] * 3, [0x2000] * 64, [], [0x3000] * 64, descs)
+
+
+def test_conv_validation():
+    conv = ck.DeviceConvFwd()
+    mk = lambda **kw: conv.MakeArgument(0x1000, 0x2000, 0x3000, kw.get("N", 128), 256, kw.get("C", 192), (71, 71),
+                                        (3, 3), kw.get("out", (36, 36)), kw.get("s", (2, 2)), (1, 1), (1, 1), (1, 1),
+                                        None, None, ck.AddRelu(), p_bias=0x4000)
+    assert conv.IsSupportedArgument(mk())
+    assert not conv.IsSupportedArgument(mk(out=(35, 36)))      # inconsistent geometry
+    assert not conv.IsSupportedArgument(mk(C=12))               # pixel pitch not 16-byte
+    assert not conv.IsSupportedArgument(mk(s=(9, 9), out=(8, 8)))  # stride beyond the TMA limit
