@@ -1,0 +1,538 @@
+#!/usr/bin/env python
+"""Benchmark of the dense-contraction hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+Headline workload (default): fp16 GEMM 3840 x 4096 x 4096, A row-major, B column-major, fp32
+accumulate (the reference's example/01_gemm shape).  A "step" is one launch of the kernel over one
+set of synthetic inputs already resident in HBM; several input sets are rotated so that a step
+never finds its operands in L2.  Prints ONE JSON line on rank 0.
+
+N > 1 (launched under torch.distributed.run, one rank per GPU): the headline GEMM runs as
+independent replicas (weak scaling, no collective on the data path); the convolution is sharded
+over the batch and the grouped GEMM over groups (FLOP-balanced), reported under "workloads".
+
+--impl reference times the CPU restatement of the reference's own host operators (oracle/) on the
+host cores, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# fp16 GEMM 3840x4096x4096 on MI100: example/01_gemm/README.md:11-22 of the reference
+PUBLISHED_MI100_TFLOPS = {"gemm_fp16": 107.657, "gemm_fastgelu": 101.525, "conv": 105.581}
+FALLBACK_PEAK_TFLOPS = 1590.0
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return {"bf16_tflops": FALLBACK_PEAK_TFLOPS, "hbm_gbs": 6650.0}, "fallback"
+
+
+def ncu_traffic(workload):
+    """Per-launch DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of the workload's kernel,
+    taken from the committed ncu summary profiles/dram_traffic_per_launch.txt ("name bytes" lines)."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic_per_launch.txt")
+    if os.path.exists(path):
+        for ln in open(path):
+            parts = ln.split()
+            if len(parts) >= 2 and parts[0] == workload:
+                return float(parts[1])
+    return None
+
+
+# ------------------------------------------------------------------------------------------------
+# clocks sampling (NVML, read-only) during the timed region
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _loop(self):
+        nv = self._nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.001)
+
+    def start(self):
+        if self._nv:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ------------------------------------------------------------------------------------------------
+# workloads
+# ------------------------------------------------------------------------------------------------
+def lpt_partition(weights, parts):
+    """Longest-processing-time greedy: returns a list of index lists, one per part."""
+    order = sorted(range(len(weights)), key=lambda i: -weights[i])
+    loads, out = [0] * parts, [[] for _ in range(parts)]
+    for i in order:
+        j = loads.index(min(loads))
+        out[j].append(i)
+        loads[j] += weights[i]
+    return out
+
+
+class GemmWorkload:
+    """C1 / C2 / C3: M=3840 N=4096 K=4096, A row-major, B column-major."""
+
+    def __init__(self, name, torch, ck, capi):
+        self.name, self.torch, self.ck, self.capi = name, torch, ck, capi
+        self.M, self.N, self.K = 3840, 4096, 4096
+        self.i8 = name == "gemm_int8"
+        self.flop = 2 * self.M * self.N * self.K
+        eb = 1 if self.i8 else 2
+        self.bytes = eb * (self.M * self.K + self.K * self.N + self.M * self.N)
+        if name == "gemm_fastgelu":
+            self.bytes += 2 * self.N + 2 * self.M * self.N  # example/04...:202-204
+        self.dtype = "i8" if self.i8 else "f16"
+        self.unit = "TOPS" if self.i8 else "TFLOPS"
+        self.desc = {
+            "gemm_fp16": "fp16 GEMM 3840x4096x4096, A row-major, B column-major, fp32 accumulate, PassThrough",
+            "gemm_int8": "int8 GEMM 3840x4096x4096 + Requant-ReLU-Requant (rne, s0=0.03, s1=14), int32 accumulate",
+            "gemm_fastgelu": "fp16 GEMM 3840x4096x4096 + Add + Add + FastGelu (D0 bias stride 0, D1 MxN)",
+        }[name]
+
+    def host_inputs(self, seed):
+        rng = np.random.default_rng(seed)
+        M, N, K = self.M, self.N, self.K
+        if self.i8:
+            return [rng.integers(-5, 6, (M, K)).astype(np.int8), rng.integers(-5, 6, (N, K)).astype(np.int8)]
+        if self.name == "gemm_fp16":
+            return [rng.integers(-5, 6, (M, K)).astype(np.float16), rng.integers(-5, 6, (N, K)).astype(np.float16)]
+        return [rng.uniform(-1, 1, (M, K)).astype(np.float16), rng.uniform(-1, 1, (N, K)).astype(np.float16),
+                rng.uniform(-1, 1, (N,)).astype(np.float16), rng.uniform(-1, 1, (M, N)).astype(np.float16)]
+
+    def op(self):
+        ck = self.ck
+        return {"gemm_fp16": ck.PassThrough(), "gemm_int8": ck.RequantReluRequantRne(0.03, 14.0),
+                "gemm_fastgelu": ck.AddAddFastGelu()}[self.name]
+
+    def make_set(self, host):
+        torch = self.torch
+        dev = [torch.from_numpy(h).cuda() for h in host]
+        e = torch.empty((self.M, self.N), dtype=torch.int8 if self.i8 else torch.float16, device="cuda")
+        return self.bind(dev, e)
+
+    def bind(self, dev, e):
+        ck, capi = self.ck, self.capi
+        gemm = ck.DeviceGemmMultipleD(capi.CKB_I8 if self.i8 else capi.CKB_F16)
+        ds = [t.data_ptr() for t in dev[2:]]
+        lds = [0, self.N][:len(ds)]
+        arg = gemm.MakeArgument(dev[0].data_ptr(), dev[1].data_ptr(), ds, e.data_ptr(), self.M, self.N, self.K,
+                                self.K, self.K, lds, self.N, None, None, self.op())
+        if not gemm.IsSupportedArgument(arg):
+            raise RuntimeError("unsupported: " + capi.last_error())
+        return {"op": gemm, "arg": arg, "inv": gemm.MakeInvoker(), "dev": dev, "e": e}
+
+    def n_sets(self):
+        return 4  # 4 x ~96 MB (fp16) of operands: a set is out of the 126 MB L2 before it is reused
+
+    def oracle_rows(self, host, rows, oracle, threads):
+        """Reference CPU path on the first `rows` rows of E; returns flop done."""
+        a, bt = host[0][:rows], host[1]
+        d0 = np.broadcast_to(host[2], (rows, self.N)) if len(host) > 2 else None
+        d1 = host[3][:rows] if len(host) > 3 else None
+        op = self.op()
+        oracle.gemm(a, bt.T, op.kind, op.params, d0, d1, fast=False, threads=threads)
+        return 2 * rows * self.N * self.K
+
+
+class ConvWorkload:
+    """C4: N128 C192 71x71 K256 3x3 s2 p1 + bias + ReLU; batch-sharded over ranks."""
+
+    def __init__(self, torch, ck, capi, rank, world):
+        self.name, self.torch, self.ck, self.capi = "conv", torch, ck, capi
+        self.Ntot, self.C, self.Hi, self.Wi, self.K, self.Ho, self.Wo = 128, 192, 71, 71, 256, 36, 36
+        self.Nloc = self.Ntot // world
+        self.flop_total = 2 * self.Ntot * self.K * self.Ho * self.Wo * self.C * 9
+        self.flop = self.flop_total // world
+        self.bytes = 2 * (self.Nloc * self.C * self.Hi * self.Wi + self.K * self.C * 9 +
+                          self.Nloc * self.K * self.Ho * self.Wo) + 2 * self.K
+        self.dtype, self.unit = "f16", "TFLOPS"
+        self.desc = ("fp16 conv2d fwd NHWC/KYXC/NHWK + bias + ReLU, N128 C192 71x71 K256 3x3 s2 p1 "
+                     f"(batch shard {self.Nloc} per GPU)")
+        self.rank = rank
+
+    def host_inputs(self, seed):
+        rng = np.random.default_rng(seed)
+        return [rng.uniform(-1, 1, (self.Nloc, self.Hi, self.Wi, self.C)).astype(np.float16),
+                rng.uniform(-1, 1, (self.K, 3, 3, self.C)).astype(np.float16),
+                rng.uniform(-1, 1, (self.K,)).astype(np.float16)]
+
+    def make_set(self, host):
+        torch = self.torch
+        dev = [torch.from_numpy(h).cuda() for h in host]
+        e = torch.empty((self.Nloc, self.Ho, self.Wo, self.K), dtype=torch.float16, device="cuda")
+        return self.bind(dev, e)
+
+    def bind(self, dev, e):
+        ck = self.ck
+        conv = ck.DeviceConvFwd()
+        arg = conv.MakeArgument(dev[0].data_ptr(), dev[1].data_ptr(), e.data_ptr(), self.Nloc, self.K, self.C,
+                                (self.Hi, self.Wi), (3, 3), (self.Ho, self.Wo), (2, 2), (1, 1), (1, 1), (1, 1),
+                                None, None, ck.AddRelu(), p_bias=dev[2].data_ptr())
+        if not conv.IsSupportedArgument(arg):
+            raise RuntimeError("unsupported: " + self.capi.last_error())
+        return {"op": conv, "arg": arg, "inv": conv.MakeInvoker(), "dev": dev, "e": e}
+
+    def n_sets(self):
+        return 2  # one input shard is 248 MB at N=1; two sets stay beyond L2 down to 8 GPUs
+
+    def oracle_rows(self, host, images, oracle, threads):
+        oracle.conv2d_fwd(host[0][:images], host[1], (2, 2), (1, 1), (1, 1), epilogue=oracle.EPI_ADD_RELU,
+                          bias=host[2], fast=False, threads=threads)
+        return 2 * images * self.K * self.Ho * self.Wo * self.C * 9
+
+
+class GroupedWorkload:
+    """C5: 64 groups, M_g = 256*(1 + g mod 16), N = K = 4096; groups partitioned over ranks by LPT."""
+
+    def __init__(self, torch, ck, capi, rank, world):
+        self.name, self.torch, self.ck, self.capi = "grouped", torch, ck, capi
+        self.N = self.K = 4096
+        all_m = [256 * (1 + g % 16) for g in range(64)]
+        self.mine = sorted(lpt_partition(all_m, world)[rank])
+        self.Ms = [all_m[g] for g in self.mine]
+        self.flop_total = sum(2 * m * self.N * self.K for m in all_m)
+        self.flop = sum(2 * m * self.N * self.K for m in self.Ms)
+        self.bytes = sum(2 * (m * self.K + self.K * self.N + m * self.N) for m in self.Ms)
+        self.dtype, self.unit = "f16", "TFLOPS"
+        self.desc = (f"fp16 grouped GEMM, 64 groups M_g=256*(1+g%16) N=K=4096, "
+                     f"{len(self.mine)} groups on this GPU (FLOP-balanced LPT)")
+
+    def make_set(self, host=None):
+        torch, ck = self.torch, self.ck
+        gen = torch.Generator(device="cuda").manual_seed(11939 + 5000)
+        dA = [torch.empty((m, self.K), dtype=torch.float16, device="cuda").uniform_(-1, 1, generator=gen) for m in self.Ms]
+        dB = [torch.empty((self.N, self.K), dtype=torch.float16, device="cuda").uniform_(-1, 1, generator=gen) for _ in self.Ms]
+        dE = [torch.empty((m, self.N), dtype=torch.float16, device="cuda") for m in self.Ms]
+        gg = ck.DeviceGroupedGemm()
+        arg = gg.MakeArgument([x.data_ptr() for x in dA], [x.data_ptr() for x in dB], [], [x.data_ptr() for x in dE],
+                              [ck.GemmDescHost(m, self.N, self.K, self.K, self.K, self.N) for m in self.Ms])
+        ws = torch.empty(gg.GetWorkSpaceSize(arg), dtype=torch.uint8, device="cuda")
+        gg.SetWorkSpacePointer(arg, ws.data_ptr())
+        if not gg.IsSupportedArgument(arg):
+            raise RuntimeError("unsupported: " + self.capi.last_error())
+        return {"op": gg, "arg": arg, "inv": gg.MakeInvoker(), "dev": (dA, dB, ws), "e": dE}
+
+    def n_sets(self):
+        return 1  # > 0.5 GB of operands per GPU even at 8 GPUs: far beyond L2
+
+
+# ------------------------------------------------------------------------------------------------
+def time_steps(torch, sets, steps, warmup, stream_cfg, dist_barrier):
+    """W warm-up steps, then K timed steps bracketed by barrier + synchronize.  Returns
+    (total_ms over the K steps, [per-launch ms])."""
+    n = len(sets)
+    for i in range(warmup):
+        s = sets[i % n]
+        s["inv"].Run(s["arg"], stream_cfg)
+    torch.cuda.synchronize()
+    dist_barrier()
+    torch.cuda.synchronize()
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    evs[0].record()
+    for i in range(steps):
+        s = sets[i % n]
+        s["inv"].Run(s["arg"], stream_cfg)
+        evs[i + 1].record()
+    torch.cuda.synchronize()
+    dist_barrier()
+    torch.cuda.synchronize()
+    total = evs[0].elapsed_time(evs[steps])
+    per = [evs[i].elapsed_time(evs[i + 1]) for i in range(steps)]
+    return total, per
+
+
+def run_reference_arm(args, rank, world):
+    """CPU restatement of the reference's host operators, all host threads, bounded sample."""
+    if rank != 0:
+        return
+    from oracle import ck_oracle as oracle
+    name = args.workload
+    threads = oracle.hardware_concurrency()
+
+    class _NoTorch:
+        pass
+    if name in ("gemm_fp16", "gemm_int8", "gemm_fastgelu"):
+        wl = GemmWorkload(name, None, __import__("composable_kernel_b200"), None)
+        host = wl.host_inputs(11939)
+        unit_rows, full = 64, wl.M
+    elif name == "conv":
+        wl = ConvWorkload(None, __import__("composable_kernel_b200"), None, 0, 1)
+        host = wl.host_inputs(11939)
+        host[0] = host[0][:4]
+        unit_rows, full = 1, wl.Ntot
+    else:
+        wl = GemmWorkload("gemm_fp16", None, __import__("composable_kernel_b200"), None)
+        wl.desc = "fp16 grouped GEMM (one 256-row slice of a group: N=K=4096)"
+        host = wl.host_inputs(11939)
+        unit_rows, full = 64, wl.M
+    # size the per-step sample to roughly one second
+    t0 = time.perf_counter()
+    flop = wl.oracle_rows(host, unit_rows, oracle, threads)
+    dt = max(time.perf_counter() - t0, 1e-3)
+    rows = int(max(unit_rows, min(full if name != "conv" else 4, unit_rows * (1.0 / dt))))
+    for _ in range(args.warmup):
+        wl.oracle_rows(host, rows, oracle, threads)
+    t0 = time.perf_counter()
+    done = 0
+    for _ in range(args.steps):
+        done += wl.oracle_rows(host, rows, oracle, threads)
+    dt = time.perf_counter() - t0
+    value = done / dt / 1e12
+    sample = (f"{rows} of {full} output rows per step" if name != "conv" else f"{rows} of {full} images per step")
+    line = {
+        "impl": "reference", "metric": f"{wl.unit} (reference CPU path, host cores)", "value": value,
+        "unit": wl.unit, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": wl.dtype, "data": "synthetic", "config": {"workload": wl.desc, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": wl.unit, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="gemm_fp16",
+                    choices=["gemm_fp16", "gemm_int8", "gemm_fastgelu", "conv", "grouped"])
+    ap.add_argument("--no-extra", action="store_true", help="skip the other workloads / e2e / cpu baseline")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return 0
+
+    import torch
+    import composable_kernel_b200 as ck
+    from composable_kernel_b200 import capi
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the library has no CPU path")
+    capi.lib()
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        dist = dist_mod
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+
+    def max_over_ranks(x):
+        if dist is None:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    stream_cfg = ck.StreamConfig(torch.cuda.current_stream().cuda_stream, False)
+    peaks, peak_kind = measured_peaks()
+
+    def make_workload(name):
+        if name == "conv":
+            return ConvWorkload(torch, ck, capi, rank, world)
+        if name == "grouped":
+            return GroupedWorkload(torch, ck, capi, rank, world)
+        return GemmWorkload(name, torch, ck, capi)
+
+    def measure(name, steps, warmup, sample_clocks=False):
+        wl = make_workload(name)
+        hosts = None
+        if name == "grouped":
+            sets = [wl.make_set() for _ in range(wl.n_sets())]
+        else:
+            hosts = [wl.host_inputs(11939 + 17 * i + 1000 * rank) for i in range(wl.n_sets())]
+            sets = [wl.make_set(h) for h in hosts]
+        sampler = ClockSampler(local_rank) if sample_clocks else None
+        before = ck.launch_count()
+        if sampler:
+            sampler.start()
+        total_ms, per = time_steps(torch, sets, steps, warmup, stream_cfg, barrier)
+        clocks = sampler.stop() if sampler else None
+        launches = ck.launch_count() - before - warmup
+        if ck.device_status() != 0:
+            raise RuntimeError("kernel reported a wait time-out")
+        total_ms = max_over_ranks(total_ms)
+        sharded = name in ("conv", "grouped")
+        flop_job = (wl.flop_total if sharded else wl.flop * world)
+        value = flop_job * steps / (total_ms * 1e-3) / 1e12
+        kern_ms = statistics.mean(per)
+        achieved = wl.flop / (kern_ms * 1e-3) / 1e12
+        peak = peaks["bf16_tflops"] * (2.0 if wl.dtype == "i8" else 1.0)
+        res = {
+            "workload": wl.desc, "value": value, "unit": wl.unit, "ms_per_step": total_ms / steps,
+            "scaling": "strong" if sharded else "weak",
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s" if wl.dtype == "i8" else "TFLOP/s",
+                         "frac": achieved / peak, "traffic": ncu_traffic(name),
+                         "peak_source": f"{peak_kind} bf16 burst" + (" x2 (int8)" if wl.dtype == "i8" else ""),
+                         "kernel_ms": kern_ms, "hbm_gbs_algorithmic": wl.bytes / (kern_ms * 1e-3) / 1e9},
+            "gpu_launches": launches,
+        }
+        return wl, sets, hosts, res, clocks
+
+    wl, sets, hosts, head, clocks = measure(args.workload, args.steps, args.warmup, sample_clocks=True)
+
+    # ---- end to end through the public API with host buffers (pinned), copies inside the timed region
+    e2e = None
+    if hosts is not None:
+        e2e_steps = max(5, min(args.steps, 20))
+        pinned_in = [torch.from_numpy(h).pin_memory() for h in hosts[0]]
+        dev_in = [torch.empty_like(t, device="cuda") for t in pinned_in]
+        e_dev = sets[0]["e"]
+        e_host = torch.empty(e_dev.shape, dtype=e_dev.dtype).pin_memory()
+        bound = wl.bind(dev_in, e_dev)
+        h2d = sum(t.numel() * t.element_size() for t in pinned_in)
+        d2h = e_host.numel() * e_host.element_size()
+
+        def e2e_step():
+            for d, p in zip(dev_in, pinned_in):
+                d.copy_(p, non_blocking=True)
+            bound["inv"].Run(bound["arg"], stream_cfg)
+            e_host.copy_(e_dev, non_blocking=True)
+
+        for _ in range(3):
+            e2e_step()
+        torch.cuda.synchronize()
+        barrier()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        e.record()
+        torch.cuda.synchronize()
+        barrier()
+        ms = max_over_ranks(s.elapsed_time(e))
+        sharded = args.workload in ("conv", "grouped")
+        flop_job = wl.flop_total if sharded else wl.flop * world
+        e2e = {"value": flop_job * e2e_steps / (ms * 1e-3) / 1e12, "unit": wl.unit,
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+               "ms_per_step": ms / e2e_steps}
+        del pinned_in, dev_in, e_host
+
+    # ---- CPU baseline (rank 0, N = 1): the reference's host path restated, bounded sample
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_extra and hosts is not None:
+        from oracle import ck_oracle as oracle
+        threads = oracle.hardware_concurrency()
+        unit = 64 if args.workload != "conv" else 1
+        t0 = time.perf_counter()
+        wl.oracle_rows(hosts[0], unit, oracle, threads)
+        dt = max(time.perf_counter() - t0, 1e-3)
+        full = wl.M if args.workload != "conv" else wl.Nloc
+        rows = int(max(unit, min(full, unit * 12.0 / dt)))  # about 12 s of CPU work
+        t0 = time.perf_counter()
+        flop = wl.oracle_rows(hosts[0], rows, oracle, threads)
+        dt = time.perf_counter() - t0
+        what = "output rows" if args.workload != "conv" else "images"
+        cpu = {"value": flop / dt / 1e12, "unit": wl.unit, "cores": threads, "kind": "port",
+               "sample": f"first {rows} of {full} {what} of the same inputs, naive per-output loops, {dt:.1f} s"}
+
+    del sets
+    torch.cuda.empty_cache()
+
+    # ---- the other configurations (not part of the headline timed region)
+    others = {}
+    if not args.no_extra:
+        for name in ["gemm_fp16", "gemm_int8", "gemm_fastgelu", "conv", "grouped"]:
+            if name == args.workload:
+                continue
+            _, s2, _, r2, _ = measure(name, 20, 3)
+            others[name] = r2
+            del s2
+            torch.cuda.empty_cache()
+
+    if rank == 0:
+        pub = PUBLISHED_MI100_TFLOPS.get(args.workload)
+        roof = dict(head["roofline"])
+        line = {
+            "metric": "TFLOPS per GPU vs B200 dense peak; box TFLOPS over all GPUs" if wl.unit == "TFLOPS"
+                      else "TOPS per GPU vs B200 dense peak; box TOPS over all GPUs",
+            "value": head["value"], "unit": wl.unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": head["scaling"],
+            "vs_baseline": (head["value"] / pub) if pub else None,
+            "dtype": wl.dtype, "data": "synthetic",
+            "config": {"workload": head["workload"],
+                       "l2": f"{wl.n_sets()} input sets rotated; operands of a step are beyond the 126 MB L2 when reused"
+                             if wl.n_sets() > 1 else "operands per step far exceed the 126 MB L2",
+                       "parallelism": ("replicas" if head["scaling"] == "weak" else "sharded, no collective") +
+                                      f" x{world}",
+                       "vs_baseline_note": "published number is the reference's MI100 figure for the same shape"},
+            "roofline": {k: roof[k] for k in ("bound", "achieved", "peak", "unit", "frac", "traffic")},
+            "roofline_detail": {k: roof[k] for k in ("peak_source", "kernel_ms", "hbm_gbs_algorithmic")},
+            "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": head["gpu_launches"], "clocks": clocks,
+            "workloads": others,
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

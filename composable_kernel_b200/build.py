@@ -37,7 +37,7 @@ def sources():
 
 
 def _headers():
-    hs = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cuh")]
+    hs = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".def"))]
     hs.append(os.path.join(HERE, "..", "include", "ckb200.h"))
     return hs
 
@@ -69,6 +69,10 @@ def build(force: bool = False, verbose: bool = False) -> str:
             if f.endswith(".o"):
                 os.remove(os.path.join(OBJ_DIR, f))
     srcs = sources()
+    keep = {os.path.basename(s)[:-3] + ".o" for s in srcs}
+    for f in os.listdir(OBJ_DIR):  # objects of translation units that no longer exist
+        if f.endswith(".o") and f not in keep:
+            os.remove(os.path.join(OBJ_DIR, f))
     with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, len(srcs))) as pool:
         objs = list(pool.map(lambda s: _compile(s, verbose), srcs))
     if force or _stale(LIB_PATH, objs):

@@ -185,6 +185,34 @@ int pick_bn(int64_t M, int64_t N, int sm_count)
     return 256;
 }
 
+// Splits the last, partial wave of tiles into column slices so that it occupies every SM
+// (see "Work items" in ckb_kernel.cuh).  Slices are at least 64 columns wide.
+struct WorkPlan
+{
+    int32_t split_start, split, total_work, grid;
+};
+
+WorkPlan plan_work(int64_t total_tiles, int sm_count, int bn)
+{
+    WorkPlan w;
+    const int64_t G    = sm_count;
+    const int64_t full = (total_tiles / G) * G;
+    const int64_t rem  = total_tiles - full;
+    int split          = 1;
+    const char* env    = getenv("CKB_NO_TAIL_SPLIT");
+    if(rem > 0 && !(env && atoi(env) != 0))
+    {
+        const int max_split = bn / 64; // 256 -> 4, 128 -> 2, 64 -> 1
+        while(split * 2 <= max_split && rem * split * 2 <= G)
+            split *= 2;
+    }
+    w.split       = split;
+    w.split_start = static_cast<int32_t>(split > 1 ? full : total_tiles);
+    w.total_work  = static_cast<int32_t>(split > 1 ? full + rem * split : total_tiles);
+    w.grid        = static_cast<int32_t>(w.total_work < G ? w.total_work : G);
+    return w;
+}
+
 bool epilogue_valid_for(int epi, int ab_dtype)
 {
     if(epi < 0 || epi >= CKB_EPI_COUNT_)
@@ -261,8 +289,6 @@ void fill_epilogue(EpilogueArgs& ea, const ckb_gemm_desc* d)
     ea.ldd1 = d->n_ds > 1 ? d->ldd[1] : 0;
 }
 
-typedef cudaError_t (*LaunchFn)(int, const KernelParams&, int, cudaStream_t);
-
 // One launch, or the reference timing protocol (kernel_launch.hpp:12-74): a warm-up launch, then
 // n_rep launches between two events.
 int run_timed(LaunchFn fn, int bn, const KernelParams& p, int grid, cudaStream_t stream, int n_rep,
@@ -306,6 +332,22 @@ int run_timed(LaunchFn fn, int bn, const KernelParams& p, int grid, cudaStream_t
 }
 
 } // namespace
+
+namespace ckb {
+#define CKB_INST(M, K, E) extern template cudaError_t launch_epi<M, K, E>(int, const KernelParams&, int, cudaStream_t);
+#include "ckb_instances.def"
+#undef CKB_INST
+
+LaunchFn find_launch(int mode, int kind, int epi)
+{
+#define CKB_INST(M, K, E)                   \
+    if(mode == M && kind == K && epi == E)  \
+        return &launch_epi<M, K, E>;
+#include "ckb_instances.def"
+#undef CKB_INST
+    return nullptr;
+}
+} // namespace ckb
 
 extern "C" {
 
@@ -412,8 +454,15 @@ int ckb_gemm_run(const ckb_gemm_desc* d, void* stream, int n_rep, float* avg_ms)
     fill_epilogue(p.epi, d);
     const int64_t tiles_m = (d->M + BM - 1) / BM;
     const int64_t tiles_n = (d->N + bn - 1) / bn;
-    if(tiles_m * tiles_n > 0x7FFFFFFFll)
+    if(tiles_m * tiles_n > 0x3FFFFFFFll)
         return fail(CKB_ERR_UNSUPPORTED, "too many tiles");
+    const WorkPlan plan = plan_work(tiles_m * tiles_n, dev->sm_count, bn);
+    rc = encode_kmajor_2d(&p.tm_b_split, d->ab_dtype, d->p_b, d->N, d->K, d->ldb, bn / plan.split);
+    if(rc)
+        return rc;
+    p.split_start   = plan.split_start;
+    p.split         = plan.split;
+    p.total_work    = plan.total_work;
     p.total_tiles   = static_cast<int32_t>(tiles_m * tiles_n);
     p.M             = static_cast<int32_t>(d->M);
     p.N             = static_cast<int32_t>(d->N);
@@ -423,9 +472,10 @@ int ckb_gemm_run(const ckb_gemm_desc* d, void* stream, int n_rep, float* avg_ms)
     p.vec_ok        = gemm_vec_ok(d) ? 1 : 0;
     p.wait_limit_ns = wait_limit_ns();
     p.status        = dev->status;
-    const int grid  = p.total_tiles < dev->sm_count ? p.total_tiles : dev->sm_count;
-    LaunchFn fn     = d->ab_dtype == CKB_I8 ? launch_gemm_i8 : launch_gemm_f16;
-    return run_timed(fn, bn, p, grid, static_cast<cudaStream_t>(stream), n_rep, avg_ms);
+    LaunchFn fn     = find_launch(MODE_GEMM, d->ab_dtype == CKB_I8 ? KIND_I8 : KIND_F16, d->epilogue);
+    if(!fn)
+        return fail(CKB_ERR_UNSUPPORTED, "no kernel instance for epilogue %d", d->epilogue);
+    return run_timed(fn, bn, p, plan.grid, static_cast<cudaStream_t>(stream), n_rep, avg_ms);
 }
 
 // ---- grouped GEMM -------------------------------------------------------------------------------
@@ -488,6 +538,13 @@ int ckb_grouped_gemm_run(const ckb_grouped_gemm_desc* g, void* workspace, size_t
     }
     const int bn = pick_bn(sum_m, max_n, dev->sm_count);
 
+    int64_t all_tiles = 0;
+    for(int i = 0; i < g->group_count; ++i)
+        all_tiles += ((g->groups[i].M + BM - 1) / BM) * ((g->groups[i].N + bn - 1) / bn);
+    if(all_tiles > 0x3FFFFFFFll)
+        return fail(CKB_ERR_UNSUPPORTED, "too many tiles");
+    const WorkPlan plan = plan_work(all_tiles, dev->sm_count, bn);
+
     std::vector<GroupEntry> table(g->group_count);
     int64_t tile_start = 0;
     for(int i = 0; i < g->group_count; ++i)
@@ -499,6 +556,9 @@ int ckb_grouped_gemm_run(const ckb_grouped_gemm_desc* g, void* workspace, size_t
         if(rc)
             return rc;
         rc = encode_kmajor_2d(&ge.tm_b, dtype, d.p_b, d.N, d.K, d.ldb, bn);
+        if(rc)
+            return rc;
+        rc = encode_kmajor_2d(&ge.tm_b_split, dtype, d.p_b, d.N, d.K, d.ldb, bn / plan.split);
         if(rc)
             return rc;
         const int64_t tm = (d.M + BM - 1) / BM, tn = (d.N + bn - 1) / bn;
@@ -516,8 +576,6 @@ int ckb_grouped_gemm_run(const ckb_grouped_gemm_desc* g, void* workspace, size_t
         ge.ldd0       = d.n_ds > 0 ? d.ldd[0] : 0;
         ge.ldd1       = d.n_ds > 1 ? d.ldd[1] : 0;
         tile_start += tm * tn;
-        if(tile_start > 0x7FFFFFFFll)
-            return fail(CKB_ERR_UNSUPPORTED, "too many tiles");
     }
     uintptr_t ws_addr = (reinterpret_cast<uintptr_t>(workspace) + 127u) & ~static_cast<uintptr_t>(127u);
     GroupEntry* d_table = reinterpret_cast<GroupEntry*>(ws_addr);
@@ -531,11 +589,15 @@ int ckb_grouped_gemm_run(const ckb_grouped_gemm_desc* g, void* workspace, size_t
     p.groups        = d_table;
     p.group_count   = g->group_count;
     p.total_tiles   = static_cast<int32_t>(tile_start);
+    p.split_start   = plan.split_start;
+    p.split         = plan.split;
+    p.total_work    = plan.total_work;
     p.wait_limit_ns = wait_limit_ns();
     p.status        = dev->status;
-    const int grid  = p.total_tiles < dev->sm_count ? p.total_tiles : dev->sm_count;
-    LaunchFn fn     = dtype == CKB_I8 ? launch_grouped_i8 : launch_grouped_f16;
-    return run_timed(fn, bn, p, grid, stream, n_rep, avg_ms);
+    LaunchFn fn     = find_launch(MODE_GROUPED, dtype == CKB_I8 ? KIND_I8 : KIND_F16, g->groups[0].epilogue);
+    if(!fn)
+        return fail(CKB_ERR_UNSUPPORTED, "no kernel instance for epilogue %d", g->groups[0].epilogue);
+    return run_timed(fn, bn, p, plan.grid, stream, n_rep, avg_ms);
 }
 
 // ---- conv2d forward -------------------------------------------------------------------------------
@@ -639,16 +701,23 @@ int ckb_conv2d_fwd_run(const ckb_conv2d_fwd_desc* d, void* stream, int n_rep, fl
         if(g_driver_version <= 13010 && in_bytes < 131072)
             reinterpret_cast<uint64_t*>(&p.tm_a)[1] &= ~(1ull << 21);
     }
+    const int64_t tiles_m = (gm + BM - 1) / BM;
+    const int64_t tiles_n = (d->K + bn - 1) / bn;
+    if(tiles_m * tiles_n > 0x3FFFFFFFll)
+        return fail(CKB_ERR_UNSUPPORTED, "too many tiles");
+    const WorkPlan plan = plan_work(tiles_m * tiles_n, dev->sm_count, bn);
+    for(int which = 0; which < 2; ++which)
     {
         // Weights KYXC as (C, Y*X, K): a box never crosses a filter tap, channels beyond C read 0.
         cuuint64_t dims[3]    = {static_cast<cuuint64_t>(d->C), static_cast<cuuint64_t>(d->Y) * d->X,
                               static_cast<cuuint64_t>(d->K)};
         cuuint64_t strides[2] = {static_cast<cuuint64_t>(d->C) * 2,
                                  static_cast<cuuint64_t>(d->Y) * d->X * d->C * 2};
-        cuuint32_t box[3]     = {static_cast<cuuint32_t>(bk), 1, static_cast<cuuint32_t>(bn)};
+        cuuint32_t box[3]     = {static_cast<cuuint32_t>(bk), 1,
+                             static_cast<cuuint32_t>(which == 0 ? bn : bn / plan.split)};
         cuuint32_t estr[3]    = {1, 1, 1};
-        CUresult r = g_encode_tiled(&p.tm_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
-                                    const_cast<void*>(d->p_wei), dims, strides, box, estr,
+        CUresult r = g_encode_tiled(which == 0 ? &p.tm_b : &p.tm_b_split, CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                                    3, const_cast<void*>(d->p_wei), dims, strides, box, estr,
                                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -670,11 +739,10 @@ int ckb_conv2d_fwd_run(const ckb_conv2d_fwd_desc* d, void* stream, int n_rep, fl
         vec = vec && aligned16(d->p_bias);
     if(nd >= 2)
         vec = vec && aligned16(d->p_resi);
-    const int64_t tiles_m = (gm + BM - 1) / BM;
-    const int64_t tiles_n = (d->K + bn - 1) / bn;
-    if(tiles_m * tiles_n > 0x7FFFFFFFll)
-        return fail(CKB_ERR_UNSUPPORTED, "too many tiles");
     p.total_tiles   = static_cast<int32_t>(tiles_m * tiles_n);
+    p.split_start   = plan.split_start;
+    p.split         = plan.split;
+    p.total_work    = plan.total_work;
     p.M             = static_cast<int32_t>(gm);
     p.N             = d->K;
     p.tiles_n       = static_cast<int32_t>(tiles_n);
@@ -694,8 +762,10 @@ int ckb_conv2d_fwd_run(const ckb_conv2d_fwd_desc* d, void* stream, int n_rep, fl
     p.vec_ok        = vec ? 1 : 0;
     p.wait_limit_ns = wait_limit_ns();
     p.status        = dev->status;
-    const int grid  = p.total_tiles < dev->sm_count ? p.total_tiles : dev->sm_count;
-    return run_timed(launch_conv_f16, bn, p, grid, static_cast<cudaStream_t>(stream), n_rep, avg_ms);
+    LaunchFn fn = find_launch(MODE_CONV, KIND_F16, d->epilogue);
+    if(!fn)
+        return fail(CKB_ERR_UNSUPPORTED, "no kernel instance for epilogue %d", d->epilogue);
+    return run_timed(fn, bn, p, plan.grid, static_cast<cudaStream_t>(stream), n_rep, avg_ms);
 }
 
 } // extern "C"

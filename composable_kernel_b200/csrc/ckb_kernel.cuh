@@ -1,13 +1,19 @@
 // The persistent, warp-specialised tcgen05 contraction kernel.
 //
-// One CTA per SM walks tiles  t = blockIdx.x, blockIdx.x + gridDim.x, ...  of the output.
-//   warp 0   TMA producer : fills a ring of STAGES shared-memory stages (A tile 128 x 128 B,
-//                           B tile BN x 128 B, both K-major, 128-byte swizzle)
-//   warp 1   MMA issuer   : one thread issues tcgen05.mma (128 x BN x 16|32) into one of two
-//                           TMEM accumulators (2 x BN columns) and commits to mbarriers
-//   warps 2-5 epilogue    : tcgen05.ld the finished accumulator (each warp its lane quarter),
-//                           apply the fused epilogue, store E with 128-bit stores
-// The second accumulator lets the epilogue of tile i overlap the main loop of tile i+1.
+// One CTA per SM walks work items  w = blockIdx.x, blockIdx.x + gridDim.x, ...
+//   warp 0     TMA producer : fills a ring of STAGES shared-memory stages (A tile 128 x 128 B,
+//                             B tile <=BN x 128 B, both K-major, 128-byte swizzle)
+//   warp 1     MMA issuer   : one thread issues tcgen05.mma (128 x width x 16|32) into one of two
+//                             TMEM accumulators (2 x BN columns) and commits to mbarriers
+//   warps 2-9  epilogue     : tcgen05.ld the finished accumulator (two warps per TMEM lane
+//                             quarter, each half of the columns), apply the fused epilogue with
+//                             the D values prefetched one segment ahead, store E with 128-bit stores
+// The second accumulator lets the epilogue of item i overlap the main loop of item i+1.
+//
+// Work items.  The output is cut into 128 x BN tiles.  With G CTAs, the first floor(T/G)*G tiles
+// are whole-tile items; the R = T mod G tiles of the last, partial wave are each cut into
+// `split` column slices of BN/split columns (R*split <= G), so that the tail occupies all SMs
+// instead of R of them.
 //
 // Three problem sources share the kernel:
 //   MODE_GEMM     one A/B tensor-map pair in the kernel parameters
@@ -22,6 +28,8 @@
 // word, raises the CTA's abort flag, and all roles drain and leave through the common exit,
 // which frees the tensor memory.
 #pragma once
+#include <type_traits>
+
 #include "ckb_epilogue.cuh"
 #include "ckb_ptx.cuh"
 
@@ -30,14 +38,13 @@ namespace ckb {
 enum { MODE_GEMM = 0, MODE_GROUPED = 1, MODE_CONV = 2 };
 enum { KIND_F16 = 0, KIND_BF16 = 1, KIND_I8 = 2 };
 
-constexpr int BM          = 128; // rows of an output tile = TMEM lanes
-constexpr int BK_BYTES    = 128; // bytes of K per stage row = one swizzle span
-constexpr int NUM_THREADS = 192;
-constexpr int EPI_WARP0   = 2;
+constexpr int BM            = 128; // rows of an output tile = TMEM lanes
+constexpr int BK_BYTES      = 128; // bytes of K per stage row = one swizzle span
+constexpr int NUM_EPI_WARPS = 8;
+constexpr int NUM_THREADS   = 64 + 32 * NUM_EPI_WARPS;
 
 // Device status word (KernelParams::status points at it): 0 = fine; otherwise
 // (code << 24) | (block & 0xFFFFFF) of the first wait that gave up.
-
 enum {
     WAIT_EMPTY      = 1, // producer waiting for a free stage
     WAIT_FULL       = 2, // MMA waiting for TMA data
@@ -49,8 +56,9 @@ enum {
 // One group of a grouped GEMM (lives in the caller's device workspace).
 struct alignas(128) GroupEntry
 {
-    CUtensorMap tm_a; // 128 B
-    CUtensorMap tm_b; // 128 B
+    CUtensorMap tm_a;       // 128 B
+    CUtensorMap tm_b;       // box of BN rows
+    CUtensorMap tm_b_split; // box of BN/split rows (tail slices)
     int32_t M, N, K;
     int32_t tiles_n;
     int32_t tile_start; // first global tile index of this group
@@ -72,16 +80,20 @@ struct ConvGeom
 
 struct KernelParams
 {
-    CUtensorMap tm_a; // GEMM: A (K, M).  CONV: im2col map over the NHWC input
-    CUtensorMap tm_b; // GEMM: B^T (K, N). CONV: weights as (C, Y*X, K)
-    EpilogueArgs epi; // GROUPED: e/d/ld fields come from the group entry instead
+    CUtensorMap tm_a;       // GEMM: A (K, M).  CONV: im2col map over the NHWC input
+    CUtensorMap tm_b;       // GEMM: B^T (K, N). CONV: weights as (C, Y*X, K); box of BN rows
+    CUtensorMap tm_b_split; // same tensor, box of BN/split rows
+    EpilogueArgs epi;       // GROUPED: e/d/ld fields come from the group entry instead
     const GroupEntry* groups;
     int32_t group_count;
-    int32_t total_tiles;
-    int32_t M, N;     // GEMM / CONV problem (CONV: M = N*Ho*Wo, N = K_out)
+    int32_t total_tiles; // T: 128 x BN tiles over all groups
+    int32_t split_start; // first tile index whose tile is cut into column slices (= T if none)
+    int32_t split;       // slices per tail tile (1, 2 or 4)
+    int32_t total_work;  // split_start + (T - split_start) * split
+    int32_t M, N;        // GEMM / CONV problem (CONV: M = N*Ho*Wo, N = K_out)
     int32_t tiles_n;
-    int32_t num_kb;   // k blocks per tile (GEMM / CONV)
-    int32_t vec_ok;   // 128-bit epilogue access allowed
+    int32_t num_kb;      // k blocks per tile (GEMM / CONV)
+    int32_t vec_ok;      // 128-bit epilogue access allowed
     int32_t pad_;
     ConvGeom conv;
     uint64_t wait_limit_ns;
@@ -96,7 +108,7 @@ struct SmemLayout
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int BAR_OFFSET  = STAGES * STAGE_BYTES;
     // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], drain
-    static constexpr int NUM_BARS = 2 * STAGES + 5;
+    static constexpr int NUM_BARS    = 2 * STAGES + 5;
     static constexpr int MISC_OFFSET = BAR_OFFSET + NUM_BARS * 8;
     static constexpr int TOTAL       = MISC_OFFSET + 16;
     static constexpr int DYN_BYTES   = TOTAL + 1024; // slack to align the base to 1024 B
@@ -150,35 +162,102 @@ __device__ __forceinline__ int find_group(const GroupEntry* groups, int group_co
     return lo;
 }
 
-template <int EPI, int KIND>
-__device__ __forceinline__ void epilogue_rows(uint32_t tmem_acc, int lane_quarter, int lane,
-                                              const EpilogueArgs& ea, int64_t m, bool row_ok,
-                                              int64_t n_base, int64_t n_limit, int bn,
-                                              bool vec_ok)
+// What one work item covers.
+struct WorkItem
 {
-    for(int chunk = 0; chunk < bn / 32; ++chunk)
+    int m_blk;   // row tile
+    int n_start; // first output column
+    int width;   // columns of this item (BN, or BN/split for a tail slice)
+    int num_kb;
+    const GroupEntry* group; // MODE_GROUPED only
+    bool is_slice;
+};
+
+template <int MODE, int BN>
+__device__ __forceinline__ WorkItem decode_work(const KernelParams& P, int w)
+{
+    WorkItem wi;
+    int tile, slice = 0;
+    wi.width    = BN;
+    wi.is_slice = false;
+    if(w < P.split_start)
+        tile = w;
+    else
     {
-        const int64_t n0 = n_base + chunk * 32;
-        if(n0 >= n_limit)
-            break; // uniform over the CTA: the rest of the tile is out of range
+        const int q = w - P.split_start;
+        tile        = P.split_start + q / P.split;
+        slice       = q % P.split;
+        wi.width    = BN / P.split;
+        wi.is_slice = P.split > 1;
+    }
+    int n_blk;
+    if constexpr(MODE == MODE_GROUPED)
+    {
+        const GroupEntry* G = P.groups + find_group(P.groups, P.group_count, tile);
+        const int local     = tile - G->tile_start;
+        wi.m_blk            = local / G->tiles_n;
+        n_blk               = local % G->tiles_n;
+        wi.num_kb           = G->num_kb;
+        wi.group            = G;
+    }
+    else
+    {
+        wi.m_blk  = tile / P.tiles_n;
+        n_blk     = tile % P.tiles_n;
+        wi.num_kb = P.num_kb;
+        wi.group  = nullptr;
+    }
+    wi.n_start = n_blk * BN + slice * wi.width;
+    return wi;
+}
+
+// Epilogue of one warp: rows = its TMEM lane quarter, columns [n_begin, n_end) of row m.
+// tmem_addr = lane base | first column of the span inside the accumulator.
+template <int EPI, int KIND>
+__device__ __forceinline__ void epilogue_span(uint32_t tmem_addr, const EpilogueArgs& ea, int64_t m,
+                                              bool row_ok, int64_t n_begin, int64_t n_end, bool vec_ok)
+{
+    using T          = typename std::conditional<KIND == KIND_BF16, __nv_bfloat16, __half>::type;
+    constexpr int ND = (KIND == KIND_I8) ? 0 : epi_num_d(EPI);
+    const int nchunks = n_end > n_begin ? static_cast<int>((n_end - n_begin + 31) / 32) : 0;
+    DChunk cur, nxt;
+    if constexpr(ND > 0)
+    {
+        if(row_ok && vec_ok && n_end - n_begin >= 32)
+            epi_load_d<EPI, T>(cur, ea, m, n_begin);
+    }
+    for(int c = 0; c < nchunks; ++c)
+    {
+        const int64_t n0 = n_begin + c * 32;
+        const int ncols  = static_cast<int>(n_end - n0 < 32 ? n_end - n0 : 32);
+        if constexpr(ND > 0)
+        {
+            if(row_ok && vec_ok && n_end - (n0 + 32) >= 32)
+                epi_load_d<EPI, T>(nxt, ea, m, n0 + 32);
+        }
         uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem_acc + (static_cast<uint32_t>(lane_quarter * 32) << 16) + chunk * 32, v);
+        tmem_ld_32x32b_x32(tmem_addr + c * 32, v);
         tmem_ld_wait();
         if(row_ok)
         {
-            const int ncols = static_cast<int>(n_limit - n0 < 32 ? n_limit - n0 : 32);
             if constexpr(KIND == KIND_I8)
                 epi_store_row_i8<EPI>(v, ea, m, n0, ncols, vec_ok);
-            else if constexpr(KIND == KIND_BF16)
-                epi_store_row_f<EPI, __nv_bfloat16>(v, ea, m, n0, ncols, vec_ok);
             else
-                epi_store_row_f<EPI, __half>(v, ea, m, n0, ncols, vec_ok);
+            {
+                if(vec_ok && ncols == 32)
+                    epi_store_vec_f<EPI, T>(v, cur, ea, m, n0);
+                else
+                    epi_store_scalar_f<EPI, T>(v, ea, m, n0, ncols);
+            }
         }
+        if constexpr(ND > 0)
+            cur = nxt;
     }
-    (void)lane;
 }
 
-template <int MODE, int KIND, int BN, int STAGES>
+// EPI (the fused epilogue functor) is a template parameter: one functor per kernel keeps the
+// epilogue warps inside the 168-register budget that ten warps per SM leave.
+template <int MODE, int KIND, int EPI, int BN, int STAGES>
 __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __grid_constant__ KernelParams P)
 {
     using L = SmemLayout<BN, STAGES>;
@@ -186,8 +265,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
     constexpr int UMMA_K_BYTES   = 32; // 16 x 16-bit or 32 x 8-bit
     constexpr int K_STEPS        = BK_BYTES / UMMA_K_BYTES;
     constexpr int BK_ELEMS       = (KIND == KIND_I8) ? 128 : 64;
-    constexpr uint32_t IDESC =
-        (KIND == KIND_I8) ? make_idesc(2u, 1u, BM, BN) : make_idesc(1u, KIND == KIND_BF16 ? 1u : 0u, BM, BN);
+    constexpr uint32_t C_FMT     = (KIND == KIND_I8) ? 2u : 1u;
+    constexpr uint32_t AB_FMT    = (KIND == KIND_F16) ? 0u : 1u; // f16 | bf16 or s8
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr  = smem_u32(smem_raw);
@@ -216,7 +295,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
         for(int a = 0; a < 2; ++a)
         {
             mbar_init(tmem_full_bar(a), 1);
-            mbar_init(tmem_empty_bar(a), 4); // one arrival per epilogue warp
+            mbar_init(tmem_empty_bar(a), NUM_EPI_WARPS); // one arrival per epilogue warp
         }
         mbar_init(drain_bar, 1);
         misc[1] = 0;
@@ -245,38 +324,27 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                 tma_prefetch_desc(&P.tm_a);
                 tma_prefetch_desc(&P.tm_b);
             }
-            int stage = 0;
-            uint32_t phase = 0;
-            uint32_t issued = 0; // bit s set: stage s holds a load this thread has not seen land
+            int stage           = 0;
+            uint32_t phase      = 0;
+            uint32_t issued     = 0; // bit s: a load was issued into stage s
             uint32_t last_phase = 0; // bit s: phase of the last load issued into stage s
-            bool ok = true;
-            for(int tile = blockIdx.x; ok && tile < P.total_tiles; tile += gridDim.x)
+            bool ok             = true;
+            for(int w = blockIdx.x; ok && w < P.total_work; w += gridDim.x)
             {
+                const WorkItem wi       = decode_work<MODE, BN>(P, w);
                 const CUtensorMap* tm_a = &P.tm_a;
-                const CUtensorMap* tm_b = &P.tm_b;
-                int m_blk, n_blk, num_kb;
+                const CUtensorMap* tm_b = wi.is_slice ? &P.tm_b_split : &P.tm_b;
                 if constexpr(MODE == MODE_GROUPED)
                 {
-                    const int g         = find_group(P.groups, P.group_count, tile);
-                    const GroupEntry* G = P.groups + g;
-                    const int local     = tile - G->tile_start;
-                    m_blk               = local / G->tiles_n;
-                    n_blk               = local % G->tiles_n;
-                    num_kb              = G->num_kb;
-                    tm_a                = &G->tm_a;
-                    tm_b                = &G->tm_b;
+                    tm_a = &wi.group->tm_a;
+                    tm_b = wi.is_slice ? &wi.group->tm_b_split : &wi.group->tm_b;
                 }
-                else
-                {
-                    m_blk  = tile / P.tiles_n;
-                    n_blk  = tile % P.tiles_n;
-                    num_kb = P.num_kb;
-                }
+                const uint32_t tx_bytes = L::A_BYTES + wi.width * BK_BYTES;
                 // CONV: first output pixel of the tile in (n, ho, wo)
                 int cv_n = 0, cv_h = 0, cv_w = 0;
                 if constexpr(MODE == MODE_CONV)
                 {
-                    const int m0  = m_blk * BM;
+                    const int m0  = wi.m_blk * BM;
                     cv_n          = m0 / P.conv.HoWo;
                     const int rem = m0 - cv_n * P.conv.HoWo;
                     const int ho  = rem / P.conv.Wo;
@@ -285,21 +353,21 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                     cv_w          = wo * P.conv.stride_w - P.conv.pad_w;
                 }
                 int cv_y = 0, cv_x = 0, cv_cb = 0;
-                for(int kb = 0; kb < num_kb; ++kb)
+                for(int kb = 0; kb < wi.num_kb; ++kb)
                 {
                     ok = bounded_wait(empty_bar(stage), phase ^ 1u, wc, WAIT_EMPTY);
                     if(!ok)
                         break;
                     const uint32_t a_dst = base_addr + stage * L::STAGE_BYTES;
                     const uint32_t b_dst = a_dst + L::A_BYTES;
-                    mbar_arrive_expect_tx(full_bar(stage), L::STAGE_BYTES);
+                    mbar_arrive_expect_tx(full_bar(stage), tx_bytes);
                     if constexpr(MODE == MODE_CONV)
                     {
                         tma_load_im2col_4d(a_dst, tm_a, full_bar(stage), cv_cb * BK_ELEMS, cv_w, cv_h,
                                            cv_n, static_cast<uint16_t>(cv_x * P.conv.dil_w),
                                            static_cast<uint16_t>(cv_y * P.conv.dil_h));
                         tma_load_3d(b_dst, tm_b, full_bar(stage), cv_cb * BK_ELEMS,
-                                    cv_y * P.conv.X + cv_x, n_blk * BN);
+                                    cv_y * P.conv.X + cv_x, wi.n_start);
                         if(++cv_cb == P.conv.c_blocks)
                         {
                             cv_cb = 0;
@@ -312,8 +380,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                     }
                     else
                     {
-                        tma_load_2d(a_dst, tm_a, full_bar(stage), kb * BK_ELEMS, m_blk * BM);
-                        tma_load_2d(b_dst, tm_b, full_bar(stage), kb * BK_ELEMS, n_blk * BN);
+                        tma_load_2d(a_dst, tm_a, full_bar(stage), kb * BK_ELEMS, wi.m_blk * BM);
+                        tma_load_2d(b_dst, tm_b, full_bar(stage), kb * BK_ELEMS, wi.n_start);
                     }
                     issued |= 1u << stage;
                     last_phase = (last_phase & ~(1u << stage)) | (phase << stage);
@@ -338,18 +406,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
         // ------------------------------------------------------------------ MMA issuer
         if(lane == 0)
         {
-            int stage = 0;
-            uint32_t phase = 0;
-            int iter = 0;
-            bool ok = true;
+            int stage       = 0;
+            uint32_t phase  = 0;
+            int iter        = 0;
+            bool ok         = true;
             bool issued_any = false;
-            for(int tile = blockIdx.x; ok && tile < P.total_tiles; tile += gridDim.x, ++iter)
+            for(int w = blockIdx.x; ok && w < P.total_work; w += gridDim.x, ++iter)
             {
-                int num_kb;
-                if constexpr(MODE == MODE_GROUPED)
-                    num_kb = P.groups[find_group(P.groups, P.group_count, tile)].num_kb;
-                else
-                    num_kb = P.num_kb;
+                const WorkItem wi        = decode_work<MODE, BN>(P, w);
+                const uint32_t idesc     = make_idesc(C_FMT, AB_FMT, BM, static_cast<uint32_t>(wi.width));
                 const int acc            = iter & 1;
                 const uint32_t acc_phase = (iter >> 1) & 1;
                 ok = bounded_wait(tmem_empty_bar(acc), acc_phase ^ 1u, wc, WAIT_TMEM_EMPTY);
@@ -357,7 +422,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                     break;
                 tc_fence_after_sync();
                 const uint32_t tmem_d = tmem_base + acc * BN;
-                for(int kb = 0; kb < num_kb; ++kb)
+                for(int kb = 0; kb < wi.num_kb; ++kb)
                 {
                     ok = bounded_wait(full_bar(stage), phase, wc, WAIT_FULL);
                     if(!ok)
@@ -371,9 +436,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                     {
                         const uint64_t koff = static_cast<uint64_t>((k * UMMA_K_BYTES) >> 4);
                         if constexpr(KIND == KIND_I8)
-                            mma_i8_ss(tmem_d, a_desc + koff, b_desc + koff, IDESC, (kb | k) != 0);
+                            mma_i8_ss(tmem_d, a_desc + koff, b_desc + koff, idesc, (kb | k) != 0);
                         else
-                            mma_f16_ss(tmem_d, a_desc + koff, b_desc + koff, IDESC, (kb | k) != 0);
+                            mma_f16_ss(tmem_d, a_desc + koff, b_desc + koff, idesc, (kb | k) != 0);
                     }
                     issued_any = true;
                     mma_commit(empty_bar(stage)); // stage is free once these MMAs have read it
@@ -398,21 +463,19 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
     else
     {
         // ------------------------------------------------------------------ epilogue warps
-        const int quarter = warp & 3; // TMEM lane quarter this warp may read
+        const int quarter = warp & 3;        // TMEM lane quarter this warp may read
+        const int half    = (warp - 2) >> 2; // which half of the item's columns
         int iter          = 0;
         bool ok           = true;
-        for(int tile = blockIdx.x; ok && tile < P.total_tiles; tile += gridDim.x, ++iter)
+        for(int w = blockIdx.x; ok && w < P.total_work; w += gridDim.x, ++iter)
         {
-            EpilogueArgs ea = P.epi;
-            int m_blk, n_blk, Mdim, Ndim;
-            bool vec_ok;
+            const WorkItem wi = decode_work<MODE, BN>(P, w);
+            EpilogueArgs ea   = P.epi;
+            int Mdim = P.M, Ndim = P.N;
+            bool vec_ok = P.vec_ok != 0;
             if constexpr(MODE == MODE_GROUPED)
             {
-                const int g         = find_group(P.groups, P.group_count, tile);
-                const GroupEntry* G = P.groups + g;
-                const int local     = tile - G->tile_start;
-                m_blk               = local / G->tiles_n;
-                n_blk               = local % G->tiles_n;
+                const GroupEntry* G = wi.group;
                 Mdim                = G->M;
                 Ndim                = G->N;
                 vec_ok              = G->vec_ok != 0;
@@ -423,14 +486,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                 ea.ldd0             = G->ldd0;
                 ea.ldd1             = G->ldd1;
             }
-            else
-            {
-                m_blk  = tile / P.tiles_n;
-                n_blk  = tile % P.tiles_n;
-                Mdim   = P.M;
-                Ndim   = P.N;
-                vec_ok = P.vec_ok != 0;
-            }
+            const int span          = wi.width >> 1; // columns per epilogue warp (>= 32)
+            const int64_t m         = static_cast<int64_t>(wi.m_blk) * BM + quarter * 32 + lane;
+            const bool row_ok       = m < Mdim;
+            const int64_t n_begin   = static_cast<int64_t>(wi.n_start) + half * span;
+            const int64_t n_end_raw = n_begin + span;
+            const int64_t n_end     = n_end_raw < Ndim ? n_end_raw : Ndim;
+
             const int acc            = iter & 1;
             const uint32_t acc_phase = (iter >> 1) & 1;
             ok = bounded_wait(tmem_full_bar(acc), acc_phase, wc, WAIT_TMEM_FULL);
@@ -438,49 +500,43 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
             if(!ok)
                 break;
             tc_fence_after_sync();
-            const uint32_t tmem_acc = tmem_base + acc * BN;
-            const int64_t m         = static_cast<int64_t>(m_blk) * BM + quarter * 32 + lane;
-            const bool row_ok       = m < Mdim;
-            const int64_t n_base    = static_cast<int64_t>(n_blk) * BN;
-#define CKB_EPI_CASE(E)                                                                         \
-    case E:                                                                                     \
-        epilogue_rows<E, KIND>(tmem_acc, quarter, lane, ea, m, row_ok, n_base, Ndim, BN, vec_ok); \
-        break;
-            if constexpr(KIND == KIND_I8)
-            {
-                switch(ea.kind)
-                {
-                    CKB_EPI_CASE(CKB_EPI_PASSTHROUGH)
-                    CKB_EPI_CASE(CKB_EPI_RELU)
-                    CKB_EPI_CASE(CKB_EPI_REQUANT_RELU_REQUANT)
-                    CKB_EPI_CASE(CKB_EPI_REQUANT_RELU_REQUANT_RNE)
-                default: break;
-                }
-            }
-            else
-            {
-                switch(ea.kind)
-                {
-                    CKB_EPI_CASE(CKB_EPI_PASSTHROUGH)
-                    CKB_EPI_CASE(CKB_EPI_RELU)
-                    CKB_EPI_CASE(CKB_EPI_SCALE)
-                    CKB_EPI_CASE(CKB_EPI_FASTGELU)
-                    CKB_EPI_CASE(CKB_EPI_ADD)
-                    CKB_EPI_CASE(CKB_EPI_ADD_RELU_F16)
-                    CKB_EPI_CASE(CKB_EPI_BILINEAR)
-                    CKB_EPI_CASE(CKB_EPI_ADD_ADD_FASTGELU)
-                    CKB_EPI_CASE(CKB_EPI_ADD_RELU_ADD)
-                    CKB_EPI_CASE(CKB_EPI_ADD_RELU)
-                    CKB_EPI_CASE(CKB_EPI_ADD_HARDSWISH)
-                default: break;
-                }
-            }
-#undef CKB_EPI_CASE
+            const uint32_t tmem_addr =
+                tmem_base + acc * BN + half * span + (static_cast<uint32_t>(quarter * 32) << 16);
+            epilogue_span<EPI, KIND>(tmem_addr, ea, m, row_ok, n_begin, n_end, vec_ok);
             // Release the accumulator: all of this warp's tcgen05.ld have completed.
             tc_fence_before_sync();
             __syncwarp();
             if(lane == 0)
                 mbar_arrive(tmem_empty_bar(acc));
+
+            // Ask L2 for the D values of this CTA's next item while its main loop runs.
+            if constexpr(KIND != KIND_I8)
+            {
+                const int wn = w + gridDim.x;
+                if(epi_num_d(EPI) > 0 && wn < P.total_work)
+                {
+                    const WorkItem nx = decode_work<MODE, BN>(P, wn);
+                    EpilogueArgs en   = P.epi;
+                    int Mn = P.M, Nn = P.N;
+                    if constexpr(MODE == MODE_GROUPED)
+                    {
+                        en.d0   = nx.group->d0;
+                        en.d1   = nx.group->d1;
+                        en.ldd0 = nx.group->ldd0;
+                        en.ldd1 = nx.group->ldd1;
+                        Mn      = nx.group->M;
+                        Nn      = nx.group->N;
+                    }
+                    const int spn    = nx.width >> 1;
+                    const int64_t mn = static_cast<int64_t>(nx.m_blk) * BM + quarter * 32 + lane;
+                    const int64_t nb = static_cast<int64_t>(nx.n_start) + half * spn;
+                    if(mn < Mn && nb < Nn)
+                    {
+                        const int64_t ne = nb + spn < Nn ? nb + spn : Nn;
+                        epi_prefetch_d(en, mn, nb, static_cast<int>(ne - nb) * 2, 2);
+                    }
+                }
+            }
         }
     }
 

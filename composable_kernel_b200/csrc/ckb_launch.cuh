@@ -1,6 +1,5 @@
-// Launch helpers: each ckb_inst_*.cu translation unit instantiates the kernel template for one
-// (MODE, KIND) pair and exposes one of the launch_* functions declared here, so that the
-// instantiations compile in parallel.
+// Launch helpers.  launch_epi<MODE, KIND, EPI> is explicitly instantiated in the generated
+// ckb_inst_*.cu files (so that they compile in parallel); find_launch() maps runtime ids to them.
 #pragma once
 #include "ckb_kernel.cuh"
 
@@ -26,12 +25,12 @@ struct StagesFor<64>
     static constexpr int value = 8;
 };
 
-template <int MODE, int KIND, int BN>
+template <int MODE, int KIND, int EPI, int BN>
 cudaError_t launch_one(const KernelParams& p, int grid, cudaStream_t stream)
 {
     constexpr int STAGES = StagesFor<BN>::value;
     constexpr int SMEM   = SmemLayout<BN, STAGES>::DYN_BYTES;
-    auto kern            = contraction_kernel<MODE, KIND, BN, STAGES>;
+    auto kern            = contraction_kernel<MODE, KIND, EPI, BN, STAGES>;
     static bool attr_done[64] = {};
     int dev                   = 0;
     cudaError_t err           = cudaGetDevice(&dev);
@@ -49,22 +48,21 @@ cudaError_t launch_one(const KernelParams& p, int grid, cudaStream_t stream)
     return cudaGetLastError();
 }
 
-template <int MODE, int KIND>
-cudaError_t launch_bn(int bn, const KernelParams& p, int grid, cudaStream_t stream)
+template <int MODE, int KIND, int EPI>
+cudaError_t launch_epi(int bn, const KernelParams& p, int grid, cudaStream_t stream)
 {
     switch(bn)
     {
-    case 256: return launch_one<MODE, KIND, 256>(p, grid, stream);
-    case 128: return launch_one<MODE, KIND, 128>(p, grid, stream);
-    case 64: return launch_one<MODE, KIND, 64>(p, grid, stream);
+    case 256: return launch_one<MODE, KIND, EPI, 256>(p, grid, stream);
+    case 128: return launch_one<MODE, KIND, EPI, 128>(p, grid, stream);
+    case 64: return launch_one<MODE, KIND, EPI, 64>(p, grid, stream);
     default: return cudaErrorInvalidValue;
     }
 }
 
-cudaError_t launch_gemm_f16(int bn, const KernelParams& p, int grid, cudaStream_t stream);
-cudaError_t launch_gemm_i8(int bn, const KernelParams& p, int grid, cudaStream_t stream);
-cudaError_t launch_grouped_f16(int bn, const KernelParams& p, int grid, cudaStream_t stream);
-cudaError_t launch_grouped_i8(int bn, const KernelParams& p, int grid, cudaStream_t stream);
-cudaError_t launch_conv_f16(int bn, const KernelParams& p, int grid, cudaStream_t stream);
+typedef cudaError_t (*LaunchFn)(int, const KernelParams&, int, cudaStream_t);
+
+// nullptr when the (mode, kind, epilogue) combination is not instantiated.
+LaunchFn find_launch(int mode, int kind, int epi);
 
 } // namespace ckb

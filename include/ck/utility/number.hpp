@@ -1,0 +1,2 @@
+#pragma once
+#include "ck/b200/core.hpp"
