@@ -192,10 +192,11 @@ struct WorkPlan
     int32_t split_start, split, total_work, grid;
 };
 
-WorkPlan plan_work(int64_t total_tiles, int sm_count, int bn)
+// `units` = CTAs (one CTA per tile) or CTA pairs (cg = 2) that run concurrently.
+WorkPlan plan_work(int64_t total_tiles, int units, int bn, int cg)
 {
     WorkPlan w;
-    const int64_t G    = sm_count;
+    const int64_t G    = units;
     const int64_t full = (total_tiles / G) * G;
     const int64_t rem  = total_tiles - full;
     int split          = 1;
@@ -209,8 +210,18 @@ WorkPlan plan_work(int64_t total_tiles, int sm_count, int bn)
     w.split       = split;
     w.split_start = static_cast<int32_t>(split > 1 ? full : total_tiles);
     w.total_work  = static_cast<int32_t>(split > 1 ? full + rem * split : total_tiles);
-    w.grid        = static_cast<int32_t>(w.total_work < G ? w.total_work : G);
+    w.grid        = static_cast<int32_t>((w.total_work < G ? w.total_work : G) * cg);
     return w;
+}
+
+// CTAs per tile: pairs (256 x 256 tiles, tcgen05 cta_group::2) once the problem fills the machine
+// with 128 x 256 tiles at least once; single CTAs for small problems.
+int pick_cg(int64_t tiles_128, int bn, int sm_count)
+{
+    const char* s = getenv("CKB_FORCE_CG");
+    if(s && (atoi(s) == 1 || atoi(s) == 2))
+        return bn == 256 ? atoi(s) : 1;
+    return (bn == 256 && tiles_128 >= sm_count) ? 2 : 1;
 }
 
 bool epilogue_valid_for(int epi, int ab_dtype)
@@ -291,18 +302,18 @@ void fill_epilogue(EpilogueArgs& ea, const ckb_gemm_desc* d)
 
 // One launch, or the reference timing protocol (kernel_launch.hpp:12-74): a warm-up launch, then
 // n_rep launches between two events.
-int run_timed(LaunchFn fn, int bn, const KernelParams& p, int grid, cudaStream_t stream, int n_rep,
+int run_timed(LaunchFn fn, int bn, int cg, const KernelParams& p, int grid, cudaStream_t stream, int n_rep,
               float* avg_ms)
 {
     if(avg_ms)
         *avg_ms = 0.f;
     if(n_rep <= 0)
     {
-        CKB_CUDA(fn(bn, p, grid, stream));
+        CKB_CUDA(fn(bn, cg, p, grid, stream));
         g_launches.fetch_add(1);
         return CKB_OK;
     }
-    CKB_CUDA(fn(bn, p, grid, stream)); // warm-up
+    CKB_CUDA(fn(bn, cg, p, grid, stream)); // warm-up
     g_launches.fetch_add(1);
     cudaEvent_t start, stop;
     CKB_CUDA(cudaEventCreate(&start));
@@ -311,7 +322,7 @@ int run_timed(LaunchFn fn, int bn, const KernelParams& p, int grid, cudaStream_t
     CKB_CUDA(cudaEventRecord(start, stream));
     for(int i = 0; i < n_rep; ++i)
     {
-        cudaError_t e = fn(bn, p, grid, stream);
+        cudaError_t e = fn(bn, cg, p, grid, stream);
         if(e != cudaSuccess)
         {
             cudaEventDestroy(start);
@@ -334,7 +345,7 @@ int run_timed(LaunchFn fn, int bn, const KernelParams& p, int grid, cudaStream_t
 } // namespace
 
 namespace ckb {
-#define CKB_INST(M, K, E) extern template cudaError_t launch_epi<M, K, E>(int, const KernelParams&, int, cudaStream_t);
+#define CKB_INST(M, K, E) extern template cudaError_t launch_epi<M, K, E>(int, int, const KernelParams&, int, cudaStream_t);
 #include "ckb_instances.def"
 #undef CKB_INST
 
@@ -448,16 +459,17 @@ int ckb_gemm_run(const ckb_gemm_desc* d, void* stream, int n_rep, float* avg_ms)
     rc = encode_kmajor_2d(&p.tm_a, d->ab_dtype, d->p_a, d->M, d->K, d->lda, BM);
     if(rc)
         return rc;
-    rc = encode_kmajor_2d(&p.tm_b, d->ab_dtype, d->p_b, d->N, d->K, d->ldb, bn);
-    if(rc)
-        return rc;
     fill_epilogue(p.epi, d);
-    const int64_t tiles_m = (d->M + BM - 1) / BM;
     const int64_t tiles_n = (d->N + bn - 1) / bn;
+    const int cg          = pick_cg(((d->M + BM - 1) / BM) * tiles_n, bn, dev->sm_count);
+    const int64_t tiles_m = (d->M + BM * cg - 1) / (BM * cg);
     if(tiles_m * tiles_n > 0x3FFFFFFFll)
         return fail(CKB_ERR_UNSUPPORTED, "too many tiles");
-    const WorkPlan plan = plan_work(tiles_m * tiles_n, dev->sm_count, bn);
-    rc = encode_kmajor_2d(&p.tm_b_split, d->ab_dtype, d->p_b, d->N, d->K, d->ldb, bn / plan.split);
+    const WorkPlan plan = plan_work(tiles_m * tiles_n, dev->sm_count / cg, bn, cg);
+    rc = encode_kmajor_2d(&p.tm_b, d->ab_dtype, d->p_b, d->N, d->K, d->ldb, bn / cg);
+    if(rc)
+        return rc;
+    rc = encode_kmajor_2d(&p.tm_b_split, d->ab_dtype, d->p_b, d->N, d->K, d->ldb, bn / plan.split / cg);
     if(rc)
         return rc;
     p.split_start   = plan.split_start;
@@ -475,7 +487,7 @@ int ckb_gemm_run(const ckb_gemm_desc* d, void* stream, int n_rep, float* avg_ms)
     LaunchFn fn     = find_launch(MODE_GEMM, d->ab_dtype == CKB_I8 ? KIND_I8 : KIND_F16, d->epilogue);
     if(!fn)
         return fail(CKB_ERR_UNSUPPORTED, "no kernel instance for epilogue %d", d->epilogue);
-    return run_timed(fn, bn, p, plan.grid, static_cast<cudaStream_t>(stream), n_rep, avg_ms);
+    return run_timed(fn, bn, cg, p, plan.grid, static_cast<cudaStream_t>(stream), n_rep, avg_ms);
 }
 
 // ---- grouped GEMM -------------------------------------------------------------------------------
@@ -538,12 +550,16 @@ int ckb_grouped_gemm_run(const ckb_grouped_gemm_desc* g, void* workspace, size_t
     }
     const int bn = pick_bn(sum_m, max_n, dev->sm_count);
 
+    int64_t tiles_128 = 0;
+    for(int i = 0; i < g->group_count; ++i)
+        tiles_128 += ((g->groups[i].M + BM - 1) / BM) * ((g->groups[i].N + bn - 1) / bn);
+    const int cg      = pick_cg(tiles_128, bn, dev->sm_count);
     int64_t all_tiles = 0;
     for(int i = 0; i < g->group_count; ++i)
-        all_tiles += ((g->groups[i].M + BM - 1) / BM) * ((g->groups[i].N + bn - 1) / bn);
+        all_tiles += ((g->groups[i].M + BM * cg - 1) / (BM * cg)) * ((g->groups[i].N + bn - 1) / bn);
     if(all_tiles > 0x3FFFFFFFll)
         return fail(CKB_ERR_UNSUPPORTED, "too many tiles");
-    const WorkPlan plan = plan_work(all_tiles, dev->sm_count, bn);
+    const WorkPlan plan = plan_work(all_tiles, dev->sm_count / cg, bn, cg);
 
     std::vector<GroupEntry> table(g->group_count);
     int64_t tile_start = 0;
@@ -555,13 +571,13 @@ int ckb_grouped_gemm_run(const ckb_grouped_gemm_desc* g, void* workspace, size_t
         rc = encode_kmajor_2d(&ge.tm_a, dtype, d.p_a, d.M, d.K, d.lda, BM);
         if(rc)
             return rc;
-        rc = encode_kmajor_2d(&ge.tm_b, dtype, d.p_b, d.N, d.K, d.ldb, bn);
+        rc = encode_kmajor_2d(&ge.tm_b, dtype, d.p_b, d.N, d.K, d.ldb, bn / cg);
         if(rc)
             return rc;
-        rc = encode_kmajor_2d(&ge.tm_b_split, dtype, d.p_b, d.N, d.K, d.ldb, bn / plan.split);
+        rc = encode_kmajor_2d(&ge.tm_b_split, dtype, d.p_b, d.N, d.K, d.ldb, bn / plan.split / cg);
         if(rc)
             return rc;
-        const int64_t tm = (d.M + BM - 1) / BM, tn = (d.N + bn - 1) / bn;
+        const int64_t tm = (d.M + BM * cg - 1) / (BM * cg), tn = (d.N + bn - 1) / bn;
         ge.M          = static_cast<int32_t>(d.M);
         ge.N          = static_cast<int32_t>(d.N);
         ge.K          = static_cast<int32_t>(d.K);
@@ -597,7 +613,7 @@ int ckb_grouped_gemm_run(const ckb_grouped_gemm_desc* g, void* workspace, size_t
     LaunchFn fn     = find_launch(MODE_GROUPED, dtype == CKB_I8 ? KIND_I8 : KIND_F16, g->groups[0].epilogue);
     if(!fn)
         return fail(CKB_ERR_UNSUPPORTED, "no kernel instance for epilogue %d", g->groups[0].epilogue);
-    return run_timed(fn, bn, p, plan.grid, stream, n_rep, avg_ms);
+    return run_timed(fn, bn, cg, p, plan.grid, stream, n_rep, avg_ms);
 }
 
 // ---- conv2d forward -------------------------------------------------------------------------------
@@ -701,11 +717,12 @@ int ckb_conv2d_fwd_run(const ckb_conv2d_fwd_desc* d, void* stream, int n_rep, fl
         if(g_driver_version <= 13010 && in_bytes < 131072)
             reinterpret_cast<uint64_t*>(&p.tm_a)[1] &= ~(1ull << 21);
     }
-    const int64_t tiles_m = (gm + BM - 1) / BM;
     const int64_t tiles_n = (d->K + bn - 1) / bn;
+    const int cg          = pick_cg(((gm + BM - 1) / BM) * tiles_n, bn, dev->sm_count);
+    const int64_t tiles_m = (gm + BM * cg - 1) / (BM * cg);
     if(tiles_m * tiles_n > 0x3FFFFFFFll)
         return fail(CKB_ERR_UNSUPPORTED, "too many tiles");
-    const WorkPlan plan = plan_work(tiles_m * tiles_n, dev->sm_count, bn);
+    const WorkPlan plan = plan_work(tiles_m * tiles_n, dev->sm_count / cg, bn, cg);
     for(int which = 0; which < 2; ++which)
     {
         // Weights KYXC as (C, Y*X, K): a box never crosses a filter tap, channels beyond C read 0.
@@ -714,7 +731,7 @@ int ckb_conv2d_fwd_run(const ckb_conv2d_fwd_desc* d, void* stream, int n_rep, fl
         cuuint64_t strides[2] = {static_cast<cuuint64_t>(d->C) * 2,
                                  static_cast<cuuint64_t>(d->Y) * d->X * d->C * 2};
         cuuint32_t box[3]     = {static_cast<cuuint32_t>(bk), 1,
-                             static_cast<cuuint32_t>(which == 0 ? bn : bn / plan.split)};
+                             static_cast<cuuint32_t>((which == 0 ? bn : bn / plan.split) / cg)};
         cuuint32_t estr[3]    = {1, 1, 1};
         CUresult r = g_encode_tiled(which == 0 ? &p.tm_b : &p.tm_b_split, CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
                                     3, const_cast<void*>(d->p_wei), dims, strides, box, estr,
@@ -765,7 +782,7 @@ int ckb_conv2d_fwd_run(const ckb_conv2d_fwd_desc* d, void* stream, int n_rep, fl
     LaunchFn fn = find_launch(MODE_CONV, KIND_F16, d->epilogue);
     if(!fn)
         return fail(CKB_ERR_UNSUPPORTED, "no kernel instance for epilogue %d", d->epilogue);
-    return run_timed(fn, bn, p, plan.grid, static_cast<cudaStream_t>(stream), n_rep, avg_ms);
+    return run_timed(fn, bn, cg, p, plan.grid, static_cast<cudaStream_t>(stream), n_rep, avg_ms);
 }
 
 } // extern "C"

@@ -24,6 +24,16 @@
 //                 implicit-GEMM address generation of
 //                 device_convnd_fwd_xdl_nhwc_kyxc_nhwk.hpp:311-369 happens in the TMA unit
 //
+// CTA pairs (CG = 2).  Large problems run with thread-block clusters of two CTAs on one
+// 256 x BN tile: tcgen05.mma.cta_group::2 is issued by the leader CTA (cluster rank 0) and reads
+// both CTAs' shared memory; each CTA loads its own 128 rows of A and its own half of the B rows
+// (no load has more than one destination CTA), keeps 128 rows of the accumulator in its own
+// tensor memory and runs its own epilogue.  All loads post their bytes on the LEADER's "full"
+// barrier; the leader's tcgen05.commit fans the "empty" / "accumulator full" arrivals out to both
+// CTAs; the epilogue warps of both CTAs release the accumulator on the leader's barrier.
+// Compared with CG = 1 a stage holds half the B tile, so the ring is 6 deep instead of 4 and
+// every SM pulls a third less operand traffic through L2.
+//
 // Every wait is bounded: after `wait_limit_ns` the waiting thread records a code in the status
 // word, raises the CTA's abort flag, and all roles drain and leave through the common exit,
 // which frees the tensor memory.
@@ -100,11 +110,11 @@ struct KernelParams
     uint32_t* status; // device status word
 };
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int CG>
 struct SmemLayout
 {
     static constexpr int A_BYTES     = BM * BK_BYTES;
-    static constexpr int B_BYTES     = BN * BK_BYTES;
+    static constexpr int B_BYTES     = (BN / CG) * BK_BYTES; // a CTA of a pair holds half the B rows
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int BAR_OFFSET  = STAGES * STAGE_BYTES;
     // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], drain
@@ -257,10 +267,11 @@ __device__ __forceinline__ void epilogue_span(uint32_t tmem_addr, const Epilogue
 
 // EPI (the fused epilogue functor) is a template parameter: one functor per kernel keeps the
 // epilogue warps inside the 168-register budget that ten warps per SM leave.
-template <int MODE, int KIND, int EPI, int BN, int STAGES>
+template <int MODE, int KIND, int EPI, int BN, int STAGES, int CG>
 __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __grid_constant__ KernelParams P)
 {
-    using L = SmemLayout<BN, STAGES>;
+    using L = SmemLayout<BN, STAGES, CG>;
+    constexpr int TILE_M = BM * CG;
     constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
     constexpr int UMMA_K_BYTES   = 32; // 16 x 16-bit or 32 x 8-bit
     constexpr int K_STEPS        = BK_BYTES / UMMA_K_BYTES;
@@ -284,18 +295,23 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    // CG = 2: rank of this CTA in its pair (0 = leader), work is indexed by pair.
+    const uint32_t cta_rank = (CG == 2) ? cluster_ctarank() : 0u;
+    const bool is_leader    = cta_rank == 0;
+    const int unit          = (CG == 2) ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+    const int num_units     = (CG == 2) ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
     if(threadIdx.x == 0)
     {
         for(int s = 0; s < STAGES; ++s)
         {
-            mbar_init(full_bar(s), 1);
-            mbar_init(empty_bar(s), 1);
+            mbar_init(full_bar(s), 1);  // the (leader's) producer arrival + all bytes of the stage
+            mbar_init(empty_bar(s), 1); // one tcgen05.commit arrival
         }
         for(int a = 0; a < 2; ++a)
         {
             mbar_init(tmem_full_bar(a), 1);
-            mbar_init(tmem_empty_bar(a), NUM_EPI_WARPS); // one arrival per epilogue warp
+            mbar_init(tmem_empty_bar(a), NUM_EPI_WARPS * CG); // one arrival per epilogue warp (of both CTAs)
         }
         mbar_init(drain_bar, 1);
         misc[1] = 0;
@@ -304,11 +320,22 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
     }
     if(warp == 1)
     {
-        tmem_alloc(smem_u32(const_cast<uint32_t*>(&misc[0])), TMEM_COLS);
-        tmem_relinquish();
+        if constexpr(CG == 2)
+        {
+            tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(&misc[0])), TMEM_COLS);
+            tmem_relinquish_pair();
+        }
+        else
+        {
+            tmem_alloc(smem_u32(const_cast<uint32_t*>(&misc[0])), TMEM_COLS);
+            tmem_relinquish();
+        }
     }
     tc_fence_before_sync();
-    __syncthreads();
+    if constexpr(CG == 2)
+        cluster_sync_all(); // the peer's barriers must exist before anything is posted on them
+    else
+        __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = misc[0];
 
@@ -329,7 +356,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
             uint32_t issued     = 0; // bit s: a load was issued into stage s
             uint32_t last_phase = 0; // bit s: phase of the last load issued into stage s
             bool ok             = true;
-            for(int w = blockIdx.x; ok && w < P.total_work; w += gridDim.x)
+            for(int w = unit; ok && w < P.total_work; w += num_units)
             {
                 const WorkItem wi       = decode_work<MODE, BN>(P, w);
                 const CUtensorMap* tm_a = &P.tm_a;
@@ -339,12 +366,17 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                     tm_a = &wi.group->tm_a;
                     tm_b = wi.is_slice ? &wi.group->tm_b_split : &wi.group->tm_b;
                 }
-                const uint32_t tx_bytes = L::A_BYTES + wi.width * BK_BYTES;
-                // CONV: first output pixel of the tile in (n, ho, wo)
+                // bytes of one stage over the whole CTA group (posted on the leader's barrier)
+                const uint32_t tx_bytes = CG * L::A_BYTES + wi.width * BK_BYTES;
+                const int b_rows        = wi.width / CG;                       // B rows this CTA loads
+                const int a_row0        = wi.m_blk * TILE_M + cta_rank * BM;  // first A row of this CTA
+                const int b_row0        = wi.n_start + cta_rank * b_rows;
+                (void)b_rows;
+                // CONV: first output pixel of this CTA's rows in (n, ho, wo)
                 int cv_n = 0, cv_h = 0, cv_w = 0;
                 if constexpr(MODE == MODE_CONV)
                 {
-                    const int m0  = wi.m_blk * BM;
+                    const int m0  = a_row0;
                     cv_n          = m0 / P.conv.HoWo;
                     const int rem = m0 - cv_n * P.conv.HoWo;
                     const int ho  = rem / P.conv.Wo;
@@ -360,14 +392,40 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                         break;
                     const uint32_t a_dst = base_addr + stage * L::STAGE_BYTES;
                     const uint32_t b_dst = a_dst + L::A_BYTES;
-                    mbar_arrive_expect_tx(full_bar(stage), tx_bytes);
-                    if constexpr(MODE == MODE_CONV)
+                    if(is_leader)
+                        mbar_arrive_expect_tx(full_bar(stage), tx_bytes);
+                    if constexpr(CG == 2)
+                    {
+                        const uint32_t bar = mapa_shared(full_bar(stage), 0); // the leader's barrier
+                        if constexpr(MODE == MODE_CONV)
+                        {
+                            tma_load_im2col_4d_pair(a_dst, tm_a, bar, cv_cb * BK_ELEMS, cv_w, cv_h, cv_n,
+                                                    static_cast<uint16_t>(cv_x * P.conv.dil_w),
+                                                    static_cast<uint16_t>(cv_y * P.conv.dil_h));
+                            tma_load_3d_pair(b_dst, tm_b, bar, cv_cb * BK_ELEMS, cv_y * P.conv.X + cv_x,
+                                             b_row0);
+                        }
+                        else
+                        {
+                            tma_load_2d_pair(a_dst, tm_a, bar, kb * BK_ELEMS, a_row0);
+                            tma_load_2d_pair(b_dst, tm_b, bar, kb * BK_ELEMS, b_row0);
+                        }
+                    }
+                    else if constexpr(MODE == MODE_CONV)
                     {
                         tma_load_im2col_4d(a_dst, tm_a, full_bar(stage), cv_cb * BK_ELEMS, cv_w, cv_h,
                                            cv_n, static_cast<uint16_t>(cv_x * P.conv.dil_w),
                                            static_cast<uint16_t>(cv_y * P.conv.dil_h));
                         tma_load_3d(b_dst, tm_b, full_bar(stage), cv_cb * BK_ELEMS,
                                     cv_y * P.conv.X + cv_x, wi.n_start);
+                    }
+                    else
+                    {
+                        tma_load_2d(a_dst, tm_a, full_bar(stage), kb * BK_ELEMS, a_row0);
+                        tma_load_2d(b_dst, tm_b, full_bar(stage), kb * BK_ELEMS, b_row0);
+                    }
+                    if constexpr(MODE == MODE_CONV)
+                    {
                         if(++cv_cb == P.conv.c_blocks)
                         {
                             cv_cb = 0;
@@ -378,11 +436,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                             }
                         }
                     }
-                    else
-                    {
-                        tma_load_2d(a_dst, tm_a, full_bar(stage), kb * BK_ELEMS, wi.m_blk * BM);
-                        tma_load_2d(b_dst, tm_b, full_bar(stage), kb * BK_ELEMS, wi.n_start);
-                    }
                     issued |= 1u << stage;
                     last_phase = (last_phase & ~(1u << stage)) | (phase << stage);
                     if(++stage == STAGES)
@@ -392,9 +445,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                     }
                 }
             }
-            // Do not leave while a bulk copy may still write this CTA's shared memory.
+            // Do not leave while a bulk copy may still write shared memory.  The leader's barriers
+            // count the bytes of both CTAs, and the pair leaves together (cluster sync at the exit).
             for(int s = 0; s < STAGES; ++s)
-                if(issued & (1u << s))
+                if(is_leader && (issued & (1u << s)))
                 {
                     WaitCtx drain{&misc[2], P.wait_limit_ns, P.status}; // misc[2] stays 0: wait regardless of abort
                     bounded_wait(full_bar(s), (last_phase >> s) & 1u, drain, WAIT_DRAIN);
@@ -404,17 +458,17 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
     else if(warp == 1)
     {
         // ------------------------------------------------------------------ MMA issuer
-        if(lane == 0)
+        if(lane == 0 && is_leader)
         {
             int stage       = 0;
             uint32_t phase  = 0;
             int iter        = 0;
             bool ok         = true;
             bool issued_any = false;
-            for(int w = blockIdx.x; ok && w < P.total_work; w += gridDim.x, ++iter)
+            for(int w = unit; ok && w < P.total_work; w += num_units, ++iter)
             {
                 const WorkItem wi        = decode_work<MODE, BN>(P, w);
-                const uint32_t idesc     = make_idesc(C_FMT, AB_FMT, BM, static_cast<uint32_t>(wi.width));
+                const uint32_t idesc     = make_idesc(C_FMT, AB_FMT, TILE_M, static_cast<uint32_t>(wi.width));
                 const int acc            = iter & 1;
                 const uint32_t acc_phase = (iter >> 1) & 1;
                 ok = bounded_wait(tmem_empty_bar(acc), acc_phase ^ 1u, wc, WAIT_TMEM_EMPTY);
@@ -435,26 +489,48 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                     for(int k = 0; k < K_STEPS; ++k)
                     {
                         const uint64_t koff = static_cast<uint64_t>((k * UMMA_K_BYTES) >> 4);
-                        if constexpr(KIND == KIND_I8)
-                            mma_i8_ss(tmem_d, a_desc + koff, b_desc + koff, idesc, (kb | k) != 0);
+                        if constexpr(CG == 2)
+                        {
+                            if constexpr(KIND == KIND_I8)
+                                mma_i8_ss_pair(tmem_d, a_desc + koff, b_desc + koff, idesc, (kb | k) != 0);
+                            else
+                                mma_f16_ss_pair(tmem_d, a_desc + koff, b_desc + koff, idesc, (kb | k) != 0);
+                        }
                         else
-                            mma_f16_ss(tmem_d, a_desc + koff, b_desc + koff, idesc, (kb | k) != 0);
+                        {
+                            if constexpr(KIND == KIND_I8)
+                                mma_i8_ss(tmem_d, a_desc + koff, b_desc + koff, idesc, (kb | k) != 0);
+                            else
+                                mma_f16_ss(tmem_d, a_desc + koff, b_desc + koff, idesc, (kb | k) != 0);
+                        }
                     }
                     issued_any = true;
-                    mma_commit(empty_bar(stage)); // stage is free once these MMAs have read it
+                    // the stage is free (in both CTAs) once these MMAs have read it
+                    if constexpr(CG == 2)
+                        mma_commit_pair_mc(empty_bar(stage), 3);
+                    else
+                        mma_commit(empty_bar(stage));
                     if(++stage == STAGES)
                     {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
-                if(ok)
-                    mma_commit(tmem_full_bar(acc)); // accumulator complete
+                if(ok) // accumulator complete (in both CTAs)
+                {
+                    if constexpr(CG == 2)
+                        mma_commit_pair_mc(tmem_full_bar(acc), 3);
+                    else
+                        mma_commit(tmem_full_bar(acc));
+                }
             }
             // Every MMA issued must be finished before the tensor memory is freed.
             if(issued_any)
             {
-                mma_commit(drain_bar);
+                if constexpr(CG == 2)
+                    mma_commit_pair(drain_bar);
+                else
+                    mma_commit(drain_bar);
                 WaitCtx drain{&misc[2], P.wait_limit_ns, P.status};
                 bounded_wait(drain_bar, 0, drain, WAIT_DRAIN);
             }
@@ -467,7 +543,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
         const int half    = (warp - 2) >> 2; // which half of the item's columns
         int iter          = 0;
         bool ok           = true;
-        for(int w = blockIdx.x; ok && w < P.total_work; w += gridDim.x, ++iter)
+        for(int w = unit; ok && w < P.total_work; w += num_units, ++iter)
         {
             const WorkItem wi = decode_work<MODE, BN>(P, w);
             EpilogueArgs ea   = P.epi;
@@ -487,7 +563,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                 ea.ldd1             = G->ldd1;
             }
             const int span          = wi.width >> 1; // columns per epilogue warp (>= 32)
-            const int64_t m         = static_cast<int64_t>(wi.m_blk) * BM + quarter * 32 + lane;
+            const int64_t m =
+                static_cast<int64_t>(wi.m_blk) * TILE_M + cta_rank * BM + quarter * 32 + lane;
             const bool row_ok       = m < Mdim;
             const int64_t n_begin   = static_cast<int64_t>(wi.n_start) + half * span;
             const int64_t n_end_raw = n_begin + span;
@@ -507,12 +584,17 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
             tc_fence_before_sync();
             __syncwarp();
             if(lane == 0)
-                mbar_arrive(tmem_empty_bar(acc));
+            {
+                if constexpr(CG == 2)
+                    mbar_arrive_cluster(mapa_shared(tmem_empty_bar(acc), 0)); // the leader's barrier
+                else
+                    mbar_arrive(tmem_empty_bar(acc));
+            }
 
             // Ask L2 for the D values of this CTA's next item while its main loop runs.
             if constexpr(KIND != KIND_I8)
             {
-                const int wn = w + gridDim.x;
+                const int wn = w + num_units;
                 if(epi_num_d(EPI) > 0 && wn < P.total_work)
                 {
                     const WorkItem nx = decode_work<MODE, BN>(P, wn);
@@ -528,7 +610,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                         Nn      = nx.group->N;
                     }
                     const int spn    = nx.width >> 1;
-                    const int64_t mn = static_cast<int64_t>(nx.m_blk) * BM + quarter * 32 + lane;
+                    const int64_t mn =
+                        static_cast<int64_t>(nx.m_blk) * TILE_M + cta_rank * BM + quarter * 32 + lane;
                     const int64_t nb = static_cast<int64_t>(nx.n_start) + half * spn;
                     if(mn < Mn && nb < Nn)
                     {
@@ -542,10 +625,18 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
 
     // ---------------------------------------------------------------------- common exit
     tc_fence_before_sync();
-    __syncthreads();
+    if constexpr(CG == 2)
+        cluster_sync_all(); // the leader's MMAs read the peer's shared memory until the very end
+    else
+        __syncthreads();
     tc_fence_after_sync();
     if(warp == 1)
-        tmem_dealloc(tmem_base, TMEM_COLS);
+    {
+        if constexpr(CG == 2)
+            tmem_dealloc_pair(tmem_base, TMEM_COLS);
+        else
+            tmem_dealloc(tmem_base, TMEM_COLS);
+    }
 }
 
 } // namespace ckb
