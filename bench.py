@@ -31,6 +31,8 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+from composable_kernel_b200.sharding import batch_shard, grouped_gemm_shard  # noqa: E402
+
 # fp16 GEMM 3840x4096x4096 on MI100: example/01_gemm/README.md:11-22 of the reference
 PUBLISHED_MI100_TFLOPS = {"gemm_fp16": 107.657, "gemm_fastgelu": 101.525, "conv": 105.581}
 FALLBACK_PEAK_TFLOPS = 1590.0
@@ -111,17 +113,6 @@ class ClockSampler:
 # ------------------------------------------------------------------------------------------------
 # workloads
 # ------------------------------------------------------------------------------------------------
-def lpt_partition(weights, parts):
-    """Longest-processing-time greedy: returns a list of index lists, one per part."""
-    order = sorted(range(len(weights)), key=lambda i: -weights[i])
-    loads, out = [0] * parts, [[] for _ in range(parts)]
-    for i in order:
-        j = loads.index(min(loads))
-        out[j].append(i)
-        loads[j] += weights[i]
-    return out
-
-
 class GemmWorkload:
     """C1 / C2 / C3: M=3840 N=4096 K=4096, A row-major, B column-major."""
 
@@ -193,9 +184,10 @@ class ConvWorkload:
     def __init__(self, torch, ck, capi, rank, world):
         self.name, self.torch, self.ck, self.capi = "conv", torch, ck, capi
         self.Ntot, self.C, self.Hi, self.Wi, self.K, self.Ho, self.Wo = 128, 192, 71, 71, 256, 36, 36
-        self.Nloc = self.Ntot // world
+        b0, b1 = batch_shard(self.Ntot, rank, world)
+        self.Nloc = b1 - b0
         self.flop_total = 2 * self.Ntot * self.K * self.Ho * self.Wo * self.C * 9
-        self.flop = self.flop_total // world
+        self.flop = 2 * self.Nloc * self.K * self.Ho * self.Wo * self.C * 9
         self.bytes = 2 * (self.Nloc * self.C * self.Hi * self.Wi + self.K * self.C * 9 +
                           self.Nloc * self.K * self.Ho * self.Wo) + 2 * self.K
         self.dtype, self.unit = "f16", "TFLOPS"
@@ -241,7 +233,7 @@ class GroupedWorkload:
         self.name, self.torch, self.ck, self.capi = "grouped", torch, ck, capi
         self.N = self.K = 4096
         all_m = [256 * (1 + g % 16) for g in range(64)]
-        self.mine = sorted(lpt_partition(all_m, world)[rank])
+        self.mine = grouped_gemm_shard(all_m, rank, world)
         self.Ms = [all_m[g] for g in self.mine]
         self.flop_total = sum(2 * m * self.N * self.K for m in all_m)
         self.flop = sum(2 * m * self.N * self.K for m in self.Ms)
