@@ -23,6 +23,7 @@ CKB_ROW_MAJOR, CKB_COL_MAJOR = 0, 1
  CKB_EPI_REQUANT_RELU_REQUANT, CKB_EPI_REQUANT_RELU_REQUANT_RNE, CKB_EPI_ADD_RELU,
  CKB_EPI_ADD_HARDSWISH) = range(13)
 CKB_MAX_DS = 2
+CKB_NOALLOC_MAX_GROUPS = 256
 
 EPI_NUM_D = {CKB_EPI_ADD: 1, CKB_EPI_ADD_RELU_F16: 1, CKB_EPI_BILINEAR: 1, CKB_EPI_ADD_RELU: 1,
              CKB_EPI_ADD_HARDSWISH: 1, CKB_EPI_ADD_ADD_FASTGELU: 2, CKB_EPI_ADD_RELU_ADD: 2}
@@ -86,6 +87,7 @@ SYMBOLS = {
     "ckb_grouped_gemm_workspace_size": (c_int, [POINTER(GroupedGemmDesc), POINTER(c_size_t)]),
     "ckb_grouped_gemm_run": (c_int, [POINTER(GroupedGemmDesc), c_void_p, c_size_t, c_void_p, c_int,
                                      POINTER(c_float)]),
+    "ckb_grouped_gemm_run_noalloc": (c_int, [POINTER(GroupedGemmDesc), c_void_p]),
     "ckb_conv2d_fwd_supported": (c_int, [POINTER(Conv2dFwdDesc)]),
     "ckb_conv2d_fwd_run": (c_int, [POINTER(Conv2dFwdDesc), c_void_p, c_int, POINTER(c_float)]),
 }

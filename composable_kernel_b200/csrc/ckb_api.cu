@@ -616,6 +616,124 @@ int ckb_grouped_gemm_run(const ckb_grouped_gemm_desc* g, void* workspace, size_t
     return run_timed(fn, bn, cg, p, plan.grid, stream, n_rep, avg_ms);
 }
 
+// ---- grouped GEMM without allocation ----------------------------------------------------------------
+// The per-group table of the grouped kernel, for callers that cannot hand over a workspace.  The
+// array lives in the library image on every device.  In HOST code its name is only a handle:
+// the device address comes from cudaGetSymbolAddress (looked up once per device, with that device
+// current) and that pointer is what the kernel receives.
+static __device__ __align__(256) unsigned char g_noalloc_group_table[CKB_NOALLOC_MAX_GROUPS * sizeof(GroupEntry)];
+static_assert(sizeof(GroupEntry) == 512, "the documented size of the fixed table assumes 512-byte entries");
+
+static GroupEntry* g_noalloc_dev_ptr[64] = {};
+static GroupEntry g_noalloc_host_table[CKB_NOALLOC_MAX_GROUPS]; // host staging, fixed size
+static std::mutex g_noalloc_mutex;
+
+int ckb_grouped_gemm_run_noalloc(const ckb_grouped_gemm_desc* g, void* stream_)
+{
+    int rc = check_grouped(g, true);
+    if(rc)
+        return rc;
+    if(g->group_count > CKB_NOALLOC_MAX_GROUPS)
+        return fail(CKB_ERR_LIMIT,
+                    "ckb_grouped_gemm_run_noalloc holds at most %d groups in its fixed table, got %d; "
+                    "use ckb_grouped_gemm_run with a caller-provided workspace",
+                    CKB_NOALLOC_MAX_GROUPS, g->group_count);
+    DeviceInfo* dev = nullptr;
+    rc              = current_device(&dev);
+    if(rc)
+        return rc;
+    int ordinal = 0;
+    CKB_CUDA(cudaGetDevice(&ordinal));
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if(!g_noalloc_dev_ptr[ordinal])
+    {
+        // once per device, with that device current
+        GroupEntry* ptr = nullptr;
+        CKB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_group_table));
+        if(!ptr)
+            return fail(CKB_ERR_CUDA, "cudaGetSymbolAddress returned a null address for the fixed group table");
+        g_noalloc_dev_ptr[ordinal] = ptr;
+    }
+    GroupEntry* d_table = g_noalloc_dev_ptr[ordinal];
+
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    const int dtype     = g->groups[0].ab_dtype;
+    const int eb        = elem_bytes(dtype);
+    const int bk        = BK_BYTES / eb;
+    int64_t max_n = 0, sum_m = 0;
+    for(int i = 0; i < g->group_count; ++i)
+    {
+        max_n = max_n > g->groups[i].N ? max_n : g->groups[i].N;
+        sum_m += g->groups[i].M;
+    }
+    const int bn      = pick_bn(sum_m, max_n, dev->sm_count);
+    int64_t tiles_128 = 0;
+    for(int i = 0; i < g->group_count; ++i)
+        tiles_128 += ((g->groups[i].M + BM - 1) / BM) * ((g->groups[i].N + bn - 1) / bn);
+    const int cg      = pick_cg(tiles_128, bn, dev->sm_count);
+    int64_t all_tiles = 0;
+    for(int i = 0; i < g->group_count; ++i)
+        all_tiles += ((g->groups[i].M + BM * cg - 1) / (BM * cg)) * ((g->groups[i].N + bn - 1) / bn);
+    if(all_tiles > 0x3FFFFFFFll)
+        return fail(CKB_ERR_UNSUPPORTED, "too many tiles");
+    const WorkPlan plan = plan_work(all_tiles, dev->sm_count / cg, bn, cg);
+
+    int64_t tile_start = 0;
+    for(int i = 0; i < g->group_count; ++i)
+    {
+        const ckb_gemm_desc& d = g->groups[i];
+        GroupEntry& ge         = g_noalloc_host_table[i];
+        memset(&ge, 0, sizeof(ge));
+        rc = encode_kmajor_2d(&ge.tm_a, dtype, d.p_a, d.M, d.K, d.lda, BM);
+        if(rc)
+            return rc;
+        rc = encode_kmajor_2d(&ge.tm_b, dtype, d.p_b, d.N, d.K, d.ldb, bn / cg);
+        if(rc)
+            return rc;
+        rc = encode_kmajor_2d(&ge.tm_b_split, dtype, d.p_b, d.N, d.K, d.ldb, bn / plan.split / cg);
+        if(rc)
+            return rc;
+        const int64_t tm = (d.M + BM * cg - 1) / (BM * cg), tn = (d.N + bn - 1) / bn;
+        ge.M          = static_cast<int32_t>(d.M);
+        ge.N          = static_cast<int32_t>(d.N);
+        ge.K          = static_cast<int32_t>(d.K);
+        ge.tiles_n    = static_cast<int32_t>(tn);
+        ge.tile_start = static_cast<int32_t>(tile_start);
+        ge.num_kb     = static_cast<int32_t>((d.K + bk - 1) / bk);
+        ge.vec_ok     = gemm_vec_ok(&d) ? 1 : 0;
+        ge.e          = d.p_e;
+        ge.d0         = d.n_ds > 0 ? d.p_ds[0] : nullptr;
+        ge.d1         = d.n_ds > 1 ? d.p_ds[1] : nullptr;
+        ge.lde        = d.lde;
+        ge.ldd0       = d.n_ds > 0 ? d.ldd[0] : 0;
+        ge.ldd1       = d.n_ds > 1 ? d.ldd[1] : 0;
+        tile_start += tm * tn;
+    }
+    // Every entry this launch reads is rewritten here; stale entries beyond group_count are never
+    // read.  Pageable source: the runtime stages the bytes before returning, so the host staging
+    // table may be reused as soon as the mutex is released.
+    CKB_CUDA(cudaMemcpyAsync(d_table, g_noalloc_host_table, static_cast<size_t>(g->group_count) * sizeof(GroupEntry),
+                             cudaMemcpyHostToDevice, stream));
+
+    KernelParams p;
+    memset(&p, 0, sizeof(p));
+    fill_epilogue(p.epi, &g->groups[0]);
+    p.groups        = d_table;
+    p.group_count   = g->group_count;
+    p.total_tiles   = static_cast<int32_t>(tile_start);
+    p.split_start   = plan.split_start;
+    p.split         = plan.split;
+    p.total_work    = plan.total_work;
+    p.wait_limit_ns = wait_limit_ns();
+    p.status        = dev->status;
+    LaunchFn fn     = find_launch(MODE_GROUPED, dtype == CKB_I8 ? KIND_I8 : KIND_F16, g->groups[0].epilogue);
+    if(!fn)
+        return fail(CKB_ERR_UNSUPPORTED, "no kernel instance for epilogue %d", g->groups[0].epilogue);
+    CKB_CUDA(fn(bn, cg, p, plan.grid, stream));
+    g_launches.fetch_add(1);
+    return CKB_OK;
+}
+
 // ---- conv2d forward -------------------------------------------------------------------------------
 static int check_conv(const ckb_conv2d_fwd_desc* d, bool need_pointers)
 {

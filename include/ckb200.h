@@ -153,6 +153,32 @@ int ckb_grouped_gemm_workspace_size(const ckb_grouped_gemm_desc* desc, size_t* b
 int ckb_grouped_gemm_run(const ckb_grouped_gemm_desc* desc, void* workspace,
                          size_t workspace_bytes, void* stream, int n_rep, float* avg_ms);
 
+/* Grouped GEMM for callers that must not allocate.  It has no counterpart in the reference.
+ *
+ * Who needs it: host code that runs under a fixed device-memory plan - a serving loop whose
+ * arena already owns all of HBM, a plug-in called from inside another framework's memory
+ * planner, a latency-critical path where cudaMalloc's implicit device synchronisation is not
+ * acceptable - cannot provide the workspace that ckb_grouped_gemm_run asks for at call time.
+ * This variant keeps the per-group table (the kernel's only scratch memory) in a fixed array
+ * that is part of the library image, so the call makes no cudaMalloc / cudaFree and uses no
+ * allocating library routine; the caller still passes every input and output buffer.
+ *
+ * Limits and rules
+ *   - at most CKB_NOALLOC_MAX_GROUPS groups; more is rejected with CKB_ERR_LIMIT and a message.
+ *     The array costs CKB_NOALLOC_MAX_GROUPS * 512 bytes (128 KiB) of device memory on every
+ *     GPU that loads the library, until the process exits.
+ *   - the FIRST call on a device looks up the array's device address (cudaGetSymbolAddress with
+ *     that device current) and sets the kernel's shared-memory attribute.  Make that first call
+ *     during set-up, before any stream capture begins.
+ *   - every call on a device shares the one array.  A call rewrites all entries it uses, so
+ *     nothing has to be cleared between calls, but two calls whose kernels may overlap on the
+ *     GPU (different streams, or host threads racing on one device) would overwrite each
+ *     other's table: serialise them on one stream.
+ *   - one asynchronous launch on `stream`; there is no timing mode (events would allocate).
+ * Results are identical to ckb_grouped_gemm_run on the same descriptors. */
+#define CKB_NOALLOC_MAX_GROUPS 256
+int ckb_grouped_gemm_run_noalloc(const ckb_grouped_gemm_desc* desc, void* stream);
+
 /* ---- 2-D convolution forward, NHWC / KYXC / NHWK ---------------------------- */
 /* Replaces DeviceConvFwd::MakeArgumentPointer (device/device_conv_fwd.hpp:20-36) and
  * DeviceConvFwdBiasActivation::MakeArgumentPointer
