@@ -1,0 +1,253 @@
+// CPU reference operators with the reference's class names and call sequence, restated for g++:
+//   ReferenceGemm                      .../reference_tensor_operation/cpu/reference_gemm.hpp:23-133
+//   ReferenceConvFwd (2-D)             .../cpu/reference_conv_fwd.hpp:41-313
+//   ReferenceConvFwd_Bias_Activation   .../cpu/reference_conv_fwd_bias_activation.hpp:24-188
+// One output element per call of the inner lambda, sequential float (or AccDataType) accumulation,
+// element-wise operators applied exactly where the reference applies them, work split over
+// std::thread::hardware_concurrency() threads by ParallelTensorFunctor.
+#pragma once
+#include <thread>
+
+#include "ck/b200/device_ops.hpp"
+#include "ck/b200/host_tensor.hpp"
+
+namespace ck {
+namespace tensor_operation {
+namespace host {
+
+template <typename ADataType, typename BDataType, typename CDataType, typename AccDataType,
+          typename AElementwiseOperation, typename BElementwiseOperation, typename CElementwiseOperation>
+struct ReferenceGemm : public device::BaseOperator
+{
+    struct Argument : public device::BaseArgument
+    {
+        Argument(const Tensor<ADataType>& a_m_k, const Tensor<BDataType>& b_k_n, Tensor<CDataType>& c_m_n,
+                 AElementwiseOperation a_element_op, BElementwiseOperation b_element_op,
+                 CElementwiseOperation c_element_op)
+            : a_m_k_{a_m_k}, b_k_n_{b_k_n}, c_m_n_{c_m_n}, a_element_op_{a_element_op},
+              b_element_op_{b_element_op}, c_element_op_{c_element_op}
+        {
+        }
+        const Tensor<ADataType>& a_m_k_;
+        const Tensor<BDataType>& b_k_n_;
+        Tensor<CDataType>& c_m_n_;
+        AElementwiseOperation a_element_op_;
+        BElementwiseOperation b_element_op_;
+        CElementwiseOperation c_element_op_;
+    };
+
+    struct Invoker : public device::BaseInvoker
+    {
+        float Run(const Argument& arg)
+        {
+            auto f_mk_kn_mn = [&](auto m, auto n) {
+                const int K = static_cast<int>(arg.a_m_k_.mDesc.GetLengths()[1]);
+                AccDataType v_acc = 0;
+                for(int k = 0; k < K; ++k)
+                {
+                    ADataType v_a;
+                    BDataType v_b;
+                    arg.a_element_op_(v_a, arg.a_m_k_(m, k));
+                    arg.b_element_op_(v_b, arg.b_k_n_(k, n));
+                    v_acc += type_convert<AccDataType>(v_a) * type_convert<AccDataType>(v_b);
+                }
+                AccDataType v_c;
+                arg.c_element_op_(v_c, v_acc);
+                arg.c_m_n_(m, n) = type_convert<CDataType>(v_c);
+            };
+            make_ParallelTensorFunctor(f_mk_kn_mn, arg.c_m_n_.mDesc.GetLengths()[0],
+                                       arg.c_m_n_.mDesc.GetLengths()[1])(std::thread::hardware_concurrency());
+            return 0;
+        }
+        float Run(const device::BaseArgument* p_arg, const StreamConfig& = StreamConfig{}) override
+        {
+            return Run(*dynamic_cast<const Argument*>(p_arg));
+        }
+    };
+
+    bool IsSupportedArgument(const device::BaseArgument*) override { return true; }
+    static auto MakeArgument(const Tensor<ADataType>& a_m_k, const Tensor<BDataType>& b_k_n, Tensor<CDataType>& c_m_n,
+                             AElementwiseOperation a_element_op, BElementwiseOperation b_element_op,
+                             CElementwiseOperation c_element_op)
+    {
+        return Argument{a_m_k, b_k_n, c_m_n, a_element_op, b_element_op, c_element_op};
+    }
+    static auto MakeInvoker() { return Invoker{}; }
+    std::string GetTypeString() const override { return "ReferenceGemm"; }
+};
+
+// 2-D only: tensors carry NCHW-ordered lengths (any strides), see conv_util host descriptors.
+template <typename InDataType, typename WeiDataType, typename OutDataType, typename InElementwiseOperation,
+          typename WeiElementwiseOperation, typename OutElementwiseOperation, index_t NumDimSpatial = 2>
+struct ReferenceConvFwd : public device::BaseOperator
+{
+    static_assert(NumDimSpatial == 2, "only the 2-D convolution is on the B200 path");
+    struct Argument : public device::BaseArgument
+    {
+        Argument(const Tensor<InDataType>& input, const Tensor<WeiDataType>& weight, Tensor<OutDataType>& output,
+                 std::vector<index_t> conv_filter_strides, std::vector<index_t> conv_filter_dilations,
+                 std::vector<index_t> input_left_pads, std::vector<index_t> input_right_pads,
+                 InElementwiseOperation in_element_op, WeiElementwiseOperation wei_element_op,
+                 OutElementwiseOperation out_element_op)
+            : input_{input}, weight_{weight}, output_{output}, conv_strides_{conv_filter_strides},
+              conv_dilations_{conv_filter_dilations}, in_left_pads_{input_left_pads},
+              in_right_pads_{input_right_pads}, in_element_op_{in_element_op}, wei_element_op_{wei_element_op},
+              out_element_op_{out_element_op}
+        {
+        }
+        const Tensor<InDataType>& input_;
+        const Tensor<WeiDataType>& weight_;
+        Tensor<OutDataType>& output_;
+        std::vector<index_t> conv_strides_, conv_dilations_, in_left_pads_, in_right_pads_;
+        InElementwiseOperation in_element_op_;
+        WeiElementwiseOperation wei_element_op_;
+        OutElementwiseOperation out_element_op_;
+    };
+
+    struct Invoker : public device::BaseInvoker
+    {
+        float Run(const Argument& arg)
+        {
+            const auto& wl = arg.weight_.mDesc.GetLengths(); // K, C, Y, X
+            const auto& il = arg.input_.mDesc.GetLengths();  // N, C, Hi, Wi
+            auto f_nchw    = [&](auto n, auto k, auto ho, auto wo) {
+                float v_acc = 0;
+                for(std::size_t c = 0; c < wl[1]; ++c)
+                    for(std::size_t y = 0; y < wl[2]; ++y)
+                    {
+                        const long_index_t hi = static_cast<long_index_t>(ho * arg.conv_strides_[0]) +
+                                                static_cast<long_index_t>(y * arg.conv_dilations_[0]) -
+                                                static_cast<long_index_t>(arg.in_left_pads_[0]);
+                        for(std::size_t x = 0; x < wl[3]; ++x)
+                        {
+                            const long_index_t wi = static_cast<long_index_t>(wo * arg.conv_strides_[1]) +
+                                                    static_cast<long_index_t>(x * arg.conv_dilations_[1]) -
+                                                    static_cast<long_index_t>(arg.in_left_pads_[1]);
+                            if(hi >= 0 && static_cast<std::size_t>(hi) < il[2] && wi >= 0 &&
+                               static_cast<std::size_t>(wi) < il[3])
+                            {
+                                float v_in, v_wei;
+                                arg.in_element_op_(v_in, type_convert<float>(arg.input_(n, c, hi, wi)));
+                                arg.wei_element_op_(v_wei, type_convert<float>(arg.weight_(k, c, y, x)));
+                                v_acc += v_in * v_wei;
+                            }
+                        }
+                    }
+                float v_out;
+                arg.out_element_op_(v_out, v_acc);
+                arg.output_(n, k, ho, wo) = type_convert<OutDataType>(v_out);
+            };
+            const auto& ol = arg.output_.mDesc.GetLengths();
+            make_ParallelTensorFunctor(f_nchw, ol[0], ol[1], ol[2], ol[3])(std::thread::hardware_concurrency());
+            return 0;
+        }
+        float Run(const device::BaseArgument* p_arg, const StreamConfig& = StreamConfig{}) override
+        {
+            return Run(*dynamic_cast<const Argument*>(p_arg));
+        }
+    };
+
+    bool IsSupportedArgument(const device::BaseArgument*) override { return true; }
+    static auto MakeArgument(const Tensor<InDataType>& input, const Tensor<WeiDataType>& weight,
+                             Tensor<OutDataType>& output, std::vector<index_t> conv_filter_strides,
+                             std::vector<index_t> conv_filter_dilations, std::vector<index_t> input_left_pads,
+                             std::vector<index_t> input_right_pads, InElementwiseOperation in_element_op,
+                             WeiElementwiseOperation wei_element_op, OutElementwiseOperation out_element_op)
+    {
+        return Argument{input, weight, output, conv_filter_strides, conv_filter_dilations, input_left_pads,
+                        input_right_pads, in_element_op, wei_element_op, out_element_op};
+    }
+    static auto MakeInvoker() { return Invoker{}; }
+    std::string GetTypeString() const override { return "ReferenceConvFwd"; }
+};
+
+// out = out_op(acc, float(bias[k])) stored through the implicit float -> OutDataType conversion
+template <typename InDataType, typename WeiDataType, typename OutDataType, typename InElementwiseOperation,
+          typename WeiElementwiseOperation, typename OutElementwiseOperation>
+struct ReferenceConvFwd_Bias_Activation : public device::BaseOperator
+{
+    struct Argument : public device::BaseArgument
+    {
+        Argument(const Tensor<InDataType>& in_n_c_hi_wi, const Tensor<WeiDataType>& wei_k_c_y_x,
+                 Tensor<OutDataType>& out_n_k_ho_wo, const Tensor<OutDataType>& bias_k,
+                 std::vector<index_t> conv_filter_strides, std::vector<index_t> conv_filter_dilations,
+                 std::vector<index_t> input_left_pads, std::vector<index_t> input_right_pads,
+                 InElementwiseOperation in_element_op, WeiElementwiseOperation wei_element_op,
+                 OutElementwiseOperation out_element_op)
+            : in_n_c_hi_wi_{in_n_c_hi_wi}, wei_k_c_y_x_{wei_k_c_y_x}, out_n_k_ho_wo_{out_n_k_ho_wo}, bias_k_{bias_k},
+              conv_strides_{conv_filter_strides}, conv_dilations_{conv_filter_dilations},
+              in_left_pads_{input_left_pads}, in_right_pads_{input_right_pads}, in_element_op_{in_element_op},
+              wei_element_op_{wei_element_op}, out_element_op_{out_element_op}
+        {
+        }
+        const Tensor<InDataType>& in_n_c_hi_wi_;
+        const Tensor<WeiDataType>& wei_k_c_y_x_;
+        Tensor<OutDataType>& out_n_k_ho_wo_;
+        const Tensor<OutDataType>& bias_k_;
+        std::vector<index_t> conv_strides_, conv_dilations_, in_left_pads_, in_right_pads_;
+        InElementwiseOperation in_element_op_;
+        WeiElementwiseOperation wei_element_op_;
+        OutElementwiseOperation out_element_op_;
+    };
+
+    struct Invoker : public device::BaseInvoker
+    {
+        float Run(const Argument& arg)
+        {
+            const auto& wl = arg.wei_k_c_y_x_.mDesc.GetLengths();
+            const auto& il = arg.in_n_c_hi_wi_.mDesc.GetLengths();
+            auto f_nchw    = [&](auto n, auto k, auto ho, auto wo) {
+                float v_acc = 0;
+                for(std::size_t c = 0; c < wl[1]; ++c)
+                    for(std::size_t y = 0; y < wl[2]; ++y)
+                    {
+                        const long_index_t hi = static_cast<long_index_t>(ho * arg.conv_strides_[0]) +
+                                                static_cast<long_index_t>(y * arg.conv_dilations_[0]) -
+                                                static_cast<long_index_t>(arg.in_left_pads_[0]);
+                        for(std::size_t x = 0; x < wl[3]; ++x)
+                        {
+                            const long_index_t wi = static_cast<long_index_t>(wo * arg.conv_strides_[1]) +
+                                                    static_cast<long_index_t>(x * arg.conv_dilations_[1]) -
+                                                    static_cast<long_index_t>(arg.in_left_pads_[1]);
+                            if(hi >= 0 && static_cast<std::size_t>(hi) < il[2] && wi >= 0 &&
+                               static_cast<std::size_t>(wi) < il[3])
+                            {
+                                float v_in, v_wei;
+                                arg.in_element_op_(v_in, static_cast<const float>(arg.in_n_c_hi_wi_(n, c, hi, wi)));
+                                arg.wei_element_op_(v_wei, static_cast<const float>(arg.wei_k_c_y_x_(k, c, y, x)));
+                                v_acc += v_in * v_wei;
+                            }
+                        }
+                    }
+                float v_out;
+                arg.out_element_op_(v_out, v_acc, static_cast<float>(arg.bias_k_(k)));
+                arg.out_n_k_ho_wo_(n, k, ho, wo) = static_cast<OutDataType>(v_out);
+            };
+            const auto& ol = arg.out_n_k_ho_wo_.mDesc.GetLengths();
+            make_ParallelTensorFunctor(f_nchw, ol[0], ol[1], ol[2], ol[3])(std::thread::hardware_concurrency());
+            return 0;
+        }
+        float Run(const device::BaseArgument* p_arg, const StreamConfig& = StreamConfig{}) override
+        {
+            return Run(*dynamic_cast<const Argument*>(p_arg));
+        }
+    };
+
+    bool IsSupportedArgument(const device::BaseArgument*) override { return true; }
+    static auto MakeArgument(const Tensor<InDataType>& in_n_c_hi_wi, const Tensor<WeiDataType>& wei_k_c_y_x,
+                             Tensor<OutDataType>& out_n_k_ho_wo, const Tensor<OutDataType>& bias_k,
+                             std::vector<index_t> conv_filter_strides, std::vector<index_t> conv_filter_dilations,
+                             std::vector<index_t> input_left_pads, std::vector<index_t> input_right_pads,
+                             InElementwiseOperation in_element_op, WeiElementwiseOperation wei_element_op,
+                             OutElementwiseOperation out_element_op)
+    {
+        return Argument{in_n_c_hi_wi, wei_k_c_y_x, out_n_k_ho_wo, bias_k, conv_filter_strides, conv_filter_dilations,
+                        input_left_pads, input_right_pads, in_element_op, wei_element_op, out_element_op};
+    }
+    static auto MakeInvoker() { return Invoker{}; }
+    std::string GetTypeString() const override { return "ReferenceConvFwd_Bias_Activation"; }
+};
+
+} // namespace host
+} // namespace tensor_operation
+} // namespace ck
