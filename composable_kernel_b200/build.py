@@ -61,6 +61,29 @@ def _compile(src: str, verbose: bool) -> str:
     return obj
 
 
+def build_variant(name: str, defines) -> str:
+    """Builds lib/libckb200_<name>.so with extra -D macros (tuning experiments; select it with CKB200_LIB)."""
+    obj_dir = os.path.join(HERE, "build", "variant_" + name)
+    os.makedirs(obj_dir, exist_ok=True)
+    os.makedirs(LIB_DIR, exist_ok=True)
+    flags = NVCC_FLAGS + ["-D" + d for d in defines]
+
+    def one(src):
+        obj = os.path.join(obj_dir, os.path.basename(src)[:-3] + ".o")
+        res = subprocess.run([_nvcc()] + flags + ["-c", src, "-o", obj], capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"nvcc failed for {src}:\n{res.stderr}")
+        return obj
+    with concurrent.futures.ThreadPoolExecutor(max_workers=8) as pool:
+        objs = list(pool.map(one, sources()))
+    out = os.path.join(LIB_DIR, f"libckb200_{name}.so")
+    res = subprocess.run([_nvcc(), "-shared", "-o", out] + objs + ["-gencode", "arch=compute_100a,code=sm_100a"],
+                         capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"link failed:\n{res.stderr}")
+    return out
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(OBJ_DIR, exist_ok=True)
     os.makedirs(LIB_DIR, exist_ok=True)
@@ -84,5 +107,9 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 
 if __name__ == "__main__":
+    if "--variant" in sys.argv:  # python -m composable_kernel_b200.build --variant NAME MACRO[=VALUE] ...
+        i = sys.argv.index("--variant")
+        print(build_variant(sys.argv[i + 1], sys.argv[i + 2:]))
+        sys.exit(0)
     path = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
     print(path)

@@ -11,7 +11,8 @@ from ctypes import (POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int
                     c_uint32, c_uint64, c_void_p)
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "lib", "libckb200.so")
+# CKB200_LIB selects another build of the library (e.g. one compiled with different tuning macros).
+LIB_PATH = os.environ.get("CKB200_LIB") or os.path.join(HERE, "lib", "libckb200.so")
 
 # ---- enums (include/ckb200.h) -------------------------------------------------------------------
 CKB_OK, CKB_ERR_UNSUPPORTED, CKB_ERR_INVALID, CKB_ERR_CUDA, CKB_ERR_DEVICE, CKB_ERR_WORKSPACE, \

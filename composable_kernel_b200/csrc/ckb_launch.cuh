@@ -28,7 +28,11 @@ struct StagesFor<64, 1>
 template <>
 struct StagesFor<256, 2>
 {
+#ifdef CKB_PAIR_STAGES
+    static constexpr int value = CKB_PAIR_STAGES; // build-time override for pipeline-depth experiments (at most 7 fit)
+#else
     static constexpr int value = 6;
+#endif
 };
 
 template <int MODE, int KIND, int EPI, int BN, int CG>
