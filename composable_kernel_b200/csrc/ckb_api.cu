@@ -224,10 +224,15 @@ int pick_cg(int64_t tiles_128, int bn, int sm_count)
     return (bn == 256 && tiles_128 >= sm_count) ? 2 : 1;
 }
 
+int kind_of(int dtype) { return dtype == CKB_I8 ? KIND_I8 : dtype == CKB_BF16 ? KIND_BF16 : KIND_F16; }
+
 bool epilogue_valid_for(int epi, int ab_dtype)
 {
     if(epi < 0 || epi >= CKB_EPI_COUNT_)
         return false;
+    if(ab_dtype == CKB_BF16) // float functors with one rounding; see gen_instances.py for the instantiated sets
+        return epi == CKB_EPI_PASSTHROUGH || epi == CKB_EPI_RELU || epi == CKB_EPI_SCALE || epi == CKB_EPI_FASTGELU ||
+               epi == CKB_EPI_ADD_RELU || epi == CKB_EPI_ADD_HARDSWISH || epi == CKB_EPI_ADD_RELU_ADD;
     if(ab_dtype == CKB_I8)
         return epi == CKB_EPI_PASSTHROUGH || epi == CKB_EPI_RELU ||
                epi == CKB_EPI_REQUANT_RELU_REQUANT || epi == CKB_EPI_REQUANT_RELU_REQUANT_RNE;
@@ -239,10 +244,10 @@ int check_gemm(const ckb_gemm_desc* d, bool need_pointers)
 {
     if(!d)
         return fail(CKB_ERR_INVALID, "null descriptor");
-    if(d->ab_dtype != CKB_F16 && d->ab_dtype != CKB_I8)
-        return fail(CKB_ERR_UNSUPPORTED, "A/B dtype %d not supported (f16 and int8 are)", d->ab_dtype);
+    if(d->ab_dtype != CKB_F16 && d->ab_dtype != CKB_I8 && d->ab_dtype != CKB_BF16)
+        return fail(CKB_ERR_UNSUPPORTED, "A/B dtype %d not supported (f16, bf16 and int8 are)", d->ab_dtype);
     if(d->e_dtype != d->ab_dtype)
-        return fail(CKB_ERR_UNSUPPORTED, "E dtype must equal the A/B dtype (f16->f16, int8->int8)");
+        return fail(CKB_ERR_UNSUPPORTED, "E dtype must equal the A/B dtype (f16->f16, bf16->bf16, int8->int8)");
     if(d->a_layout != CKB_ROW_MAJOR || d->b_layout != CKB_COL_MAJOR || d->e_layout != CKB_ROW_MAJOR)
         return fail(CKB_ERR_UNSUPPORTED,
                     "only A row-major, B column-major, E row-major (both operands K-contiguous) is supported");
@@ -484,7 +489,7 @@ int ckb_gemm_run(const ckb_gemm_desc* d, void* stream, int n_rep, float* avg_ms)
     p.vec_ok        = gemm_vec_ok(d) ? 1 : 0;
     p.wait_limit_ns = wait_limit_ns();
     p.status        = dev->status;
-    LaunchFn fn     = find_launch(MODE_GEMM, d->ab_dtype == CKB_I8 ? KIND_I8 : KIND_F16, d->epilogue);
+    LaunchFn fn     = find_launch(MODE_GEMM, kind_of(d->ab_dtype), d->epilogue);
     if(!fn)
         return fail(CKB_ERR_UNSUPPORTED, "no kernel instance for epilogue %d", d->epilogue);
     return run_timed(fn, bn, cg, p, plan.grid, static_cast<cudaStream_t>(stream), n_rep, avg_ms);
@@ -610,7 +615,7 @@ int ckb_grouped_gemm_run(const ckb_grouped_gemm_desc* g, void* workspace, size_t
     p.total_work    = plan.total_work;
     p.wait_limit_ns = wait_limit_ns();
     p.status        = dev->status;
-    LaunchFn fn     = find_launch(MODE_GROUPED, dtype == CKB_I8 ? KIND_I8 : KIND_F16, g->groups[0].epilogue);
+    LaunchFn fn     = find_launch(MODE_GROUPED, kind_of(dtype), g->groups[0].epilogue);
     if(!fn)
         return fail(CKB_ERR_UNSUPPORTED, "no kernel instance for epilogue %d", g->groups[0].epilogue);
     return run_timed(fn, bn, cg, p, plan.grid, stream, n_rep, avg_ms);
@@ -726,7 +731,7 @@ int ckb_grouped_gemm_run_noalloc(const ckb_grouped_gemm_desc* g, void* stream_)
     p.total_work    = plan.total_work;
     p.wait_limit_ns = wait_limit_ns();
     p.status        = dev->status;
-    LaunchFn fn     = find_launch(MODE_GROUPED, dtype == CKB_I8 ? KIND_I8 : KIND_F16, g->groups[0].epilogue);
+    LaunchFn fn     = find_launch(MODE_GROUPED, kind_of(dtype), g->groups[0].epilogue);
     if(!fn)
         return fail(CKB_ERR_UNSUPPORTED, "no kernel instance for epilogue %d", g->groups[0].epilogue);
     CKB_CUDA(fn(bn, cg, p, plan.grid, stream));
@@ -739,8 +744,10 @@ static int check_conv(const ckb_conv2d_fwd_desc* d, bool need_pointers)
 {
     if(!d)
         return fail(CKB_ERR_INVALID, "null descriptor");
-    if(d->dtype != CKB_F16)
-        return fail(CKB_ERR_UNSUPPORTED, "conv2d forward supports f16 only");
+    if(d->dtype != CKB_F16 && d->dtype != CKB_BF16)
+        return fail(CKB_ERR_UNSUPPORTED, "conv2d forward supports f16 and bf16");
+    if(d->dtype == CKB_BF16 && d->epilogue == CKB_EPI_ADD)
+        return fail(CKB_ERR_UNSUPPORTED, "the binary16 Add functor has no bfloat16 instance");
     const int e = d->epilogue;
     if(!(e == CKB_EPI_PASSTHROUGH || e == CKB_EPI_RELU || e == CKB_EPI_ADD_RELU ||
          e == CKB_EPI_ADD_HARDSWISH || e == CKB_EPI_ADD_RELU_ADD || e == CKB_EPI_ADD))
@@ -820,7 +827,7 @@ int ckb_conv2d_fwd_run(const ckb_conv2d_fwd_desc* d, void* stream, int n_rep, fl
                         d->pad_h_right - (d->Y - 1) * d->dilation_h};
         cuuint32_t estr[4]    = {1, static_cast<cuuint32_t>(d->stride_w),
                               static_cast<cuuint32_t>(d->stride_h), 1};
-        CUresult r = g_encode_im2col(&p.tm_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+        CUresult r = g_encode_im2col(&p.tm_a, tm_dtype(d->dtype), 4,
                                      const_cast<void*>(d->p_in), dims, strides, lower, upper,
                                      static_cast<cuuint32_t>(bk), static_cast<cuuint32_t>(BM), estr,
                                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -851,7 +858,7 @@ int ckb_conv2d_fwd_run(const ckb_conv2d_fwd_desc* d, void* stream, int n_rep, fl
         cuuint32_t box[3]     = {static_cast<cuuint32_t>(bk), 1,
                              static_cast<cuuint32_t>((which == 0 ? bn : bn / plan.split) / cg)};
         cuuint32_t estr[3]    = {1, 1, 1};
-        CUresult r = g_encode_tiled(which == 0 ? &p.tm_b : &p.tm_b_split, CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+        CUresult r = g_encode_tiled(which == 0 ? &p.tm_b : &p.tm_b_split, tm_dtype(d->dtype),
                                     3, const_cast<void*>(d->p_wei), dims, strides, box, estr,
                                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -897,7 +904,7 @@ int ckb_conv2d_fwd_run(const ckb_conv2d_fwd_desc* d, void* stream, int n_rep, fl
     p.vec_ok        = vec ? 1 : 0;
     p.wait_limit_ns = wait_limit_ns();
     p.status        = dev->status;
-    LaunchFn fn = find_launch(MODE_CONV, KIND_F16, d->epilogue);
+    LaunchFn fn = find_launch(MODE_CONV, kind_of(d->dtype), d->epilogue);
     if(!fn)
         return fail(CKB_ERR_UNSUPPORTED, "no kernel instance for epilogue %d", d->epilogue);
     return run_timed(fn, bn, cg, p, plan.grid, static_cast<cudaStream_t>(stream), n_rep, avg_ms);

@@ -184,7 +184,7 @@ class BaseOperator:
 class DeviceGemmMultipleD(BaseOperator):
     """DeviceGemmMultipleD (device_gemm_multiple_d.hpp:32-53), realised by one sm_100a kernel.
 
-    ``dtype`` is CKB_F16 or CKB_I8; layouts are the gemm layout tags of
+    ``dtype`` is CKB_F16, CKB_BF16 or CKB_I8; layouts are the gemm layout tags of
     device/tensor_layout.hpp:13-25 (row-major A, column-major B, row-major E are supported).
     """
 
@@ -317,7 +317,10 @@ class ConvArgument(BaseArgument):
 
 class DeviceConvFwd(BaseOperator):
     """DeviceConvFwd (device_conv_fwd.hpp:18-39) / DeviceConvFwdBiasActivation
-    (device_conv_fwd_bias_activation.hpp:19-41) for 2-D NHWC/KYXC/NHWK, f16."""
+    (device_conv_fwd_bias_activation.hpp:19-41) for 2-D NHWC/KYXC/NHWK; ``dtype`` is CKB_F16 or CKB_BF16."""
+
+    def __init__(self, dtype=CKB_F16):
+        self.dtype = dtype
 
     def MakeArgument(self, p_in, p_wei, p_out, N, K, C, input_spatial_lengths, filter_spatial_lengths,
                      output_spatial_lengths, conv_filter_strides, conv_filter_dilations,
@@ -325,7 +328,7 @@ class DeviceConvFwd(BaseOperator):
                      out_element_op: ElementOp = PassThrough(), p_bias=None, p_resi=None) -> ConvArgument:
         arg = ConvArgument()
         d = arg.desc
-        d.dtype = CKB_F16
+        d.dtype = self.dtype
         d.epilogue = out_element_op.kind
         d.N, d.K, d.C = int(N), int(K), int(C)
         d.Hi, d.Wi = map(int, input_spatial_lengths)

@@ -87,9 +87,10 @@ inline bhalf_t type_convert<bhalf_t, float>(float x)
 {
     uint32_t bits;
     std::memcpy(&bits, &x, 4);
-    if((~bits & 0x7f800000u) == 0) // inf / nan: keep a nan a nan
-        return static_cast<bhalf_t>((bits & 0xffffu) ? (bits >> 16) | 0x40u : bits >> 16);
-    bits += 0x7fffu + ((bits >> 16) & 1u); // round to nearest even
+    if(~bits & 0x7f800000u)
+        bits += 0x7fffu + ((bits >> 16) & 1u); // zero, normal or subnormal: round to nearest even
+    else if(bits & 0xffffu)
+        bits |= 0x10000u; // NaN whose payload sits in the low half: keep it a NaN
     return static_cast<bhalf_t>(bits >> 16);
 }
 

@@ -32,12 +32,19 @@ struct default_tolerance<half_t>
 {
     static constexpr double rtol = 1e-3, atol = 1e-3; // check_err.hpp:109-113
 };
+template <>
+struct default_tolerance<bhalf_t>
+{
+    static constexpr double rtol = 1e-3, atol = 1e-3; // check_err.hpp:63-69
+};
 } // namespace detail
 
-// Floating-point types (float, double, half_t): an element fails when |o - r| > atol + rtol*|r| or either
+// Floating-point types (float, double, half_t, and bhalf_t bit patterns): an element fails when |o - r| > atol + rtol*|r| or either
 // value is not finite.  Prints the first few failures and the largest error, like the reference.
 template <typename T>
-typename std::enable_if<std::is_floating_point<T>::value || std::is_same<T, half_t>::value, bool>::type
+typename std::enable_if<std::is_floating_point<T>::value || std::is_same<T, half_t>::value ||
+                            std::is_same<T, bhalf_t>::value,
+                        bool>::type
 check_err(const std::vector<T>& out, const std::vector<T>& ref, const std::string& msg = "Error: Incorrect results!",
           double rtol = detail::default_tolerance<T>::rtol, double atol = detail::default_tolerance<T>::atol)
 {
@@ -70,7 +77,7 @@ check_err(const std::vector<T>& out, const std::vector<T>& ref, const std::strin
 
 // Integers: exact unless atol is given (check_err.hpp:150-193).
 template <typename T>
-typename std::enable_if<std::is_integral<T>::value, bool>::type
+typename std::enable_if<std::is_integral<T>::value && !std::is_same<T, bhalf_t>::value, bool>::type
 check_err(const std::vector<T>& out, const std::vector<T>& ref, const std::string& msg = "Error: Incorrect results!",
           double = 0, double atol = 0)
 {

@@ -90,6 +90,59 @@ inline half apply_f16(int epi, const float* p, float c, half d0, half d1)
     }
 }
 
+// bfloat16 as its bit pattern (ck::bhalf_t = ushort, include/ck/utility/data_type.hpp:10) with the
+// reference's conversions (data_type.hpp:940-990): widening is a shift, narrowing rounds to nearest even.
+struct bf16
+{
+    uint16_t bits;
+};
+inline float bf16_to_float(bf16 x)
+{
+    const uint32_t u = static_cast<uint32_t>(x.bits) << 16;
+    float f;
+    __builtin_memcpy(&f, &u, 4);
+    return f;
+}
+inline bf16 float_to_bf16(float x)
+{
+    uint32_t u;
+    __builtin_memcpy(&u, &x, 4);
+    if(~u & 0x7f800000u)
+        u += 0x7fffu + ((u >> 16) & 1u);
+    else if(u & 0xffffu)
+        u |= 0x10000u;
+    return bf16{static_cast<uint16_t>(u >> 16)};
+}
+
+// Epilogues whose output type is bfloat16: the functors that work in float and round once
+// (the reference defines no binary16-style arithmetic functors for bhalf_t).
+inline bf16 apply_bf16(int epi, const float* p, float c, bf16 d0b, bf16 d1b)
+{
+    const float d0 = bf16_to_float(d0b), d1 = bf16_to_float(d1b);
+    switch(epi)
+    {
+    case EPI_PASSTHROUGH: return float_to_bf16(c);
+    case EPI_SCALE: return float_to_bf16(p[0] * c);
+    case EPI_RELU: return float_to_bf16(c > 0 ? c : 0);
+    case EPI_FASTGELU: return float_to_bf16(fast_gelu(c));
+    case EPI_ADD_RELU: {
+        float a = c + d0;
+        return float_to_bf16(a > 0.0f ? a : 0.0f);
+    }
+    case EPI_ADD_HARDSWISH: {
+        float a = c + d0;
+        float b = a + float{3};
+        return float_to_bf16((b > 0) * (b > 6.0f ? 6.0f : b) * a * 0.166667f);
+    }
+    case EPI_ADD_RELU_ADD: {
+        float a = c + d0;
+        float b = a > 0 ? a : 0;
+        return float_to_bf16(b + d1);
+    }
+    default: return float_to_bf16(NAN);
+    }
+}
+
 // Epilogues whose output type is int8.  acc = int32 accumulator.  PassThrough keeps the
 // integer path of test/gemm/gemm_int8.cpp:32 (AccDataType = int32_t, static_cast<int8_t>);
 // every other functor sees the accumulator as float, as example 14's host reference does

@@ -115,6 +115,24 @@ int oracle_gemm_naive(int ab_dtype, int epi, const float* params,
         });
         return 0;
     }
+    if(ab_dtype == 2) // bfloat16 bit patterns, float accumulate
+    {
+        const bf16* A  = static_cast<const bf16*>(a);
+        const bf16* B  = static_cast<const bf16*>(b);
+        const bf16* D0 = static_cast<const bf16*>(d0);
+        const bf16* D1 = static_cast<const bf16*>(d1);
+        bf16* E        = static_cast<bf16*>(e);
+        parallel_for(M * N, threads, [=](int64_t i) {
+            const int64_t m = i / N, n = i % N;
+            float v_acc = 0;
+            for(int64_t k = 0; k < K; ++k)
+                v_acc += bf16_to_float(A[m * a_sm + k * a_sk]) * bf16_to_float(B[k * b_sk + n * b_sn]);
+            const bf16 v_d0 = D0 ? D0[m * d0_sm + n * d0_sn] : bf16{0};
+            const bf16 v_d1 = D1 ? D1[m * d1_sm + n * d1_sn] : bf16{0};
+            E[m * e_sm + n * e_sn] = apply_bf16(epi, p, v_acc, v_d0, v_d1);
+        });
+        return 0;
+    }
     return 1;
 }
 
@@ -131,6 +149,10 @@ int oracle_conv_out_len(int in_len, int filter_len, int stride, int dilation, in
 // T = half: any epilogue.  T = float: PassThrough only (the element type of the reference's
 // golden-vector test, test/reference_conv_fwd/reference_conv_fwd.cpp:25-33).
 } // extern "C"
+
+static inline float elem_to_float(float v) { return v; }
+static inline float elem_to_float(half v) { return static_cast<float>(v); }
+static inline float elem_to_float(bf16 v) { return bf16_to_float(v); }
 
 template <typename T>
 static int conv2d_fwd_naive_t(int epi, const float* params,
@@ -166,9 +188,9 @@ static int conv2d_fwd_naive_t(int epi, const float* params,
                     if(hi >= 0 && hi < Hi && wi >= 0 && wi < Wi)
                     {
                         const float v_in =
-                            static_cast<float>(In[((static_cast<int64_t>(n) * Hi + hi) * Wi + wi) * C + c]);
+                            elem_to_float(In[((static_cast<int64_t>(n) * Hi + hi) * Wi + wi) * C + c]);
                         const float v_wei =
-                            static_cast<float>(Wei[((static_cast<int64_t>(k) * Y + y) * X + x) * C + c]);
+                            elem_to_float(Wei[((static_cast<int64_t>(k) * Y + y) * X + x) * C + c]);
                         v_acc += v_in * v_wei;
                     }
                 }
@@ -177,6 +199,12 @@ static int conv2d_fwd_naive_t(int epi, const float* params,
         if constexpr(std::is_same<T, float>::value)
         {
             Out[o] = v_acc; // PassThrough, reference_conv_fwd.hpp:169-172
+        }
+        else if constexpr(std::is_same<T, bf16>::value)
+        {
+            const bf16 v_d0 = Bias ? Bias[k] : bf16{0};
+            const bf16 v_d1 = Resi ? Resi[o] : bf16{0};
+            Out[o]          = apply_bf16(epi, p, v_acc, v_d0, v_d1);
         }
         else
         {
@@ -197,6 +225,16 @@ int oracle_conv2d_fwd_naive(int epi, const float* params,
                             int sh, int sw, int dh, int dw, int ph, int pw, int threads)
 {
     return conv2d_fwd_naive_t<half>(epi, params, in, wei, out, bias, resi, N, K, C, Hi, Wi, Y, X,
+                                    Ho, Wo, sh, sw, dh, dw, ph, pw, threads);
+}
+
+int oracle_conv2d_fwd_naive_bf16(int epi, const float* params,
+                                 const void* in, const void* wei, void* out,
+                                 const void* bias, const void* resi,
+                                 int N, int K, int C, int Hi, int Wi, int Y, int X, int Ho, int Wo,
+                                 int sh, int sw, int dh, int dw, int ph, int pw, int threads)
+{
+    return conv2d_fwd_naive_t<bf16>(epi, params, in, wei, out, bias, resi, N, K, C, Hi, Wi, Y, X,
                                     Ho, Wo, sh, sw, dh, dw, ph, pw, threads);
 }
 

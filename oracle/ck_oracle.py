@@ -68,6 +68,8 @@ def lib() -> ctypes.CDLL:
             getattr(L, name).restype = ctypes.c_int
         L.oracle_conv2d_fwd_naive_f32.argtypes = [vp, vp, vp] + [ctypes.c_int] * 16
         L.oracle_conv2d_fwd_naive_f32.restype = ctypes.c_int
+        L.oracle_conv2d_fwd_naive_bf16.argtypes = conv_args
+        L.oracle_conv2d_fwd_naive_bf16.restype = ctypes.c_int
         L.oracle_conv_out_len.argtypes = [ctypes.c_int] * 6
         L.oracle_conv_out_len.restype = ctypes.c_int
         L.oracle_epilogue_f16.argtypes = [ctypes.c_int, fp, ctypes.c_float, ctypes.c_uint16, ctypes.c_uint16]
@@ -113,7 +115,8 @@ def gemm(a: np.ndarray, b: np.ndarray, epilogue: int = EPI_PASSTHROUGH,
 
     ``a`` is an (M, K) view, ``b`` a (K, N) view (any strides, so a column-major B is just
     ``bt.T``); ``d0`` / ``d1`` are (M, N) views (use ``np.broadcast_to`` for a stride-0 bias).
-    float16 inputs give a float16 result, int8 inputs an int8 result.
+    float16 inputs give a float16 result, int8 inputs an int8 result, uint16 inputs are bfloat16
+    bit patterns (see :func:`to_bf16`) and give bfloat16 bits.
     """
     assert a.ndim == 2 and b.ndim == 2 and a.shape[1] == b.shape[0]
     M, K = a.shape
@@ -122,6 +125,8 @@ def gemm(a: np.ndarray, b: np.ndarray, epilogue: int = EPI_PASSTHROUGH,
         dt = 0
     elif a.dtype == np.int8:
         dt = 1
+    elif a.dtype == np.uint16:  # bfloat16 bit patterns (ck::bhalf_t)
+        dt = 2
     else:
         raise TypeError(a.dtype)
     assert b.dtype == a.dtype
@@ -143,6 +148,18 @@ def gemm(a: np.ndarray, b: np.ndarray, epilogue: int = EPI_PASSTHROUGH,
     return e
 
 
+def to_bf16(x: np.ndarray) -> np.ndarray:
+    """float32 -> bfloat16 bit patterns (uint16), round to nearest even as ck::type_convert<bhalf_t>
+    (include/ck/utility/data_type.hpp:953-990) does for finite values."""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def from_bf16(b: np.ndarray) -> np.ndarray:
+    """bfloat16 bit patterns -> float32 (data_type.hpp:940-950)."""
+    return (np.ascontiguousarray(b, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
 def conv_out_len(in_len, filter_len, stride, dilation, lpad, rpad) -> int:
     return int(lib().oracle_conv_out_len(in_len, filter_len, stride, dilation, lpad, rpad))
 
@@ -152,8 +169,11 @@ def conv2d_fwd(inp: np.ndarray, wei: np.ndarray, stride=(1, 1), dilation=(1, 1),
                params: Optional[Sequence[float]] = None,
                bias: Optional[np.ndarray] = None, resi: Optional[np.ndarray] = None,
                fast: bool = True, threads: Optional[int] = None) -> np.ndarray:
-    """NHWC float16 input (N,Hi,Wi,C), KYXC weights (K,Y,X,C) -> NHWK output (N,Ho,Wo,K)."""
-    assert inp.dtype == np.float16 and wei.dtype == np.float16
+    """NHWC float16 input (N,Hi,Wi,C), KYXC weights (K,Y,X,C) -> NHWK output (N,Ho,Wo,K).
+    uint16 arrays are bfloat16 bit patterns (naive loops only)."""
+    is_bf16 = inp.dtype == np.uint16
+    assert inp.dtype in (np.float16, np.uint16) and wei.dtype == inp.dtype
+    dt = inp.dtype
     inp = np.ascontiguousarray(inp)
     wei = np.ascontiguousarray(wei)
     N, Hi, Wi, C = inp.shape
@@ -162,19 +182,21 @@ def conv2d_fwd(inp: np.ndarray, wei: np.ndarray, stride=(1, 1), dilation=(1, 1),
     pad_right = pad if pad_right is None else pad_right
     Ho = conv_out_len(Hi, Y, stride[0], dilation[0], pad[0], pad_right[0])
     Wo = conv_out_len(Wi, X, stride[1], dilation[1], pad[1], pad_right[1])
-    out = np.empty((N, Ho, Wo, K), dtype=np.float16)
+    out = np.empty((N, Ho, Wo, K), dtype=dt)
     pb = None
     if bias is not None:
-        bias = np.ascontiguousarray(bias, dtype=np.float16)
+        bias = np.ascontiguousarray(bias, dtype=dt)
         assert bias.shape == (K,)
         pb = bias.ctypes.data
     pr = None
     if resi is not None:
-        resi = np.ascontiguousarray(resi, dtype=np.float16)
+        resi = np.ascontiguousarray(resi, dtype=dt)
         assert resi.shape == out.shape
         pr = resi.ctypes.data
     th = threads or hardware_concurrency()
     fn = lib().oracle_conv2d_fwd_fast if fast else lib().oracle_conv2d_fwd_naive
+    if is_bf16:
+        fn = lib().oracle_conv2d_fwd_naive_bf16
     rc = fn(epilogue, _params(params), inp.ctypes.data, wei.ctypes.data, out.ctypes.data, pb, pr,
             N, K, C, Hi, Wi, Y, X, Ho, Wo, stride[0], stride[1], dilation[0], dilation[1],
             pad[0], pad[1], th)

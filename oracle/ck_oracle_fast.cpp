@@ -8,7 +8,7 @@
 // order in which DIFFERENT outputs are visited changes (register tiles of 6 x 16 outputs).
 //
 // Fused multiply-add is used in the inner loop.  That is exact here because the product of
-// two binary16 (or two int8) values is representable in binary32 without rounding, so
+// two binary16 (or bfloat16, or int8) values is representable in binary32 without rounding, so
 // fma(a,b,acc) == acc + a*b bit for bit.  tests/test_oracle_golden.py asserts fast == naive
 // bit-for-bit on small shapes.
 //
@@ -147,7 +147,7 @@ int oracle_gemm_fast(int ab_dtype, int epi, const float* params,
     float p[4] = {0, 0, 0, 0};
     if(params)
         std::memcpy(p, params, sizeof(p));
-    if(ab_dtype != 0 && ab_dtype != 1)
+    if(ab_dtype != 0 && ab_dtype != 1 && ab_dtype != 2)
         return 1;
     if(M <= 0 || N <= 0)
         return 0;
@@ -189,6 +189,12 @@ int oracle_gemm_fast(int ab_dtype, int epi, const float* params,
                 for(int64_t k = 0; k < K; ++k)
                     Afp[m * K + k] = to_f32(A[m * a_sm + k * a_sk]);
             }
+            else if(ab_dtype == 2)
+            {
+                const bf16* A = static_cast<const bf16*>(a);
+                for(int64_t k = 0; k < K; ++k)
+                    Afp[m * K + k] = bf16_to_float(A[m * a_sm + k * a_sk]);
+            }
             else
             {
                 const int8_t* A = static_cast<const int8_t*>(a);
@@ -207,8 +213,9 @@ int oracle_gemm_fast(int ab_dtype, int epi, const float* params,
                 {
                     const int64_t n = j * NR + c;
                     Bpp[(j * K + k) * NR + c] =
-                        ab_dtype == 0 ? to_f32(static_cast<const half*>(b)[k * b_sk + n * b_sn])
-                                      : to_f32(static_cast<const int8_t*>(b)[k * b_sk + n * b_sn]);
+                        ab_dtype == 0   ? to_f32(static_cast<const half*>(b)[k * b_sk + n * b_sn])
+                        : ab_dtype == 2 ? bf16_to_float(static_cast<const bf16*>(b)[k * b_sk + n * b_sn])
+                                        : to_f32(static_cast<const int8_t*>(b)[k * b_sk + n * b_sn]);
                 }
         }
     });
@@ -224,7 +231,19 @@ int oracle_gemm_fast(int ab_dtype, int epi, const float* params,
             const int64_t m = pm->fetch_add(1);
             if(m >= M)
                 break;
-            if(ab_dtype == 0)
+            if(ab_dtype == 2)
+            {
+                const bf16* D0 = static_cast<const bf16*>(d0);
+                const bf16* D1 = static_cast<const bf16*>(d1);
+                bf16* E        = static_cast<bf16*>(e);
+                for(int64_t n = 0; n < N; ++n)
+                {
+                    const bf16 v_d0 = D0 ? D0[m * d0_sm + n * d0_sn] : bf16{0};
+                    const bf16 v_d1 = D1 ? D1[m * d1_sm + n * d1_sn] : bf16{0};
+                    E[m * e_sm + n * e_sn] = apply_bf16(epi, p, Cfp[m * Npad + n], v_d0, v_d1);
+                }
+            }
+            else if(ab_dtype == 0)
             {
                 const half* D0 = static_cast<const half*>(d0);
                 const half* D1 = static_cast<const half*>(d1);

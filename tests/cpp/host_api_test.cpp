@@ -12,6 +12,9 @@
 #include "ck/library/reference_tensor_operation/cpu/reference_conv_fwd.hpp"
 #include "ck/library/reference_tensor_operation/cpu/reference_conv_fwd_bias_activation.hpp"
 #include "ck/library/reference_tensor_operation/cpu/reference_gemm.hpp"
+#include "ck/library/tensor_operation_instance/gpu/gemm.hpp"
+#include "ck/library/tensor_operation_instance/gpu/gemm_add_add_fastgelu.hpp"
+#include "ck/library/tensor_operation_instance/gpu/grouped_gemm.hpp"
 #include "ck/library/utility/check_err.hpp"
 #include "ck/library/utility/conv_util.hpp"
 #include "ck/library/utility/fill.hpp"
@@ -274,8 +277,69 @@ static void test_traits_and_support()
     EXPECT(!conv.IsSupportedArgument(cb));
 }
 
+// The instance lists a profiler-style client walks: non-empty for the kernels that exist, each instance
+// answering IsSupportedArgument through the abstract interface; float GEMM has an instance that refuses.
+static void test_instance_factory()
+{
+    namespace inst = dev::instance;
+    using inst::Col;
+    using inst::Row;
+    using PT = inst::PassThrough;
+    const void* pa = reinterpret_cast<const void*>(0x1000);
+    void* pc       = reinterpret_cast<void*>(0x3000);
+    {
+        using Op = dev::DeviceGemm<Row, Col, Row, ck::half_t, ck::half_t, ck::half_t, PT, PT, PT>;
+        auto ops = inst::DeviceOperationInstanceFactory<Op>::GetInstances();
+        EXPECT(ops.size() == 1);
+        auto arg = ops[0]->MakeArgumentPointer(pa, pa, pc, 256, 256, 64, 64, 64, 256, {}, {}, {});
+        EXPECT(ops[0]->IsSupportedArgument(arg.get()));
+        EXPECT(ops[0]->GetTypeString().find("DeviceGemm_Xdl_CShuffle") != std::string::npos);
+        auto bad = ops[0]->MakeArgumentPointer(pa, pa, pc, 256, 256, 64, 60, 64, 256, {}, {}, {});
+        EXPECT(!ops[0]->IsSupportedArgument(bad.get())); // StrideA < K
+    }
+    {
+        using Op = dev::DeviceGemm<Row, Col, Row, ck::bhalf_t, ck::bhalf_t, ck::bhalf_t, PT, PT, PT>;
+        auto ops = inst::DeviceOperationInstanceFactory<Op>::GetInstances();
+        auto arg = ops[0]->MakeArgumentPointer(pa, pa, pc, 256, 256, 64, 64, 64, 256, {}, {}, {});
+        EXPECT(ops[0]->IsSupportedArgument(arg.get()));
+    }
+    {
+        using Op = dev::DeviceGemm<Row, Col, Row, int8_t, int8_t, int8_t, PT, PT, PT>;
+        auto ops = inst::DeviceOperationInstanceFactory<Op>::GetInstances();
+        auto arg = ops[0]->MakeArgumentPointer(pa, pa, pc, 256, 256, 64, 64, 64, 256, {}, {}, {});
+        EXPECT(ops[0]->IsSupportedArgument(arg.get()));
+    }
+    {
+        using Op = dev::DeviceGemm<Row, Col, Row, float, float, float, PT, PT, PT>;
+        auto ops = inst::DeviceOperationInstanceFactory<Op>::GetInstances();
+        auto arg = ops[0]->MakeArgumentPointer(pa, pa, pc, 256, 256, 64, 64, 64, 256, {}, {}, {});
+        EXPECT(!ops[0]->IsSupportedArgument(arg.get())); // no fp32 kernels
+    }
+    {
+        using Op = dev::DeviceGemmMultipleD<Row, Col, Row, ck::half_t, ck::half_t, inst::F16_F16_TUPLE, ck::half_t, PT, PT,
+                                            inst::AddAddFastGelu>;
+        auto ops = inst::DeviceOperationInstanceFactory<Op>::GetInstances();
+        EXPECT(ops.size() == 1);
+        auto arg = ops[0]->MakeArgumentPointer(pa, pa, std::array<const void*, 2>{pa, pa}, pc, 256, 256, 64, 64, 64,
+                                               std::array<ck::index_t, 2>{0, 256}, 256, {}, {}, {});
+        EXPECT(ops[0]->IsSupportedArgument(arg.get()));
+    }
+    {
+        using Op = dev::DeviceGroupedGemm<Row, Col, Row, ck::half_t, ck::half_t, inst::EMPTY_TUPLE, ck::half_t, PT, PT, PT>;
+        auto ops = inst::DeviceOperationInstanceFactory<Op>::GetInstances();
+        EXPECT(ops.size() == 1);
+        std::vector<const void*> as{pa, pa}, bs{pa, pa};
+        std::vector<void*> cs{pc, pc};
+        std::vector<std::array<const void*, 0>> ds(2);
+        std::vector<dev::GemmDesc> descs{{256, 128, 64, 64, 64, 128, {}}, {512, 256, 128, 128, 128, 256, {}}};
+        auto arg = ops[0]->MakeArgumentPointer(as, bs, ds, cs, descs, {}, {}, {});
+        EXPECT(ops[0]->GetWorkSpaceSize(arg.get()) > 0);
+    }
+}
+
 int main()
 {
+    test_instance_factory();
     test_descriptors();
     test_conv_params();
     test_check_err();

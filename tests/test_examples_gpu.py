@@ -61,3 +61,18 @@ def test_default_shapes_timing_only(examples_built):
     assert out.count("Perf:") == 2
     out = run_example("conv2d_fwd_xdl_bias_relu", 0, 2, 1)
     assert "Perf:" in out
+
+
+def test_profiler_driver_walks_instance_lists(examples_built):
+    """ckProfiler-style sub-commands: instances come from DeviceOperationInstanceFactory, every one is
+    verified against the CPU reference operator and the best one is reported."""
+    # gemm <dtype> <layout> verify init log time M N K StrideA StrideB StrideC
+    for dtype in (1, 2, 3):  # fp16, bf16, int8
+        out = run_example("ck_profiler", "gemm", dtype, 1, 1, 1, 0, 1, 512, 768, 256, 256, 256, 768)
+        assert "Best Perf for gemm" in out and "DeviceGemm_Xdl_CShuffle" in out
+    out = run_example("ck_profiler", "gemm_add_add_fastgelu", 1, 1, 1, 2, 0, 1, 384, 512, 256, 256, 256, 0, 512, 512)
+    assert "Best Perf for gemm_add_add_fastgelu" in out
+    out = run_example("ck_profiler", "grouped_gemm", 1, 1, 1, 1, 0, 1, "256,512,768", "128,256,384", "64,128,192")
+    assert "Best Perf for grouped_gemm" in out
+    out = run_example("ck_profiler", "conv_fwd_bias_relu", 1, 1, 2, 0, 1, 4, 64, 64, 3, 3, 17, 17, 2, 2, 1, 1, 1, 1, 1, 1)
+    assert "Best Perf for conv_fwd_bias_relu" in out

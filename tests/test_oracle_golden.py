@@ -156,3 +156,30 @@ def test_conv_bias_relu_against_direct_numpy():
             ref[:, ho, wo, :] = np.einsum("nyxc,kyxc->nk", win, wei.astype(np.float64))
     ref = np.maximum(ref + bias.astype(np.float64), 0)
     assert np.all(np.abs(out.astype(np.float64) - ref) <= 1e-3 + 1e-3 * np.abs(ref))
+
+
+def test_bf16_conversion_known_answers():
+    """type_convert<bhalf_t>(float), include/ck/utility/data_type.hpp:953-990: round to nearest even."""
+    f = np.array([1.0, 1.00390625, 1.01171875, -2.5, 3.140625, 0.0], dtype=np.float32)
+    b = oracle.to_bf16(f)
+    # 1.00390625 = 1 + 2^-8 is a tie between 1.0 (even mantissa) and 1.0078125 -> 1.0;
+    # 1.01171875 = 1 + 3*2^-8 is a tie between 1.0078125 (odd) and 1.015625 (even) -> 1.015625
+    np.testing.assert_array_equal(oracle.from_bf16(b), np.array([1.0, 1.0, 1.015625, -2.5, 3.140625, 0.0], np.float32))
+    assert b[0] == 0x3F80 and b[3] == 0xC020
+
+
+def test_bf16_gemm_blocked_equals_naive_and_integer_exact():
+    rng = np.random.default_rng(12)
+    M, N, K = 37, 29, 150
+    a = rng.integers(-5, 6, (M, K)).astype(np.float32)
+    bt = rng.integers(-5, 6, (N, K)).astype(np.float32)
+    e1 = oracle.gemm(oracle.to_bf16(a), oracle.to_bf16(bt).T, fast=False)
+    e2 = oracle.gemm(oracle.to_bf16(a), oracle.to_bf16(bt).T, fast=True)
+    np.testing.assert_array_equal(e1, e2)
+    np.testing.assert_array_equal(e1, oracle.to_bf16((a @ bt.T).astype(np.float32)))
+    ar = oracle.to_bf16(rng.uniform(-1, 1, (M, K)).astype(np.float32))
+    br = oracle.to_bf16(rng.uniform(-1, 1, (N, K)).astype(np.float32))
+    d0 = np.broadcast_to(oracle.to_bf16(rng.uniform(-1, 1, (N,)).astype(np.float32)), (M, N))
+    for epi, d in [(oracle.EPI_FASTGELU, None), (oracle.EPI_ADD_RELU, d0)]:
+        np.testing.assert_array_equal(oracle.gemm(ar, br.T, epi, None, d, fast=False),
+                                      oracle.gemm(ar, br.T, epi, None, d, fast=True))
