@@ -168,12 +168,49 @@ int encode_kmajor_2d(CUtensorMap* tm, int dtype, const void* ptr, int64_t rows, 
     return CKB_OK;
 }
 
-int pick_bn(int64_t M, int64_t N, int sm_count)
+// MN-major matrix (the M or N index contiguous, pitch `ld` elements between consecutive k) -> 2-D map
+// whose box is one swizzle atom column: 128 bytes of MN positions x the k rows of one stage.
+int encode_mnmajor_2d(CUtensorMap* tm, int dtype, const void* ptr, int64_t mn, int64_t k, int64_t ld)
+{
+    load_entry_points();
+    if(!g_encode_tiled)
+        return fail(CKB_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+    const int eb          = elem_bytes(dtype);
+    cuuint64_t dims[2]    = {static_cast<cuuint64_t>(mn), static_cast<cuuint64_t>(k)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * eb};
+    cuuint32_t box[2]     = {static_cast<cuuint32_t>(BK_BYTES / eb), static_cast<cuuint32_t>(BK_BYTES / eb)};
+    cuuint32_t estr[2]    = {1, 1};
+    CUresult r            = g_encode_tiled(tm, tm_dtype(dtype), 2, const_cast<void*>(ptr), dims, strides,
+                                box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if(r != CUDA_SUCCESS)
+        return fail(CKB_ERR_CUDA, "cuTensorMapEncodeTiled failed (CUresult %d) mn=%lld k=%lld ld=%lld",
+                    static_cast<int>(r), (long long)mn, (long long)k, (long long)ld);
+    return CKB_OK;
+}
+
+// A is M x K: row-major = K-major, column-major = M-major.  B is K x N: column-major = K-major,
+// row-major = N-major.
+bool a_is_mn_major(const ckb_gemm_desc* d) { return d->a_layout == CKB_COL_MAJOR; }
+bool b_is_mn_major(const ckb_gemm_desc* d) { return d->b_layout == CKB_ROW_MAJOR; }
+
+// Tensor map of one operand of a GEMM problem, seen as [mn][k]; box_mn = rows of a K-major box.
+int encode_operand(CUtensorMap* tm, int dtype, const void* ptr, int64_t mn, int64_t k, int64_t ld, bool mn_major,
+                   int box_mn)
+{
+    return mn_major ? encode_mnmajor_2d(tm, dtype, ptr, mn, k, ld) : encode_kmajor_2d(tm, dtype, ptr, mn, k, ld, box_mn);
+}
+
+// Narrowest B slice one CTA can load: 64 rows of a K-major tile, one whole swizzle atom (128 bytes of N
+// positions) of an N-major one.
+int min_b_rows(int dtype, bool b_mn) { return b_mn ? BK_BYTES / elem_bytes(dtype) : 64; }
+
+int pick_bn(int64_t M, int64_t N, int sm_count, int min_bn = 64)
 {
     const int f = forced_bn();
-    if(f == 256 || f == 128 || f == 64)
+    if((f == 256 || f == 128 || f == 64) && f >= min_bn)
         return f;
-    if(N <= 64)
+    if(N <= 64 && min_bn <= 64)
         return 64;
     if(N <= 128)
         return 128;
@@ -193,7 +230,7 @@ struct WorkPlan
 };
 
 // `units` = CTAs (one CTA per tile) or CTA pairs (cg = 2) that run concurrently.
-WorkPlan plan_work(int64_t total_tiles, int units, int bn, int cg)
+WorkPlan plan_work(int64_t total_tiles, int units, int bn, int cg, int min_rows = 64)
 {
     WorkPlan w;
     const int64_t G    = units;
@@ -203,7 +240,9 @@ WorkPlan plan_work(int64_t total_tiles, int units, int bn, int cg)
     const char* env    = getenv("CKB_NO_TAIL_SPLIT");
     if(rem > 0 && !(env && atoi(env) != 0))
     {
-        const int max_split = bn / 64; // 256 -> 4, 128 -> 2, 64 -> 1
+        // slices of >= 64 columns whose per-CTA share is >= min_rows: K-major 256 -> 4, 128 -> 2, 64 -> 1
+        const int min_width = min_rows * cg > 64 ? min_rows * cg : 64;
+        const int max_split = bn / min_width;
         while(split * 2 <= max_split && rem * split * 2 <= G)
             split *= 2;
     }
@@ -248,9 +287,11 @@ int check_gemm(const ckb_gemm_desc* d, bool need_pointers)
         return fail(CKB_ERR_UNSUPPORTED, "A/B dtype %d not supported (f16, bf16 and int8 are)", d->ab_dtype);
     if(d->e_dtype != d->ab_dtype)
         return fail(CKB_ERR_UNSUPPORTED, "E dtype must equal the A/B dtype (f16->f16, bf16->bf16, int8->int8)");
-    if(d->a_layout != CKB_ROW_MAJOR || d->b_layout != CKB_COL_MAJOR || d->e_layout != CKB_ROW_MAJOR)
-        return fail(CKB_ERR_UNSUPPORTED,
-                    "only A row-major, B column-major, E row-major (both operands K-contiguous) is supported");
+    if((d->a_layout != CKB_ROW_MAJOR && d->a_layout != CKB_COL_MAJOR) ||
+       (d->b_layout != CKB_ROW_MAJOR && d->b_layout != CKB_COL_MAJOR))
+        return fail(CKB_ERR_INVALID, "unknown A or B layout");
+    if(d->e_layout != CKB_ROW_MAJOR)
+        return fail(CKB_ERR_UNSUPPORTED, "E (and every D) must be row-major");
     if(!epilogue_valid_for(d->epilogue, d->ab_dtype))
         return fail(CKB_ERR_UNSUPPORTED, "epilogue %d not available for dtype %d", d->epilogue, d->ab_dtype);
     if(d->n_ds != epi_num_d(d->epilogue))
@@ -261,7 +302,7 @@ int check_gemm(const ckb_gemm_desc* d, bool need_pointers)
     if(d->M > 0x7FFFFF00ll || d->N > 0x7FFFFF00ll || d->K > 0x7FFFFF00ll)
         return fail(CKB_ERR_UNSUPPORTED, "M, N, K must fit in int32");
     const int eb = elem_bytes(d->ab_dtype);
-    if(d->lda < d->K || d->ldb < d->K || d->lde < d->N)
+    if(d->lda < (a_is_mn_major(d) ? d->M : d->K) || d->ldb < (b_is_mn_major(d) ? d->N : d->K) || d->lde < d->N)
         return fail(CKB_ERR_INVALID, "leading dimension smaller than the row length");
     if((d->lda * eb) % 16 != 0 || (d->ldb * eb) % 16 != 0)
         return fail(CKB_ERR_UNSUPPORTED, "lda and ldb must be multiples of 16 bytes (TMA row pitch)");
@@ -457,11 +498,13 @@ int ckb_gemm_run(const ckb_gemm_desc* d, void* stream, int n_rep, float* avg_ms)
     rc              = current_device(&dev);
     if(rc)
         return rc;
-    const int bn = pick_bn(d->M, d->N, dev->sm_count);
-    const int eb = elem_bytes(d->ab_dtype);
+    const bool a_mn  = a_is_mn_major(d), b_mn = b_is_mn_major(d);
+    const int b_min  = min_b_rows(d->ab_dtype, b_mn);
+    const int bn     = pick_bn(d->M, d->N, dev->sm_count, b_min);
+    const int eb     = elem_bytes(d->ab_dtype);
     KernelParams p;
     memset(&p, 0, sizeof(p));
-    rc = encode_kmajor_2d(&p.tm_a, d->ab_dtype, d->p_a, d->M, d->K, d->lda, BM);
+    rc = encode_operand(&p.tm_a, d->ab_dtype, d->p_a, d->M, d->K, d->lda, a_mn, BM);
     if(rc)
         return rc;
     fill_epilogue(p.epi, d);
@@ -470,13 +513,14 @@ int ckb_gemm_run(const ckb_gemm_desc* d, void* stream, int n_rep, float* avg_ms)
     const int64_t tiles_m = (d->M + BM * cg - 1) / (BM * cg);
     if(tiles_m * tiles_n > 0x3FFFFFFFll)
         return fail(CKB_ERR_UNSUPPORTED, "too many tiles");
-    const WorkPlan plan = plan_work(tiles_m * tiles_n, dev->sm_count / cg, bn, cg);
-    rc = encode_kmajor_2d(&p.tm_b, d->ab_dtype, d->p_b, d->N, d->K, d->ldb, bn / cg);
+    const WorkPlan plan = plan_work(tiles_m * tiles_n, dev->sm_count / cg, bn, cg, b_min);
+    rc = encode_operand(&p.tm_b, d->ab_dtype, d->p_b, d->N, d->K, d->ldb, b_mn, bn / cg);
     if(rc)
         return rc;
-    rc = encode_kmajor_2d(&p.tm_b_split, d->ab_dtype, d->p_b, d->N, d->K, d->ldb, bn / plan.split / cg);
+    rc = encode_operand(&p.tm_b_split, d->ab_dtype, d->p_b, d->N, d->K, d->ldb, b_mn, bn / plan.split / cg);
     if(rc)
         return rc;
+    p.mn_major      = (a_mn ? 1 : 0) | (b_mn ? 2 : 0);
     p.split_start   = plan.split_start;
     p.split         = plan.split;
     p.total_work    = plan.total_work;
@@ -512,8 +556,9 @@ static int check_grouped(const ckb_grouped_gemm_desc* g, bool need_pointers)
             return rc;
         }
         if(gi.ab_dtype != g0.ab_dtype || gi.epilogue != g0.epilogue || gi.n_ds != g0.n_ds ||
+           gi.a_layout != g0.a_layout || gi.b_layout != g0.b_layout ||
            memcmp(gi.epi_params, g0.epi_params, sizeof(g0.epi_params)) != 0)
-            return fail(CKB_ERR_UNSUPPORTED, "group %d: dtype / epilogue differ from group 0", i);
+            return fail(CKB_ERR_UNSUPPORTED, "group %d: dtype / layout / epilogue differ from group 0", i);
     }
     return CKB_OK;
 }
@@ -528,33 +573,26 @@ int ckb_grouped_gemm_workspace_size(const ckb_grouped_gemm_desc* desc, size_t* b
     return CKB_OK;
 }
 
-int ckb_grouped_gemm_run(const ckb_grouped_gemm_desc* g, void* workspace, size_t workspace_bytes,
-                         void* stream_, int n_rep, float* avg_ms)
+// Tile shape, CTA grouping and work plan of a grouped problem, and its device table entries.
+struct GroupedPlan
 {
-    int rc = check_grouped(g, true);
-    if(rc)
-        return rc;
-    size_t need = 0;
-    ckb_grouped_gemm_workspace_size(g, &need);
-    if(!workspace || workspace_bytes < need)
-        return fail(CKB_ERR_WORKSPACE, "grouped GEMM needs %zu bytes of device workspace, got %zu", need,
-                    workspace ? workspace_bytes : 0);
-    DeviceInfo* dev = nullptr;
-    rc              = current_device(&dev);
-    if(rc)
-        return rc;
-    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    const int dtype     = g->groups[0].ab_dtype;
-    const int eb        = elem_bytes(dtype);
-    const int bk        = BK_BYTES / eb;
+    int bn, cg, mn_major;
+    WorkPlan plan;
+    int64_t total_tiles;
+};
+
+static int plan_grouped(const ckb_grouped_gemm_desc* g, const DeviceInfo* dev, GroupedPlan* gp)
+{
+    const int dtype = g->groups[0].ab_dtype;
+    const bool a_mn = a_is_mn_major(&g->groups[0]), b_mn = b_is_mn_major(&g->groups[0]);
+    const int b_min = min_b_rows(dtype, b_mn);
     int64_t max_n = 0, sum_m = 0;
     for(int i = 0; i < g->group_count; ++i)
     {
         max_n = max_n > g->groups[i].N ? max_n : g->groups[i].N;
         sum_m += g->groups[i].M;
     }
-    const int bn = pick_bn(sum_m, max_n, dev->sm_count);
-
+    const int bn      = pick_bn(sum_m, max_n, dev->sm_count, b_min);
     int64_t tiles_128 = 0;
     for(int i = 0; i < g->group_count; ++i)
         tiles_128 += ((g->groups[i].M + BM - 1) / BM) * ((g->groups[i].N + bn - 1) / bn);
@@ -564,22 +602,33 @@ int ckb_grouped_gemm_run(const ckb_grouped_gemm_desc* g, void* workspace, size_t
         all_tiles += ((g->groups[i].M + BM * cg - 1) / (BM * cg)) * ((g->groups[i].N + bn - 1) / bn);
     if(all_tiles > 0x3FFFFFFFll)
         return fail(CKB_ERR_UNSUPPORTED, "too many tiles");
-    const WorkPlan plan = plan_work(all_tiles, dev->sm_count / cg, bn, cg);
+    gp->bn          = bn;
+    gp->cg          = cg;
+    gp->mn_major    = (a_mn ? 1 : 0) | (b_mn ? 2 : 0);
+    gp->plan        = plan_work(all_tiles, dev->sm_count / cg, bn, cg, b_min);
+    gp->total_tiles = all_tiles;
+    return CKB_OK;
+}
 
-    std::vector<GroupEntry> table(g->group_count);
+static int fill_group_table(const ckb_grouped_gemm_desc* g, const GroupedPlan& gp, GroupEntry* table)
+{
+    const int dtype = g->groups[0].ab_dtype;
+    const int bk    = BK_BYTES / elem_bytes(dtype);
+    const bool a_mn = (gp.mn_major & 1) != 0, b_mn = (gp.mn_major & 2) != 0;
+    const int bn = gp.bn, cg = gp.cg;
     int64_t tile_start = 0;
     for(int i = 0; i < g->group_count; ++i)
     {
         const ckb_gemm_desc& d = g->groups[i];
         GroupEntry& ge         = table[i];
         memset(&ge, 0, sizeof(ge));
-        rc = encode_kmajor_2d(&ge.tm_a, dtype, d.p_a, d.M, d.K, d.lda, BM);
+        int rc = encode_operand(&ge.tm_a, dtype, d.p_a, d.M, d.K, d.lda, a_mn, BM);
         if(rc)
             return rc;
-        rc = encode_kmajor_2d(&ge.tm_b, dtype, d.p_b, d.N, d.K, d.ldb, bn / cg);
+        rc = encode_operand(&ge.tm_b, dtype, d.p_b, d.N, d.K, d.ldb, b_mn, bn / cg);
         if(rc)
             return rc;
-        rc = encode_kmajor_2d(&ge.tm_b_split, dtype, d.p_b, d.N, d.K, d.ldb, bn / plan.split / cg);
+        rc = encode_operand(&ge.tm_b_split, dtype, d.p_b, d.N, d.K, d.ldb, b_mn, bn / gp.plan.split / cg);
         if(rc)
             return rc;
         const int64_t tm = (d.M + BM * cg - 1) / (BM * cg), tn = (d.N + bn - 1) / bn;
@@ -598,6 +647,49 @@ int ckb_grouped_gemm_run(const ckb_grouped_gemm_desc* g, void* workspace, size_t
         ge.ldd1       = d.n_ds > 1 ? d.ldd[1] : 0;
         tile_start += tm * tn;
     }
+    return CKB_OK;
+}
+
+static void fill_grouped_params(KernelParams& p, const ckb_grouped_gemm_desc* g, const GroupedPlan& gp,
+                                const GroupEntry* d_table, const DeviceInfo* dev)
+{
+    memset(&p, 0, sizeof(p));
+    fill_epilogue(p.epi, &g->groups[0]);
+    p.groups        = d_table;
+    p.group_count   = g->group_count;
+    p.total_tiles   = static_cast<int32_t>(gp.total_tiles);
+    p.split_start   = gp.plan.split_start;
+    p.split         = gp.plan.split;
+    p.total_work    = gp.plan.total_work;
+    p.mn_major      = gp.mn_major;
+    p.wait_limit_ns = wait_limit_ns();
+    p.status        = dev->status;
+}
+
+int ckb_grouped_gemm_run(const ckb_grouped_gemm_desc* g, void* workspace, size_t workspace_bytes,
+                         void* stream_, int n_rep, float* avg_ms)
+{
+    int rc = check_grouped(g, true);
+    if(rc)
+        return rc;
+    size_t need = 0;
+    ckb_grouped_gemm_workspace_size(g, &need);
+    if(!workspace || workspace_bytes < need)
+        return fail(CKB_ERR_WORKSPACE, "grouped GEMM needs %zu bytes of device workspace, got %zu", need,
+                    workspace ? workspace_bytes : 0);
+    DeviceInfo* dev = nullptr;
+    rc              = current_device(&dev);
+    if(rc)
+        return rc;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    GroupedPlan gp;
+    rc = plan_grouped(g, dev, &gp);
+    if(rc)
+        return rc;
+    std::vector<GroupEntry> table(g->group_count);
+    rc = fill_group_table(g, gp, table.data());
+    if(rc)
+        return rc;
     uintptr_t ws_addr = (reinterpret_cast<uintptr_t>(workspace) + 127u) & ~static_cast<uintptr_t>(127u);
     GroupEntry* d_table = reinterpret_cast<GroupEntry*>(ws_addr);
     // Pageable source: the runtime stages the bytes before returning, so `table` may go out of scope.
@@ -605,20 +697,11 @@ int ckb_grouped_gemm_run(const ckb_grouped_gemm_desc* g, void* workspace, size_t
                              cudaMemcpyHostToDevice, stream));
 
     KernelParams p;
-    memset(&p, 0, sizeof(p));
-    fill_epilogue(p.epi, &g->groups[0]);
-    p.groups        = d_table;
-    p.group_count   = g->group_count;
-    p.total_tiles   = static_cast<int32_t>(tile_start);
-    p.split_start   = plan.split_start;
-    p.split         = plan.split;
-    p.total_work    = plan.total_work;
-    p.wait_limit_ns = wait_limit_ns();
-    p.status        = dev->status;
-    LaunchFn fn     = find_launch(MODE_GROUPED, kind_of(dtype), g->groups[0].epilogue);
+    fill_grouped_params(p, g, gp, d_table, dev);
+    LaunchFn fn = find_launch(MODE_GROUPED, kind_of(g->groups[0].ab_dtype), g->groups[0].epilogue);
     if(!fn)
         return fail(CKB_ERR_UNSUPPORTED, "no kernel instance for epilogue %d", g->groups[0].epilogue);
-    return run_timed(fn, bn, cg, p, plan.grid, stream, n_rep, avg_ms);
+    return run_timed(fn, gp.bn, gp.cg, p, gp.plan.grid, stream, n_rep, avg_ms);
 }
 
 // ---- grouped GEMM without allocation ----------------------------------------------------------------
@@ -662,58 +745,13 @@ int ckb_grouped_gemm_run_noalloc(const ckb_grouped_gemm_desc* g, void* stream_)
     GroupEntry* d_table = g_noalloc_dev_ptr[ordinal];
 
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    const int dtype     = g->groups[0].ab_dtype;
-    const int eb        = elem_bytes(dtype);
-    const int bk        = BK_BYTES / eb;
-    int64_t max_n = 0, sum_m = 0;
-    for(int i = 0; i < g->group_count; ++i)
-    {
-        max_n = max_n > g->groups[i].N ? max_n : g->groups[i].N;
-        sum_m += g->groups[i].M;
-    }
-    const int bn      = pick_bn(sum_m, max_n, dev->sm_count);
-    int64_t tiles_128 = 0;
-    for(int i = 0; i < g->group_count; ++i)
-        tiles_128 += ((g->groups[i].M + BM - 1) / BM) * ((g->groups[i].N + bn - 1) / bn);
-    const int cg      = pick_cg(tiles_128, bn, dev->sm_count);
-    int64_t all_tiles = 0;
-    for(int i = 0; i < g->group_count; ++i)
-        all_tiles += ((g->groups[i].M + BM * cg - 1) / (BM * cg)) * ((g->groups[i].N + bn - 1) / bn);
-    if(all_tiles > 0x3FFFFFFFll)
-        return fail(CKB_ERR_UNSUPPORTED, "too many tiles");
-    const WorkPlan plan = plan_work(all_tiles, dev->sm_count / cg, bn, cg);
-
-    int64_t tile_start = 0;
-    for(int i = 0; i < g->group_count; ++i)
-    {
-        const ckb_gemm_desc& d = g->groups[i];
-        GroupEntry& ge         = g_noalloc_host_table[i];
-        memset(&ge, 0, sizeof(ge));
-        rc = encode_kmajor_2d(&ge.tm_a, dtype, d.p_a, d.M, d.K, d.lda, BM);
-        if(rc)
-            return rc;
-        rc = encode_kmajor_2d(&ge.tm_b, dtype, d.p_b, d.N, d.K, d.ldb, bn / cg);
-        if(rc)
-            return rc;
-        rc = encode_kmajor_2d(&ge.tm_b_split, dtype, d.p_b, d.N, d.K, d.ldb, bn / plan.split / cg);
-        if(rc)
-            return rc;
-        const int64_t tm = (d.M + BM * cg - 1) / (BM * cg), tn = (d.N + bn - 1) / bn;
-        ge.M          = static_cast<int32_t>(d.M);
-        ge.N          = static_cast<int32_t>(d.N);
-        ge.K          = static_cast<int32_t>(d.K);
-        ge.tiles_n    = static_cast<int32_t>(tn);
-        ge.tile_start = static_cast<int32_t>(tile_start);
-        ge.num_kb     = static_cast<int32_t>((d.K + bk - 1) / bk);
-        ge.vec_ok     = gemm_vec_ok(&d) ? 1 : 0;
-        ge.e          = d.p_e;
-        ge.d0         = d.n_ds > 0 ? d.p_ds[0] : nullptr;
-        ge.d1         = d.n_ds > 1 ? d.p_ds[1] : nullptr;
-        ge.lde        = d.lde;
-        ge.ldd0       = d.n_ds > 0 ? d.ldd[0] : 0;
-        ge.ldd1       = d.n_ds > 1 ? d.ldd[1] : 0;
-        tile_start += tm * tn;
-    }
+    GroupedPlan gp;
+    rc = plan_grouped(g, dev, &gp);
+    if(rc)
+        return rc;
+    rc = fill_group_table(g, gp, g_noalloc_host_table);
+    if(rc)
+        return rc;
     // Every entry this launch reads is rewritten here; stale entries beyond group_count are never
     // read.  Pageable source: the runtime stages the bytes before returning, so the host staging
     // table may be reused as soon as the mutex is released.
@@ -721,20 +759,11 @@ int ckb_grouped_gemm_run_noalloc(const ckb_grouped_gemm_desc* g, void* stream_)
                              cudaMemcpyHostToDevice, stream));
 
     KernelParams p;
-    memset(&p, 0, sizeof(p));
-    fill_epilogue(p.epi, &g->groups[0]);
-    p.groups        = d_table;
-    p.group_count   = g->group_count;
-    p.total_tiles   = static_cast<int32_t>(tile_start);
-    p.split_start   = plan.split_start;
-    p.split         = plan.split;
-    p.total_work    = plan.total_work;
-    p.wait_limit_ns = wait_limit_ns();
-    p.status        = dev->status;
-    LaunchFn fn     = find_launch(MODE_GROUPED, kind_of(dtype), g->groups[0].epilogue);
+    fill_grouped_params(p, g, gp, d_table, dev);
+    LaunchFn fn = find_launch(MODE_GROUPED, kind_of(g->groups[0].ab_dtype), g->groups[0].epilogue);
     if(!fn)
         return fail(CKB_ERR_UNSUPPORTED, "no kernel instance for epilogue %d", g->groups[0].epilogue);
-    CKB_CUDA(fn(bn, cg, p, plan.grid, stream));
+    CKB_CUDA(fn(gp.bn, gp.cg, p, gp.plan.grid, stream));
     g_launches.fetch_add(1);
     return CKB_OK;
 }

@@ -2,7 +2,8 @@
 //
 // One CTA per SM walks work items  w = blockIdx.x, blockIdx.x + gridDim.x, ...
 //   warp 0     TMA producer : fills a ring of STAGES shared-memory stages (A tile 128 x 128 B,
-//                             B tile <=BN x 128 B, both K-major, 128-byte swizzle)
+//                             B tile <=BN x 128 B, 128-byte swizzle; K-major, or for the other
+//                             GEMM layouts MN-major: boxes of 128 B of M|N positions x the k rows)
 //   warp 1     MMA issuer   : one thread issues tcgen05.mma (128 x width x 16|32) into one of two
 //                             TMEM accumulators (2 x BN columns) and commits to mbarriers
 //   warps 2-9  epilogue     : tcgen05.ld the finished accumulator (two warps per TMEM lane
@@ -104,7 +105,7 @@ struct KernelParams
     int32_t tiles_n;
     int32_t num_kb;      // k blocks per tile (GEMM / CONV)
     int32_t vec_ok;      // 128-bit epilogue access allowed
-    int32_t pad_;
+    int32_t mn_major;    // bit 0: A is M-contiguous (column-major A); bit 1: B is N-contiguous (row-major B)
     ConvGeom conv;
     uint64_t wait_limit_ns;
     uint32_t* status; // device status word
@@ -278,6 +279,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
     constexpr int BK_ELEMS       = (KIND == KIND_I8) ? 128 : 64;
     constexpr uint32_t C_FMT     = (KIND == KIND_I8) ? 2u : 1u;
     constexpr uint32_t AB_FMT    = (KIND == KIND_F16) ? 0u : 1u; // f16 | bf16 or s8
+    // MN-major operands (GEMM layouts other than row-major A x column-major B): one TMA box = one
+    // swizzle atom column = BK_ELEMS positions of M|N (128 bytes) x BK_ELEMS rows of k
+    constexpr int ATOM_BYTES     = BK_ELEMS * BK_BYTES;
+    const bool a_mn              = MODE != MODE_CONV && (P.mn_major & 1) != 0;
+    const bool b_mn              = MODE != MODE_CONV && (P.mn_major & 2) != 0;
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr  = smem_u32(smem_raw);
@@ -371,7 +377,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                 const int b_rows        = wi.width / CG;                       // B rows this CTA loads
                 const int a_row0        = wi.m_blk * TILE_M + cta_rank * BM;  // first A row of this CTA
                 const int b_row0        = wi.n_start + cta_rank * b_rows;
-                (void)b_rows;
                 // CONV: first output pixel of this CTA's rows in (n, ho, wo)
                 int cv_n = 0, cv_h = 0, cv_w = 0;
                 if constexpr(MODE == MODE_CONV)
@@ -407,8 +412,18 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                         }
                         else
                         {
-                            tma_load_2d_pair(a_dst, tm_a, bar, kb * BK_ELEMS, a_row0);
-                            tma_load_2d_pair(b_dst, tm_b, bar, kb * BK_ELEMS, b_row0);
+                            if(a_mn)
+                                for(int j = 0; j < BM / BK_ELEMS; ++j)
+                                    tma_load_2d_pair(a_dst + j * ATOM_BYTES, tm_a, bar, a_row0 + j * BK_ELEMS,
+                                                     kb * BK_ELEMS);
+                            else
+                                tma_load_2d_pair(a_dst, tm_a, bar, kb * BK_ELEMS, a_row0);
+                            if(b_mn)
+                                for(int j = 0; j * BK_ELEMS < b_rows; ++j)
+                                    tma_load_2d_pair(b_dst + j * ATOM_BYTES, tm_b, bar, b_row0 + j * BK_ELEMS,
+                                                     kb * BK_ELEMS);
+                            else
+                                tma_load_2d_pair(b_dst, tm_b, bar, kb * BK_ELEMS, b_row0);
                         }
                     }
                     else if constexpr(MODE == MODE_CONV)
@@ -421,8 +436,18 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                     }
                     else
                     {
-                        tma_load_2d(a_dst, tm_a, full_bar(stage), kb * BK_ELEMS, a_row0);
-                        tma_load_2d(b_dst, tm_b, full_bar(stage), kb * BK_ELEMS, b_row0);
+                        if(a_mn)
+                            for(int j = 0; j < BM / BK_ELEMS; ++j)
+                                tma_load_2d(a_dst + j * ATOM_BYTES, tm_a, full_bar(stage), a_row0 + j * BK_ELEMS,
+                                            kb * BK_ELEMS);
+                        else
+                            tma_load_2d(a_dst, tm_a, full_bar(stage), kb * BK_ELEMS, a_row0);
+                        if(b_mn)
+                            for(int j = 0; j * BK_ELEMS < b_rows; ++j)
+                                tma_load_2d(b_dst + j * ATOM_BYTES, tm_b, full_bar(stage), b_row0 + j * BK_ELEMS,
+                                            kb * BK_ELEMS);
+                        else
+                            tma_load_2d(b_dst, tm_b, full_bar(stage), kb * BK_ELEMS, b_row0);
                     }
                     if constexpr(MODE == MODE_CONV)
                     {
@@ -468,7 +493,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
             for(int w = unit; ok && w < P.total_work; w += num_units, ++iter)
             {
                 const WorkItem wi        = decode_work<MODE, BN>(P, w);
-                const uint32_t idesc     = make_idesc(C_FMT, AB_FMT, TILE_M, static_cast<uint32_t>(wi.width));
+                const uint32_t idesc     = make_idesc(C_FMT, AB_FMT, TILE_M, static_cast<uint32_t>(wi.width),
+                                                      a_mn ? 1u : 0u, b_mn ? 1u : 0u);
                 const int acc            = iter & 1;
                 const uint32_t acc_phase = (iter >> 1) & 1;
                 ok = bounded_wait(tmem_empty_bar(acc), acc_phase ^ 1u, wc, WAIT_TMEM_EMPTY);
@@ -483,25 +509,32 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                         break;
                     tc_fence_after_sync();
                     const uint32_t a_addr = base_addr + stage * L::STAGE_BYTES;
-                    const uint64_t a_desc = make_smem_desc_k_sw128(a_addr);
-                    const uint64_t b_desc = make_smem_desc_k_sw128(a_addr + L::A_BYTES);
+                    const uint64_t a_desc = a_mn ? make_smem_desc_mn_sw128(a_addr, ATOM_BYTES)
+                                                 : make_smem_desc_k_sw128(a_addr);
+                    const uint64_t b_desc = b_mn ? make_smem_desc_mn_sw128(a_addr + L::A_BYTES, ATOM_BYTES)
+                                                 : make_smem_desc_k_sw128(a_addr + L::A_BYTES);
 #pragma unroll
                     for(int k = 0; k < K_STEPS; ++k)
                     {
-                        const uint64_t koff = static_cast<uint64_t>((k * UMMA_K_BYTES) >> 4);
+                        // one UMMA K step: 32 bytes along a K-major row, or (BK_ELEMS / K_STEPS) rows of
+                        // 128 bytes in an MN-major tile
+                        const uint64_t koff_k  = static_cast<uint64_t>((k * UMMA_K_BYTES) >> 4);
+                        const uint64_t koff_mn = static_cast<uint64_t>((k * (BK_ELEMS / K_STEPS) * BK_BYTES) >> 4);
+                        const uint64_t koff_a  = a_mn ? koff_mn : koff_k;
+                        const uint64_t koff_b  = b_mn ? koff_mn : koff_k;
                         if constexpr(CG == 2)
                         {
                             if constexpr(KIND == KIND_I8)
-                                mma_i8_ss_pair(tmem_d, a_desc + koff, b_desc + koff, idesc, (kb | k) != 0);
+                                mma_i8_ss_pair(tmem_d, a_desc + koff_a, b_desc + koff_b, idesc, (kb | k) != 0);
                             else
-                                mma_f16_ss_pair(tmem_d, a_desc + koff, b_desc + koff, idesc, (kb | k) != 0);
+                                mma_f16_ss_pair(tmem_d, a_desc + koff_a, b_desc + koff_b, idesc, (kb | k) != 0);
                         }
                         else
                         {
                             if constexpr(KIND == KIND_I8)
-                                mma_i8_ss(tmem_d, a_desc + koff, b_desc + koff, idesc, (kb | k) != 0);
+                                mma_i8_ss(tmem_d, a_desc + koff_a, b_desc + koff_b, idesc, (kb | k) != 0);
                             else
-                                mma_f16_ss(tmem_d, a_desc + koff, b_desc + koff, idesc, (kb | k) != 0);
+                                mma_f16_ss(tmem_d, a_desc + koff_a, b_desc + koff_b, idesc, (kb | k) != 0);
                         }
                     }
                     issued_any = true;

@@ -321,14 +321,32 @@ __device__ __forceinline__ uint64_t make_smem_desc_k_sw128(uint32_t smem_addr)
     return d;
 }
 
-// Instruction descriptor for tcgen05.mma kind::f16 / kind::i8, both operands K-major:
+// Shared-memory matrix descriptor for an MN-major operand tile (the M or N index is the contiguous
+// one) stored by TMA with 128-byte swizzle: the tile is a row of "atoms" along MN, each atom being
+// `k_rows` rows of 128 bytes (one row per k, 128 bytes = 64 16-bit or 128 8-bit MN positions).
+//   leading byte offset = distance between atoms along MN (= k_rows * 128 B, the size of one TMA box)
+//   stride byte offset  = distance between groups of 8 k-rows = 1024 B
+// Stepping along K moves the start address by (k step) * 128 bytes.
+__device__ __forceinline__ uint64_t make_smem_desc_mn_sw128(uint32_t smem_addr, uint32_t atom_bytes)
+{
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>((atom_bytes >> 4) & 0x3FFFu) << 16;
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+
+// Instruction descriptor for tcgen05.mma kind::f16 / kind::i8:
 //   bits 4-5 accumulator format (1 = f32, 2 = s32); bits 7-9 A format; bits 10-12 B format
-//   (f16 kind: 0 = f16, 1 = bf16; i8 kind: 0 = u8, 1 = s8); bit 15 / 16 A / B major (0 = K);
+//   (f16 kind: 0 = f16, 1 = bf16; i8 kind: 0 = u8, 1 = s8); bit 15 / 16 A / B major (0 = K, 1 = MN);
 //   bits 17-22 N >> 3; bits 24-28 M >> 4.
 __host__ __device__ constexpr uint32_t make_idesc(uint32_t c_fmt, uint32_t ab_fmt, uint32_t m,
-                                                  uint32_t n)
+                                                  uint32_t n, uint32_t a_mn_major = 0, uint32_t b_mn_major = 0)
 {
-    return (c_fmt << 4) | (ab_fmt << 7) | (ab_fmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+    return (c_fmt << 4) | (ab_fmt << 7) | (ab_fmt << 10) | (a_mn_major << 15) | (b_mn_major << 16) |
+           ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
 } // namespace ckb

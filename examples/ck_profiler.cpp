@@ -4,11 +4,12 @@
 // argument, asks IsSupportedArgument, times the kernel, prints a "Perf:" line, verifies against the CPU reference and
 // finally prints "Best Perf" (profiler/include/profile_gemm_impl.hpp:139-249).
 //
-//   ck_profiler gemm                  <dtype 1 fp16|2 bf16|3 int8> <layout 1> <verify> <init> <log> <time> M N K StrideA StrideB StrideC
+//   ck_profiler gemm                  <dtype 1 fp16|2 bf16|3 int8> <layout 0..3> <verify> <init> <log> <time> M N K StrideA StrideB StrideC
 //   ck_profiler gemm_add_add_fastgelu <dtype 1> <layout 1> <verify> <init> <log> <time> M N K StrideA StrideB StrideD0 StrideD1 StrideE
 //   ck_profiler grouped_gemm          <dtype 1> <layout 1> <verify> <init> <log> <time> Ms Ns Ks          (comma separated lists)
 //   ck_profiler conv_fwd_bias_relu    <dtype 1> <verify> <init> <log> <time> N K C Y X Hi Wi Sy Sx Dy Dx LeftPy LeftPx RightPy RightPx
-// Only matrix layout 1 (A[m,k] * B[n,k] = C[m,n]) has kernels; the others report "no instance".
+// gemm takes the reference's four matrix layouts (0: mk_kn, 1: mk_nk, 2: km_kn, 3: km_nk); the fused and grouped
+// sub-commands take layout 1.
 #include <cstring>
 #include <iostream>
 #include <sstream>
@@ -67,11 +68,11 @@ void init_tensor(Tensor<T>& t, int init_method, bool is_b)
     }
 }
 
-template <typename T, typename AccT>
+template <typename T, typename AccT, typename ALayout, typename BLayout>
 bool profile_gemm_typed(bool verify, int init, bool time, int M, int N, int K, int sa, int sb, int sc)
 {
-    using DeviceOp = dev::DeviceGemm<Row, Col, Row, T, T, T, PassThrough, PassThrough, PassThrough>;
-    Tensor<T> a(example::matrix_descriptor(M, K, sa, Row{})), b(example::matrix_descriptor(K, N, sb, Col{}));
+    using DeviceOp = dev::DeviceGemm<ALayout, BLayout, Row, T, T, T, PassThrough, PassThrough, PassThrough>;
+    Tensor<T> a(example::matrix_descriptor(M, K, sa, ALayout{})), b(example::matrix_descriptor(K, N, sb, BLayout{}));
     Tensor<T> c_host(example::matrix_descriptor(M, N, sc, Row{})), c_dev(example::matrix_descriptor(M, N, sc, Row{}));
     init_tensor(a, init, false);
     init_tensor(b, init, true);
@@ -120,7 +121,10 @@ int profile_gemm(int argc, char* argv[])
     if(argc != 14)
     {
         std::printf("arg1: tensor operation (gemm: GEMM)\narg2: data type (1: fp16; 2: bf16; 3: int8)\n"
-                    "arg3: matrix layout (1: A[m, k] * B[n, k] = C[m, n])\narg4: verification (0: no; 1: yes)\n"
+                    "arg3: matrix layout (0: A[m, k] * B[k, n] = C[m, n];\n"
+                    "                     1: A[m, k] * B[n, k] = C[m, n];\n"
+                    "                     2: A[k, m] * B[k, n] = C[m, n];\n"
+                    "                     3: A[k, m] * B[n, k] = C[m, n])\narg4: verification (0: no; 1: yes)\n"
                     "arg5: initialization (0: no init; 1: integer value; 2: decimal value)\n"
                     "arg6: print tensor value (0: no; 1: yes)\narg7: time kernel (0=no, 1=yes)\n"
                     "arg8 to 13: M, N, K, StrideA, StrideB, StrideC\n");
@@ -131,20 +135,26 @@ int profile_gemm(int argc, char* argv[])
     const int init = std::stoi(argv[5]);
     const int M = std::stoi(argv[8]), N = std::stoi(argv[9]), K = std::stoi(argv[10]);
     const int sa = std::stoi(argv[11]), sb = std::stoi(argv[12]), sc = std::stoi(argv[13]);
-    if(layout != 1)
+    if(layout < 0 || layout > 3 || dtype < 1 || dtype > 3)
     {
-        std::cout << "no instance for matrix layout " << layout << std::endl;
+        std::cout << "no instance for data type " << dtype << ", matrix layout " << layout << std::endl;
         return 1;
     }
-    bool ok = false;
-    if(dtype == 1)
-        ok = profile_gemm_typed<ck::half_t, float>(verify, init, time, M, N, K, sa, sb, sc);
-    else if(dtype == 2)
-        ok = profile_gemm_typed<ck::bhalf_t, float>(verify, init, time, M, N, K, sa, sb, sc);
-    else if(dtype == 3)
-        ok = profile_gemm_typed<int8_t, int32_t>(verify, init, time, M, N, K, sa, sb, sc);
-    else
-        std::cout << "no instance for data type " << dtype << std::endl;
+    auto run = [&](auto t, auto acc, auto la, auto lb) {
+        return profile_gemm_typed<decltype(t), decltype(acc), decltype(la), decltype(lb)>(verify, init, time, M, N, K, sa,
+                                                                                         sb, sc);
+    };
+    auto by_layout = [&](auto t, auto acc) {
+        switch(layout)
+        {
+        case 0: return run(t, acc, Row{}, Row{}); // MK_KN_MN
+        case 1: return run(t, acc, Row{}, Col{}); // MK_NK_MN
+        case 2: return run(t, acc, Col{}, Row{}); // KM_KN_MN
+        default: return run(t, acc, Col{}, Col{}); // KM_NK_MN
+        }
+    };
+    const bool ok = dtype == 1 ? by_layout(ck::half_t{}, float{})
+                               : dtype == 2 ? by_layout(ck::bhalf_t{}, float{}) : by_layout(int8_t{}, int32_t{});
     return ok ? 0 : 1;
 }
 

@@ -213,6 +213,23 @@ struct DeviceConvFwdBiasActivation : public BaseOperator
 template <typename I, typename W, typename O>
 using DeviceConvFwdBiasActivationPtr = std::unique_ptr<DeviceConvFwdBiasActivation<I, W, O>>;
 
+// device_conv_fwd_bias_activation_add.hpp:15-45
+template <typename InElementwiseOperation, typename WeiElementwiseOperation, typename OutElementwiseOperation>
+struct DeviceConvFwdBiasActivationAdd : public BaseOperator
+{
+    virtual std::unique_ptr<BaseArgument>
+    MakeArgumentPointer(const void* p_in, const void* p_wei, void* p_out, const void* p_bias, const void* p_resi,
+                        index_t N, index_t K, index_t C, std::vector<index_t> input_spatial_lengths,
+                        std::vector<index_t> filter_spatial_lengths, std::vector<index_t> output_spatial_lengths,
+                        std::vector<index_t> conv_filter_strides, std::vector<index_t> conv_filter_dilations,
+                        std::vector<index_t> input_left_pads, std::vector<index_t> input_right_pads,
+                        InElementwiseOperation in_element_op, WeiElementwiseOperation wei_element_op,
+                        OutElementwiseOperation out_element_op) = 0;
+    virtual std::unique_ptr<BaseInvoker> MakeInvokerPointer()  = 0;
+};
+template <typename I, typename W, typename O>
+using DeviceConvFwdBiasActivationAddPtr = std::unique_ptr<DeviceConvFwdBiasActivationAdd<I, W, O>>;
+
 } // namespace device
 } // namespace tensor_operation
 
@@ -781,6 +798,68 @@ struct DeviceConv2dFwdXdl_C_Shuffle_Bias_Activation_Input_N_Hi_Wi_C_Weight_K_Y_X
         std::ostringstream s;
         s << "DeviceConv2dFwdXdl_C_Shuffle_Bias_Activation_Input_N_Hi_Wi_C_Weight_K_Y_X_C_Output_N_Ho_Wo_K<" << BlockSize
           << ", " << MPerBlock << ", " << NPerBlock << ", " << K0PerBlock
+          << "> on B200 tcgen05 + im2col TMA (tuning parameters ignored)";
+        return s.str();
+    }
+};
+
+// device_conv2d_fwd_xdl_c_shuffle_bias_activation_add_nhwc_kyxc_nhwk.hpp:25-66: out = out_op(conv, bias[k], resi)
+// with the residual tensor laid out like the output (NHWK).
+template <typename InDataType, typename WeiDataType, typename OutDataType, typename AccDataType,
+          typename InElementwiseOperation, typename WeiElementwiseOperation, typename OutElementwiseOperation,
+          ConvolutionForwardSpecialization ConvForwardSpecialization, index_t BlockSize, index_t MPerBlock,
+          index_t NPerBlock, index_t K0PerBlock, index_t K1, index_t MPerXDL, index_t NPerXDL, index_t MXdlPerWave,
+          index_t NXdlPerWave, CKB_XFER(ABlockTransfer), CKB_XFER(BBlockTransfer), index_t CShuffleMXdlPerWavePerShuffle,
+          index_t CShuffleNXdlPerWavePerShuffle, typename CBlockTransferClusterLengths,
+          index_t CBlockTransferScalarPerVector>
+struct DeviceConv2dFwdXdl_C_Shuffle_Bias_Activation_Add_Input_N_Hi_Wi_C_Weight_K_Y_X_C_Output_N_Ho_Wo_K
+    : public DeviceConvFwdBiasActivationAdd<InElementwiseOperation, WeiElementwiseOperation, OutElementwiseOperation>
+{
+    using Argument = b200::ConvArgument;
+    using Invoker  = b200::ConvInvoker;
+
+    static auto MakeArgument(const InDataType* p_in, const WeiDataType* p_wei, OutDataType* p_out,
+                             const OutDataType* p_bias, const OutDataType* p_resi, index_t N, index_t K, index_t C,
+                             std::vector<index_t> input_spatial_lengths, std::vector<index_t> filter_spatial_lengths,
+                             std::vector<index_t> output_spatial_lengths, std::vector<index_t> conv_filter_strides,
+                             std::vector<index_t> conv_filter_dilations, std::vector<index_t> input_left_pads,
+                             std::vector<index_t> input_right_pads, InElementwiseOperation, WeiElementwiseOperation,
+                             OutElementwiseOperation out_element_op)
+    {
+        auto arg = b200::make_conv_argument<InDataType, InElementwiseOperation, WeiElementwiseOperation,
+                                            OutElementwiseOperation>(
+            p_in, p_wei, p_out, p_bias, p_resi, N, K, C, input_spatial_lengths, filter_spatial_lengths,
+            output_spatial_lengths, conv_filter_strides, conv_filter_dilations, input_left_pads, input_right_pads,
+            out_element_op);
+        arg.host_ok = arg.host_ok && std::is_same<InDataType, WeiDataType>::value &&
+                      std::is_same<InDataType, OutDataType>::value;
+        return arg;
+    }
+    static auto MakeInvoker() { return Invoker{}; }
+    static bool IsSupportedArgument(const Argument& arg) { return b200::conv_supported(arg); }
+    bool IsSupportedArgument(const BaseArgument* p_arg) override
+    {
+        return IsSupportedArgument(b200::argument_cast<Argument>(p_arg));
+    }
+    std::unique_ptr<BaseArgument>
+    MakeArgumentPointer(const void* p_in, const void* p_wei, void* p_out, const void* p_bias, const void* p_resi,
+                        index_t N, index_t K, index_t C, std::vector<index_t> in_sp, std::vector<index_t> filt_sp,
+                        std::vector<index_t> out_sp, std::vector<index_t> strides, std::vector<index_t> dilations,
+                        std::vector<index_t> lpads, std::vector<index_t> rpads, InElementwiseOperation in_op,
+                        WeiElementwiseOperation wei_op, OutElementwiseOperation out_op) override
+    {
+        return std::make_unique<Argument>(
+            MakeArgument(static_cast<const InDataType*>(p_in), static_cast<const WeiDataType*>(p_wei),
+                         static_cast<OutDataType*>(p_out), static_cast<const OutDataType*>(p_bias),
+                         static_cast<const OutDataType*>(p_resi), N, K, C, in_sp, filt_sp, out_sp, strides, dilations,
+                         lpads, rpads, in_op, wei_op, out_op));
+    }
+    std::unique_ptr<BaseInvoker> MakeInvokerPointer() override { return std::make_unique<Invoker>(); }
+    std::string GetTypeString() const override
+    {
+        std::ostringstream s;
+        s << "DeviceConv2dFwdXdl_C_Shuffle_Bias_Activation_Add_Input_N_Hi_Wi_C_Weight_K_Y_X_C_Output_N_Ho_Wo_K<"
+          << BlockSize << ", " << MPerBlock << ", " << NPerBlock << ", " << K0PerBlock
           << "> on B200 tcgen05 + im2col TMA (tuning parameters ignored)";
         return s.str();
     }

@@ -161,6 +161,40 @@ struct ReferenceConvFwd : public device::BaseOperator
     std::string GetTypeString() const override { return "ReferenceConvFwd"; }
 };
 
+namespace detail {
+// Float accumulation of one output element of a 2-D convolution over c, y, x (in that order); taps outside the
+// image are skipped (reference_conv_fwd_bias_activation.hpp:77-112).  Arg supplies in_n_c_hi_wi_, wei_k_c_y_x_,
+// the stride / dilation / left-pad vectors and the input / weight element ops.
+template <typename Arg>
+float conv2d_accumulate(const Arg& arg, std::size_t n, std::size_t k, std::size_t ho, std::size_t wo)
+{
+    const auto& wl = arg.wei_k_c_y_x_.mDesc.GetLengths();
+    const auto& il = arg.in_n_c_hi_wi_.mDesc.GetLengths();
+    float v_acc    = 0;
+    for(std::size_t c = 0; c < wl[1]; ++c)
+        for(std::size_t y = 0; y < wl[2]; ++y)
+        {
+            const long_index_t hi = static_cast<long_index_t>(ho * arg.conv_strides_[0]) +
+                                    static_cast<long_index_t>(y * arg.conv_dilations_[0]) -
+                                    static_cast<long_index_t>(arg.in_left_pads_[0]);
+            for(std::size_t x = 0; x < wl[3]; ++x)
+            {
+                const long_index_t wi = static_cast<long_index_t>(wo * arg.conv_strides_[1]) +
+                                        static_cast<long_index_t>(x * arg.conv_dilations_[1]) -
+                                        static_cast<long_index_t>(arg.in_left_pads_[1]);
+                if(hi >= 0 && static_cast<std::size_t>(hi) < il[2] && wi >= 0 && static_cast<std::size_t>(wi) < il[3])
+                {
+                    float v_in, v_wei;
+                    arg.in_element_op_(v_in, static_cast<const float>(arg.in_n_c_hi_wi_(n, c, hi, wi)));
+                    arg.wei_element_op_(v_wei, static_cast<const float>(arg.wei_k_c_y_x_(k, c, y, x)));
+                    v_acc += v_in * v_wei;
+                }
+            }
+        }
+    return v_acc;
+}
+} // namespace detail
+
 // out = out_op(acc, float(bias[k])) stored through the implicit float -> OutDataType conversion
 template <typename InDataType, typename WeiDataType, typename OutDataType, typename InElementwiseOperation,
           typename WeiElementwiseOperation, typename OutElementwiseOperation>
@@ -194,31 +228,8 @@ struct ReferenceConvFwd_Bias_Activation : public device::BaseOperator
     {
         float Run(const Argument& arg)
         {
-            const auto& wl = arg.wei_k_c_y_x_.mDesc.GetLengths();
-            const auto& il = arg.in_n_c_hi_wi_.mDesc.GetLengths();
-            auto f_nchw    = [&](auto n, auto k, auto ho, auto wo) {
-                float v_acc = 0;
-                for(std::size_t c = 0; c < wl[1]; ++c)
-                    for(std::size_t y = 0; y < wl[2]; ++y)
-                    {
-                        const long_index_t hi = static_cast<long_index_t>(ho * arg.conv_strides_[0]) +
-                                                static_cast<long_index_t>(y * arg.conv_dilations_[0]) -
-                                                static_cast<long_index_t>(arg.in_left_pads_[0]);
-                        for(std::size_t x = 0; x < wl[3]; ++x)
-                        {
-                            const long_index_t wi = static_cast<long_index_t>(wo * arg.conv_strides_[1]) +
-                                                    static_cast<long_index_t>(x * arg.conv_dilations_[1]) -
-                                                    static_cast<long_index_t>(arg.in_left_pads_[1]);
-                            if(hi >= 0 && static_cast<std::size_t>(hi) < il[2] && wi >= 0 &&
-                               static_cast<std::size_t>(wi) < il[3])
-                            {
-                                float v_in, v_wei;
-                                arg.in_element_op_(v_in, static_cast<const float>(arg.in_n_c_hi_wi_(n, c, hi, wi)));
-                                arg.wei_element_op_(v_wei, static_cast<const float>(arg.wei_k_c_y_x_(k, c, y, x)));
-                                v_acc += v_in * v_wei;
-                            }
-                        }
-                    }
+            auto f_nchw = [&](auto n, auto k, auto ho, auto wo) {
+                const float v_acc = detail::conv2d_accumulate(arg, n, k, ho, wo);
                 float v_out;
                 arg.out_element_op_(v_out, v_acc, static_cast<float>(arg.bias_k_(k)));
                 arg.out_n_k_ho_wo_(n, k, ho, wo) = static_cast<OutDataType>(v_out);
@@ -246,6 +257,74 @@ struct ReferenceConvFwd_Bias_Activation : public device::BaseOperator
     }
     static auto MakeInvoker() { return Invoker{}; }
     std::string GetTypeString() const override { return "ReferenceConvFwd_Bias_Activation"; }
+};
+
+// out = out_op(acc, float(bias[k]), float(resi[n,k,ho,wo]))
+// (reference_conv_fwd_bias_activation_add.hpp:20-185)
+template <typename InDataType, typename WeiDataType, typename OutDataType, typename InElementwiseOperation,
+          typename WeiElementwiseOperation, typename OutElementwiseOperation>
+struct ReferenceConvFwd_Bias_Activation_Add : public device::BaseOperator
+{
+    struct Argument : public device::BaseArgument
+    {
+        Argument(const Tensor<InDataType>& in_n_c_hi_wi, const Tensor<WeiDataType>& wei_k_c_y_x,
+                 Tensor<OutDataType>& out_n_k_ho_wo, const Tensor<OutDataType>& bias_k,
+                 const Tensor<OutDataType>& resi_n_k_ho_wo, std::vector<index_t> conv_filter_strides,
+                 std::vector<index_t> conv_filter_dilations, std::vector<index_t> input_left_pads,
+                 std::vector<index_t> input_right_pads, InElementwiseOperation in_element_op,
+                 WeiElementwiseOperation wei_element_op, OutElementwiseOperation out_element_op)
+            : in_n_c_hi_wi_{in_n_c_hi_wi}, wei_k_c_y_x_{wei_k_c_y_x}, out_n_k_ho_wo_{out_n_k_ho_wo}, bias_k_{bias_k},
+              resi_n_k_ho_wo_{resi_n_k_ho_wo}, conv_strides_{conv_filter_strides},
+              conv_dilations_{conv_filter_dilations}, in_left_pads_{input_left_pads}, in_right_pads_{input_right_pads},
+              in_element_op_{in_element_op}, wei_element_op_{wei_element_op}, out_element_op_{out_element_op}
+        {
+        }
+        const Tensor<InDataType>& in_n_c_hi_wi_;
+        const Tensor<WeiDataType>& wei_k_c_y_x_;
+        Tensor<OutDataType>& out_n_k_ho_wo_;
+        const Tensor<OutDataType>& bias_k_;
+        const Tensor<OutDataType>& resi_n_k_ho_wo_;
+        std::vector<index_t> conv_strides_, conv_dilations_, in_left_pads_, in_right_pads_;
+        InElementwiseOperation in_element_op_;
+        WeiElementwiseOperation wei_element_op_;
+        OutElementwiseOperation out_element_op_;
+    };
+
+    struct Invoker : public device::BaseInvoker
+    {
+        float Run(const Argument& arg)
+        {
+            auto f_nchw = [&](auto n, auto k, auto ho, auto wo) {
+                const float v_acc = detail::conv2d_accumulate(arg, n, k, ho, wo);
+                float v_out;
+                arg.out_element_op_(v_out, v_acc, static_cast<float>(arg.bias_k_(k)),
+                                    static_cast<float>(arg.resi_n_k_ho_wo_(n, k, ho, wo)));
+                arg.out_n_k_ho_wo_(n, k, ho, wo) = static_cast<OutDataType>(v_out);
+            };
+            const auto& ol = arg.out_n_k_ho_wo_.mDesc.GetLengths();
+            make_ParallelTensorFunctor(f_nchw, ol[0], ol[1], ol[2], ol[3])(std::thread::hardware_concurrency());
+            return 0;
+        }
+        float Run(const device::BaseArgument* p_arg, const StreamConfig& = StreamConfig{}) override
+        {
+            return Run(*dynamic_cast<const Argument*>(p_arg));
+        }
+    };
+
+    bool IsSupportedArgument(const device::BaseArgument*) override { return true; }
+    static auto MakeArgument(const Tensor<InDataType>& in_n_c_hi_wi, const Tensor<WeiDataType>& wei_k_c_y_x,
+                             Tensor<OutDataType>& out_n_k_ho_wo, const Tensor<OutDataType>& bias_k,
+                             const Tensor<OutDataType>& resi_n_k_ho_wo, std::vector<index_t> conv_filter_strides,
+                             std::vector<index_t> conv_filter_dilations, std::vector<index_t> input_left_pads,
+                             std::vector<index_t> input_right_pads, InElementwiseOperation in_element_op,
+                             WeiElementwiseOperation wei_element_op, OutElementwiseOperation out_element_op)
+    {
+        return Argument{in_n_c_hi_wi, wei_k_c_y_x, out_n_k_ho_wo, bias_k, resi_n_k_ho_wo, conv_filter_strides,
+                        conv_filter_dilations, input_left_pads, input_right_pads, in_element_op, wei_element_op,
+                        out_element_op};
+    }
+    static auto MakeInvoker() { return Invoker{}; }
+    std::string GetTypeString() const override { return "ReferenceConvFwd_Bias_Activation_Add"; }
 };
 
 } // namespace host

@@ -46,7 +46,10 @@ enum {
     CKB_BF16 = 2 /* bfloat16 (ck::bhalf_t, utility/data_type.hpp:10)           */
 };
 
-/* ---- matrix layouts (tensor_layout::gemm, device/tensor_layout.hpp:13-25) */
+/* ---- matrix layouts (tensor_layout::gemm, device/tensor_layout.hpp:13-25).
+ * All four A/B combinations of the reference's GEMM instances run (mk_nk, mk_kn, km_kn, km_nk,
+ * library/src/tensor_operation_instance/gpu/gemm/): a K-contiguous operand (row-major A,
+ * column-major B) is read as a K-major tile, the other kind as an MN-major tile. */
 enum {
     CKB_ROW_MAJOR = 0,
     CKB_COL_MAJOR = 1
@@ -103,8 +106,8 @@ enum {
 typedef struct ckb_gemm_desc {
     int32_t ab_dtype;            /* CKB_F16 / CKB_BF16 / CKB_I8 (A and B share it)      */
     int32_t e_dtype;             /* CKB_F16 / CKB_BF16 for float inputs, CKB_I8 for int8 */
-    int32_t a_layout;            /* A is M x K                                           */
-    int32_t b_layout;            /* B is K x N                                           */
+    int32_t a_layout;            /* A is M x K: row-major (lda >= K) or column-major (lda >= M) */
+    int32_t b_layout;            /* B is K x N: column-major (ldb >= K) or row-major (ldb >= N) */
     int32_t e_layout;            /* E (and every D) is M x N; only CKB_ROW_MAJOR         */
     int32_t epilogue;            /* CKB_EPI_*                                            */
     int32_t n_ds;                /* number of D tensors the epilogue reads (0..2)        */

@@ -211,9 +211,14 @@ static void test_traits_and_support()
     EXPECT(threw); // device_gemm_xdl_cshuffle.hpp:475-481
     EXPECT(gemm.GetTypeString().find("DeviceGemm_Xdl_CShuffle<256, 256, 128, 32, 8, 8>") == 0);
 
-    Gemm<Col, Col, F16, ew::PassThrough> gemm_km; // A column-major: no kernel yet
-    auto km = gemm_km.MakeArgument(pa, pb, pc, 256, 256, 256, 256, 256, 256, {}, {}, {});
-    EXPECT(!gemm_km.IsSupportedArgument(km));
+    Gemm<Col, Col, F16, ew::PassThrough> gemm_km; // A column-major (km_nk): lda counts M
+    auto km = gemm_km.MakeArgument(pa, pb, pc, 256, 256, 128, 256, 128, 256, {}, {}, {});
+    EXPECT(gemm_km.IsSupportedArgument(km));
+    auto km_bad = gemm_km.MakeArgument(pa, pb, pc, 256, 256, 128, 128, 128, 256, {}, {}, {});
+    EXPECT(!gemm_km.IsSupportedArgument(km_bad));
+    Gemm<Row, Row, F16, ew::PassThrough> gemm_kn; // B row-major (mk_kn): ldb counts N
+    auto kn = gemm_kn.MakeArgument(pa, pb, pc, 256, 512, 128, 128, 512, 512, {}, {}, {});
+    EXPECT(gemm_kn.IsSupportedArgument(kn));
     Gemm<Row, Col, F16, LocalFunctor> gemm_local;
     auto loc = gemm_local.MakeArgument(pa, pb, pc, 256, 256, 256, 256, 256, 256, {}, {}, LocalFunctor{});
     EXPECT(!gemm_local.IsSupportedArgument(loc));

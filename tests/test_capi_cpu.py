@@ -72,10 +72,17 @@ def test_gemm_supported_rules():
     assert not op.IsSupportedArgument(op.MakeArgument(0x1000, 0x2000, 0x3000, 0, 8, 8, 8, 8, 8))
     # non-PassThrough A/B element ops cannot be applied by TMA
     assert not op.IsSupportedArgument(op.MakeArgument(0x1000, 0x2000, 0x3000, 8, 8, 8, 8, 8, 8, ck.Scale(2.0)))
-    # layouts other than row x col
-    assert not ck.DeviceGemm(capi.CKB_F16, capi.CKB_COL_MAJOR, capi.CKB_COL_MAJOR).IsSupportedArgument(
-        ck.DeviceGemm(capi.CKB_F16, capi.CKB_COL_MAJOR, capi.CKB_COL_MAJOR).MakeArgument(
-            0x1000, 0x2000, 0x3000, 8, 8, 8, 8, 8, 8))
+    # all four A/B layout combinations; the leading dimension rule follows the layout
+    for la in (capi.CKB_ROW_MAJOR, capi.CKB_COL_MAJOR):
+        for lb in (capi.CKB_ROW_MAJOR, capi.CKB_COL_MAJOR):
+            g = ck.DeviceGemm(capi.CKB_F16, la, lb)
+            lda = 64 if la == capi.CKB_ROW_MAJOR else 256  # M=256, N=512, K=64
+            ldb = 64 if lb == capi.CKB_COL_MAJOR else 512
+            assert g.IsSupportedArgument(g.MakeArgument(0x1000, 0x2000, 0x3000, 256, 512, 64, lda, ldb, 512))
+    km = ck.DeviceGemm(capi.CKB_F16, capi.CKB_COL_MAJOR, capi.CKB_COL_MAJOR)
+    assert not km.IsSupportedArgument(km.MakeArgument(0x1000, 0x2000, 0x3000, 256, 512, 64, 64, 64, 512))  # lda < M
+    assert not ck.DeviceGemm(capi.CKB_F16, 7, capi.CKB_COL_MAJOR).IsSupportedArgument(
+        ck.DeviceGemm(capi.CKB_F16, 7, capi.CKB_COL_MAJOR).MakeArgument(0x1000, 0x2000, 0x3000, 8, 8, 8, 8, 8, 8))
     # int8 epilogues are int8-only
     assert not op.IsSupportedArgument(op.MakeArgument(0x1000, 0x2000, 0x3000, 8, 8, 8, 8, 8, 8, None, None,
                                                       ck.RequantReluRequant(0.03, 1.0)))

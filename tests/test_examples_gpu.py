@@ -53,6 +53,8 @@ def test_conv_examples(examples_built):
     out = run_example("conv2d_fwd_xdl_bias_relu", 1, 2, 1, 1, *geom)
     assert "im2col TMA" in out
     run_example("conv2d_fwd_xdl_bias_relu", 1, 1, 0, 0, *geom)  # plain convolution, integer init
+    out = run_example("conv2d_fwd_xdl_bias_relu", 1, 2, 1, 2, *geom)  # bias + ReLU + residual add (example 07)
+    assert "Bias_Activation_Add" in out
 
 
 def test_default_shapes_timing_only(examples_built):
@@ -70,6 +72,10 @@ def test_profiler_driver_walks_instance_lists(examples_built):
     for dtype in (1, 2, 3):  # fp16, bf16, int8
         out = run_example("ck_profiler", "gemm", dtype, 1, 1, 1, 0, 1, 512, 768, 256, 256, 256, 768)
         assert "Best Perf for gemm" in out and "DeviceGemm_Xdl_CShuffle" in out
+    # the other three matrix layouts of profile_gemm.cpp (0: mk_kn, 2: km_kn, 3: km_nk); M N K = 512 768 256
+    for layout, sa, sb in ((0, 256, 768), (2, 512, 768), (3, 512, 256)):
+        out = run_example("ck_profiler", "gemm", 1, layout, 1, 1, 0, 1, 512, 768, 256, sa, sb, 768)
+        assert "Best Perf for gemm" in out
     out = run_example("ck_profiler", "gemm_add_add_fastgelu", 1, 1, 1, 2, 0, 1, 384, 512, 256, 256, 256, 0, 512, 512)
     assert "Best Perf for gemm_add_add_fastgelu" in out
     out = run_example("ck_profiler", "grouped_gemm", 1, 1, 1, 1, 0, 1, "256,512,768", "128,256,384", "64,128,192")
