@@ -46,6 +46,12 @@ class GemmDesc(Structure):
     ]
 
 
+class BatchedGemmDesc(Structure):
+    """struct ckb_batched_gemm_desc"""
+    _fields_ = [("gemm", GemmDesc), ("batch", c_int64), ("batch_stride_a", c_int64), ("batch_stride_b", c_int64),
+                ("batch_stride_e", c_int64), ("batch_stride_d", c_int64 * CKB_MAX_DS)]
+
+
 class GroupedGemmDesc(Structure):
     """struct ckb_grouped_gemm_desc"""
     _fields_ = [("group_count", c_int32), ("reserved0", c_int32), ("groups", POINTER(GemmDesc))]
@@ -84,6 +90,8 @@ SYMBOLS = {
     "ckb_device_synchronize": (c_int, []),
     "ckb_gemm_supported": (c_int, [POINTER(GemmDesc)]),
     "ckb_gemm_run": (c_int, [POINTER(GemmDesc), c_void_p, c_int, POINTER(c_float)]),
+    "ckb_batched_gemm_supported": (c_int, [POINTER(BatchedGemmDesc)]),
+    "ckb_batched_gemm_run": (c_int, [POINTER(BatchedGemmDesc), c_void_p, c_int, POINTER(c_float)]),
     "ckb_grouped_gemm_supported": (c_int, [POINTER(GroupedGemmDesc)]),
     "ckb_grouped_gemm_workspace_size": (c_int, [POINTER(GroupedGemmDesc), POINTER(c_size_t)]),
     "ckb_grouped_gemm_run": (c_int, [POINTER(GroupedGemmDesc), c_void_p, c_size_t, c_void_p, c_int,

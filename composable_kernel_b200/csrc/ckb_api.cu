@@ -148,18 +148,19 @@ CUtensorMapDataType tm_dtype(int dtype)
 }
 
 // K-major matrix [rows][k] with row pitch `ld` elements -> 2-D map, box = 128 bytes x box_rows.
+// batch >= 1 adds a third dimension of `batch` matrices `batch_stride` elements apart (box extent 1).
 int encode_kmajor_2d(CUtensorMap* tm, int dtype, const void* ptr, int64_t rows, int64_t k,
-                     int64_t ld, int box_rows)
+                     int64_t ld, int box_rows, int64_t batch = 0, int64_t batch_stride = 0)
 {
     load_entry_points();
     if(!g_encode_tiled)
         return fail(CKB_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
     const int eb          = elem_bytes(dtype);
-    cuuint64_t dims[2]    = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
-    cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * eb};
-    cuuint32_t box[2]     = {static_cast<cuuint32_t>(BK_BYTES / eb), static_cast<cuuint32_t>(box_rows)};
-    cuuint32_t estr[2]    = {1, 1};
-    CUresult r            = g_encode_tiled(tm, tm_dtype(dtype), 2, const_cast<void*>(ptr), dims, strides,
+    cuuint64_t dims[3]    = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(batch)};
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * eb, static_cast<cuuint64_t>(batch_stride) * eb};
+    cuuint32_t box[3]     = {static_cast<cuuint32_t>(BK_BYTES / eb), static_cast<cuuint32_t>(box_rows), 1};
+    cuuint32_t estr[3]    = {1, 1, 1};
+    CUresult r            = g_encode_tiled(tm, tm_dtype(dtype), batch >= 1 ? 3 : 2, const_cast<void*>(ptr), dims, strides,
                                 box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if(r != CUDA_SUCCESS)
@@ -170,17 +171,18 @@ int encode_kmajor_2d(CUtensorMap* tm, int dtype, const void* ptr, int64_t rows, 
 
 // MN-major matrix (the M or N index contiguous, pitch `ld` elements between consecutive k) -> 2-D map
 // whose box is one swizzle atom column: 128 bytes of MN positions x the k rows of one stage.
-int encode_mnmajor_2d(CUtensorMap* tm, int dtype, const void* ptr, int64_t mn, int64_t k, int64_t ld)
+int encode_mnmajor_2d(CUtensorMap* tm, int dtype, const void* ptr, int64_t mn, int64_t k, int64_t ld,
+                      int64_t batch = 0, int64_t batch_stride = 0)
 {
     load_entry_points();
     if(!g_encode_tiled)
         return fail(CKB_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
     const int eb          = elem_bytes(dtype);
-    cuuint64_t dims[2]    = {static_cast<cuuint64_t>(mn), static_cast<cuuint64_t>(k)};
-    cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * eb};
-    cuuint32_t box[2]     = {static_cast<cuuint32_t>(BK_BYTES / eb), static_cast<cuuint32_t>(BK_BYTES / eb)};
-    cuuint32_t estr[2]    = {1, 1};
-    CUresult r            = g_encode_tiled(tm, tm_dtype(dtype), 2, const_cast<void*>(ptr), dims, strides,
+    cuuint64_t dims[3]    = {static_cast<cuuint64_t>(mn), static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(batch)};
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * eb, static_cast<cuuint64_t>(batch_stride) * eb};
+    cuuint32_t box[3]     = {static_cast<cuuint32_t>(BK_BYTES / eb), static_cast<cuuint32_t>(BK_BYTES / eb), 1};
+    cuuint32_t estr[3]    = {1, 1, 1};
+    CUresult r            = g_encode_tiled(tm, tm_dtype(dtype), batch >= 1 ? 3 : 2, const_cast<void*>(ptr), dims, strides,
                                 box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if(r != CUDA_SUCCESS)
@@ -196,9 +198,10 @@ bool b_is_mn_major(const ckb_gemm_desc* d) { return d->b_layout == CKB_ROW_MAJOR
 
 // Tensor map of one operand of a GEMM problem, seen as [mn][k]; box_mn = rows of a K-major box.
 int encode_operand(CUtensorMap* tm, int dtype, const void* ptr, int64_t mn, int64_t k, int64_t ld, bool mn_major,
-                   int box_mn)
+                   int box_mn, int64_t batch = 0, int64_t batch_stride = 0)
 {
-    return mn_major ? encode_mnmajor_2d(tm, dtype, ptr, mn, k, ld) : encode_kmajor_2d(tm, dtype, ptr, mn, k, ld, box_mn);
+    return mn_major ? encode_mnmajor_2d(tm, dtype, ptr, mn, k, ld, batch, batch_stride)
+                    : encode_kmajor_2d(tm, dtype, ptr, mn, k, ld, box_mn, batch, batch_stride);
 }
 
 // Narrowest B slice one CTA can load: 64 rows of a K-major tile, one whole swizzle atom (128 bytes of N
@@ -348,9 +351,26 @@ void fill_epilogue(EpilogueArgs& ea, const ckb_gemm_desc* d)
 
 // One launch, or the reference timing protocol (kernel_launch.hpp:12-74): a warm-up launch, then
 // n_rep launches between two events.
-int run_timed(LaunchFn fn, int bn, int cg, const KernelParams& p, int grid, cudaStream_t stream, int n_rep,
+#ifdef CKB_TRACE
+__device__ unsigned long long g_trace[1024 * 16];
+#endif
+
+// Profiling builds (-DCKB_TRACE) hand every launch the role cycle counter array; regular builds pass null.
+unsigned long long* trace_buffer()
+{
+#ifdef CKB_TRACE
+    void* sym = nullptr;
+    return cudaGetSymbolAddress(&sym, g_trace) == cudaSuccess ? static_cast<unsigned long long*>(sym) : nullptr;
+#else
+    return nullptr;
+#endif
+}
+
+int run_timed(LaunchFn fn, int bn, int cg, const KernelParams& p_in, int grid, cudaStream_t stream, int n_rep,
               float* avg_ms)
 {
+    KernelParams p = p_in;
+    p.trace        = trace_buffer();
     if(avg_ms)
         *avg_ms = 0.f;
     if(n_rep <= 0)
@@ -409,6 +429,16 @@ LaunchFn find_launch(int mode, int kind, int epi)
 extern "C" {
 
 int ckb_abi_version(void) { return CKB_ABI_VERSION; }
+
+#ifdef CKB_TRACE
+// Profiling builds only: copies the role cycle counters of the last launch (16 words per CTA) to the host.
+int ckb_trace_read(unsigned long long* host, int words)
+{
+    CKB_CUDA(cudaDeviceSynchronize());
+    CKB_CUDA(cudaMemcpyFromSymbol(host, g_trace, sizeof(unsigned long long) * words));
+    return CKB_OK;
+}
+#endif
 
 const char* ckb_last_error(void) { return t_last_error.c_str(); }
 
@@ -489,11 +519,16 @@ int ckb_device_synchronize(void)
 // ---- GEMM ---------------------------------------------------------------------------------------
 int ckb_gemm_supported(const ckb_gemm_desc* desc) { return check_gemm(desc, false); }
 
-int ckb_gemm_run(const ckb_gemm_desc* d, void* stream, int n_rep, float* avg_ms)
+// Strides between the matrices of a batch (elements); batch = 0 for a plain GEMM.
+struct BatchInfo
 {
-    int rc = check_gemm(d, true);
-    if(rc)
-        return rc;
+    int64_t batch, stride_a, stride_b, stride_e, stride_d[2];
+    bool vec_ok; // every batch of E / D keeps the 16-byte alignment of the first
+};
+
+static int gemm_run_impl(const ckb_gemm_desc* d, const BatchInfo& bi, void* stream, int n_rep, float* avg_ms)
+{
+    int rc = CKB_OK;
     DeviceInfo* dev = nullptr;
     rc              = current_device(&dev);
     if(rc)
@@ -504,39 +539,97 @@ int ckb_gemm_run(const ckb_gemm_desc* d, void* stream, int n_rep, float* avg_ms)
     const int eb     = elem_bytes(d->ab_dtype);
     KernelParams p;
     memset(&p, 0, sizeof(p));
-    rc = encode_operand(&p.tm_a, d->ab_dtype, d->p_a, d->M, d->K, d->lda, a_mn, BM);
+    rc = encode_operand(&p.tm_a, d->ab_dtype, d->p_a, d->M, d->K, d->lda, a_mn, BM, bi.batch, bi.stride_a);
     if(rc)
         return rc;
     fill_epilogue(p.epi, d);
     const int64_t tiles_n = (d->N + bn - 1) / bn;
-    const int cg          = pick_cg(((d->M + BM - 1) / BM) * tiles_n, bn, dev->sm_count);
+    const int64_t nb      = bi.batch > 0 ? bi.batch : 1;
+    const int cg          = pick_cg(((d->M + BM - 1) / BM) * tiles_n * nb, bn, dev->sm_count);
     const int64_t tiles_m = (d->M + BM * cg - 1) / (BM * cg);
-    if(tiles_m * tiles_n > 0x3FFFFFFFll)
+    const int64_t all_tiles = tiles_m * tiles_n * nb;
+    if(all_tiles > 0x3FFFFFFFll)
         return fail(CKB_ERR_UNSUPPORTED, "too many tiles");
-    const WorkPlan plan = plan_work(tiles_m * tiles_n, dev->sm_count / cg, bn, cg, b_min);
-    rc = encode_operand(&p.tm_b, d->ab_dtype, d->p_b, d->N, d->K, d->ldb, b_mn, bn / cg);
+    const WorkPlan plan = plan_work(all_tiles, dev->sm_count / cg, bn, cg, b_min);
+    rc = encode_operand(&p.tm_b, d->ab_dtype, d->p_b, d->N, d->K, d->ldb, b_mn, bn / cg, bi.batch, bi.stride_b);
     if(rc)
         return rc;
-    rc = encode_operand(&p.tm_b_split, d->ab_dtype, d->p_b, d->N, d->K, d->ldb, b_mn, bn / plan.split / cg);
+    rc = encode_operand(&p.tm_b_split, d->ab_dtype, d->p_b, d->N, d->K, d->ldb, b_mn, bn / plan.split / cg, bi.batch,
+                        bi.stride_b);
     if(rc)
         return rc;
+    p.batch_tiles     = bi.batch > 0 ? static_cast<int32_t>(tiles_m * tiles_n) : 0;
+    p.batch_stride_e  = bi.stride_e;
+    p.batch_stride_d0 = bi.stride_d[0];
+    p.batch_stride_d1 = bi.stride_d[1];
     p.mn_major      = (a_mn ? 1 : 0) | (b_mn ? 2 : 0);
     p.split_start   = plan.split_start;
     p.split         = plan.split;
     p.total_work    = plan.total_work;
-    p.total_tiles   = static_cast<int32_t>(tiles_m * tiles_n);
+    p.total_tiles   = static_cast<int32_t>(all_tiles);
     p.M             = static_cast<int32_t>(d->M);
     p.N             = static_cast<int32_t>(d->N);
     p.tiles_n       = static_cast<int32_t>(tiles_n);
     const int bk    = BK_BYTES / eb;
     p.num_kb        = static_cast<int32_t>((d->K + bk - 1) / bk);
-    p.vec_ok        = gemm_vec_ok(d) ? 1 : 0;
+    p.vec_ok        = gemm_vec_ok(d) && bi.vec_ok ? 1 : 0;
     p.wait_limit_ns = wait_limit_ns();
     p.status        = dev->status;
     LaunchFn fn     = find_launch(MODE_GEMM, kind_of(d->ab_dtype), d->epilogue);
     if(!fn)
         return fail(CKB_ERR_UNSUPPORTED, "no kernel instance for epilogue %d", d->epilogue);
     return run_timed(fn, bn, cg, p, plan.grid, static_cast<cudaStream_t>(stream), n_rep, avg_ms);
+}
+
+int ckb_gemm_run(const ckb_gemm_desc* d, void* stream, int n_rep, float* avg_ms)
+{
+    int rc = check_gemm(d, true);
+    if(rc)
+        return rc;
+    BatchInfo bi{0, 0, 0, 0, {0, 0}, true}; // batch 0: 2-D operand maps
+    return gemm_run_impl(d, bi, stream, n_rep, avg_ms);
+}
+
+// ---- batched GEMM -------------------------------------------------------------------------------
+static int check_batched(const ckb_batched_gemm_desc* b, bool need_pointers)
+{
+    if(!b)
+        return fail(CKB_ERR_INVALID, "null descriptor");
+    int rc = check_gemm(&b->gemm, need_pointers);
+    if(rc)
+        return rc;
+    if(b->batch < 1 || b->batch > 0x7FFFFFFFll)
+        return fail(CKB_ERR_UNSUPPORTED, "batch count must be in [1, 2^31)");
+    const int eb = elem_bytes(b->gemm.ab_dtype);
+    if(b->batch > 1)
+    {
+        if(b->batch_stride_a < 1 || b->batch_stride_b < 1 || b->batch_stride_e < 0)
+            return fail(CKB_ERR_INVALID, "batch strides of A and B must be positive");
+        if((b->batch_stride_a * eb) % 16 != 0 || (b->batch_stride_b * eb) % 16 != 0)
+            return fail(CKB_ERR_UNSUPPORTED, "batch strides of A and B must be multiples of 16 bytes (TMA pitch)");
+    }
+    return CKB_OK;
+}
+
+int ckb_batched_gemm_supported(const ckb_batched_gemm_desc* desc) { return check_batched(desc, false); }
+
+int ckb_batched_gemm_run(const ckb_batched_gemm_desc* b, void* stream, int n_rep, float* avg_ms)
+{
+    int rc = check_batched(b, true);
+    if(rc)
+        return rc;
+    const ckb_gemm_desc* d = &b->gemm;
+    if(b->batch == 1)
+        return ckb_gemm_run(d, stream, n_rep, avg_ms);
+    BatchInfo bi{b->batch, b->batch_stride_a, b->batch_stride_b, b->batch_stride_e,
+                 {b->batch_stride_d[0], b->batch_stride_d[1]}, true};
+    // the 128-bit epilogue path needs every batch of E / D to keep the 16-byte alignment of the first
+    const int per16 = 16 / elem_bytes(d->ab_dtype);
+    bool strides_vec_ok = bi.stride_e % per16 == 0;
+    for(int i = 0; i < d->n_ds; ++i)
+        strides_vec_ok = strides_vec_ok && bi.stride_d[i] % per16 == 0;
+    bi.vec_ok = strides_vec_ok;
+    return gemm_run_impl(d, bi, stream, n_rep, avg_ms);
 }
 
 // ---- grouped GEMM -------------------------------------------------------------------------------
@@ -763,6 +856,7 @@ int ckb_grouped_gemm_run_noalloc(const ckb_grouped_gemm_desc* g, void* stream_)
     LaunchFn fn = find_launch(MODE_GROUPED, kind_of(g->groups[0].ab_dtype), g->groups[0].epilogue);
     if(!fn)
         return fail(CKB_ERR_UNSUPPORTED, "no kernel instance for epilogue %d", g->groups[0].epilogue);
+    p.trace = trace_buffer();
     CKB_CUDA(fn(gp.bn, gp.cg, p, gp.plan.grid, stream));
     g_launches.fetch_add(1);
     return CKB_OK;

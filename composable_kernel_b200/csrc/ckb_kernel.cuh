@@ -1,9 +1,10 @@
 // The persistent, warp-specialised tcgen05 contraction kernel.
 //
 // One CTA per SM walks work items  w = blockIdx.x, blockIdx.x + gridDim.x, ...
-//   warp 0     TMA producer : fills a ring of STAGES shared-memory stages (A tile 128 x 128 B,
-//                             B tile <=BN x 128 B, 128-byte swizzle; K-major, or for the other
-//                             GEMM layouts MN-major: boxes of 128 B of M|N positions x the k rows)
+//   warp 0     TMA producer : fills a ring of STAGES shared-memory stages, each KSUB k blocks of an
+//                             A tile (128 x 128 B) and a B tile (<=BN x 128 B), 128-byte swizzle;
+//                             K-major, or for the other GEMM layouts MN-major: boxes of 128 B of
+//                             M|N positions x the k rows.  One lane per box, one warp-wide copy.
 //   warp 1     MMA issuer   : one thread issues tcgen05.mma (128 x width x 16|32) into one of two
 //                             TMEM accumulators (2 x BN columns) and commits to mbarriers
 //   warps 2-9  epilogue     : tcgen05.ld the finished accumulator (two warps per TMEM lane
@@ -43,6 +44,19 @@
 
 #include "ckb_epilogue.cuh"
 #include "ckb_ptx.cuh"
+
+// Cycle counters of the three roles, compiled in only with -DCKB_TRACE (a profiling build): per CTA
+// sixteen 64-bit words in KernelParams::trace
+//   [0] producer: cycles waiting for a free stage     [1] producer: cycles in its loop
+//   [2] MMA: cycles waiting for operand data          [3] MMA: cycles waiting for a free accumulator
+//   [4] MMA: cycles in its loop                       [5] first epilogue warp: cycles waiting for the MMA
+//   [6] first epilogue warp: cycles in its loop       [7] k blocks issued by the MMA role
+//   [8] MMA: cycles issuing tcgen05.mma               [9] MMA: cycles issuing tcgen05.commit
+#ifdef CKB_TRACE
+#define CKB_TR(...) __VA_ARGS__
+#else
+#define CKB_TR(...)
+#endif
 
 namespace ckb {
 
@@ -91,8 +105,8 @@ struct ConvGeom
 
 struct KernelParams
 {
-    CUtensorMap tm_a;       // GEMM: A (K, M).  CONV: im2col map over the NHWC input
-    CUtensorMap tm_b;       // GEMM: B^T (K, N). CONV: weights as (C, Y*X, K); box of BN rows
+    CUtensorMap tm_a;       // GEMM: A (K, M[, batch]).  CONV: im2col map over the NHWC input
+    CUtensorMap tm_b;       // GEMM: B^T (K, N[, batch]). CONV: weights as (C, Y*X, K); box of BN rows
     CUtensorMap tm_b_split; // same tensor, box of BN/split rows
     EpilogueArgs epi;       // GROUPED: e/d/ld fields come from the group entry instead
     const GroupEntry* groups;
@@ -106,16 +120,23 @@ struct KernelParams
     int32_t num_kb;      // k blocks per tile (GEMM / CONV)
     int32_t vec_ok;      // 128-bit epilogue access allowed
     int32_t mn_major;    // bit 0: A is M-contiguous (column-major A); bit 1: B is N-contiguous (row-major B)
+    int32_t batch_tiles; // batched GEMM: tiles per batch (0 = not batched)
+    int32_t pad_;
+    int64_t batch_stride_e, batch_stride_d0, batch_stride_d1; // elements between batches of E / D0 / D1
     ConvGeom conv;
     uint64_t wait_limit_ns;
     uint32_t* status; // device status word
+    unsigned long long* trace; // role cycle counters (profiling builds only, else null)
 };
 
-template <int BN, int STAGES, int CG>
+// One stage holds KSUB consecutive k blocks (each 128 bytes of K): A block 0 .. KSUB-1, then B block 0 .. KSUB-1.
+template <int BN, int STAGES, int CG, int KSUB>
 struct SmemLayout
 {
-    static constexpr int A_BYTES     = BM * BK_BYTES;
-    static constexpr int B_BYTES     = (BN / CG) * BK_BYTES; // a CTA of a pair holds half the B rows
+    static constexpr int A_SUB_BYTES = BM * BK_BYTES;
+    static constexpr int B_SUB_BYTES = (BN / CG) * BK_BYTES; // a CTA of a pair holds half the B rows
+    static constexpr int A_BYTES     = KSUB * A_SUB_BYTES;
+    static constexpr int B_BYTES     = KSUB * B_SUB_BYTES;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int BAR_OFFSET  = STAGES * STAGE_BYTES;
     // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], drain
@@ -181,6 +202,7 @@ struct WorkItem
     int width;   // columns of this item (BN, or BN/split for a tail slice)
     int num_kb;
     const GroupEntry* group; // MODE_GROUPED only
+    int batch;               // MODE_GEMM: batch index (0 unless batched)
     bool is_slice;
 };
 
@@ -191,6 +213,7 @@ __device__ __forceinline__ WorkItem decode_work(const KernelParams& P, int w)
     int tile, slice = 0;
     wi.width    = BN;
     wi.is_slice = false;
+    wi.batch    = 0;
     if(w < P.split_start)
         tile = w;
     else
@@ -213,6 +236,11 @@ __device__ __forceinline__ WorkItem decode_work(const KernelParams& P, int w)
     }
     else
     {
+        if(MODE == MODE_GEMM && P.batch_tiles > 0) // batched GEMM: batch-major tile order
+        {
+            wi.batch = tile / P.batch_tiles;
+            tile -= wi.batch * P.batch_tiles;
+        }
         wi.m_blk  = tile / P.tiles_n;
         n_blk     = tile % P.tiles_n;
         wi.num_kb = P.num_kb;
@@ -220,6 +248,28 @@ __device__ __forceinline__ WorkItem decode_work(const KernelParams& P, int w)
     }
     wi.n_start = n_blk * BN + slice * wi.width;
     return wi;
+}
+
+// One TMA box of a GEMM operand.  The operand maps of a batched GEMM are 3-D (the third coordinate is the
+// batch index); those of a plain GEMM and the per-group maps of MODE_GROUPED are 2-D.
+template <int MODE, int CG>
+__device__ __forceinline__ void load_matrix_box(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int c0, int c1,
+                                                bool batched, int batch)
+{
+    if(MODE == MODE_GEMM && batched)
+    {
+        if constexpr(CG == 2)
+            tma_load_3d_pair(dst, tm, bar, c0, c1, batch);
+        else
+            tma_load_3d(dst, tm, bar, c0, c1, batch);
+    }
+    else
+    {
+        if constexpr(CG == 2)
+            tma_load_2d_pair(dst, tm, bar, c0, c1);
+        else
+            tma_load_2d(dst, tm, bar, c0, c1);
+    }
 }
 
 // Epilogue of one warp: rows = its TMEM lane quarter, columns [n_begin, n_end) of row m.
@@ -268,10 +318,10 @@ __device__ __forceinline__ void epilogue_span(uint32_t tmem_addr, const Epilogue
 
 // EPI (the fused epilogue functor) is a template parameter: one functor per kernel keeps the
 // epilogue warps inside the 168-register budget that ten warps per SM leave.
-template <int MODE, int KIND, int EPI, int BN, int STAGES, int CG>
+template <int MODE, int KIND, int EPI, int BN, int STAGES, int CG, int KSUB>
 __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __grid_constant__ KernelParams P)
 {
-    using L = SmemLayout<BN, STAGES, CG>;
+    using L = SmemLayout<BN, STAGES, CG, KSUB>;
     constexpr int TILE_M = BM * CG;
     constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
     constexpr int UMMA_K_BYTES   = 32; // 16 x 16-bit or 32 x 8-bit
@@ -284,6 +334,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
     constexpr int ATOM_BYTES     = BK_ELEMS * BK_BYTES;
     const bool a_mn              = MODE != MODE_CONV && (P.mn_major & 1) != 0;
     const bool b_mn              = MODE != MODE_CONV && (P.mn_major & 2) != 0;
+    const bool batched           = MODE == MODE_GEMM && P.batch_tiles > 0;
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr  = smem_u32(smem_raw);
@@ -350,135 +401,157 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
     if(warp == 0)
     {
         // ------------------------------------------------------------------ TMA producer
-        if(lane == 0)
+        // One lane per TMA box of a stage: the lanes compute their destinations and coordinates side by
+        // side and the whole stage is issued by one warp-wide copy instruction (two for the convolution,
+        // whose A box is an im2col copy), instead of one thread issuing the boxes one after the other.
+        //   K-major GEMM operand : 1 box per k block              MN-major: one box per 128 bytes of M|N
+        //   lanes [0, n_a) load A boxes, lanes [n_a, n_a + n_b) load B boxes, k block j = box / boxes per block
+        if constexpr(MODE != MODE_GROUPED)
         {
-            if constexpr(MODE != MODE_GROUPED)
+            if(lane == 0)
             {
                 tma_prefetch_desc(&P.tm_a);
                 tma_prefetch_desc(&P.tm_b);
             }
-            int stage           = 0;
-            uint32_t phase      = 0;
-            uint32_t issued     = 0; // bit s: a load was issued into stage s
-            uint32_t last_phase = 0; // bit s: phase of the last load issued into stage s
-            bool ok             = true;
-            for(int w = unit; ok && w < P.total_work; w += num_units)
+        }
+        int stage      = 0;
+        uint32_t phase = 0;
+        int loads      = 0; // stages filled so far
+        bool ok        = true;
+        // all bytes of a stage are counted on the leader's barrier
+        const uint32_t bar0 = (CG == 2) ? mapa_shared(full_bar(0), 0) : full_bar(0);
+        const int a_per_kb  = a_mn ? BM / BK_ELEMS : 1; // A boxes per k block
+        CKB_TR(long long tr_wait = 0; const long long tr_start = clock64();)
+        for(int w = unit; ok && w < P.total_work; w += num_units)
+        {
+            const WorkItem wi       = decode_work<MODE, BN>(P, w);
+            const CUtensorMap* tm_a = &P.tm_a;
+            const CUtensorMap* tm_b = wi.is_slice ? &P.tm_b_split : &P.tm_b;
+            if constexpr(MODE == MODE_GROUPED)
             {
-                const WorkItem wi       = decode_work<MODE, BN>(P, w);
-                const CUtensorMap* tm_a = &P.tm_a;
-                const CUtensorMap* tm_b = wi.is_slice ? &P.tm_b_split : &P.tm_b;
-                if constexpr(MODE == MODE_GROUPED)
+                tm_a = &wi.group->tm_a;
+                tm_b = wi.is_slice ? &wi.group->tm_b_split : &wi.group->tm_b;
+            }
+            // bytes of one k block over the whole CTA group (posted on the leader's barrier)
+            const uint32_t sub_bytes = CG * L::A_SUB_BYTES + wi.width * BK_BYTES;
+            const int b_rows         = wi.width / CG;                      // B rows this CTA loads
+            const int a_row0         = wi.m_blk * TILE_M + cta_rank * BM; // first A row of this CTA
+            const int b_row0         = wi.n_start + cta_rank * b_rows;
+            // this lane's box: operand, k block of the stage, offset inside the stage, MN coordinate
+            const int b_per_kb = b_mn ? b_rows / BK_ELEMS : 1;
+            const int n_a      = a_per_kb * KSUB;
+            const bool is_b    = lane >= n_a;
+            const int box      = is_b ? lane - n_a : lane;
+            const int per_kb   = is_b ? b_per_kb : a_per_kb;
+            const int box_j    = box / per_kb; // k block inside the stage
+            const int box_i    = box - box_j * per_kb;
+            const bool lane_on = lane < n_a + b_per_kb * KSUB;
+            const bool box_mn  = is_b ? b_mn : a_mn;
+            const uint32_t box_off =
+                (is_b ? L::A_BYTES + box_j * L::B_SUB_BYTES : box_j * L::A_SUB_BYTES) + box_i * ATOM_BYTES;
+            const int box_row         = (is_b ? b_row0 : a_row0) + box_i * BK_ELEMS;
+            const CUtensorMap* box_tm = is_b ? tm_b : tm_a;
+            // CONV: first output pixel of this CTA's rows in (n, ho, wo)
+            int cv_n = 0, cv_h = 0, cv_w = 0;
+            if constexpr(MODE == MODE_CONV)
+            {
+                const int m0  = a_row0;
+                cv_n          = m0 / P.conv.HoWo;
+                const int rem = m0 - cv_n * P.conv.HoWo;
+                const int ho  = rem / P.conv.Wo;
+                const int wo  = rem - ho * P.conv.Wo;
+                cv_h          = ho * P.conv.stride_h - P.conv.pad_h;
+                cv_w          = wo * P.conv.stride_w - P.conv.pad_w;
+            }
+            // CONV: filter tap and channel block of this lane's k block (advanced by KSUB per stage)
+            int cv_y = 0, cv_x = 0, cv_cb = 0;
+            if constexpr(MODE == MODE_CONV)
+            {
+                const int taps = box_j / P.conv.c_blocks;
+                cv_cb          = box_j - taps * P.conv.c_blocks;
+                cv_y           = taps / P.conv.X;
+                cv_x           = taps - cv_y * P.conv.X;
+            }
+            for(int kb = 0; kb < wi.num_kb; kb += KSUB)
+            {
+                CKB_TR(const long long tr0 = clock64();)
+                ok = bounded_wait(empty_bar(stage), phase ^ 1u, wc, WAIT_EMPTY);
+                ok = __all_sync(0xffffffffu, ok);
+                CKB_TR(tr_wait += clock64() - tr0;)
+                if(!ok)
+                    break;
+                const int nsub      = (wi.num_kb - kb < KSUB) ? wi.num_kb - kb : KSUB;
+                const uint32_t dst  = base_addr + stage * L::STAGE_BYTES + box_off;
+                const uint32_t bar  = bar0 + 8u * stage;
+                if(is_leader && lane == 0)
+                    mbar_arrive_expect_tx(full_bar(stage), sub_bytes * nsub);
+                if(lane_on && box_j < nsub)
                 {
-                    tm_a = &wi.group->tm_a;
-                    tm_b = wi.is_slice ? &wi.group->tm_b_split : &wi.group->tm_b;
-                }
-                // bytes of one stage over the whole CTA group (posted on the leader's barrier)
-                const uint32_t tx_bytes = CG * L::A_BYTES + wi.width * BK_BYTES;
-                const int b_rows        = wi.width / CG;                       // B rows this CTA loads
-                const int a_row0        = wi.m_blk * TILE_M + cta_rank * BM;  // first A row of this CTA
-                const int b_row0        = wi.n_start + cta_rank * b_rows;
-                // CONV: first output pixel of this CTA's rows in (n, ho, wo)
-                int cv_n = 0, cv_h = 0, cv_w = 0;
-                if constexpr(MODE == MODE_CONV)
-                {
-                    const int m0  = a_row0;
-                    cv_n          = m0 / P.conv.HoWo;
-                    const int rem = m0 - cv_n * P.conv.HoWo;
-                    const int ho  = rem / P.conv.Wo;
-                    const int wo  = rem - ho * P.conv.Wo;
-                    cv_h          = ho * P.conv.stride_h - P.conv.pad_h;
-                    cv_w          = wo * P.conv.stride_w - P.conv.pad_w;
-                }
-                int cv_y = 0, cv_x = 0, cv_cb = 0;
-                for(int kb = 0; kb < wi.num_kb; ++kb)
-                {
-                    ok = bounded_wait(empty_bar(stage), phase ^ 1u, wc, WAIT_EMPTY);
-                    if(!ok)
-                        break;
-                    const uint32_t a_dst = base_addr + stage * L::STAGE_BYTES;
-                    const uint32_t b_dst = a_dst + L::A_BYTES;
-                    if(is_leader)
-                        mbar_arrive_expect_tx(full_bar(stage), tx_bytes);
-                    if constexpr(CG == 2)
+                    if constexpr(MODE == MODE_CONV)
                     {
-                        const uint32_t bar = mapa_shared(full_bar(stage), 0); // the leader's barrier
-                        if constexpr(MODE == MODE_CONV)
+                        if(!is_b)
                         {
-                            tma_load_im2col_4d_pair(a_dst, tm_a, bar, cv_cb * BK_ELEMS, cv_w, cv_h, cv_n,
-                                                    static_cast<uint16_t>(cv_x * P.conv.dil_w),
-                                                    static_cast<uint16_t>(cv_y * P.conv.dil_h));
-                            tma_load_3d_pair(b_dst, tm_b, bar, cv_cb * BK_ELEMS, cv_y * P.conv.X + cv_x,
-                                             b_row0);
+                            if constexpr(CG == 2)
+                                tma_load_im2col_4d_pair(dst, box_tm, bar, cv_cb * BK_ELEMS, cv_w, cv_h, cv_n,
+                                                        static_cast<uint16_t>(cv_x * P.conv.dil_w),
+                                                        static_cast<uint16_t>(cv_y * P.conv.dil_h));
+                            else
+                                tma_load_im2col_4d(dst, box_tm, bar, cv_cb * BK_ELEMS, cv_w, cv_h, cv_n,
+                                                   static_cast<uint16_t>(cv_x * P.conv.dil_w),
+                                                   static_cast<uint16_t>(cv_y * P.conv.dil_h));
                         }
                         else
                         {
-                            if(a_mn)
-                                for(int j = 0; j < BM / BK_ELEMS; ++j)
-                                    tma_load_2d_pair(a_dst + j * ATOM_BYTES, tm_a, bar, a_row0 + j * BK_ELEMS,
-                                                     kb * BK_ELEMS);
+                            if constexpr(CG == 2)
+                                tma_load_3d_pair(dst, box_tm, bar, cv_cb * BK_ELEMS, cv_y * P.conv.X + cv_x, b_row0);
                             else
-                                tma_load_2d_pair(a_dst, tm_a, bar, kb * BK_ELEMS, a_row0);
-                            if(b_mn)
-                                for(int j = 0; j * BK_ELEMS < b_rows; ++j)
-                                    tma_load_2d_pair(b_dst + j * ATOM_BYTES, tm_b, bar, b_row0 + j * BK_ELEMS,
-                                                     kb * BK_ELEMS);
-                            else
-                                tma_load_2d_pair(b_dst, tm_b, bar, kb * BK_ELEMS, b_row0);
+                                tma_load_3d(dst, box_tm, bar, cv_cb * BK_ELEMS, cv_y * P.conv.X + cv_x, wi.n_start);
                         }
-                    }
-                    else if constexpr(MODE == MODE_CONV)
-                    {
-                        tma_load_im2col_4d(a_dst, tm_a, full_bar(stage), cv_cb * BK_ELEMS, cv_w, cv_h,
-                                           cv_n, static_cast<uint16_t>(cv_x * P.conv.dil_w),
-                                           static_cast<uint16_t>(cv_y * P.conv.dil_h));
-                        tma_load_3d(b_dst, tm_b, full_bar(stage), cv_cb * BK_ELEMS,
-                                    cv_y * P.conv.X + cv_x, wi.n_start);
                     }
                     else
                     {
-                        if(a_mn)
-                            for(int j = 0; j < BM / BK_ELEMS; ++j)
-                                tma_load_2d(a_dst + j * ATOM_BYTES, tm_a, full_bar(stage), a_row0 + j * BK_ELEMS,
-                                            kb * BK_ELEMS);
-                        else
-                            tma_load_2d(a_dst, tm_a, full_bar(stage), kb * BK_ELEMS, a_row0);
-                        if(b_mn)
-                            for(int j = 0; j * BK_ELEMS < b_rows; ++j)
-                                tma_load_2d(b_dst + j * ATOM_BYTES, tm_b, full_bar(stage), b_row0 + j * BK_ELEMS,
-                                            kb * BK_ELEMS);
-                        else
-                            tma_load_2d(b_dst, tm_b, full_bar(stage), kb * BK_ELEMS, b_row0);
+                        const int k0 = (kb + box_j) * BK_ELEMS;
+                        load_matrix_box<MODE, CG>(dst, box_tm, bar, box_mn ? box_row : k0, box_mn ? k0 : box_row,
+                                                  batched, wi.batch);
                     }
-                    if constexpr(MODE == MODE_CONV)
+                }
+                if constexpr(MODE == MODE_CONV)
+                {
+                    // advance this lane's (tap, channel block) by KSUB k blocks
+                    cv_cb += KSUB;
+                    while(cv_cb >= P.conv.c_blocks)
                     {
-                        if(++cv_cb == P.conv.c_blocks)
+                        cv_cb -= P.conv.c_blocks;
+                        if(++cv_x == P.conv.X)
                         {
-                            cv_cb = 0;
-                            if(++cv_x == P.conv.X)
-                            {
-                                cv_x = 0;
-                                ++cv_y;
-                            }
+                            cv_x = 0;
+                            ++cv_y;
                         }
                     }
-                    issued |= 1u << stage;
-                    last_phase = (last_phase & ~(1u << stage)) | (phase << stage);
-                    if(++stage == STAGES)
-                    {
-                        stage = 0;
-                        phase ^= 1u;
-                    }
+                }
+                ++loads;
+                if(++stage == STAGES)
+                {
+                    stage = 0;
+                    phase ^= 1u;
                 }
             }
-            // Do not leave while a bulk copy may still write shared memory.  The leader's barriers
-            // count the bytes of both CTAs, and the pair leaves together (cluster sync at the exit).
-            for(int s = 0; s < STAGES; ++s)
-                if(is_leader && (issued & (1u << s)))
-                {
-                    WaitCtx drain{&misc[2], P.wait_limit_ns, P.status}; // misc[2] stays 0: wait regardless of abort
-                    bounded_wait(full_bar(s), (last_phase >> s) & 1u, drain, WAIT_DRAIN);
-                }
         }
+        CKB_TR(if(P.trace && lane == 0) {
+            P.trace[blockIdx.x * 16 + 0] = tr_wait;
+            P.trace[blockIdx.x * 16 + 1] = clock64() - tr_start;
+        })
+        // Do not leave while a bulk copy may still write shared memory: wait for the last fill of every
+        // stage used.  The leader's barriers count the bytes of both CTAs, and the pair leaves together
+        // (cluster sync at the exit).  Fill number f (0-based) goes to stage f % STAGES with phase
+        // (f / STAGES) & 1.
+        if(is_leader && lane == 0)
+            for(int s = 0; s < STAGES && s < loads; ++s)
+            {
+                const int last_fill = ((loads - 1 - s) / STAGES) * STAGES + s;
+                WaitCtx drain{&misc[2], P.wait_limit_ns, P.status}; // misc[2] stays 0: wait regardless of abort
+                bounded_wait(full_bar(s), static_cast<uint32_t>(last_fill / STAGES) & 1u, drain, WAIT_DRAIN);
+            }
     }
     else if(warp == 1)
     {
@@ -490,59 +563,83 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
             int iter        = 0;
             bool ok         = true;
             bool issued_any = false;
+            // Shared-memory descriptors: the high word (swizzle mode, stride / leading offsets) is constant, the
+            // low word is the start address >> 4 and is stepped by a register per operand:
+            //   K-major : 32 bytes along the 128-byte row per UMMA K step
+            //   MN-major: (BK_ELEMS / K_STEPS) rows of 128 bytes per UMMA K step
+            // and by `*_jump` from the last K step of one k block to the first of the next block of the stage.
+            const uint64_t a_const = (a_mn ? make_smem_desc_mn_sw128(0, ATOM_BYTES) : make_smem_desc_k_sw128(0));
+            const uint64_t b_const = (b_mn ? make_smem_desc_mn_sw128(0, ATOM_BYTES) : make_smem_desc_k_sw128(0));
+            const uint32_t a_hi = static_cast<uint32_t>(a_const >> 32), b_hi = static_cast<uint32_t>(b_const >> 32);
+            const uint32_t a_lo_const = static_cast<uint32_t>(a_const), b_lo_const = static_cast<uint32_t>(b_const);
+            const uint32_t a_kstep = a_mn ? ((BK_ELEMS / K_STEPS) * BK_BYTES) >> 4 : UMMA_K_BYTES >> 4;
+            const uint32_t b_kstep = b_mn ? ((BK_ELEMS / K_STEPS) * BK_BYTES) >> 4 : UMMA_K_BYTES >> 4;
+            const uint32_t a_jump  = (L::A_SUB_BYTES >> 4) - (K_STEPS - 1) * a_kstep;
+            const uint32_t b_jump  = (L::B_SUB_BYTES >> 4) - (K_STEPS - 1) * b_kstep;
+            const uint32_t idesc_major = (a_mn ? 1u << 15 : 0u) | (b_mn ? 1u << 16 : 0u);
+            CKB_TR(long long tr_full = 0, tr_acc = 0, tr_kb = 0, tr_issue = 0, tr_commit = 0;
+                   const long long tr_start = clock64();)
             for(int w = unit; ok && w < P.total_work; w += num_units, ++iter)
             {
                 const WorkItem wi        = decode_work<MODE, BN>(P, w);
-                const uint32_t idesc     = make_idesc(C_FMT, AB_FMT, TILE_M, static_cast<uint32_t>(wi.width),
-                                                      a_mn ? 1u : 0u, b_mn ? 1u : 0u);
+                const uint32_t idesc     = make_idesc(C_FMT, AB_FMT, TILE_M, static_cast<uint32_t>(wi.width)) | idesc_major;
                 const int acc            = iter & 1;
                 const uint32_t acc_phase = (iter >> 1) & 1;
+                CKB_TR(const long long tr1 = clock64();)
                 ok = bounded_wait(tmem_empty_bar(acc), acc_phase ^ 1u, wc, WAIT_TMEM_EMPTY);
+                CKB_TR(tr_acc += clock64() - tr1;)
                 if(!ok)
                     break;
                 tc_fence_after_sync();
                 const uint32_t tmem_d = tmem_base + acc * BN;
-                for(int kb = 0; kb < wi.num_kb; ++kb)
+                uint32_t accumulate   = 0; // the first MMA of the item overwrites the accumulator
+                for(int kb = 0; kb < wi.num_kb; kb += KSUB)
                 {
+                    CKB_TR(const long long tr0 = clock64();)
                     ok = bounded_wait(full_bar(stage), phase, wc, WAIT_FULL);
+                    CKB_TR(tr_full += clock64() - tr0; ++tr_kb;)
                     if(!ok)
                         break;
-                    tc_fence_after_sync();
+                    const int nsub        = (wi.num_kb - kb < KSUB) ? wi.num_kb - kb : KSUB;
                     const uint32_t a_addr = base_addr + stage * L::STAGE_BYTES;
-                    const uint64_t a_desc = a_mn ? make_smem_desc_mn_sw128(a_addr, ATOM_BYTES)
-                                                 : make_smem_desc_k_sw128(a_addr);
-                    const uint64_t b_desc = b_mn ? make_smem_desc_mn_sw128(a_addr + L::A_BYTES, ATOM_BYTES)
-                                                 : make_smem_desc_k_sw128(a_addr + L::A_BYTES);
+                    uint32_t a_lo         = a_lo_const | ((a_addr & 0x3FFFFu) >> 4);
+                    uint32_t b_lo         = b_lo_const | (((a_addr + L::A_BYTES) & 0x3FFFFu) >> 4);
+                    CKB_TR(const long long tr2 = clock64();)
 #pragma unroll
-                    for(int k = 0; k < K_STEPS; ++k)
+                    for(int j = 0; j < KSUB; ++j)
                     {
-                        // one UMMA K step: 32 bytes along a K-major row, or (BK_ELEMS / K_STEPS) rows of
-                        // 128 bytes in an MN-major tile
-                        const uint64_t koff_k  = static_cast<uint64_t>((k * UMMA_K_BYTES) >> 4);
-                        const uint64_t koff_mn = static_cast<uint64_t>((k * (BK_ELEMS / K_STEPS) * BK_BYTES) >> 4);
-                        const uint64_t koff_a  = a_mn ? koff_mn : koff_k;
-                        const uint64_t koff_b  = b_mn ? koff_mn : koff_k;
-                        if constexpr(CG == 2)
+                        if(KSUB > 1 && j >= nsub)
+                            break;
+#pragma unroll
+                        for(int k = 0; k < K_STEPS; ++k)
                         {
-                            if constexpr(KIND == KIND_I8)
-                                mma_i8_ss_pair(tmem_d, a_desc + koff_a, b_desc + koff_b, idesc, (kb | k) != 0);
+                            if constexpr(CG == 2)
+                            {
+                                if constexpr(KIND == KIND_I8)
+                                    mma_i8_ss_pair_split(tmem_d, a_lo, a_hi, b_lo, b_hi, idesc, accumulate);
+                                else
+                                    mma_f16_ss_pair_split(tmem_d, a_lo, a_hi, b_lo, b_hi, idesc, accumulate);
+                            }
                             else
-                                mma_f16_ss_pair(tmem_d, a_desc + koff_a, b_desc + koff_b, idesc, (kb | k) != 0);
-                        }
-                        else
-                        {
-                            if constexpr(KIND == KIND_I8)
-                                mma_i8_ss(tmem_d, a_desc + koff_a, b_desc + koff_b, idesc, (kb | k) != 0);
-                            else
-                                mma_f16_ss(tmem_d, a_desc + koff_a, b_desc + koff_b, idesc, (kb | k) != 0);
+                            {
+                                if constexpr(KIND == KIND_I8)
+                                    mma_i8_ss_split(tmem_d, a_lo, a_hi, b_lo, b_hi, idesc, accumulate);
+                                else
+                                    mma_f16_ss_split(tmem_d, a_lo, a_hi, b_lo, b_hi, idesc, accumulate);
+                            }
+                            accumulate = 1;
+                            a_lo += (k == K_STEPS - 1) ? a_jump : a_kstep;
+                            b_lo += (k == K_STEPS - 1) ? b_jump : b_kstep;
                         }
                     }
                     issued_any = true;
+                    CKB_TR(const long long tr3 = clock64(); tr_issue += tr3 - tr2;)
                     // the stage is free (in both CTAs) once these MMAs have read it
                     if constexpr(CG == 2)
                         mma_commit_pair_mc(empty_bar(stage), 3);
                     else
                         mma_commit(empty_bar(stage));
+                    CKB_TR(tr_commit += clock64() - tr3;)
                     if(++stage == STAGES)
                     {
                         stage = 0;
@@ -557,6 +654,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                         mma_commit(tmem_full_bar(acc));
                 }
             }
+            CKB_TR(if(P.trace) {
+                P.trace[blockIdx.x * 16 + 2] = tr_full;
+                P.trace[blockIdx.x * 16 + 3] = tr_acc;
+                P.trace[blockIdx.x * 16 + 4] = clock64() - tr_start;
+                P.trace[blockIdx.x * 16 + 7] = tr_kb;
+                P.trace[blockIdx.x * 16 + 8] = tr_issue;
+                P.trace[blockIdx.x * 16 + 9] = tr_commit;
+            })
             // Every MMA issued must be finished before the tensor memory is freed.
             if(issued_any)
             {
@@ -576,6 +681,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
         const int half    = (warp - 2) >> 2; // which half of the item's columns
         int iter          = 0;
         bool ok           = true;
+        CKB_TR(long long tr_wait = 0; const long long tr_start = clock64();)
         for(int w = unit; ok && w < P.total_work; w += num_units, ++iter)
         {
             const WorkItem wi = decode_work<MODE, BN>(P, w);
@@ -595,6 +701,18 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                 ea.ldd0             = G->ldd0;
                 ea.ldd1             = G->ldd1;
             }
+            if constexpr(MODE == MODE_GEMM)
+            {
+                if(wi.batch != 0)
+                {
+                    constexpr int EB = (KIND == KIND_I8) ? 1 : 2;
+                    ea.e = static_cast<char*>(ea.e) + wi.batch * P.batch_stride_e * EB;
+                    if(ea.d0)
+                        ea.d0 = static_cast<const char*>(ea.d0) + wi.batch * P.batch_stride_d0 * EB;
+                    if(ea.d1)
+                        ea.d1 = static_cast<const char*>(ea.d1) + wi.batch * P.batch_stride_d1 * EB;
+                }
+            }
             const int span          = wi.width >> 1; // columns per epilogue warp (>= 32)
             const int64_t m =
                 static_cast<int64_t>(wi.m_blk) * TILE_M + cta_rank * BM + quarter * 32 + lane;
@@ -605,7 +723,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
 
             const int acc            = iter & 1;
             const uint32_t acc_phase = (iter >> 1) & 1;
+            CKB_TR(const long long tr0 = clock64();)
             ok = bounded_wait(tmem_full_bar(acc), acc_phase, wc, WAIT_TMEM_FULL);
+            CKB_TR(tr_wait += clock64() - tr0;)
             ok = __all_sync(0xffffffffu, ok);
             if(!ok)
                 break;
@@ -642,6 +762,16 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                         Mn      = nx.group->M;
                         Nn      = nx.group->N;
                     }
+                    if constexpr(MODE == MODE_GEMM)
+                    {
+                        if(nx.batch != 0)
+                        {
+                            if(en.d0)
+                                en.d0 = static_cast<const char*>(en.d0) + nx.batch * P.batch_stride_d0 * 2;
+                            if(en.d1)
+                                en.d1 = static_cast<const char*>(en.d1) + nx.batch * P.batch_stride_d1 * 2;
+                        }
+                    }
                     const int spn    = nx.width >> 1;
                     const int64_t mn =
                         static_cast<int64_t>(nx.m_blk) * TILE_M + cta_rank * BM + quarter * 32 + lane;
@@ -654,6 +784,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                 }
             }
         }
+        CKB_TR(if(P.trace && warp == 2 && lane == 0) {
+            P.trace[blockIdx.x * 16 + 5] = tr_wait;
+            P.trace[blockIdx.x * 16 + 6] = clock64() - tr_start;
+        })
     }
 
     // ---------------------------------------------------------------------- common exit

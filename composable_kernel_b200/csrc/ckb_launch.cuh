@@ -5,42 +5,36 @@
 
 namespace ckb {
 
-// Tile widths the library instantiates and the pipeline depth that fills shared memory.
-//   one CTA per tile : BN 256 -> 4 stages x 48 KiB, BN 128 -> 6 x 32 KiB, BN 64 -> 8 x 24 KiB
-//   CTA pair per tile: BN 256 -> 6 stages x 32 KiB per CTA (256 x 256 tile per pair)
-template <int BN, int CG>
-struct StagesFor;
-template <>
-struct StagesFor<256, 1>
+// Tile widths the library instantiates, the k blocks (128 bytes of K each) one pipeline stage holds and the
+// pipeline depth that fills shared memory.  Two k blocks per stage halve the per-block work of the single
+// threads that issue the copies and the MMAs (barrier wait, commit, bookkeeping), which is what limits the
+// main loop once the tiles are large.
+//   one CTA per tile : BN 256 -> 4 stages x 1 x 48 KiB, BN 128 -> 3 x 2 x 32 KiB, BN 64 -> 4 x 2 x 24 KiB
+//   CTA pair per tile: BN 256 -> 3 stages x 2 x 32 KiB per CTA (256 x 256 tile per pair)
+// The implicit-GEMM convolution keeps one k block per stage (measured faster: its k loop is short and its
+// im2col copies are the slower part).
+template <int BN, int CG, int MODE>
+struct StagesFor
 {
-    static constexpr int value = 4;
-};
-template <>
-struct StagesFor<128, 1>
-{
-    static constexpr int value = 6;
-};
-template <>
-struct StagesFor<64, 1>
-{
-    static constexpr int value = 8;
-};
-template <>
-struct StagesFor<256, 2>
-{
-#ifdef CKB_PAIR_STAGES
-    static constexpr int value = CKB_PAIR_STAGES; // build-time override for pipeline-depth experiments (at most 7 fit)
+    static constexpr bool conv = MODE == MODE_CONV;
+#if defined(CKB_PAIR_STAGES) && defined(CKB_PAIR_KSUB)
+    // build-time override for pipeline experiments (stages x ksub x 32 KiB must stay below 224 KiB)
+    static constexpr int pair_ksub = conv ? 1 : CKB_PAIR_KSUB, pair_stages = conv ? 6 : CKB_PAIR_STAGES;
 #else
-    static constexpr int value = 6;
+    static constexpr int pair_ksub = conv ? 1 : 2, pair_stages = conv ? 6 : 3;
 #endif
+    static constexpr int ksub  = CG == 2 ? pair_ksub : (BN == 256 || conv) ? 1 : 2;
+    static constexpr int value = CG == 2 ? pair_stages : BN == 256 ? 4 : BN == 128 ? (conv ? 6 : 3) : (conv ? 8 : 4);
 };
 
 template <int MODE, int KIND, int EPI, int BN, int CG>
 cudaError_t launch_one(const KernelParams& p, int grid, cudaStream_t stream)
 {
-    constexpr int STAGES = StagesFor<BN, CG>::value;
-    constexpr int SMEM   = SmemLayout<BN, STAGES, CG>::DYN_BYTES;
-    auto kern            = contraction_kernel<MODE, KIND, EPI, BN, STAGES, CG>;
+    constexpr int STAGES = StagesFor<BN, CG, MODE>::value;
+    constexpr int KSUB   = StagesFor<BN, CG, MODE>::ksub;
+    constexpr int SMEM   = SmemLayout<BN, STAGES, CG, KSUB>::DYN_BYTES;
+    static_assert(SMEM <= 227 * 1024, "pipeline does not fit in shared memory");
+    auto kern            = contraction_kernel<MODE, KIND, EPI, BN, STAGES, CG, KSUB>;
     static bool attr_done[64] = {};
     int dev                   = 0;
     cudaError_t err           = cudaGetDevice(&dev);

@@ -265,6 +265,29 @@ __device__ __forceinline__ void mma_i8_ss_pair(uint32_t tmem_d, uint64_t adesc, 
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+
+// The same four instructions with each 64-bit shared-memory descriptor given as its two 32-bit halves.
+// Only the low half (start address) changes from one MMA to the next, so the issuing thread steps a
+// 32-bit register per operand and the high half stays in a register for the whole kernel.
+#define CKB_MMA_SPLIT(NAME, INSTR)                                                                              \
+    __device__ __forceinline__ void NAME(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,           \
+                                         uint32_t b_hi, uint32_t idesc, uint32_t accumulate)                     \
+    {                                                                                                            \
+        asm volatile("{\n"                                                                                       \
+                     ".reg .pred p;\n"                                                                           \
+                     ".reg .b64 da, db;\n"                                                                       \
+                     "mov.b64 da, {%1, %2};\n"                                                                   \
+                     "mov.b64 db, {%3, %4};\n"                                                                   \
+                     "setp.ne.b32 p, %6, 0;\n" INSTR " [%0], da, db, %5, p;\n"                                   \
+                     "}\n" ::"r"(tmem_d),                                                                        \
+                     "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)                     \
+                     : "memory");                                                                                \
+    }
+CKB_MMA_SPLIT(mma_f16_ss_split, "tcgen05.mma.cta_group::1.kind::f16")
+CKB_MMA_SPLIT(mma_i8_ss_split, "tcgen05.mma.cta_group::1.kind::i8")
+CKB_MMA_SPLIT(mma_f16_ss_pair_split, "tcgen05.mma.cta_group::2.kind::f16")
+CKB_MMA_SPLIT(mma_i8_ss_pair_split, "tcgen05.mma.cta_group::2.kind::i8")
+#undef CKB_MMA_SPLIT
 // One arrival on the barrier at offset `bar` in EACH CTA of `cta_mask` once the pair's MMAs issued
 // so far are done (only the barrier arrival fans out; no data does).
 __device__ __forceinline__ void mma_commit_pair_mc(uint32_t bar, uint16_t cta_mask)

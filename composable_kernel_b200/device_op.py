@@ -185,7 +185,7 @@ class DeviceGemmMultipleD(BaseOperator):
     """DeviceGemmMultipleD (device_gemm_multiple_d.hpp:32-53), realised by one sm_100a kernel.
 
     ``dtype`` is CKB_F16, CKB_BF16 or CKB_I8; layouts are the gemm layout tags of
-    device/tensor_layout.hpp:13-25 (row-major A, column-major B, row-major E are supported).
+    device/tensor_layout.hpp:13-25 (A and B in either order, E row-major).
     """
 
     def __init__(self, dtype=CKB_F16, a_layout=CKB_ROW_MAJOR, b_layout=CKB_COL_MAJOR):
@@ -235,6 +235,51 @@ class DeviceGemm(DeviceGemmMultipleD):
 
     def GetTypeString(self) -> str:
         return "DeviceGemm_B200_Tcgen05<128, 256|128|64, 128B>"
+
+
+class BatchedGemmArgument(BaseArgument):
+    def __init__(self):
+        super().__init__()
+        self.desc = capi.BatchedGemmDesc()
+        self.ab_ops_passthrough = True
+
+
+class DeviceBatchedGemm(BaseOperator):
+    """DeviceBatchedGemm (device_batched_gemm.hpp:15-44): `Batch` problems of one shape whose matrices lie
+    BatchStrideA / BatchStrideB / BatchStrideC elements apart; all batches run in one launch."""
+
+    def __init__(self, dtype=CKB_F16, a_layout=CKB_ROW_MAJOR, b_layout=CKB_COL_MAJOR):
+        self.dtype, self.a_layout, self.b_layout = dtype, a_layout, b_layout
+
+    def MakeArgument(self, p_a, p_b, p_c, M, N, K, StrideA, StrideB, StrideC, BatchStrideA, BatchStrideB,
+                     BatchStrideC, Batch, a_element_op=None, b_element_op=None,
+                     c_element_op: ElementOp = PassThrough()) -> BatchedGemmArgument:
+        arg = BatchedGemmArgument()
+        _fill_gemm_desc(arg.desc.gemm, self.dtype, self.a_layout, self.b_layout, p_a, p_b, [], p_c, M, N, K,
+                        StrideA, StrideB, [], StrideC, c_element_op)
+        arg.desc.batch = int(Batch)
+        arg.desc.batch_stride_a, arg.desc.batch_stride_b = int(BatchStrideA), int(BatchStrideB)
+        arg.desc.batch_stride_e = int(BatchStrideC)
+        arg.ab_ops_passthrough = _is_passthrough(a_element_op) and _is_passthrough(b_element_op)
+        return arg
+
+    MakeArgumentPointer = MakeArgument
+
+    def IsSupportedArgument(self, arg: BatchedGemmArgument) -> bool:
+        if not arg.ab_ops_passthrough:
+            return False
+        return capi.lib().ckb_batched_gemm_supported(ctypes.byref(arg.desc)) == capi.CKB_OK
+
+    def _run(self, arg: BatchedGemmArgument, sc: StreamConfig) -> float:
+        if not self.IsSupportedArgument(arg):
+            raise RuntimeError("wrong! GridwiseGemm has invalid setting: " + capi.last_error())
+        ms = ctypes.c_float(0.0)
+        capi.check(capi.lib().ckb_batched_gemm_run(ctypes.byref(arg.desc), sc.stream_id,
+                                                   sc.nrepeat if sc.time_kernel else 0, ctypes.byref(ms)))
+        return float(ms.value)
+
+    def GetTypeString(self) -> str:
+        return "DeviceBatchedGemm_B200_Tcgen05<128, 256|128|64, 128B>"
 
 
 @dataclass

@@ -157,6 +157,22 @@ struct DeviceGemmMultipleD : public BaseOperator
 template <typename... Ts>
 using DeviceGemmMultipleDPtr = std::unique_ptr<DeviceGemmMultipleD<Ts...>>;
 
+// device_batched_gemm.hpp:15-52
+template <typename ALayout, typename BLayout, typename CLayout, typename ADataType, typename BDataType,
+          typename CDataType, typename AElementwiseOperation, typename BElementwiseOperation,
+          typename CElementwiseOperation>
+struct DeviceBatchedGemm : public BaseOperator
+{
+    virtual std::unique_ptr<BaseArgument>
+    MakeArgumentPointer(const void* p_a, const void* p_b, void* p_c, index_t M, index_t N, index_t K, index_t StrideA,
+                        index_t StrideB, index_t StrideC, index_t BatchStrideA, index_t BatchStrideB,
+                        index_t BatchStrideC, index_t Batch, AElementwiseOperation a_element_op,
+                        BElementwiseOperation b_element_op, CElementwiseOperation c_element_op) = 0;
+    virtual std::unique_ptr<BaseInvoker> MakeInvokerPointer()                                    = 0;
+};
+template <typename... Ts>
+using DeviceBatchedGemmPtr = std::unique_ptr<DeviceBatchedGemm<Ts...>>;
+
 // device_grouped_gemm.hpp:11-44
 struct GemmDesc
 {
@@ -295,6 +311,30 @@ struct GemmInvoker : dev::BaseInvoker
     float Run(const dev::BaseArgument* p_arg, const StreamConfig& stream_config = StreamConfig{}) override
     {
         return Run(argument_cast<GemmArgument>(p_arg), stream_config);
+    }
+};
+
+// -------- batched GEMM --------
+struct BatchedGemmArgument : dev::BaseArgument
+{
+    ckb_batched_gemm_desc desc{};
+    bool host_ok = true;
+};
+
+struct BatchedGemmInvoker : dev::BaseInvoker
+{
+    float Run(const BatchedGemmArgument& arg, const StreamConfig& stream_config = StreamConfig{})
+    {
+        if(!arg.host_ok || ckb_batched_gemm_supported(&arg.desc) != CKB_OK)
+            throw_invalid_setting();
+        float ms = 0.f;
+        check_runtime(ckb_batched_gemm_run(&arg.desc, stream_config.stream_id_,
+                                           stream_config.time_kernel_ ? kTimedRepeats : 0, &ms));
+        return ms;
+    }
+    float Run(const dev::BaseArgument* p_arg, const StreamConfig& stream_config = StreamConfig{}) override
+    {
+        return Run(argument_cast<BatchedGemmArgument>(p_arg), stream_config);
     }
 };
 
@@ -543,6 +583,66 @@ struct DeviceGemmXdl : public DeviceGemm<ALayout, BLayout, CLayout, ADataType, B
         std::ostringstream s; // device_gemm_xdl.hpp:522-541
         s << "DeviceGemmXdl<" << BlockSize << ", " << MPerBlock << ", " << NPerBlock << ", " << K0PerBlock << ", " << K1
           << ", " << MPerXDL << ", " << NPerXDL << ", " << MXdlPerWave << ", " << NXdlPerWave
+          << "> on B200 tcgen05 (tuning parameters ignored)";
+        return s.str();
+    }
+};
+
+// device_batched_gemm_xdl.hpp:119-153
+template <typename ADataType, typename BDataType, typename CDataType, typename AccDataType, typename ALayout,
+          typename BLayout, typename CLayout, typename AElementwiseOperation, typename BElementwiseOperation,
+          typename CElementwiseOperation, index_t BlockSize, index_t MPerBlock, index_t NPerBlock, index_t K0PerBlock,
+          index_t K1, index_t MPerXDL, index_t NPerXDL, index_t MXdlPerWave, index_t NXdlPerWave,
+          CKB_XFER(ABlockTransfer), CKB_XFER(BBlockTransfer), index_t CThreadTransferSrcDstVectorDim,
+          index_t CThreadTransferDstScalarPerVector>
+struct DeviceBatchedGemmXdl : public DeviceBatchedGemm<ALayout, BLayout, CLayout, ADataType, BDataType, CDataType,
+                                                       AElementwiseOperation, BElementwiseOperation, CElementwiseOperation>
+{
+    using Argument = b200::BatchedGemmArgument;
+    using Invoker  = b200::BatchedGemmInvoker;
+
+    static auto MakeArgument(const ADataType* p_a, const BDataType* p_b, CDataType* p_c, index_t M, index_t N,
+                             index_t K, index_t StrideA, index_t StrideB, index_t StrideC, index_t BatchStrideA,
+                             index_t BatchStrideB, index_t BatchStrideC, index_t Batch, AElementwiseOperation,
+                             BElementwiseOperation, CElementwiseOperation c_element_op)
+    {
+        const auto one = b200::make_gemm_argument<ALayout, BLayout, CLayout, ADataType, BDataType, CDataType,
+                                                  AElementwiseOperation, BElementwiseOperation, CElementwiseOperation,
+                                                  b200::ctx_gemm_c, 0>(p_a, p_b, {}, p_c, M, N, K, StrideA, StrideB, {},
+                                                                       StrideC, c_element_op);
+        Argument arg;
+        arg.host_ok             = one.host_ok;
+        arg.desc.gemm           = one.desc;
+        arg.desc.batch          = Batch;
+        arg.desc.batch_stride_a = BatchStrideA;
+        arg.desc.batch_stride_b = BatchStrideB;
+        arg.desc.batch_stride_e = BatchStrideC;
+        return arg;
+    }
+    static auto MakeInvoker() { return Invoker{}; }
+    static bool IsSupportedArgument(const Argument& arg)
+    {
+        return arg.host_ok && ckb_batched_gemm_supported(&arg.desc) == CKB_OK;
+    }
+    bool IsSupportedArgument(const BaseArgument* p_arg) override
+    {
+        return IsSupportedArgument(b200::argument_cast<Argument>(p_arg));
+    }
+    std::unique_ptr<BaseArgument>
+    MakeArgumentPointer(const void* p_a, const void* p_b, void* p_c, index_t M, index_t N, index_t K, index_t StrideA,
+                        index_t StrideB, index_t StrideC, index_t BatchStrideA, index_t BatchStrideB,
+                        index_t BatchStrideC, index_t Batch, AElementwiseOperation a_op, BElementwiseOperation b_op,
+                        CElementwiseOperation c_op) override
+    {
+        return std::make_unique<Argument>(MakeArgument(
+            static_cast<const ADataType*>(p_a), static_cast<const BDataType*>(p_b), static_cast<CDataType*>(p_c), M, N, K,
+            StrideA, StrideB, StrideC, BatchStrideA, BatchStrideB, BatchStrideC, Batch, a_op, b_op, c_op));
+    }
+    std::unique_ptr<BaseInvoker> MakeInvokerPointer() override { return std::make_unique<Invoker>(); }
+    std::string GetTypeString() const override
+    {
+        std::ostringstream s; // device_batched_gemm_xdl.hpp:625-644
+        s << "DeviceBatchedGemmXdl<" << BlockSize << ", " << MPerBlock << ", " << NPerBlock << ", " << K0PerBlock
           << "> on B200 tcgen05 (tuning parameters ignored)";
         return s.str();
     }

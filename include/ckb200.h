@@ -134,6 +134,24 @@ int ckb_gemm_supported(const ckb_gemm_desc* desc);
  * Replaces DeviceGemm_Xdl_CShuffle::Invoker::Run (device_gemm_xdl_cshuffle.hpp:456-563). */
 int ckb_gemm_run(const ckb_gemm_desc* desc, void* stream, int n_rep, float* avg_ms);
 
+/* ---- batched GEMM: E[g] = epilogue(A[g]*B[g], D0[g], D1[g]), g = 0..batch-1 -------------- */
+/* Replaces DeviceBatchedGemm::MakeArgumentPointer (device/device_batched_gemm.hpp:24-44: one
+ * problem shape, pointers of batch 0, BatchStrideA/B/C in elements, Batch) and DeviceBatchedGemmXdl
+ * (device/device_batched_gemm_xdl.hpp:119-153).  All batches run in one launch of the persistent
+ * kernel; batch strides of A and B must be multiples of 16 bytes. */
+typedef struct ckb_batched_gemm_desc {
+    ckb_gemm_desc gemm;          /* shape, dtypes, layouts, epilogue; pointers of batch 0   */
+    int64_t batch;               /* number of matrices, >= 1                               */
+    int64_t batch_stride_a;      /* elements between A[g] and A[g+1]                       */
+    int64_t batch_stride_b;
+    int64_t batch_stride_e;
+    int64_t batch_stride_d[2];   /* 0 = the same D for every batch                         */
+} ckb_batched_gemm_desc;
+
+int ckb_batched_gemm_supported(const ckb_batched_gemm_desc* desc);
+/* n_rep / avg_ms as ckb_gemm_run. */
+int ckb_batched_gemm_run(const ckb_batched_gemm_desc* desc, void* stream, int n_rep, float* avg_ms);
+
 /* ---- grouped GEMM ---------------------------------------------------------- */
 /* Replaces DeviceGroupedGemm::MakeArgumentPointer (device/device_grouped_gemm.hpp:33-41);
  * one ckb_gemm_desc per group (GemmDesc, device_grouped_gemm.hpp:11-17).  All groups must

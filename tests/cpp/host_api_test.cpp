@@ -19,6 +19,7 @@
 #include "ck/library/utility/conv_util.hpp"
 #include "ck/library/utility/fill.hpp"
 #include "ck/tensor_operation/gpu/device/device_conv2d_fwd_xdl_c_shuffle_bias_activation_nhwc_kyxc_nhwk.hpp"
+#include "ck/tensor_operation/gpu/device/device_batched_gemm_xdl.hpp"
 #include "ck/tensor_operation/gpu/device/device_gemm_multiple_d_xdl_cshuffle.hpp"
 #include "ck/tensor_operation/gpu/device/device_gemm_xdl_cshuffle.hpp"
 #include "ck/tensor_operation/gpu/device/device_grouped_gemm_xdl.hpp"
@@ -342,8 +343,30 @@ static void test_instance_factory()
     }
 }
 
+// DeviceBatchedGemmXdl with the reference's positional template list (example/../batched_gemm test instances)
+static void test_batched_gemm_host_side()
+{
+    // clang-format off
+    using Batched = dev::DeviceBatchedGemmXdl<F16, F16, F16, float, Row, Col, Row, ew::PassThrough, ew::PassThrough, ew::PassThrough,
+        256, 256, 128, 4, 8, 32, 32, 4, 2, S<4, 64, 1>, S<1, 0, 2>, S<1, 0, 2>, 2, 8, 8, true,
+        S<4, 64, 1>, S<1, 0, 2>, S<1, 0, 2>, 2, 8, 8, true, 7, 1>;
+    // clang-format on
+    const F16* pa = reinterpret_cast<const F16*>(0x1000);
+    F16* pc       = reinterpret_cast<F16*>(0x3000);
+    Batched op;
+    auto arg = op.MakeArgument(pa, pa, pc, 256, 256, 64, 64, 64, 256, 256 * 64, 256 * 64, 256 * 256, 8, {}, {}, {});
+    EXPECT(op.IsSupportedArgument(arg));
+    auto none = op.MakeArgument(pa, pa, pc, 256, 256, 64, 64, 64, 256, 256 * 64, 256 * 64, 256 * 256, 0, {}, {}, {});
+    EXPECT(!op.IsSupportedArgument(none));
+    EXPECT(op.GetTypeString().find("DeviceBatchedGemmXdl<256, 256, 128, 4>") == 0);
+    dev::DeviceBatchedGemm<Row, Col, Row, F16, F16, F16, ew::PassThrough, ew::PassThrough, ew::PassThrough>* base = &op;
+    auto parg = base->MakeArgumentPointer(pa, pa, pc, 256, 256, 64, 64, 64, 256, 256 * 64, 256 * 64, 256 * 256, 8, {}, {}, {});
+    EXPECT(base->IsSupportedArgument(parg.get()));
+}
+
 int main()
 {
+    test_batched_gemm_host_side();
     test_instance_factory();
     test_descriptors();
     test_conv_params();
