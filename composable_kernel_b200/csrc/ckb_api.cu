@@ -9,6 +9,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <map>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -79,12 +80,21 @@ void load_entry_points()
     });
 }
 
+// Scratch of the K-split tail (parked accumulator slices + one counter per tail tile), one buffer per stream:
+// launches on one stream run one after the other, launches on different streams must not share it.
+struct Scratch
+{
+    void* ptr    = nullptr;
+    size_t bytes = 0;
+};
+
 struct DeviceInfo
 {
     int sm_count = 0;
     int cc_major = 0, cc_minor = 0;
     uint32_t* status = nullptr;
     bool ready       = false;
+    std::map<cudaStream_t, Scratch> scratch;
 };
 DeviceInfo g_dev[64];
 std::mutex g_dev_mutex;
@@ -116,6 +126,40 @@ int current_device(DeviceInfo** out)
     }
     *out = &d;
     return CKB_OK;
+}
+
+constexpr size_t kScratchCounterBytes = 4096; // 1024 tail-tile counters at the front of a scratch buffer
+
+// Grow-only scratch of `stream` with room for `bytes` after the counters; nullptr when the device has no memory
+// left for it (the caller then falls back to a plan that needs none).  The counters are zero on return the
+// first time and are left at zero by every kernel that uses them.
+void* scratch_for(DeviceInfo* dev, cudaStream_t stream, size_t bytes)
+{
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    Scratch& sc       = dev->scratch[stream];
+    const size_t need = kScratchCounterBytes + bytes;
+    if(sc.bytes >= need)
+        return sc.ptr;
+    if(sc.ptr)
+    {
+        cudaFree(sc.ptr); // synchronises: no kernel is still using the old buffer
+        sc.ptr   = nullptr;
+        sc.bytes = 0;
+    }
+    void* ptr = nullptr;
+    if(cudaMalloc(&ptr, need) != cudaSuccess)
+    {
+        cudaGetLastError();
+        return nullptr;
+    }
+    if(cudaMemset(ptr, 0, kScratchCounterBytes) != cudaSuccess)
+    {
+        cudaFree(ptr);
+        return nullptr;
+    }
+    sc.ptr   = ptr;
+    sc.bytes = need;
+    return ptr;
 }
 
 uint64_t wait_limit_ns()
@@ -474,7 +518,14 @@ int ckb_device_status(uint32_t* word)
     uint32_t w = 0;
     CKB_CUDA(cudaMemcpy(&w, dev->status, sizeof(w), cudaMemcpyDeviceToHost));
     if(w != 0)
+    {
         CKB_CUDA(cudaMemset(dev->status, 0, sizeof(w)));
+        // a kernel that gave up may have left tail-tile counters of the K-split scratch half way
+        std::lock_guard<std::mutex> lock(g_dev_mutex);
+        for(auto& kv : dev->scratch)
+            if(kv.second.ptr)
+                cudaMemset(kv.second.ptr, 0, kScratchCounterBytes);
+    }
     if(word)
         *word = w;
     if(w != 0)
@@ -550,7 +601,52 @@ static int gemm_run_impl(const ckb_gemm_desc* d, const BatchInfo& bi, void* stre
     const int64_t all_tiles = tiles_m * tiles_n * nb;
     if(all_tiles > 0x3FFFFFFFll)
         return fail(CKB_ERR_UNSUPPORTED, "too many tiles");
-    const WorkPlan plan = plan_work(all_tiles, dev->sm_count / cg, bn, cg, b_min);
+    WorkPlan plan = plan_work(all_tiles, dev->sm_count / cg, bn, cg, b_min);
+    // K-split tail: with whole waves before it and a tail of at most half the units, cut the tail tiles along K
+    // (see "K-split tail" in ckb_kernel.cuh); needs scratch, else the column-slice plan above stands.
+    const int bk      = BK_BYTES / eb;
+    const int num_kb  = static_cast<int>((d->K + bk - 1) / bk);
+    const int64_t G   = dev->sm_count / cg;
+    const int64_t ful = (all_tiles / G) * G, rem = all_tiles - ful;
+    const char* no_ks = getenv("CKB_NO_SPLITK");
+    // Measured on 3840 x 4096 x 4096: +5 % for 16-bit operands with a D-less epilogue; a loss for int8 (tiles
+    // half as long) and for epilogues that read D tensors, where the epilogue warps have no slack for the
+    // parking and the reduction - those keep the column slices.
+    const bool ks_pays = d->ab_dtype != CKB_I8 && d->n_ds == 0;
+    if(ks_pays && rem > 0 && ful > 0 && rem * 2 <= G && rem <= 1024 && !(no_ks && atoi(no_ks) != 0))
+    {
+        // 4 or 2 slices; the reduction is shared out in column parts of bn / ksplit >= 64 columns
+        int ksplit = (G / rem >= 4 && bn >= 256) ? 4 : (bn >= 128 ? 2 : 0);
+        int ks_kb  = 0;
+        for(; ksplit >= 2; ksplit -= 2)
+        {
+            ks_kb = (num_kb + ksplit - 1) / ksplit;
+            ks_kb = (ks_kb + 1) & ~1; // slices start on a stage boundary (at most two k blocks per stage)
+            if(ks_kb >= 4 && static_cast<int64_t>(ksplit - 1) * ks_kb < num_kb)
+                break;
+        }
+        if(ksplit >= 2)
+        {
+            const size_t part_bytes = static_cast<size_t>(rem) * ksplit * (BM * cg) * bn * sizeof(uint32_t);
+            void* sc                = scratch_for(dev, static_cast<cudaStream_t>(stream), part_bytes);
+            if(sc)
+            {
+                p.ksplit      = ksplit;
+                p.ks_kb       = ks_kb;
+                p.ks_full     = static_cast<int32_t>(ful);
+                p.ks_rem      = static_cast<int32_t>(rem);
+                p.ks_counters = static_cast<uint32_t*>(sc);
+                p.ks_partials = reinterpret_cast<uint32_t*>(static_cast<char*>(sc) + kScratchCounterBytes);
+                p.num_slots   = static_cast<int32_t>(ful / G + 2 < 4 ? 4 : ful / G + 2);
+                plan.split    = 1;
+                plan.split_start = static_cast<int32_t>(all_tiles);
+                plan.total_work  = static_cast<int32_t>(all_tiles);
+                plan.grid        = static_cast<int32_t>(G * cg);
+            }
+        }
+    }
+    if(p.ksplit < 2)
+        p.num_slots = static_cast<int32_t>((plan.total_work + G - 1) / G);
     rc = encode_operand(&p.tm_b, d->ab_dtype, d->p_b, d->N, d->K, d->ldb, b_mn, bn / cg, bi.batch, bi.stride_b);
     if(rc)
         return rc;
@@ -570,8 +666,7 @@ static int gemm_run_impl(const ckb_gemm_desc* d, const BatchInfo& bi, void* stre
     p.M             = static_cast<int32_t>(d->M);
     p.N             = static_cast<int32_t>(d->N);
     p.tiles_n       = static_cast<int32_t>(tiles_n);
-    const int bk    = BK_BYTES / eb;
-    p.num_kb        = static_cast<int32_t>((d->K + bk - 1) / bk);
+    p.num_kb        = num_kb;
     p.vec_ok        = gemm_vec_ok(d) && bi.vec_ok ? 1 : 0;
     p.wait_limit_ns = wait_limit_ns();
     p.status        = dev->status;
@@ -754,6 +849,7 @@ static void fill_grouped_params(KernelParams& p, const ckb_grouped_gemm_desc* g,
     p.split_start   = gp.plan.split_start;
     p.split         = gp.plan.split;
     p.total_work    = gp.plan.total_work;
+    p.num_slots     = (gp.plan.total_work + gp.plan.grid / gp.cg - 1) / (gp.plan.grid / gp.cg);
     p.mn_major      = gp.mn_major;
     p.wait_limit_ns = wait_limit_ns();
     p.status        = dev->status;
@@ -1008,6 +1104,7 @@ int ckb_conv2d_fwd_run(const ckb_conv2d_fwd_desc* d, void* stream, int n_rep, fl
     p.split_start   = plan.split_start;
     p.split         = plan.split;
     p.total_work    = plan.total_work;
+    p.num_slots     = (plan.total_work + plan.grid / cg - 1) / (plan.grid / cg);
     p.M             = static_cast<int32_t>(gm);
     p.N             = d->K;
     p.tiles_n       = static_cast<int32_t>(tiles_n);

@@ -17,6 +17,15 @@
 // `split` column slices of BN/split columns (R*split <= G), so that the tail occupies all SMs
 // instead of R of them.
 //
+// K-split tail (MODE_GEMM with a scratch buffer).  Column slices of a tail tile cost almost as much as a whole
+// tile, because the MMA role is bound by the number of instructions it issues, not by their width.  When
+// KernelParams::ksplit > 1 the R tail tiles are cut along K instead: after its first whole tile every unit runs
+// one K slice of a tail tile (full-width MMAs over 1/ksplit of the k blocks) and parks the raw accumulator in the
+// scratch buffer; after its next whole tile the unit that ran slice i sums column part i (BN / ksplit columns)
+// of that tail tile over all slices, in slice order (deterministic), and applies the epilogue - on the epilogue
+// warps only, while the MMA role already works on the next tile.  A per-tile counter in global memory (release /
+// acquire, bounded wait) orders slices and reduction.
+//
 // Three problem sources share the kernel:
 //   MODE_GEMM     one A/B tensor-map pair in the kernel parameters
 //   MODE_GROUPED  a device table of per-group tensor maps + tile prefix sums; each role
@@ -75,7 +84,8 @@ enum {
     WAIT_FULL       = 2, // MMA waiting for TMA data
     WAIT_TMEM_EMPTY = 3, // MMA waiting for the epilogue to release an accumulator
     WAIT_TMEM_FULL  = 4, // epilogue waiting for the MMA
-    WAIT_DRAIN      = 5  // exit path waiting for copies / MMAs in flight
+    WAIT_DRAIN      = 5, // exit path waiting for copies / MMAs in flight
+    WAIT_KSLICES    = 6  // reduction waiting for the K slices of its tail tile
 };
 
 // One group of a grouped GEMM (lives in the caller's device workspace).
@@ -123,6 +133,15 @@ struct KernelParams
     int32_t batch_tiles; // batched GEMM: tiles per batch (0 = not batched)
     int32_t pad_;
     int64_t batch_stride_e, batch_stride_d0, batch_stride_d1; // elements between batches of E / D0 / D1
+    // K-split tail (0 / 1 = off): see "K-split tail" above
+    int32_t ksplit;      // K slices per tail tile
+    int32_t ks_kb;       // k blocks per slice (a multiple of the k blocks per stage)
+    int32_t ks_full;     // tiles that run whole (a multiple of the number of units); tail tiles follow
+    int32_t ks_rem;      // tail tiles
+    int32_t num_slots;   // work slots per unit
+    int32_t pad2_;
+    uint32_t* ks_partials; // [tail tile][slice][TILE_M rows][BN columns] raw 32-bit accumulators
+    uint32_t* ks_counters; // one per tail tile, zero between launches
     ConvGeom conv;
     uint64_t wait_limit_ns;
     uint32_t* status; // device status word
@@ -195,34 +214,85 @@ __device__ __forceinline__ int find_group(const GroupEntry* groups, int group_co
 }
 
 // What one work item covers.
+enum { ITEM_NONE = 0, ITEM_TILE = 1, ITEM_KSLICE = 2, ITEM_REDUCE = 3 };
 struct WorkItem
 {
+    int kind;    // ITEM_*: TILE runs all roles; KSLICE is a TILE over part of K whose accumulator is parked;
+                 // REDUCE is epilogue-only
     int m_blk;   // row tile
     int n_start; // first output column
     int width;   // columns of this item (BN, or BN/split for a tail slice)
-    int num_kb;
+    int kb_begin, num_kb;    // k blocks [kb_begin, kb_begin + num_kb)
     const GroupEntry* group; // MODE_GROUPED only
     int batch;               // MODE_GEMM: batch index (0 unless batched)
-    bool is_slice;
+    int tail;                // KSLICE / REDUCE: index of the tail tile
+    int slice;               // KSLICE: which K slice; REDUCE: which column part (of width BN / ksplit)
+    bool is_slice;           // a column slice of a tail tile
 };
 
+// Item of `unit` (CTA or CTA pair) in its work slot `slot`.
+//   plain / column-slice plan: item w = unit + slot * num_units of the list described under "Work items"
+//   K-split plan             : whole tile, K slice, whole tile, reduction of one column part of the tail tile,
+//                              then the remaining whole tiles (parking and reduction both overlap a main loop)
 template <int MODE, int BN>
-__device__ __forceinline__ WorkItem decode_work(const KernelParams& P, int w)
+__device__ __forceinline__ WorkItem decode_work(const KernelParams& P, int unit, int num_units, int slot)
 {
     WorkItem wi;
     int tile, slice = 0;
+    wi.kind     = ITEM_TILE;
     wi.width    = BN;
     wi.is_slice = false;
     wi.batch    = 0;
-    if(w < P.split_start)
-        tile = w;
+    wi.tail     = 0;
+    wi.slice    = 0;
+    wi.kb_begin = 0;
+    wi.group    = nullptr;
+    if(MODE == MODE_GEMM && P.ksplit > 1)
+    {
+        if(slot == 1)
+        {
+            wi.kind  = unit < P.ks_rem * P.ksplit ? ITEM_KSLICE : ITEM_NONE;
+            wi.tail  = unit / P.ksplit;
+            wi.slice = unit - wi.tail * P.ksplit;
+            tile     = P.ks_full + wi.tail;
+        }
+        else if(slot == 3)
+        {
+            // the unit that ran slice i of a tail tile also sums column part i of it
+            wi.kind  = unit < P.ks_rem * P.ksplit ? ITEM_REDUCE : ITEM_NONE;
+            wi.tail  = unit / P.ksplit;
+            wi.slice = unit - wi.tail * P.ksplit;
+            tile     = P.ks_full + wi.tail;
+            slice    = wi.slice;
+            wi.width = BN / P.ksplit;
+        }
+        else
+        {
+            tile = unit + (slot == 0 ? 0 : slot == 2 ? 1 : slot - 2) * num_units;
+            if(tile >= P.ks_full)
+                wi.kind = ITEM_NONE;
+        }
+        if(wi.kind == ITEM_NONE)
+            tile = 0;
+    }
     else
     {
-        const int q = w - P.split_start;
-        tile        = P.split_start + q / P.split;
-        slice       = q % P.split;
-        wi.width    = BN / P.split;
-        wi.is_slice = P.split > 1;
+        const int w = unit + slot * num_units;
+        if(w >= P.total_work)
+        {
+            wi.kind = ITEM_NONE;
+            tile    = 0;
+        }
+        else if(w < P.split_start)
+            tile = w;
+        else
+        {
+            const int q = w - P.split_start;
+            tile        = P.split_start + q / P.split;
+            slice       = q % P.split;
+            wi.width    = BN / P.split;
+            wi.is_slice = P.split > 1;
+        }
     }
     int n_blk;
     if constexpr(MODE == MODE_GROUPED)
@@ -244,7 +314,12 @@ __device__ __forceinline__ WorkItem decode_work(const KernelParams& P, int w)
         wi.m_blk  = tile / P.tiles_n;
         n_blk     = tile % P.tiles_n;
         wi.num_kb = P.num_kb;
-        wi.group  = nullptr;
+    }
+    if(wi.kind == ITEM_KSLICE)
+    {
+        wi.kb_begin   = wi.slice * P.ks_kb;
+        const int rest = P.num_kb - wi.kb_begin;
+        wi.num_kb     = rest < P.ks_kb ? rest : P.ks_kb;
     }
     wi.n_start = n_blk * BN + slice * wi.width;
     return wi;
@@ -272,11 +347,109 @@ __device__ __forceinline__ void load_matrix_box(uint32_t dst, const CUtensorMap*
     }
 }
 
-// Epilogue of one warp: rows = its TMEM lane quarter, columns [n_begin, n_end) of row m.
-// tmem_addr = lane base | first column of the span inside the accumulator.
-template <int EPI, int KIND>
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Bounded wait until *counter >= target (acquire).  Returns false when it gave up.
+__device__ __forceinline__ bool bounded_wait_counter(const uint32_t* counter, uint32_t target, const WaitCtx& w)
+{
+    if(ld_acquire_gpu(counter) >= target)
+        return true;
+    const uint64_t t0 = global_timer_ns();
+    uint32_t spins    = 0;
+    while(true)
+    {
+        if(ld_acquire_gpu(counter) >= target)
+            return true;
+        if((++spins & 15u) == 0)
+        {
+            if(*w.abort_flag != 0)
+                return false;
+            if(global_timer_ns() - t0 > w.limit_ns || spins > (1u << 28))
+            {
+                atomicCAS(w.status, 0u, (static_cast<uint32_t>(WAIT_KSLICES) << 24) | (blockIdx.x & 0xFFFFFFu));
+                *w.abort_flag = 1;
+                return false;
+            }
+        }
+    }
+}
+
+// K-split tail.  A parked slice is private to the (CTA, epilogue warp) that will read it back, so it is stored
+// in the order that makes every warp-wide access contiguous: per warp a block of 32 rows x `ncols` columns laid
+// out as [chunk of 32 columns][quad q of 4 columns][lane] of 16 bytes (lane = row), 512 contiguous bytes per
+// instruction, instead of 32 row pieces a row pitch apart.
+// Slice side: one warp parks `ncols` (a multiple of 32) raw accumulator columns of its 32 rows.
+__device__ __forceinline__ void park_span(uint32_t tmem_addr, uint32_t* block, int ncols, int lane)
+{
+    uint4* dst = reinterpret_cast<uint4*>(block) + lane;
+    for(int c = 0; c < ncols / 32; ++c)
+    {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem_addr + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for(int q = 0; q < 8; ++q)
+            __stcg(dst + (c * 8 + q) * 32, make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
+    }
+}
+
+// Reduction side: v = sum over the slices, in slice order, of chunk `c` of this lane's row.
+template <int KIND>
+__device__ __forceinline__ void reduce_chunk(uint32_t (&v)[32], const uint32_t* block, int c, int lane, int ks,
+                                             int64_t slice_stride)
+{
+    auto add = [](uint32_t a, uint32_t b) {
+        if constexpr(KIND == KIND_I8)
+            return a + b; // int32 accumulators
+        else
+            return __float_as_uint(__uint_as_float(a) + __uint_as_float(b));
+    };
+#pragma unroll
+    for(int h = 0; h < 2; ++h) // 16 columns at a time: all slices of a half chunk are in flight together
+    {
+        uint4 t[4][4];
+#pragma unroll
+        for(int sl = 0; sl < 4; ++sl)
+            if(sl < ks)
+            {
+                const uint4* src = reinterpret_cast<const uint4*>(block + sl * slice_stride) + lane;
+#pragma unroll
+                for(int q = 0; q < 4; ++q)
+                    t[sl][q] = __ldcg(src + (c * 8 + h * 4 + q) * 32);
+            }
+#pragma unroll
+        for(int q = 0; q < 4; ++q)
+        {
+            uint4 a = t[0][q];
+#pragma unroll
+            for(int sl = 1; sl < 4; ++sl)
+                if(sl < ks)
+                {
+                    a.x = add(a.x, t[sl][q].x);
+                    a.y = add(a.y, t[sl][q].y);
+                    a.z = add(a.z, t[sl][q].z);
+                    a.w = add(a.w, t[sl][q].w);
+                }
+            v[h * 16 + q * 4 + 0] = a.x;
+            v[h * 16 + q * 4 + 1] = a.y;
+            v[h * 16 + q * 4 + 2] = a.z;
+            v[h * 16 + q * 4 + 3] = a.w;
+        }
+    }
+}
+
+// REDUCE = true: the accumulator comes from the parked K slices (`parked` = this warp's block in slice 0)
+// instead of tensor memory.
+template <int EPI, int KIND, bool REDUCE = false>
 __device__ __forceinline__ void epilogue_span(uint32_t tmem_addr, const EpilogueArgs& ea, int64_t m,
-                                              bool row_ok, int64_t n_begin, int64_t n_end, bool vec_ok)
+                                              bool row_ok, int64_t n_begin, int64_t n_end, bool vec_ok,
+                                              const uint32_t* parked = nullptr, int lane = 0, int ks = 0,
+                                              int64_t slice_stride = 0)
 {
     using T          = typename std::conditional<KIND == KIND_BF16, __nv_bfloat16, __half>::type;
     constexpr int ND = (KIND == KIND_I8) ? 0 : epi_num_d(EPI);
@@ -297,8 +470,13 @@ __device__ __forceinline__ void epilogue_span(uint32_t tmem_addr, const Epilogue
                 epi_load_d<EPI, T>(nxt, ea, m, n0 + 32);
         }
         uint32_t v[32];
-        tmem_ld_32x32b_x32(tmem_addr + c * 32, v);
-        tmem_ld_wait();
+        if constexpr(REDUCE)
+            reduce_chunk<KIND>(v, parked, c, lane, ks, slice_stride);
+        else
+        {
+            tmem_ld_32x32b_x32(tmem_addr + c * 32, v);
+            tmem_ld_wait();
+        }
         if(row_ok)
         {
             if constexpr(KIND == KIND_I8)
@@ -422,9 +600,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
         const uint32_t bar0 = (CG == 2) ? mapa_shared(full_bar(0), 0) : full_bar(0);
         const int a_per_kb  = a_mn ? BM / BK_ELEMS : 1; // A boxes per k block
         CKB_TR(long long tr_wait = 0; const long long tr_start = clock64();)
-        for(int w = unit; ok && w < P.total_work; w += num_units)
+        for(int slot = 0; ok && slot < P.num_slots; ++slot)
         {
-            const WorkItem wi       = decode_work<MODE, BN>(P, w);
+            const WorkItem wi = decode_work<MODE, BN>(P, unit, num_units, slot);
+            if(wi.kind != ITEM_TILE && wi.kind != ITEM_KSLICE)
+                continue;
             const CUtensorMap* tm_a = &P.tm_a;
             const CUtensorMap* tm_b = wi.is_slice ? &P.tm_b_split : &P.tm_b;
             if constexpr(MODE == MODE_GROUPED)
@@ -510,7 +690,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                     }
                     else
                     {
-                        const int k0 = (kb + box_j) * BK_ELEMS;
+                        const int k0 = (wi.kb_begin + kb + box_j) * BK_ELEMS;
                         load_matrix_box<MODE, CG>(dst, box_tm, bar, box_mn ? box_row : k0, box_mn ? k0 : box_row,
                                                   batched, wi.batch);
                     }
@@ -579,9 +759,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
             const uint32_t idesc_major = (a_mn ? 1u << 15 : 0u) | (b_mn ? 1u << 16 : 0u);
             CKB_TR(long long tr_full = 0, tr_acc = 0, tr_kb = 0, tr_issue = 0, tr_commit = 0;
                    const long long tr_start = clock64();)
-            for(int w = unit; ok && w < P.total_work; w += num_units, ++iter)
+            for(int slot = 0; ok && slot < P.num_slots; ++slot)
             {
-                const WorkItem wi        = decode_work<MODE, BN>(P, w);
+                const WorkItem wi = decode_work<MODE, BN>(P, unit, num_units, slot);
+                if(wi.kind != ITEM_TILE && wi.kind != ITEM_KSLICE)
+                    continue;
                 const uint32_t idesc     = make_idesc(C_FMT, AB_FMT, TILE_M, static_cast<uint32_t>(wi.width)) | idesc_major;
                 const int acc            = iter & 1;
                 const uint32_t acc_phase = (iter >> 1) & 1;
@@ -653,6 +835,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                     else
                         mma_commit(tmem_full_bar(acc));
                 }
+                ++iter;
             }
             CKB_TR(if(P.trace) {
                 P.trace[blockIdx.x * 16 + 2] = tr_full;
@@ -682,9 +865,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
         int iter          = 0;
         bool ok           = true;
         CKB_TR(long long tr_wait = 0; const long long tr_start = clock64();)
-        for(int w = unit; ok && w < P.total_work; w += num_units, ++iter)
+        for(int slot = 0; ok && slot < P.num_slots; ++slot)
         {
-            const WorkItem wi = decode_work<MODE, BN>(P, w);
+            const WorkItem wi = decode_work<MODE, BN>(P, unit, num_units, slot);
+            if(wi.kind == ITEM_NONE)
+                continue;
             EpilogueArgs ea   = P.epi;
             int Mdim = P.M, Ndim = P.N;
             bool vec_ok = P.vec_ok != 0;
@@ -721,8 +906,46 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
             const int64_t n_end_raw = n_begin + span;
             const int64_t n_end     = n_end_raw < Ndim ? n_end_raw : Ndim;
 
+            // K-split tail: this warp's block of the tail tile in slice 0 of the scratch buffer
+            // ([tail tile][slice][CTA of the pair][epilogue warp][32 rows x span columns])
+            const uint32_t* parked = nullptr;
+            if constexpr(MODE == MODE_GEMM)
+            {
+                const uint32_t* tail_base = P.ks_partials + static_cast<int64_t>(wi.tail) * P.ksplit * TILE_M * BN;
+                if(wi.kind == ITEM_KSLICE)
+                    parked = tail_base + (cta_rank * NUM_EPI_WARPS + half * 4 + quarter) * (32 * (BN / 2));
+                else if(wi.kind == ITEM_REDUCE)
+                {
+                    // chunks of 32 columns: the tile has BN / 32, each parking warp holds BN / 64 of them
+                    const int id0 = (wi.slice * wi.width + half * span) / 32; // first chunk this warp sums
+                    const int H   = id0 / (BN / 64);                          // column half of the warp that parked it
+                    parked        = tail_base + (cta_rank * NUM_EPI_WARPS + H * 4 + quarter) * (32 * (BN / 2)) +
+                             (id0 - H * (BN / 64)) * (8 * 32 * 4);
+                }
+            }
+            if constexpr(MODE == MODE_GEMM)
+            {
+                if(wi.kind == ITEM_REDUCE)
+                {
+                    // every slice of this tail tile is parked once all epilogue warps that ran one have arrived
+                    uint32_t* counter     = P.ks_counters + wi.tail;
+                    const uint32_t target = static_cast<uint32_t>(P.ksplit) * NUM_EPI_WARPS * CG;
+                    ok                    = bounded_wait_counter(counter, target, wc);
+                    ok                    = __all_sync(0xffffffffu, ok);
+                    if(!ok)
+                        break;
+                    epilogue_span<EPI, KIND, true>(0, ea, m, row_ok, n_begin, n_end, vec_ok, parked, lane, P.ksplit,
+                                                   static_cast<int64_t>(TILE_M) * BN);
+                    // the last of the reducing warps leaves the counter at zero for the next launch
+                    __syncwarp();
+                    if(lane == 0 && atomicAdd(counter, 1u) + 1u == 2u * target)
+                        atomicExch(counter, 0u);
+                    continue;
+                }
+            }
             const int acc            = iter & 1;
             const uint32_t acc_phase = (iter >> 1) & 1;
+            ++iter;
             CKB_TR(const long long tr0 = clock64();)
             ok = bounded_wait(tmem_full_bar(acc), acc_phase, wc, WAIT_TMEM_FULL);
             CKB_TR(tr_wait += clock64() - tr0;)
@@ -732,7 +955,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
             tc_fence_after_sync();
             const uint32_t tmem_addr =
                 tmem_base + acc * BN + half * span + (static_cast<uint32_t>(quarter * 32) << 16);
-            epilogue_span<EPI, KIND>(tmem_addr, ea, m, row_ok, n_begin, n_end, vec_ok);
+            if(MODE == MODE_GEMM && wi.kind == ITEM_KSLICE)
+                park_span(tmem_addr, const_cast<uint32_t*>(parked) + static_cast<int64_t>(wi.slice) * TILE_M * BN, span, lane);
+            else
+                epilogue_span<EPI, KIND>(tmem_addr, ea, m, row_ok, n_begin, n_end, vec_ok);
             // Release the accumulator: all of this warp's tcgen05.ld have completed.
             tc_fence_before_sync();
             __syncwarp();
@@ -744,13 +970,27 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                     mbar_arrive(tmem_empty_bar(acc));
             }
 
+            if constexpr(MODE == MODE_GEMM)
+            {
+                if(wi.kind == ITEM_KSLICE)
+                {
+                    // publish the parked slice: stores -> fence -> one arrival per warp
+                    __threadfence();
+                    __syncwarp();
+                    if(lane == 0)
+                        atomicAdd(P.ks_counters + wi.tail, 1u);
+                    continue;
+                }
+            }
+
             // Ask L2 for the D values of this CTA's next item while its main loop runs.
             if constexpr(KIND != KIND_I8)
             {
-                const int wn = w + num_units;
-                if(epi_num_d(EPI) > 0 && wn < P.total_work)
+                if(epi_num_d(EPI) > 0 && slot + 1 < P.num_slots)
                 {
-                    const WorkItem nx = decode_work<MODE, BN>(P, wn);
+                    const WorkItem nx = decode_work<MODE, BN>(P, unit, num_units, slot + 1);
+                    if(nx.kind != ITEM_TILE)
+                        continue;
                     EpilogueArgs en   = P.epi;
                     int Mn = P.M, Nn = P.N;
                     if constexpr(MODE == MODE_GROUPED)
