@@ -234,7 +234,15 @@ struct WorkItem
 //   plain / column-slice plan: item w = unit + slot * num_units of the list described under "Work items"
 //   K-split plan             : whole tile, K slice, whole tile, reduction of one column part of the tail tile,
 //                              then the remaining whole tiles (parking and reduction both overlap a main loop)
-template <int MODE, int BN>
+// Kernel instances that carry the K-split tail: 16-bit GEMMs whose epilogue reads no D tensor (the host enables
+// it only for those; leaving the code out of the others keeps their epilogue inside the register budget).
+template <int MODE, int KIND, int EPI>
+struct HasKSplit
+{
+    static constexpr bool value = MODE == MODE_GEMM && KIND != KIND_I8 && epi_num_d(EPI) == 0;
+};
+
+template <int MODE, int BN, bool KSPLIT = false>
 __device__ __forceinline__ WorkItem decode_work(const KernelParams& P, int unit, int num_units, int slot)
 {
     WorkItem wi;
@@ -247,7 +255,7 @@ __device__ __forceinline__ WorkItem decode_work(const KernelParams& P, int unit,
     wi.slice    = 0;
     wi.kb_begin = 0;
     wi.group    = nullptr;
-    if(MODE == MODE_GEMM && P.ksplit > 1)
+    if(KSPLIT && P.ksplit > 1)
     {
         if(slot == 1)
         {
@@ -410,20 +418,20 @@ __device__ __forceinline__ void reduce_chunk(uint32_t (&v)[32], const uint32_t* 
             return __float_as_uint(__uint_as_float(a) + __uint_as_float(b));
     };
 #pragma unroll
-    for(int h = 0; h < 2; ++h) // 16 columns at a time: all slices of a half chunk are in flight together
+    for(int h = 0; h < 4; ++h) // 8 columns at a time: all slices of a quarter chunk are in flight together
     {
-        uint4 t[4][4];
+        uint4 t[4][2];
 #pragma unroll
         for(int sl = 0; sl < 4; ++sl)
             if(sl < ks)
             {
                 const uint4* src = reinterpret_cast<const uint4*>(block + sl * slice_stride) + lane;
 #pragma unroll
-                for(int q = 0; q < 4; ++q)
-                    t[sl][q] = __ldcg(src + (c * 8 + h * 4 + q) * 32);
+                for(int q = 0; q < 2; ++q)
+                    t[sl][q] = __ldcg(src + (c * 8 + h * 2 + q) * 32);
             }
 #pragma unroll
-        for(int q = 0; q < 4; ++q)
+        for(int q = 0; q < 2; ++q)
         {
             uint4 a = t[0][q];
 #pragma unroll
@@ -435,10 +443,10 @@ __device__ __forceinline__ void reduce_chunk(uint32_t (&v)[32], const uint32_t* 
                     a.z = add(a.z, t[sl][q].z);
                     a.w = add(a.w, t[sl][q].w);
                 }
-            v[h * 16 + q * 4 + 0] = a.x;
-            v[h * 16 + q * 4 + 1] = a.y;
-            v[h * 16 + q * 4 + 2] = a.z;
-            v[h * 16 + q * 4 + 3] = a.w;
+            v[h * 8 + q * 4 + 0] = a.x;
+            v[h * 8 + q * 4 + 1] = a.y;
+            v[h * 8 + q * 4 + 2] = a.z;
+            v[h * 8 + q * 4 + 3] = a.w;
         }
     }
 }
@@ -500,7 +508,8 @@ template <int MODE, int KIND, int EPI, int BN, int STAGES, int CG, int KSUB>
 __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __grid_constant__ KernelParams P)
 {
     using L = SmemLayout<BN, STAGES, CG, KSUB>;
-    constexpr int TILE_M = BM * CG;
+    constexpr bool KSPLIT = HasKSplit<MODE, KIND, EPI>::value;
+    constexpr int TILE_M  = BM * CG;
     constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
     constexpr int UMMA_K_BYTES   = 32; // 16 x 16-bit or 32 x 8-bit
     constexpr int K_STEPS        = BK_BYTES / UMMA_K_BYTES;
@@ -602,7 +611,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
         CKB_TR(long long tr_wait = 0; const long long tr_start = clock64();)
         for(int slot = 0; ok && slot < P.num_slots; ++slot)
         {
-            const WorkItem wi = decode_work<MODE, BN>(P, unit, num_units, slot);
+            const WorkItem wi = decode_work<MODE, BN, KSPLIT>(P, unit, num_units, slot);
             if(wi.kind != ITEM_TILE && wi.kind != ITEM_KSLICE)
                 continue;
             const CUtensorMap* tm_a = &P.tm_a;
@@ -761,7 +770,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                    const long long tr_start = clock64();)
             for(int slot = 0; ok && slot < P.num_slots; ++slot)
             {
-                const WorkItem wi = decode_work<MODE, BN>(P, unit, num_units, slot);
+                const WorkItem wi = decode_work<MODE, BN, KSPLIT>(P, unit, num_units, slot);
                 if(wi.kind != ITEM_TILE && wi.kind != ITEM_KSLICE)
                     continue;
                 const uint32_t idesc     = make_idesc(C_FMT, AB_FMT, TILE_M, static_cast<uint32_t>(wi.width)) | idesc_major;
@@ -867,7 +876,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
         CKB_TR(long long tr_wait = 0; const long long tr_start = clock64();)
         for(int slot = 0; ok && slot < P.num_slots; ++slot)
         {
-            const WorkItem wi = decode_work<MODE, BN>(P, unit, num_units, slot);
+            const WorkItem wi = decode_work<MODE, BN, KSPLIT>(P, unit, num_units, slot);
             if(wi.kind == ITEM_NONE)
                 continue;
             EpilogueArgs ea   = P.epi;
@@ -909,7 +918,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
             // K-split tail: this warp's block of the tail tile in slice 0 of the scratch buffer
             // ([tail tile][slice][CTA of the pair][epilogue warp][32 rows x span columns])
             const uint32_t* parked = nullptr;
-            if constexpr(MODE == MODE_GEMM)
+            if constexpr(KSPLIT)
             {
                 const uint32_t* tail_base = P.ks_partials + static_cast<int64_t>(wi.tail) * P.ksplit * TILE_M * BN;
                 if(wi.kind == ITEM_KSLICE)
@@ -923,7 +932,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                              (id0 - H * (BN / 64)) * (8 * 32 * 4);
                 }
             }
-            if constexpr(MODE == MODE_GEMM)
+            if constexpr(KSPLIT)
             {
                 if(wi.kind == ITEM_REDUCE)
                 {
@@ -955,7 +964,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
             tc_fence_after_sync();
             const uint32_t tmem_addr =
                 tmem_base + acc * BN + half * span + (static_cast<uint32_t>(quarter * 32) << 16);
-            if(MODE == MODE_GEMM && wi.kind == ITEM_KSLICE)
+            if(KSPLIT && wi.kind == ITEM_KSLICE)
                 park_span(tmem_addr, const_cast<uint32_t*>(parked) + static_cast<int64_t>(wi.slice) * TILE_M * BN, span, lane);
             else
                 epilogue_span<EPI, KIND>(tmem_addr, ea, m, row_ok, n_begin, n_end, vec_ok);
@@ -970,7 +979,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                     mbar_arrive(tmem_empty_bar(acc));
             }
 
-            if constexpr(MODE == MODE_GEMM)
+            if constexpr(KSPLIT)
             {
                 if(wi.kind == ITEM_KSLICE)
                 {
@@ -988,7 +997,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
             {
                 if(epi_num_d(EPI) > 0 && slot + 1 < P.num_slots)
                 {
-                    const WorkItem nx = decode_work<MODE, BN>(P, unit, num_units, slot + 1);
+                    const WorkItem nx = decode_work<MODE, BN, KSPLIT>(P, unit, num_units, slot + 1);
                     if(nx.kind != ITEM_TILE)
                         continue;
                     EpilogueArgs en   = P.epi;
