@@ -11,8 +11,8 @@ namespace ckb {
 // main loop once the tiles are large.
 //   one CTA per tile : BN 256 -> 4 stages x 1 x 48 KiB, BN 128 -> 3 x 2 x 32 KiB, BN 64 -> 4 x 2 x 24 KiB
 //   CTA pair per tile: BN 256 -> 3 stages x 2 x 32 KiB per CTA (256 x 256 tile per pair)
-// The implicit-GEMM convolution keeps one k block per stage (measured faster: its k loop is short and its
-// im2col copies are the slower part).
+// The implicit-GEMM convolution keeps one k block per stage: two were slower with a single-thread producer and no
+// faster with the warp-wide one, and six shallow stages ride out the longer latency of the im2col copies.
 template <int BN, int CG, int MODE>
 struct StagesFor
 {
