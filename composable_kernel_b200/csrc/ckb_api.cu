@@ -963,14 +963,20 @@ static int check_conv(const ckb_conv2d_fwd_desc* d, bool need_pointers)
 {
     if(!d)
         return fail(CKB_ERR_INVALID, "null descriptor");
-    if(d->dtype != CKB_F16 && d->dtype != CKB_BF16)
-        return fail(CKB_ERR_UNSUPPORTED, "conv2d forward supports f16 and bf16");
+    if(d->dtype != CKB_F16 && d->dtype != CKB_BF16 && d->dtype != CKB_I8)
+        return fail(CKB_ERR_UNSUPPORTED, "conv2d forward supports f16, bf16 and int8");
     if(d->dtype == CKB_BF16 && d->epilogue == CKB_EPI_ADD)
         return fail(CKB_ERR_UNSUPPORTED, "the binary16 Add functor has no bfloat16 instance");
     const int e = d->epilogue;
-    if(!(e == CKB_EPI_PASSTHROUGH || e == CKB_EPI_RELU || e == CKB_EPI_ADD_RELU ||
-         e == CKB_EPI_ADD_HARDSWISH || e == CKB_EPI_ADD_RELU_ADD || e == CKB_EPI_ADD))
+    if(d->dtype == CKB_I8)
+    {
+        if(!epilogue_valid_for(e, CKB_I8))
+            return fail(CKB_ERR_UNSUPPORTED, "epilogue %d not available for int8 conv2d forward", e);
+    }
+    else if(!(e == CKB_EPI_PASSTHROUGH || e == CKB_EPI_RELU || e == CKB_EPI_ADD_RELU ||
+              e == CKB_EPI_ADD_HARDSWISH || e == CKB_EPI_ADD_RELU_ADD || e == CKB_EPI_ADD))
         return fail(CKB_ERR_UNSUPPORTED, "epilogue %d not available for conv2d forward", e);
+    const int eb = elem_bytes(d->dtype);
     if(d->N < 1 || d->K < 1 || d->C < 1 || d->Hi < 1 || d->Wi < 1 || d->Y < 1 || d->X < 1)
         return fail(CKB_ERR_UNSUPPORTED, "all extents must be positive");
     if(d->stride_h < 1 || d->stride_w < 1 || d->dilation_h < 1 || d->dilation_w < 1 || d->pad_h < 0 ||
@@ -981,8 +987,8 @@ static int check_conv(const ckb_conv2d_fwd_desc* d, bool need_pointers)
     if(ho != d->Ho || wo != d->Wo || ho < 1 || wo < 1)
         return fail(CKB_ERR_INVALID, "Ho/Wo (%d,%d) do not match the convolution geometry (%d,%d)", d->Ho,
                     d->Wo, ho, wo);
-    if(d->C % 8 != 0)
-        return fail(CKB_ERR_UNSUPPORTED, "C must be a multiple of 8 (16-byte pixel pitch for TMA)");
+    if(d->C % (16 / eb) != 0)
+        return fail(CKB_ERR_UNSUPPORTED, "C must be a multiple of %d (16-byte pixel pitch for TMA)", 16 / eb);
     // Limits of the im2col tensor map: traversal stride <= 8, box corners within [-128, 127].
     if(d->stride_h > 8 || d->stride_w > 8)
         return fail(CKB_ERR_UNSUPPORTED, "convolution stride > 8 not supported");
@@ -997,7 +1003,7 @@ static int check_conv(const ckb_conv2d_fwd_desc* d, bool need_pointers)
         return fail(CKB_ERR_UNSUPPORTED, "N*Ho*Wo must fit in int32");
     // 2 GB per-tensor limit of the reference (device_convnd_fwd_xdl_nhwc_kyxc_nhwk.hpp:884-892)
     const int64_t two_gb = int64_t(1) << 31;
-    if(static_cast<int64_t>(d->N) * d->Hi * d->Wi * d->C * 2 > two_gb || gm * d->K * 2 > two_gb)
+    if(static_cast<int64_t>(d->N) * d->Hi * d->Wi * d->C * eb > two_gb || gm * d->K * eb > two_gb)
         return fail(CKB_ERR_UNSUPPORTED, "tensor larger than 2 GB");
     const int nd = epi_num_d(e);
     if(need_pointers)
@@ -1030,7 +1036,8 @@ int ckb_conv2d_fwd_run(const ckb_conv2d_fwd_desc* d, void* stream, int n_rep, fl
         return fail(CKB_ERR_CUDA, "tensor-map entry points not available");
     const int64_t gm = static_cast<int64_t>(d->N) * d->Ho * d->Wo;
     const int bn     = pick_bn(gm, d->K, dev->sm_count);
-    const int bk     = BK_BYTES / 2; // channels per stage
+    const int eb     = elem_bytes(d->dtype);
+    const int bk     = BK_BYTES / eb; // channels per k block
 
     KernelParams p;
     memset(&p, 0, sizeof(p));
@@ -1038,9 +1045,9 @@ int ckb_conv2d_fwd_run(const ckb_conv2d_fwd_desc* d, void* stream, int n_rep, fl
         // Input as (C, W, H, N); the column of 128 output pixels is walked by the TMA unit.
         cuuint64_t dims[4]    = {static_cast<cuuint64_t>(d->C), static_cast<cuuint64_t>(d->Wi),
                               static_cast<cuuint64_t>(d->Hi), static_cast<cuuint64_t>(d->N)};
-        cuuint64_t strides[3] = {static_cast<cuuint64_t>(d->C) * 2,
-                                 static_cast<cuuint64_t>(d->Wi) * d->C * 2,
-                                 static_cast<cuuint64_t>(d->Hi) * d->Wi * d->C * 2};
+        cuuint64_t strides[3] = {static_cast<cuuint64_t>(d->C) * eb,
+                                 static_cast<cuuint64_t>(d->Wi) * d->C * eb,
+                                 static_cast<cuuint64_t>(d->Hi) * d->Wi * d->C * eb};
         int lower[2]          = {-d->pad_w, -d->pad_h};
         int upper[2]          = {d->pad_w_right - (d->X - 1) * d->dilation_w,
                         d->pad_h_right - (d->Y - 1) * d->dilation_h};
@@ -1057,7 +1064,7 @@ int ckb_conv2d_fwd_run(const ckb_conv2d_fwd_desc* d, void* stream, int n_rep, fl
         // Drivers up to CUDA 13.1 mis-encode im2col maps of tensors smaller than 128 KiB; the
         // published remedy (CUTLASS, cute/atom/copy_traits_sm90_im2col.hpp) clears bit 21 of the
         // descriptor's second 64-bit word.
-        const int64_t in_bytes = static_cast<int64_t>(d->N) * d->Hi * d->Wi * d->C * 2;
+        const int64_t in_bytes = static_cast<int64_t>(d->N) * d->Hi * d->Wi * d->C * eb;
         if(g_driver_version <= 13010 && in_bytes < 131072)
             reinterpret_cast<uint64_t*>(&p.tm_a)[1] &= ~(1ull << 21);
     }
@@ -1072,8 +1079,8 @@ int ckb_conv2d_fwd_run(const ckb_conv2d_fwd_desc* d, void* stream, int n_rep, fl
         // Weights KYXC as (C, Y*X, K): a box never crosses a filter tap, channels beyond C read 0.
         cuuint64_t dims[3]    = {static_cast<cuuint64_t>(d->C), static_cast<cuuint64_t>(d->Y) * d->X,
                               static_cast<cuuint64_t>(d->K)};
-        cuuint64_t strides[2] = {static_cast<cuuint64_t>(d->C) * 2,
-                                 static_cast<cuuint64_t>(d->Y) * d->X * d->C * 2};
+        cuuint64_t strides[2] = {static_cast<cuuint64_t>(d->C) * eb,
+                                 static_cast<cuuint64_t>(d->Y) * d->X * d->C * eb};
         cuuint32_t box[3]     = {static_cast<cuuint32_t>(bk), 1,
                              static_cast<cuuint32_t>((which == 0 ? bn : bn / plan.split) / cg)};
         cuuint32_t estr[3]    = {1, 1, 1};
@@ -1088,6 +1095,8 @@ int ckb_conv2d_fwd_run(const ckb_conv2d_fwd_desc* d, void* stream, int n_rep, fl
     }
     const int nd = epi_num_d(d->epilogue);
     p.epi.kind   = d->epilogue;
+    p.epi.out_i8 = d->dtype == CKB_I8;
+    p.epi.bf16   = d->dtype == CKB_BF16;
     memcpy(p.epi.p, d->epi_params, sizeof(p.epi.p));
     p.epi.e    = d->p_out;
     p.epi.lde  = d->K;
@@ -1095,7 +1104,7 @@ int ckb_conv2d_fwd_run(const ckb_conv2d_fwd_desc* d, void* stream, int n_rep, fl
     p.epi.ldd0 = 0;
     p.epi.d1   = nd >= 2 ? d->p_resi : nullptr;
     p.epi.ldd1 = d->K;
-    bool vec   = aligned16(d->p_out) && d->K % 8 == 0;
+    bool vec   = aligned16(d->p_out) && d->K % (16 / eb) == 0;
     if(nd >= 1)
         vec = vec && aligned16(d->p_bias);
     if(nd >= 2)

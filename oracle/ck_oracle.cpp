@@ -153,6 +153,7 @@ int oracle_conv_out_len(int in_len, int filter_len, int stride, int dilation, in
 static inline float elem_to_float(float v) { return v; }
 static inline float elem_to_float(half v) { return static_cast<float>(v); }
 static inline float elem_to_float(bf16 v) { return bf16_to_float(v); }
+static inline float elem_to_float(int8_t v) { return static_cast<float>(v); }
 
 template <typename T>
 static int conv2d_fwd_naive_t(int epi, const float* params,
@@ -200,6 +201,12 @@ static int conv2d_fwd_naive_t(int epi, const float* params,
         {
             Out[o] = v_acc; // PassThrough, reference_conv_fwd.hpp:169-172
         }
+        else if constexpr(std::is_same<T, int8_t>::value)
+        {
+            // int8 convolution (example/09_convnd_fwd/convnd_fwd_xdl_int8.cpp:23-26): the reference's float v_acc
+            // holds the int32 sum exactly for |sum| < 2^24 (asserted by the tests' value ranges)
+            Out[o] = apply_i8(epi, p, static_cast<int32_t>(v_acc));
+        }
         else if constexpr(std::is_same<T, bf16>::value)
         {
             const bf16 v_d0 = Bias ? Bias[k] : bf16{0};
@@ -236,6 +243,16 @@ int oracle_conv2d_fwd_naive_bf16(int epi, const float* params,
 {
     return conv2d_fwd_naive_t<bf16>(epi, params, in, wei, out, bias, resi, N, K, C, Hi, Wi, Y, X,
                                     Ho, Wo, sh, sw, dh, dw, ph, pw, threads);
+}
+
+int oracle_conv2d_fwd_naive_i8(int epi, const float* params,
+                               const void* in, const void* wei, void* out,
+                               const void* bias, const void* resi,
+                               int N, int K, int C, int Hi, int Wi, int Y, int X, int Ho, int Wo,
+                               int sh, int sw, int dh, int dw, int ph, int pw, int threads)
+{
+    return conv2d_fwd_naive_t<int8_t>(epi, params, in, wei, out, bias, resi, N, K, C, Hi, Wi, Y, X,
+                                      Ho, Wo, sh, sw, dh, dw, ph, pw, threads);
 }
 
 int oracle_conv2d_fwd_naive_f32(const void* in, const void* wei, void* out,

@@ -70,6 +70,8 @@ def lib() -> ctypes.CDLL:
         L.oracle_conv2d_fwd_naive_f32.restype = ctypes.c_int
         L.oracle_conv2d_fwd_naive_bf16.argtypes = conv_args
         L.oracle_conv2d_fwd_naive_bf16.restype = ctypes.c_int
+        L.oracle_conv2d_fwd_naive_i8.argtypes = conv_args
+        L.oracle_conv2d_fwd_naive_i8.restype = ctypes.c_int
         L.oracle_conv_out_len.argtypes = [ctypes.c_int] * 6
         L.oracle_conv_out_len.restype = ctypes.c_int
         L.oracle_epilogue_f16.argtypes = [ctypes.c_int, fp, ctypes.c_float, ctypes.c_uint16, ctypes.c_uint16]
@@ -170,9 +172,9 @@ def conv2d_fwd(inp: np.ndarray, wei: np.ndarray, stride=(1, 1), dilation=(1, 1),
                bias: Optional[np.ndarray] = None, resi: Optional[np.ndarray] = None,
                fast: bool = True, threads: Optional[int] = None) -> np.ndarray:
     """NHWC float16 input (N,Hi,Wi,C), KYXC weights (K,Y,X,C) -> NHWK output (N,Ho,Wo,K).
-    uint16 arrays are bfloat16 bit patterns (naive loops only)."""
+    uint16 arrays are bfloat16 bit patterns, int8 arrays the int8 convolution (naive loops only for both)."""
     is_bf16 = inp.dtype == np.uint16
-    assert inp.dtype in (np.float16, np.uint16) and wei.dtype == inp.dtype
+    assert inp.dtype in (np.float16, np.uint16, np.int8) and wei.dtype == inp.dtype
     dt = inp.dtype
     inp = np.ascontiguousarray(inp)
     wei = np.ascontiguousarray(wei)
@@ -197,6 +199,8 @@ def conv2d_fwd(inp: np.ndarray, wei: np.ndarray, stride=(1, 1), dilation=(1, 1),
     fn = lib().oracle_conv2d_fwd_fast if fast else lib().oracle_conv2d_fwd_naive
     if is_bf16:
         fn = lib().oracle_conv2d_fwd_naive_bf16
+    if inp.dtype == np.int8:
+        fn = lib().oracle_conv2d_fwd_naive_i8
     rc = fn(epilogue, _params(params), inp.ctypes.data, wei.ctypes.data, out.ctypes.data, pb, pr,
             N, K, C, Hi, Wi, Y, X, Ho, Wo, stride[0], stride[1], dilation[0], dilation[1],
             pad[0], pad[1], th)

@@ -122,3 +122,50 @@ def test_batch_shards_compose(cuda_device):
     whole, _ = run_conv(inp, wei, (2, 2), (1, 1), (1, 1), ck.AddRelu(), bias)
     parts = [run_conv(inp[i:i + 2], wei, (2, 2), (1, 1), (1, 1), ck.AddRelu(), bias)[0] for i in range(0, 8, 2)]
     np.testing.assert_array_equal(np.concatenate(parts).view(np.uint16), whole.view(np.uint16))
+
+
+# int8 convolution (example/09_convnd_fwd/convnd_fwd_xdl_int8.cpp:23-26: int8 in / weights / out, int32 accumulate).
+# N, C, Hi, Wi, K, Y, X, stride, dilation, pad — C is a multiple of 16 (16-byte pixel pitch)
+CASES_I8 = [
+    (4, 64, 36, 36, 256, 3, 3, (2, 2), (2, 2), (2, 2)),
+    (2, 192, 15, 15, 256, 3, 3, (2, 2), (1, 1), (1, 1)),
+    (3, 16, 11, 7, 48, 3, 2, (1, 1), (1, 1), (1, 1)),     # C far below one k block of 128 channels
+    (2, 144, 9, 12, 40, 2, 3, (1, 2), (2, 1), (1, 2)),    # channel tail (144 = 128 + 16), K not a multiple of 16
+]
+
+
+def run_conv_i8(inp, wei, stride, dilation, pad, op):
+    N, Hi, Wi, C = inp.shape
+    K, Y, X, _ = wei.shape
+    Ho = oracle.conv_out_len(Hi, Y, stride[0], dilation[0], pad[0], pad[0])
+    Wo = oracle.conv_out_len(Wi, X, stride[1], dilation[1], pad[1], pad[1])
+    di, dw = H.to_dev(inp), H.to_dev(wei)
+    out = torch.full((N, Ho, Wo, K), -77, dtype=torch.int8, device="cuda")
+    conv = ck.DeviceConvFwd(capi.CKB_I8)
+    arg = conv.MakeArgument(di.data_ptr(), dw.data_ptr(), out.data_ptr(), N, K, C, (Hi, Wi), (Y, X), (Ho, Wo),
+                            stride, dilation, pad, pad, None, None, op)
+    assert conv.IsSupportedArgument(arg), capi.last_error()
+    conv.MakeInvoker().Run(arg)
+    torch.cuda.synchronize()
+    assert ck.device_status() == 0
+    return out.cpu().numpy()
+
+
+@pytest.mark.parametrize("case", CASES_I8)
+def test_conv2d_fwd_int8_bit_exact(cuda_device, case):
+    N, C, Hi, Wi, K, Y, X, s, d, p = case
+    rng = np.random.default_rng(N * 31 + C)
+    inp = rng.integers(-5, 6, (N, Hi, Wi, C)).astype(np.int8)
+    wei = rng.integers(-5, 6, (K, Y, X, C)).astype(np.int8)
+    for op in (ck.RequantReluRequant(0.03, 1.0), ck.RequantReluRequantRne(0.03, 14.0), ck.Relu(), ck.PassThrough()):
+        out = run_conv_i8(inp, wei, s, d, p, op)
+        ref = oracle.conv2d_fwd(inp, wei, s, d, p, epilogue=op.kind, params=op.params)
+        np.testing.assert_array_equal(out, ref)
+
+
+def test_conv2d_fwd_int8_needs_16_channel_pitch(cuda_device):
+    conv = ck.DeviceConvFwd(capi.CKB_I8)
+    arg = conv.MakeArgument(0x1000, 0x2000, 0x3000, 2, 32, 24, (8, 8), (3, 3), (8, 8), (1, 1), (1, 1), (1, 1), (1, 1),
+                            None, None, ck.PassThrough())
+    assert not conv.IsSupportedArgument(arg)
+    assert "multiple of 16" in capi.last_error()

@@ -183,3 +183,22 @@ def test_bf16_gemm_blocked_equals_naive_and_integer_exact():
     for epi, d in [(oracle.EPI_FASTGELU, None), (oracle.EPI_ADD_RELU, d0)]:
         np.testing.assert_array_equal(oracle.gemm(ar, br.T, epi, None, d, fast=False),
                                       oracle.gemm(ar, br.T, epi, None, d, fast=True))
+
+
+def test_int8_conv_matches_exact_integer_arithmetic():
+    """int8 convolution of the oracle (int32-exact sum, static_cast<int8_t> store) against numpy int64 arithmetic."""
+    rng = np.random.default_rng(0)
+    inp = rng.integers(-5, 6, (2, 5, 6, 16)).astype(np.int8)
+    wei = rng.integers(-5, 6, (8, 3, 3, 16)).astype(np.int8)
+    out = oracle.conv2d_fwd(inp, wei, (1, 1), (1, 1), (1, 1), epilogue=oracle.EPI_PASSTHROUGH)
+    padded = np.zeros((2, 7, 8, 16), dtype=np.int64)
+    padded[:, 1:6, 1:7, :] = inp
+    ref = np.zeros((2, 5, 6, 8), dtype=np.int64)
+    for y in range(3):
+        for x in range(3):
+            ref += np.einsum("nhwc,kc->nhwk", padded[:, y:y + 5, x:x + 6, :], wei[:, y, x, :].astype(np.int64))
+    np.testing.assert_array_equal(out, ref.astype(np.int8))  # low 8 bits, as static_cast<int8_t>(int32)
+    relu = oracle.conv2d_fwd(inp, wei, (1, 1), (1, 1), (1, 1), epilogue=oracle.EPI_REQUANT_RELU_REQUANT,
+                             params=[0.03, 1.0])
+    expect = np.clip(np.trunc(np.float32(1.0) * np.maximum(np.float32(0.03) * ref.astype(np.float32), 0)), -128, 127)
+    np.testing.assert_array_equal(relu, expect.astype(np.int8))
