@@ -75,6 +75,25 @@ class Conv2dFwdDesc(Structure):
     ]
 
 
+class Conv3dFwdDesc(Structure):
+    """struct ckb_conv3d_fwd_desc"""
+    _fields_ = [
+        ("dtype", c_int32), ("epilogue", c_int32),
+        ("N", c_int32), ("K", c_int32), ("C", c_int32),
+        ("Di", c_int32), ("Hi", c_int32), ("Wi", c_int32),
+        ("Z", c_int32), ("Y", c_int32), ("X", c_int32),
+        ("Do", c_int32), ("Ho", c_int32), ("Wo", c_int32),
+        ("stride_d", c_int32), ("stride_h", c_int32), ("stride_w", c_int32),
+        ("dilation_d", c_int32), ("dilation_h", c_int32), ("dilation_w", c_int32),
+        ("pad_d", c_int32), ("pad_h", c_int32), ("pad_w", c_int32),
+        ("pad_d_right", c_int32), ("pad_h_right", c_int32), ("pad_w_right", c_int32),
+        ("reserved0", c_int32),
+        ("p_in", c_void_p), ("p_wei", c_void_p), ("p_out", c_void_p),
+        ("p_bias", c_void_p), ("p_resi", c_void_p),
+        ("epi_params", c_float * 4),
+    ]
+
+
 # name -> (restype, argtypes); every symbol include/ckb200.h declares.
 SYMBOLS = {
     "ckb_abi_version": (c_int, []),
@@ -99,6 +118,8 @@ SYMBOLS = {
     "ckb_grouped_gemm_run_noalloc": (c_int, [POINTER(GroupedGemmDesc), c_void_p]),
     "ckb_conv2d_fwd_supported": (c_int, [POINTER(Conv2dFwdDesc)]),
     "ckb_conv2d_fwd_run": (c_int, [POINTER(Conv2dFwdDesc), c_void_p, c_int, POINTER(c_float)]),
+    "ckb_conv3d_fwd_supported": (c_int, [POINTER(Conv3dFwdDesc)]),
+    "ckb_conv3d_fwd_run": (c_int, [POINTER(Conv3dFwdDesc), c_void_p, c_int, POINTER(c_float)]),
 }
 
 _lib = None

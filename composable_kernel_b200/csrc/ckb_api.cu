@@ -958,73 +958,120 @@ int ckb_grouped_gemm_run_noalloc(const ckb_grouped_gemm_desc* g, void* stream_)
     return CKB_OK;
 }
 
-// ---- conv2d forward -------------------------------------------------------------------------------
-static int check_conv(const ckb_conv2d_fwd_desc* d, bool need_pointers)
+// ---- convolution forward (1-D and 2-D through the 2-D entry point, 3-D) ----------------------------
+// One description for both entry points: a 2-D problem is a 3-D one with depth 1.
+struct ConvProblem
 {
-    if(!d)
-        return fail(CKB_ERR_INVALID, "null descriptor");
-    if(d->dtype != CKB_F16 && d->dtype != CKB_BF16 && d->dtype != CKB_I8)
-        return fail(CKB_ERR_UNSUPPORTED, "conv2d forward supports f16, bf16 and int8");
-    if(d->dtype == CKB_BF16 && d->epilogue == CKB_EPI_ADD)
+    int dtype, epilogue, nd; // nd = 2 (4-D im2col map) or 3 (5-D)
+    int N, K, C;
+    int Di, Hi, Wi, Z, Y, X, Do, Ho, Wo;
+    int sd, sh, sw, dd, dh, dw;
+    int pd, ph, pw, pdr, phr, pwr;
+    const void *p_in, *p_wei, *p_bias, *p_resi;
+    void* p_out;
+    float epi_params[4];
+};
+
+static ConvProblem problem_of_2d(const ckb_conv2d_fwd_desc* d)
+{
+    ConvProblem c{};
+    c.dtype = d->dtype, c.epilogue = d->epilogue, c.nd = 2;
+    c.N = d->N, c.K = d->K, c.C = d->C;
+    c.Di = 1, c.Hi = d->Hi, c.Wi = d->Wi, c.Z = 1, c.Y = d->Y, c.X = d->X, c.Do = 1, c.Ho = d->Ho, c.Wo = d->Wo;
+    c.sd = 1, c.sh = d->stride_h, c.sw = d->stride_w, c.dd = 1, c.dh = d->dilation_h, c.dw = d->dilation_w;
+    c.pd = 0, c.ph = d->pad_h, c.pw = d->pad_w, c.pdr = 0, c.phr = d->pad_h_right, c.pwr = d->pad_w_right;
+    c.p_in = d->p_in, c.p_wei = d->p_wei, c.p_bias = d->p_bias, c.p_resi = d->p_resi, c.p_out = d->p_out;
+    memcpy(c.epi_params, d->epi_params, sizeof(c.epi_params));
+    return c;
+}
+
+static ConvProblem problem_of_3d(const ckb_conv3d_fwd_desc* d)
+{
+    ConvProblem c{};
+    c.dtype = d->dtype, c.epilogue = d->epilogue, c.nd = 3;
+    c.N = d->N, c.K = d->K, c.C = d->C;
+    c.Di = d->Di, c.Hi = d->Hi, c.Wi = d->Wi, c.Z = d->Z, c.Y = d->Y, c.X = d->X;
+    c.Do = d->Do, c.Ho = d->Ho, c.Wo = d->Wo;
+    c.sd = d->stride_d, c.sh = d->stride_h, c.sw = d->stride_w;
+    c.dd = d->dilation_d, c.dh = d->dilation_h, c.dw = d->dilation_w;
+    c.pd = d->pad_d, c.ph = d->pad_h, c.pw = d->pad_w;
+    c.pdr = d->pad_d_right, c.phr = d->pad_h_right, c.pwr = d->pad_w_right;
+    c.p_in = d->p_in, c.p_wei = d->p_wei, c.p_bias = d->p_bias, c.p_resi = d->p_resi, c.p_out = d->p_out;
+    memcpy(c.epi_params, d->epi_params, sizeof(c.epi_params));
+    return c;
+}
+
+static int out_len(int in, int pad_l, int pad_r, int filt, int dil, int stride)
+{
+    return (in + pad_l + pad_r - ((filt - 1) * dil + 1)) / stride + 1;
+}
+
+static int check_conv(const ConvProblem& c, bool need_pointers)
+{
+    if(c.dtype != CKB_F16 && c.dtype != CKB_BF16 && c.dtype != CKB_I8)
+        return fail(CKB_ERR_UNSUPPORTED, "convolution forward supports f16, bf16 and int8");
+    if(c.dtype == CKB_BF16 && c.epilogue == CKB_EPI_ADD)
         return fail(CKB_ERR_UNSUPPORTED, "the binary16 Add functor has no bfloat16 instance");
-    const int e = d->epilogue;
-    if(d->dtype == CKB_I8)
+    const int e = c.epilogue;
+    if(c.dtype == CKB_I8)
     {
         if(!epilogue_valid_for(e, CKB_I8))
-            return fail(CKB_ERR_UNSUPPORTED, "epilogue %d not available for int8 conv2d forward", e);
+            return fail(CKB_ERR_UNSUPPORTED, "epilogue %d not available for int8 convolution forward", e);
     }
     else if(!(e == CKB_EPI_PASSTHROUGH || e == CKB_EPI_RELU || e == CKB_EPI_ADD_RELU ||
               e == CKB_EPI_ADD_HARDSWISH || e == CKB_EPI_ADD_RELU_ADD || e == CKB_EPI_ADD))
-        return fail(CKB_ERR_UNSUPPORTED, "epilogue %d not available for conv2d forward", e);
-    const int eb = elem_bytes(d->dtype);
-    if(d->N < 1 || d->K < 1 || d->C < 1 || d->Hi < 1 || d->Wi < 1 || d->Y < 1 || d->X < 1)
+        return fail(CKB_ERR_UNSUPPORTED, "epilogue %d not available for convolution forward", e);
+    const int eb = elem_bytes(c.dtype);
+    if(c.N < 1 || c.K < 1 || c.C < 1 || c.Di < 1 || c.Hi < 1 || c.Wi < 1 || c.Z < 1 || c.Y < 1 || c.X < 1)
         return fail(CKB_ERR_UNSUPPORTED, "all extents must be positive");
-    if(d->stride_h < 1 || d->stride_w < 1 || d->dilation_h < 1 || d->dilation_w < 1 || d->pad_h < 0 ||
-       d->pad_w < 0 || d->pad_h_right < 0 || d->pad_w_right < 0)
+    if(c.sd < 1 || c.sh < 1 || c.sw < 1 || c.dd < 1 || c.dh < 1 || c.dw < 1 || c.pd < 0 || c.ph < 0 || c.pw < 0 ||
+       c.pdr < 0 || c.phr < 0 || c.pwr < 0)
         return fail(CKB_ERR_INVALID, "strides and dilations must be >= 1, pads >= 0");
-    const int ho = (d->Hi + d->pad_h + d->pad_h_right - ((d->Y - 1) * d->dilation_h + 1)) / d->stride_h + 1;
-    const int wo = (d->Wi + d->pad_w + d->pad_w_right - ((d->X - 1) * d->dilation_w + 1)) / d->stride_w + 1;
-    if(ho != d->Ho || wo != d->Wo || ho < 1 || wo < 1)
-        return fail(CKB_ERR_INVALID, "Ho/Wo (%d,%d) do not match the convolution geometry (%d,%d)", d->Ho,
-                    d->Wo, ho, wo);
-    if(d->C % (16 / eb) != 0)
+    const int dd = out_len(c.Di, c.pd, c.pdr, c.Z, c.dd, c.sd);
+    const int ho = out_len(c.Hi, c.ph, c.phr, c.Y, c.dh, c.sh);
+    const int wo = out_len(c.Wi, c.pw, c.pwr, c.X, c.dw, c.sw);
+    if(dd != c.Do || ho != c.Ho || wo != c.Wo || dd < 1 || ho < 1 || wo < 1)
+        return fail(CKB_ERR_INVALID, "Do/Ho/Wo (%d,%d,%d) do not match the convolution geometry (%d,%d,%d)", c.Do,
+                    c.Ho, c.Wo, dd, ho, wo);
+    if(c.C % (16 / eb) != 0)
         return fail(CKB_ERR_UNSUPPORTED, "C must be a multiple of %d (16-byte pixel pitch for TMA)", 16 / eb);
-    // Limits of the im2col tensor map: traversal stride <= 8, box corners within [-128, 127].
-    if(d->stride_h > 8 || d->stride_w > 8)
+    // Limits of the im2col tensor map: traversal stride <= 8, box corners within [-128, 127] (4-D maps) or
+    // [-16, 15] (5-D maps).
+    if(c.sd > 8 || c.sh > 8 || c.sw > 8)
         return fail(CKB_ERR_UNSUPPORTED, "convolution stride > 8 not supported");
-    const int up_h = d->pad_h_right - (d->Y - 1) * d->dilation_h;
-    const int up_w = d->pad_w_right - (d->X - 1) * d->dilation_w;
-    if(d->pad_h > 128 || d->pad_w > 128 || up_h < -128 || up_w < -128 || up_h > 127 || up_w > 127)
+    const int lo = c.nd == 3 ? 16 : 128, hi = c.nd == 3 ? 15 : 127;
+    const int up_d = c.pdr - (c.Z - 1) * c.dd, up_h = c.phr - (c.Y - 1) * c.dh, up_w = c.pwr - (c.X - 1) * c.dw;
+    if(c.pd > lo || c.ph > lo || c.pw > lo || up_d < -lo || up_h < -lo || up_w < -lo || up_d > hi || up_h > hi ||
+       up_w > hi)
         return fail(CKB_ERR_UNSUPPORTED, "padding / filter extent beyond the im2col box-corner range");
-    if((d->Y - 1) * d->dilation_h > 65535 || (d->X - 1) * d->dilation_w > 65535)
-        return fail(CKB_ERR_UNSUPPORTED, "filter offset beyond 16 bits");
-    const int64_t gm = static_cast<int64_t>(d->N) * d->Ho * d->Wo;
+    const int max_off = c.nd == 3 ? 15 : 255; // im2col offsets share 16 bits: 8 bits each in a 4-D map, 4 bits each in 5-D
+    if((c.Z - 1) * c.dd > max_off || (c.Y - 1) * c.dh > max_off || (c.X - 1) * c.dw > max_off)
+        return fail(CKB_ERR_UNSUPPORTED, "filter offset beyond the im2col offset range");
+    const int64_t gm = static_cast<int64_t>(c.N) * c.Do * c.Ho * c.Wo;
     if(gm > 0x7FFFFF00ll)
-        return fail(CKB_ERR_UNSUPPORTED, "N*Ho*Wo must fit in int32");
+        return fail(CKB_ERR_UNSUPPORTED, "N*Do*Ho*Wo must fit in int32");
     // 2 GB per-tensor limit of the reference (device_convnd_fwd_xdl_nhwc_kyxc_nhwk.hpp:884-892)
     const int64_t two_gb = int64_t(1) << 31;
-    if(static_cast<int64_t>(d->N) * d->Hi * d->Wi * d->C * eb > two_gb || gm * d->K * eb > two_gb)
+    if(static_cast<int64_t>(c.N) * c.Di * c.Hi * c.Wi * c.C * eb > two_gb || gm * c.K * eb > two_gb)
         return fail(CKB_ERR_UNSUPPORTED, "tensor larger than 2 GB");
     const int nd = epi_num_d(e);
     if(need_pointers)
     {
-        if(!d->p_in || !d->p_wei || !d->p_out)
+        if(!c.p_in || !c.p_wei || !c.p_out)
             return fail(CKB_ERR_INVALID, "null tensor pointer");
-        if(!aligned16(d->p_in) || !aligned16(d->p_wei))
+        if(!aligned16(c.p_in) || !aligned16(c.p_wei))
             return fail(CKB_ERR_UNSUPPORTED, "input and weights must be 16-byte aligned");
-        if(nd >= 1 && !d->p_bias)
+        if(nd >= 1 && !c.p_bias)
             return fail(CKB_ERR_INVALID, "epilogue needs a bias pointer");
-        if(nd >= 2 && !d->p_resi)
+        if(nd >= 2 && !c.p_resi)
             return fail(CKB_ERR_INVALID, "epilogue needs a residual pointer");
     }
     return CKB_OK;
 }
 
-int ckb_conv2d_fwd_supported(const ckb_conv2d_fwd_desc* desc) { return check_conv(desc, false); }
-
-int ckb_conv2d_fwd_run(const ckb_conv2d_fwd_desc* d, void* stream, int n_rep, float* avg_ms)
+static int run_conv(const ConvProblem& c, void* stream, int n_rep, float* avg_ms)
 {
-    int rc = check_conv(d, true);
+    int rc = check_conv(c, true);
     if(rc)
         return rc;
     DeviceInfo* dev = nullptr;
@@ -1034,109 +1081,144 @@ int ckb_conv2d_fwd_run(const ckb_conv2d_fwd_desc* d, void* stream, int n_rep, fl
     load_entry_points();
     if(!g_encode_im2col || !g_encode_tiled)
         return fail(CKB_ERR_CUDA, "tensor-map entry points not available");
-    const int64_t gm = static_cast<int64_t>(d->N) * d->Ho * d->Wo;
-    const int bn     = pick_bn(gm, d->K, dev->sm_count);
-    const int eb     = elem_bytes(d->dtype);
+    const int64_t gm = static_cast<int64_t>(c.N) * c.Do * c.Ho * c.Wo;
+    const int bn     = pick_bn(gm, c.K, dev->sm_count);
+    const int eb     = elem_bytes(c.dtype);
     const int bk     = BK_BYTES / eb; // channels per k block
 
     KernelParams p;
     memset(&p, 0, sizeof(p));
     {
-        // Input as (C, W, H, N); the column of 128 output pixels is walked by the TMA unit.
-        cuuint64_t dims[4]    = {static_cast<cuuint64_t>(d->C), static_cast<cuuint64_t>(d->Wi),
-                              static_cast<cuuint64_t>(d->Hi), static_cast<cuuint64_t>(d->N)};
-        cuuint64_t strides[3] = {static_cast<cuuint64_t>(d->C) * eb,
-                                 static_cast<cuuint64_t>(d->Wi) * d->C * eb,
-                                 static_cast<cuuint64_t>(d->Hi) * d->Wi * d->C * eb};
-        int lower[2]          = {-d->pad_w, -d->pad_h};
-        int upper[2]          = {d->pad_w_right - (d->X - 1) * d->dilation_w,
-                        d->pad_h_right - (d->Y - 1) * d->dilation_h};
-        cuuint32_t estr[4]    = {1, static_cast<cuuint32_t>(d->stride_w),
-                              static_cast<cuuint32_t>(d->stride_h), 1};
-        CUresult r = g_encode_im2col(&p.tm_a, tm_dtype(d->dtype), 4,
-                                     const_cast<void*>(d->p_in), dims, strides, lower, upper,
-                                     static_cast<cuuint32_t>(bk), static_cast<cuuint32_t>(BM), estr,
+        // Input as (C, W, H[, D], N); the column of 128 output pixels is walked by the TMA unit.
+        const cuuint64_t C = c.C, W = c.Wi, H = c.Hi, D = c.Di;
+        cuuint64_t dims[5], strides[4];
+        cuuint32_t estr[5];
+        int lower[3], upper[3];
+        int rank;
+        if(c.nd == 3)
+        {
+            rank    = 5;
+            dims[0] = C, dims[1] = W, dims[2] = H, dims[3] = D, dims[4] = c.N;
+            strides[0] = C * eb, strides[1] = W * C * eb, strides[2] = H * W * C * eb, strides[3] = D * H * W * C * eb;
+            lower[0] = -c.pw, lower[1] = -c.ph, lower[2] = -c.pd;
+            upper[0] = c.pwr - (c.X - 1) * c.dw, upper[1] = c.phr - (c.Y - 1) * c.dh, upper[2] = c.pdr - (c.Z - 1) * c.dd;
+            estr[0] = 1, estr[1] = c.sw, estr[2] = c.sh, estr[3] = c.sd, estr[4] = 1;
+        }
+        else
+        {
+            rank    = 4;
+            dims[0] = C, dims[1] = W, dims[2] = H, dims[3] = c.N;
+            strides[0] = C * eb, strides[1] = W * C * eb, strides[2] = H * W * C * eb;
+            lower[0] = -c.pw, lower[1] = -c.ph;
+            upper[0] = c.pwr - (c.X - 1) * c.dw, upper[1] = c.phr - (c.Y - 1) * c.dh;
+            estr[0] = 1, estr[1] = c.sw, estr[2] = c.sh, estr[3] = 1;
+        }
+        CUresult r = g_encode_im2col(&p.tm_a, tm_dtype(c.dtype), rank, const_cast<void*>(c.p_in), dims, strides, lower,
+                                     upper, static_cast<cuuint32_t>(bk), static_cast<cuuint32_t>(BM), estr,
                                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if(r != CUDA_SUCCESS)
             return fail(CKB_ERR_CUDA, "cuTensorMapEncodeIm2col failed (CUresult %d)", static_cast<int>(r));
         // Drivers up to CUDA 13.1 mis-encode im2col maps of tensors smaller than 128 KiB; the
         // published remedy (CUTLASS, cute/atom/copy_traits_sm90_im2col.hpp) clears bit 21 of the
         // descriptor's second 64-bit word.
-        const int64_t in_bytes = static_cast<int64_t>(d->N) * d->Hi * d->Wi * d->C * eb;
+        const int64_t in_bytes = static_cast<int64_t>(c.N) * c.Di * c.Hi * c.Wi * c.C * eb;
         if(g_driver_version <= 13010 && in_bytes < 131072)
             reinterpret_cast<uint64_t*>(&p.tm_a)[1] &= ~(1ull << 21);
     }
-    const int64_t tiles_n = (d->K + bn - 1) / bn;
+    const int64_t tiles_n = (c.K + bn - 1) / bn;
     const int cg          = pick_cg(((gm + BM - 1) / BM) * tiles_n, bn, dev->sm_count);
     const int64_t tiles_m = (gm + BM * cg - 1) / (BM * cg);
     if(tiles_m * tiles_n > 0x3FFFFFFFll)
         return fail(CKB_ERR_UNSUPPORTED, "too many tiles");
     const WorkPlan plan = plan_work(tiles_m * tiles_n, dev->sm_count / cg, bn, cg);
+    const int64_t taps  = static_cast<int64_t>(c.Z) * c.Y * c.X;
     for(int which = 0; which < 2; ++which)
     {
-        // Weights KYXC as (C, Y*X, K): a box never crosses a filter tap, channels beyond C read 0.
-        cuuint64_t dims[3]    = {static_cast<cuuint64_t>(d->C), static_cast<cuuint64_t>(d->Y) * d->X,
-                              static_cast<cuuint64_t>(d->K)};
-        cuuint64_t strides[2] = {static_cast<cuuint64_t>(d->C) * eb,
-                                 static_cast<cuuint64_t>(d->Y) * d->X * d->C * eb};
+        // Weights K[Z]YXC as (C, taps, K): a box never crosses a filter tap, channels beyond C read 0.
+        cuuint64_t dims[3]    = {static_cast<cuuint64_t>(c.C), static_cast<cuuint64_t>(taps), static_cast<cuuint64_t>(c.K)};
+        cuuint64_t strides[2] = {static_cast<cuuint64_t>(c.C) * eb, static_cast<cuuint64_t>(taps) * c.C * eb};
         cuuint32_t box[3]     = {static_cast<cuuint32_t>(bk), 1,
                              static_cast<cuuint32_t>((which == 0 ? bn : bn / plan.split) / cg)};
         cuuint32_t estr[3]    = {1, 1, 1};
-        CUresult r = g_encode_tiled(which == 0 ? &p.tm_b : &p.tm_b_split, tm_dtype(d->dtype),
-                                    3, const_cast<void*>(d->p_wei), dims, strides, box, estr,
-                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+        CUresult r = g_encode_tiled(which == 0 ? &p.tm_b : &p.tm_b_split, tm_dtype(c.dtype), 3,
+                                    const_cast<void*>(c.p_wei), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if(r != CUDA_SUCCESS)
-            return fail(CKB_ERR_CUDA, "cuTensorMapEncodeTiled (weights) failed (CUresult %d)",
-                        static_cast<int>(r));
+            return fail(CKB_ERR_CUDA, "cuTensorMapEncodeTiled (weights) failed (CUresult %d)", static_cast<int>(r));
     }
-    const int nd = epi_num_d(d->epilogue);
-    p.epi.kind   = d->epilogue;
-    p.epi.out_i8 = d->dtype == CKB_I8;
-    p.epi.bf16   = d->dtype == CKB_BF16;
-    memcpy(p.epi.p, d->epi_params, sizeof(p.epi.p));
-    p.epi.e    = d->p_out;
-    p.epi.lde  = d->K;
-    p.epi.d0   = nd >= 1 ? d->p_bias : nullptr;
+    const int nd = epi_num_d(c.epilogue);
+    p.epi.kind   = c.epilogue;
+    p.epi.out_i8 = c.dtype == CKB_I8;
+    p.epi.bf16   = c.dtype == CKB_BF16;
+    memcpy(p.epi.p, c.epi_params, sizeof(p.epi.p));
+    p.epi.e    = c.p_out;
+    p.epi.lde  = c.K;
+    p.epi.d0   = nd >= 1 ? c.p_bias : nullptr;
     p.epi.ldd0 = 0;
-    p.epi.d1   = nd >= 2 ? d->p_resi : nullptr;
-    p.epi.ldd1 = d->K;
-    bool vec   = aligned16(d->p_out) && d->K % (16 / eb) == 0;
+    p.epi.d1   = nd >= 2 ? c.p_resi : nullptr;
+    p.epi.ldd1 = c.K;
+    bool vec   = aligned16(c.p_out) && c.K % (16 / eb) == 0;
     if(nd >= 1)
-        vec = vec && aligned16(d->p_bias);
+        vec = vec && aligned16(c.p_bias);
     if(nd >= 2)
-        vec = vec && aligned16(d->p_resi);
+        vec = vec && aligned16(c.p_resi);
     p.total_tiles   = static_cast<int32_t>(tiles_m * tiles_n);
     p.split_start   = plan.split_start;
     p.split         = plan.split;
     p.total_work    = plan.total_work;
     p.num_slots     = (plan.total_work + plan.grid / cg - 1) / (plan.grid / cg);
     p.M             = static_cast<int32_t>(gm);
-    p.N             = d->K;
+    p.N             = c.K;
     p.tiles_n       = static_cast<int32_t>(tiles_n);
-    p.conv.Ho       = d->Ho;
-    p.conv.Wo       = d->Wo;
-    p.conv.HoWo     = d->Ho * d->Wo;
-    p.conv.Y        = d->Y;
-    p.conv.X        = d->X;
-    p.conv.c_blocks = (d->C + bk - 1) / bk;
-    p.conv.stride_h = d->stride_h;
-    p.conv.stride_w = d->stride_w;
-    p.conv.dil_h    = d->dilation_h;
-    p.conv.dil_w    = d->dilation_w;
-    p.conv.pad_h    = d->pad_h;
-    p.conv.pad_w    = d->pad_w;
-    p.num_kb        = d->Y * d->X * p.conv.c_blocks;
+    p.conv.nd3      = c.nd == 3 ? 1 : 0;
+    p.conv.Do       = c.Do;
+    p.conv.Ho       = c.Ho;
+    p.conv.Wo       = c.Wo;
+    p.conv.HoWo     = c.Ho * c.Wo;
+    p.conv.DoHoWo   = c.Do * c.Ho * c.Wo;
+    p.conv.Z        = c.Z;
+    p.conv.Y        = c.Y;
+    p.conv.X        = c.X;
+    p.conv.c_blocks = (c.C + bk - 1) / bk;
+    p.conv.stride_d = c.sd;
+    p.conv.stride_h = c.sh;
+    p.conv.stride_w = c.sw;
+    p.conv.dil_d    = c.dd;
+    p.conv.dil_h    = c.dh;
+    p.conv.dil_w    = c.dw;
+    p.conv.pad_d    = c.pd;
+    p.conv.pad_h    = c.ph;
+    p.conv.pad_w    = c.pw;
+    p.num_kb        = static_cast<int32_t>(taps * p.conv.c_blocks);
     p.vec_ok        = vec ? 1 : 0;
     p.wait_limit_ns = wait_limit_ns();
     p.status        = dev->status;
-    LaunchFn fn = find_launch(MODE_CONV, kind_of(d->dtype), d->epilogue);
+    LaunchFn fn = find_launch(MODE_CONV, kind_of(c.dtype), c.epilogue);
     if(!fn)
-        return fail(CKB_ERR_UNSUPPORTED, "no kernel instance for epilogue %d", d->epilogue);
+        return fail(CKB_ERR_UNSUPPORTED, "no kernel instance for epilogue %d", c.epilogue);
     return run_timed(fn, bn, cg, p, plan.grid, static_cast<cudaStream_t>(stream), n_rep, avg_ms);
+}
+
+int ckb_conv2d_fwd_supported(const ckb_conv2d_fwd_desc* desc)
+{
+    return desc ? check_conv(problem_of_2d(desc), false) : fail(CKB_ERR_INVALID, "null descriptor");
+}
+
+int ckb_conv2d_fwd_run(const ckb_conv2d_fwd_desc* d, void* stream, int n_rep, float* avg_ms)
+{
+    return d ? run_conv(problem_of_2d(d), stream, n_rep, avg_ms) : fail(CKB_ERR_INVALID, "null descriptor");
+}
+
+int ckb_conv3d_fwd_supported(const ckb_conv3d_fwd_desc* desc)
+{
+    return desc ? check_conv(problem_of_3d(desc), false) : fail(CKB_ERR_INVALID, "null descriptor");
+}
+
+int ckb_conv3d_fwd_run(const ckb_conv3d_fwd_desc* d, void* stream, int n_rep, float* avg_ms)
+{
+    return d ? run_conv(problem_of_3d(d), stream, n_rep, avg_ms) : fail(CKB_ERR_INVALID, "null descriptor");
 }
 
 } // extern "C"

@@ -109,8 +109,10 @@ struct alignas(128) GroupEntry
 struct ConvGeom
 {
     int32_t Ho, Wo, HoWo;
-    int32_t Y, X, c_blocks; // c_blocks = ceil(C / channels per stage)
+    int32_t Y, X, c_blocks; // c_blocks = ceil(C / channels per k block)
     int32_t stride_h, stride_w, dil_h, dil_w, pad_h, pad_w;
+    // 3-D convolution (nd3 != 0): depth extents; a 2-D problem has Do = Z = 1
+    int32_t nd3, Do, DoHoWo, Z, stride_d, dil_d, pad_d, pad_;
 };
 
 struct KernelParams
@@ -641,25 +643,30 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
             const int box_row         = (is_b ? b_row0 : a_row0) + box_i * BK_ELEMS;
             const CUtensorMap* box_tm = is_b ? tm_b : tm_a;
             // CONV: first output pixel of this CTA's rows in (n, ho, wo)
-            int cv_n = 0, cv_h = 0, cv_w = 0;
+            int cv_n = 0, cv_d = 0, cv_h = 0, cv_w = 0;
             if constexpr(MODE == MODE_CONV)
             {
-                const int m0  = a_row0;
-                cv_n          = m0 / P.conv.HoWo;
-                const int rem = m0 - cv_n * P.conv.HoWo;
-                const int ho  = rem / P.conv.Wo;
-                const int wo  = rem - ho * P.conv.Wo;
-                cv_h          = ho * P.conv.stride_h - P.conv.pad_h;
-                cv_w          = wo * P.conv.stride_w - P.conv.pad_w;
+                const int m0 = a_row0;
+                cv_n         = m0 / P.conv.DoHoWo;
+                int rem      = m0 - cv_n * P.conv.DoHoWo;
+                const int od = rem / P.conv.HoWo;
+                rem -= od * P.conv.HoWo;
+                const int ho = rem / P.conv.Wo;
+                const int wo = rem - ho * P.conv.Wo;
+                cv_d         = od * P.conv.stride_d - P.conv.pad_d;
+                cv_h         = ho * P.conv.stride_h - P.conv.pad_h;
+                cv_w         = wo * P.conv.stride_w - P.conv.pad_w;
             }
-            // CONV: filter tap and channel block of this lane's k block (advanced by KSUB per stage)
-            int cv_y = 0, cv_x = 0, cv_cb = 0;
+            // CONV: filter tap (z, y, x) and channel block of this lane's k block (advanced by KSUB per stage)
+            int cv_z = 0, cv_y = 0, cv_x = 0, cv_cb = 0;
             if constexpr(MODE == MODE_CONV)
             {
-                const int taps = box_j / P.conv.c_blocks;
-                cv_cb          = box_j - taps * P.conv.c_blocks;
-                cv_y           = taps / P.conv.X;
-                cv_x           = taps - cv_y * P.conv.X;
+                int taps = box_j / P.conv.c_blocks;
+                cv_cb    = box_j - taps * P.conv.c_blocks;
+                cv_x     = taps % P.conv.X;
+                taps /= P.conv.X;
+                cv_y = taps % P.conv.Y;
+                cv_z = taps / P.conv.Y;
             }
             for(int kb = 0; kb < wi.num_kb; kb += KSUB)
             {
@@ -678,23 +685,32 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                 {
                     if constexpr(MODE == MODE_CONV)
                     {
-                        if(!is_b)
+                        const uint16_t off_w = static_cast<uint16_t>(cv_x * P.conv.dil_w);
+                        const uint16_t off_h = static_cast<uint16_t>(cv_y * P.conv.dil_h);
+                        if(!is_b && P.conv.nd3 == 0)
                         {
                             if constexpr(CG == 2)
-                                tma_load_im2col_4d_pair(dst, box_tm, bar, cv_cb * BK_ELEMS, cv_w, cv_h, cv_n,
-                                                        static_cast<uint16_t>(cv_x * P.conv.dil_w),
-                                                        static_cast<uint16_t>(cv_y * P.conv.dil_h));
+                                tma_load_im2col_4d_pair(dst, box_tm, bar, cv_cb * BK_ELEMS, cv_w, cv_h, cv_n, off_w, off_h);
                             else
-                                tma_load_im2col_4d(dst, box_tm, bar, cv_cb * BK_ELEMS, cv_w, cv_h, cv_n,
-                                                   static_cast<uint16_t>(cv_x * P.conv.dil_w),
-                                                   static_cast<uint16_t>(cv_y * P.conv.dil_h));
+                                tma_load_im2col_4d(dst, box_tm, bar, cv_cb * BK_ELEMS, cv_w, cv_h, cv_n, off_w, off_h);
+                        }
+                        else if(!is_b)
+                        {
+                            const uint16_t off_d = static_cast<uint16_t>(cv_z * P.conv.dil_d);
+                            if constexpr(CG == 2)
+                                tma_load_im2col_5d_pair(dst, box_tm, bar, cv_cb * BK_ELEMS, cv_w, cv_h, cv_d, cv_n, off_w,
+                                                        off_h, off_d);
+                            else
+                                tma_load_im2col_5d(dst, box_tm, bar, cv_cb * BK_ELEMS, cv_w, cv_h, cv_d, cv_n, off_w, off_h,
+                                                   off_d);
                         }
                         else
                         {
+                            const int tap = (cv_z * P.conv.Y + cv_y) * P.conv.X + cv_x;
                             if constexpr(CG == 2)
-                                tma_load_3d_pair(dst, box_tm, bar, cv_cb * BK_ELEMS, cv_y * P.conv.X + cv_x, b_row0);
+                                tma_load_3d_pair(dst, box_tm, bar, cv_cb * BK_ELEMS, tap, b_row0);
                             else
-                                tma_load_3d(dst, box_tm, bar, cv_cb * BK_ELEMS, cv_y * P.conv.X + cv_x, wi.n_start);
+                                tma_load_3d(dst, box_tm, bar, cv_cb * BK_ELEMS, tap, wi.n_start);
                         }
                     }
                     else
@@ -714,7 +730,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                         if(++cv_x == P.conv.X)
                         {
                             cv_x = 0;
-                            ++cv_y;
+                            if(++cv_y == P.conv.Y)
+                            {
+                                cv_y = 0;
+                                ++cv_z;
+                            }
                         }
                     }
                 }

@@ -111,6 +111,18 @@ __device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const void* tma
         : "memory");
 }
 
+// 5-D im2col load over an NDHWC tensor: coordinates (c, w, h, d, n), three filter-tap offsets.
+__device__ __forceinline__ void tma_load_im2col_5d(uint32_t dst, const void* tmap, uint32_t bar, int c, int w, int h,
+                                                   int d, int n, uint16_t off_w, uint16_t off_h, uint16_t off_d)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6, %7}], [%2], {%8, %9, %10};" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(d), "r"(n), "h"(off_w),
+        "h"(off_h), "h"(off_d)
+        : "memory");
+}
+
 // ---- thread-block cluster helpers (CTA pairs of the cta_group::2 kernels) ---------------------
 __device__ __forceinline__ uint32_t cluster_ctarank()
 {
@@ -166,6 +178,18 @@ __device__ __forceinline__ void tma_load_im2col_4d_pair(uint32_t dst, const void
         " [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};" ::"r"(dst),
         "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n),
         "h"(off_w), "h"(off_h)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_load_im2col_5d_pair(uint32_t dst, const void* tmap, uint32_t bar, int c, int w,
+                                                        int h, int d, int n, uint16_t off_w, uint16_t off_h,
+                                                        uint16_t off_d)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.5d.im2col.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6, %7}], [%2], {%8, %9, %10};" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(d), "r"(n), "h"(off_w),
+        "h"(off_h), "h"(off_d)
         : "memory");
 }
 

@@ -362,7 +362,9 @@ class ConvArgument(BaseArgument):
 
 class DeviceConvFwd(BaseOperator):
     """DeviceConvFwd (device_conv_fwd.hpp:18-39) / DeviceConvFwdBiasActivation
-    (device_conv_fwd_bias_activation.hpp:19-41) for 2-D NHWC/KYXC/NHWK; ``dtype`` is CKB_F16 or CKB_BF16."""
+    (device_conv_fwd_bias_activation.hpp:19-41) for channels-last tensors: 1-D NWC/KXC/NWK, 2-D NHWC/KYXC/NHWK or
+    3-D NDHWC/KZYXC/NDHWK, chosen by the length of the spatial vectors (the NumDimSpatial of
+    DeviceConvNDFwdXdl..., device_convnd_fwd_xdl_nhwc_kyxc_nhwk.hpp:76).  ``dtype`` is CKB_F16, CKB_BF16 or CKB_I8."""
 
     def __init__(self, dtype=CKB_F16):
         self.dtype = dtype
@@ -371,18 +373,39 @@ class DeviceConvFwd(BaseOperator):
                      output_spatial_lengths, conv_filter_strides, conv_filter_dilations,
                      input_left_pads, input_right_pads, in_element_op=None, wei_element_op=None,
                      out_element_op: ElementOp = PassThrough(), p_bias=None, p_resi=None) -> ConvArgument:
+        vecs = [list(map(int, v)) for v in (input_spatial_lengths, filter_spatial_lengths, output_spatial_lengths,
+                                            conv_filter_strides, conv_filter_dilations, input_left_pads,
+                                            input_right_pads)]
+        nd = len(vecs[0])
         arg = ConvArgument()
-        d = arg.desc
+        arg.consistent = nd in (1, 2, 3) and all(len(v) == nd for v in vecs)
+        if not arg.consistent:
+            return arg
+        if nd == 1:  # a 1-D problem is a 2-D one of height 1 (identity values for the missing dimension)
+            ident = [1, 1, 1, 1, 1, 0, 0]
+            vecs = [[i] + v for i, v in zip(ident, vecs)]
+        in_sp, filt, out_sp, strides, dils, lpads, rpads = vecs
+        if nd == 3:
+            arg.desc = d = capi.Conv3dFwdDesc()
+            d.Di, d.Hi, d.Wi = in_sp
+            d.Z, d.Y, d.X = filt
+            d.Do, d.Ho, d.Wo = out_sp
+            d.stride_d, d.stride_h, d.stride_w = strides
+            d.dilation_d, d.dilation_h, d.dilation_w = dils
+            d.pad_d, d.pad_h, d.pad_w = lpads
+            d.pad_d_right, d.pad_h_right, d.pad_w_right = rpads
+        else:
+            d = arg.desc
+            d.Hi, d.Wi = in_sp
+            d.Y, d.X = filt
+            d.Ho, d.Wo = out_sp
+            d.stride_h, d.stride_w = strides
+            d.dilation_h, d.dilation_w = dils
+            d.pad_h, d.pad_w = lpads
+            d.pad_h_right, d.pad_w_right = rpads
         d.dtype = self.dtype
         d.epilogue = out_element_op.kind
         d.N, d.K, d.C = int(N), int(K), int(C)
-        d.Hi, d.Wi = map(int, input_spatial_lengths)
-        d.Y, d.X = map(int, filter_spatial_lengths)
-        d.Ho, d.Wo = map(int, output_spatial_lengths)
-        d.stride_h, d.stride_w = map(int, conv_filter_strides)
-        d.dilation_h, d.dilation_w = map(int, conv_filter_dilations)
-        d.pad_h, d.pad_w = map(int, input_left_pads)
-        d.pad_h_right, d.pad_w_right = map(int, input_right_pads)
         d.p_in = int(p_in) if p_in else None
         d.p_wei = int(p_wei) if p_wei else None
         d.p_out = int(p_out) if p_out else None
@@ -395,22 +418,26 @@ class DeviceConvFwd(BaseOperator):
 
     MakeArgumentPointer = MakeArgument
 
+    @staticmethod
+    def _is_3d(arg) -> bool:
+        return isinstance(arg.desc, capi.Conv3dFwdDesc)
+
     def IsSupportedArgument(self, arg: ConvArgument) -> bool:
-        if not arg.in_wei_ops_passthrough:
+        if not getattr(arg, "consistent", True) or not arg.in_wei_ops_passthrough:
             return False
-        return capi.lib().ckb_conv2d_fwd_supported(ctypes.byref(arg.desc)) == capi.CKB_OK
+        fn = capi.lib().ckb_conv3d_fwd_supported if self._is_3d(arg) else capi.lib().ckb_conv2d_fwd_supported
+        return fn(ctypes.byref(arg.desc)) == capi.CKB_OK
 
     def _run(self, arg: ConvArgument, sc: StreamConfig) -> float:
         if not self.IsSupportedArgument(arg):
             raise RuntimeError("wrong! GridwiseGemm has invalid setting: " + capi.last_error())
         ms = ctypes.c_float(0.0)
-        rc = capi.lib().ckb_conv2d_fwd_run(ctypes.byref(arg.desc), sc.stream_id,
-                                           sc.nrepeat if sc.time_kernel else 0, ctypes.byref(ms))
-        capi.check(rc)
+        fn = capi.lib().ckb_conv3d_fwd_run if self._is_3d(arg) else capi.lib().ckb_conv2d_fwd_run
+        capi.check(fn(ctypes.byref(arg.desc), sc.stream_id, sc.nrepeat if sc.time_kernel else 0, ctypes.byref(ms)))
         return float(ms.value)
 
     def GetTypeString(self) -> str:
-        return "DeviceConv2dFwd_B200_Tcgen05_Im2colTma<128, 256|128|64, 128B>"
+        return "DeviceConvNdFwd_B200_Tcgen05_Im2colTma<128, 256|128|64, 128B>"
 
 
 def device_status() -> int:

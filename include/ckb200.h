@@ -208,7 +208,7 @@ int ckb_grouped_gemm_run_noalloc(const ckb_grouped_gemm_desc* desc, void* stream
  *                                        * wei[k,y,x,c],  bias[k] )
  * taps outside the image contribute zero.  All three tensors are packed. */
 typedef struct ckb_conv2d_fwd_desc {
-    int32_t dtype;               /* CKB_F16 / CKB_BF16 (in, wei, out, bias) */
+    int32_t dtype;               /* CKB_F16 / CKB_BF16 / CKB_I8 (in, wei, out, bias)     */
     int32_t epilogue;            /* PASSTHROUGH, RELU, ADD_RELU (bias), ADD_HARDSWISH (bias),
                                     ADD_RELU_ADD (bias + residual of the output's shape)   */
     int32_t N, K, C;
@@ -230,6 +230,36 @@ typedef struct ckb_conv2d_fwd_desc {
 
 int ckb_conv2d_fwd_supported(const ckb_conv2d_fwd_desc* desc);
 int ckb_conv2d_fwd_run(const ckb_conv2d_fwd_desc* desc, void* stream, int n_rep, float* avg_ms);
+
+/* ---- 3-D convolution forward, NDHWC / KZYXC / NDHWK -------------------------- */
+/* The NumDimSpatial = 3 case of DeviceConvNDFwdXdl_Input_N_Hi_Wi_C_Weight_K_Y_X_C_Output_N_Ho_Wo_K
+ * (device/device_convnd_fwd_xdl_nhwc_kyxc_nhwk.hpp:76-1046; 3-D descriptor :372-548).  A 1-D problem
+ * (NWC / KXC / NWK) is a 2-D one with Hi = Y = Ho = 1 and goes through ckb_conv2d_fwd_*.
+ * out[n,do,ho,wo,k] = epilogue( sum_{z,y,x,c} in[n, do*sd + z*dd - pd, ho*sh + y*dh - ph, wo*sw + x*dw - pw, c]
+ *                                            * wei[k,z,y,x,c],  bias[k] )
+ * Limits of the 5-D im2col tensor map: pads <= 16, (filter - 1) * dilation <= 15 per dimension. */
+typedef struct ckb_conv3d_fwd_desc {
+    int32_t dtype;               /* CKB_F16 / CKB_BF16 / CKB_I8                          */
+    int32_t epilogue;            /* as ckb_conv2d_fwd_desc                               */
+    int32_t N, K, C;
+    int32_t Di, Hi, Wi;
+    int32_t Z, Y, X;
+    int32_t Do, Ho, Wo;
+    int32_t stride_d, stride_h, stride_w;
+    int32_t dilation_d, dilation_h, dilation_w;
+    int32_t pad_d, pad_h, pad_w;     /* left pads */
+    int32_t pad_d_right, pad_h_right, pad_w_right;
+    int32_t reserved0;
+    const void* p_in;
+    const void* p_wei;
+    void* p_out;
+    const void* p_bias;          /* length K, or NULL                                   */
+    const void* p_resi;          /* N x Do x Ho x Wo x K residual, or NULL              */
+    float epi_params[4];
+} ckb_conv3d_fwd_desc;
+
+int ckb_conv3d_fwd_supported(const ckb_conv3d_fwd_desc* desc);
+int ckb_conv3d_fwd_run(const ckb_conv3d_fwd_desc* desc, void* stream, int n_rep, float* avg_ms);
 
 /* ---- device memory helpers (DeviceMem, library/src/host_tensor/device_memory.cpp:7-28) */
 int ckb_malloc(void** dev_ptr, size_t bytes);

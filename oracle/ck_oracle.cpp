@@ -155,12 +155,16 @@ static inline float elem_to_float(half v) { return static_cast<float>(v); }
 static inline float elem_to_float(bf16 v) { return bf16_to_float(v); }
 static inline float elem_to_float(int8_t v) { return static_cast<float>(v); }
 
+// N-D (1-D, 2-D, 3-D) forward convolution on NDHWC / KZYXC / NDHWK tensors; the 2-D and 1-D cases are the
+// 3-D one with depth (and height) 1.  Loop order c -> z -> y -> x as reference_conv_fwd.hpp:132-185 (2-D) and
+// :186-254 (3-D); the output is iterated as (n, k, do, ho, wo).
 template <typename T>
-static int conv2d_fwd_naive_t(int epi, const float* params,
+static int conv3d_fwd_naive_t(int epi, const float* params,
                               const void* in, const void* wei, void* out,
                               const void* bias, const void* resi,
-                              int N, int K, int C, int Hi, int Wi, int Y, int X, int Ho, int Wo,
-                              int sh, int sw, int dh, int dw, int ph, int pw, int threads)
+                              int N, int K, int C, int Di, int Hi, int Wi, int Z, int Y, int X,
+                              int Do, int Ho, int Wo, int sd, int sh, int sw, int dd, int dh, int dw,
+                              int pd, int ph, int pw, int threads)
 {
     float p[4] = {0, 0, 0, 0};
     if(params)
@@ -170,33 +174,36 @@ static int conv2d_fwd_naive_t(int epi, const float* params,
     const T* Bias = static_cast<const T*>(bias);
     const T* Resi = static_cast<const T*>(resi);
     T* Out        = static_cast<T*>(out);
-    // The reference iterates the output as (n, k, ho, wo) (reference_conv_fwd.hpp:176-181).
-    const int64_t total = static_cast<int64_t>(N) * K * Ho * Wo;
+    const int64_t total = static_cast<int64_t>(N) * K * Do * Ho * Wo;
     parallel_for(total, threads, [=](int64_t i) {
         const int wo = static_cast<int>(i % Wo);
         const int ho = static_cast<int>((i / Wo) % Ho);
-        const int k  = static_cast<int>((i / (static_cast<int64_t>(Wo) * Ho)) % K);
-        const int n  = static_cast<int>(i / (static_cast<int64_t>(Wo) * Ho * K));
+        const int od = static_cast<int>((i / (static_cast<int64_t>(Wo) * Ho)) % Do);
+        const int k  = static_cast<int>((i / (static_cast<int64_t>(Wo) * Ho * Do)) % K);
+        const int n  = static_cast<int>(i / (static_cast<int64_t>(Wo) * Ho * Do * K));
         float v_acc  = 0;
         for(int c = 0; c < C; ++c)
-            for(int y = 0; y < Y; ++y)
+            for(int z = 0; z < Z; ++z)
             {
-                const int64_t hi = static_cast<int64_t>(ho) * sh + static_cast<int64_t>(y) * dh - ph;
-                for(int x = 0; x < X; ++x)
+                const int64_t di = static_cast<int64_t>(od) * sd + static_cast<int64_t>(z) * dd - pd;
+                for(int y = 0; y < Y; ++y)
                 {
-                    const int64_t wi =
-                        static_cast<int64_t>(wo) * sw + static_cast<int64_t>(x) * dw - pw;
-                    if(hi >= 0 && hi < Hi && wi >= 0 && wi < Wi)
+                    const int64_t hi = static_cast<int64_t>(ho) * sh + static_cast<int64_t>(y) * dh - ph;
+                    for(int x = 0; x < X; ++x)
                     {
-                        const float v_in =
-                            elem_to_float(In[((static_cast<int64_t>(n) * Hi + hi) * Wi + wi) * C + c]);
-                        const float v_wei =
-                            elem_to_float(Wei[((static_cast<int64_t>(k) * Y + y) * X + x) * C + c]);
-                        v_acc += v_in * v_wei;
+                        const int64_t wi = static_cast<int64_t>(wo) * sw + static_cast<int64_t>(x) * dw - pw;
+                        if(di >= 0 && di < Di && hi >= 0 && hi < Hi && wi >= 0 && wi < Wi)
+                        {
+                            const float v_in = elem_to_float(
+                                In[(((static_cast<int64_t>(n) * Di + di) * Hi + hi) * Wi + wi) * C + c]);
+                            const float v_wei = elem_to_float(
+                                Wei[(((static_cast<int64_t>(k) * Z + z) * Y + y) * X + x) * C + c]);
+                            v_acc += v_in * v_wei;
+                        }
                     }
                 }
             }
-        const int64_t o = ((static_cast<int64_t>(n) * Ho + ho) * Wo + wo) * K + k;
+        const int64_t o = (((static_cast<int64_t>(n) * Do + od) * Ho + ho) * Wo + wo) * K + k;
         if constexpr(std::is_same<T, float>::value)
         {
             Out[o] = v_acc; // PassThrough, reference_conv_fwd.hpp:169-172
@@ -221,6 +228,17 @@ static int conv2d_fwd_naive_t(int epi, const float* params,
         }
     });
     return 0;
+}
+
+template <typename T>
+static int conv2d_fwd_naive_t(int epi, const float* params,
+                              const void* in, const void* wei, void* out,
+                              const void* bias, const void* resi,
+                              int N, int K, int C, int Hi, int Wi, int Y, int X, int Ho, int Wo,
+                              int sh, int sw, int dh, int dw, int ph, int pw, int threads)
+{
+    return conv3d_fwd_naive_t<T>(epi, params, in, wei, out, bias, resi, N, K, C, 1, Hi, Wi, 1, Y, X, 1, Ho, Wo, 1,
+                                 sh, sw, 1, dh, dw, 0, ph, pw, threads);
 }
 
 extern "C" {
@@ -253,6 +271,26 @@ int oracle_conv2d_fwd_naive_i8(int epi, const float* params,
 {
     return conv2d_fwd_naive_t<int8_t>(epi, params, in, wei, out, bias, resi, N, K, C, Hi, Wi, Y, X,
                                       Ho, Wo, sh, sw, dh, dw, ph, pw, threads);
+}
+
+// 3-D forward convolution: dtype 0 = binary16, 1 = int8, 2 = bfloat16 bit patterns, 3 = float (PassThrough only).
+int oracle_conv3d_fwd_naive(int dtype, int epi, const float* params,
+                            const void* in, const void* wei, void* out, const void* bias, const void* resi,
+                            int N, int K, int C, int Di, int Hi, int Wi, int Z, int Y, int X, int Do, int Ho, int Wo,
+                            int sd, int sh, int sw, int dd, int dh, int dw, int pd, int ph, int pw, int threads)
+{
+#define CKO_CONV3D(T)                                                                                             \
+    conv3d_fwd_naive_t<T>(epi, params, in, wei, out, bias, resi, N, K, C, Di, Hi, Wi, Z, Y, X, Do, Ho, Wo, sd, sh, \
+                          sw, dd, dh, dw, pd, ph, pw, threads)
+    switch(dtype)
+    {
+    case 0: return CKO_CONV3D(half);
+    case 1: return CKO_CONV3D(int8_t);
+    case 2: return CKO_CONV3D(bf16);
+    case 3: return CKO_CONV3D(float);
+    default: return 1;
+    }
+#undef CKO_CONV3D
 }
 
 int oracle_conv2d_fwd_naive_f32(const void* in, const void* wei, void* out,

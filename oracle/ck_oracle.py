@@ -72,6 +72,9 @@ def lib() -> ctypes.CDLL:
         L.oracle_conv2d_fwd_naive_bf16.restype = ctypes.c_int
         L.oracle_conv2d_fwd_naive_i8.argtypes = conv_args
         L.oracle_conv2d_fwd_naive_i8.restype = ctypes.c_int
+        L.oracle_conv3d_fwd_naive.argtypes = ([ctypes.c_int, ctypes.c_int, fp] + [ctypes.c_void_p] * 5 +
+                                              [ctypes.c_int] * 22)
+        L.oracle_conv3d_fwd_naive.restype = ctypes.c_int
         L.oracle_conv_out_len.argtypes = [ctypes.c_int] * 6
         L.oracle_conv_out_len.restype = ctypes.c_int
         L.oracle_epilogue_f16.argtypes = [ctypes.c_int, fp, ctypes.c_float, ctypes.c_uint16, ctypes.c_uint16]
@@ -207,6 +210,46 @@ def conv2d_fwd(inp: np.ndarray, wei: np.ndarray, stride=(1, 1), dilation=(1, 1),
     if rc != 0:
         raise RuntimeError(f"oracle conv failed rc={rc}")
     return out
+
+
+def conv3d_fwd(inp: np.ndarray, wei: np.ndarray, stride=(1, 1, 1), dilation=(1, 1, 1), pad=(0, 0, 0),
+               pad_right=None, epilogue: int = EPI_PASSTHROUGH, params: Optional[Sequence[float]] = None,
+               bias: Optional[np.ndarray] = None, resi: Optional[np.ndarray] = None,
+               threads: Optional[int] = None) -> np.ndarray:
+    """NDHWC input (N,Di,Hi,Wi,C), KZYXC weights (K,Z,Y,X,C) -> NDHWK output (N,Do,Ho,Wo,K); naive loops.
+    float16, int8, uint16 (bfloat16 bit patterns) or float32 (PassThrough only) arrays."""
+    code = {np.dtype(np.float16): 0, np.dtype(np.int8): 1, np.dtype(np.uint16): 2, np.dtype(np.float32): 3}[inp.dtype]
+    assert wei.dtype == inp.dtype
+    inp, wei = np.ascontiguousarray(inp), np.ascontiguousarray(wei)
+    N, Di, Hi, Wi, C = inp.shape
+    K, Z, Y, X, C2 = wei.shape
+    assert C == C2
+    pad_right = pad if pad_right is None else pad_right
+    Do, Ho, Wo = (conv_out_len(i, f, s, d, pl, pr) for i, f, s, d, pl, pr in
+                  zip((Di, Hi, Wi), (Z, Y, X), stride, dilation, pad, pad_right))
+    out = np.empty((N, Do, Ho, Wo, K), dtype=inp.dtype)
+    pb = pr = None
+    if bias is not None:
+        bias = np.ascontiguousarray(bias, dtype=inp.dtype)
+        pb = bias.ctypes.data
+    if resi is not None:
+        resi = np.ascontiguousarray(resi, dtype=inp.dtype)
+        assert resi.shape == out.shape
+        pr = resi.ctypes.data
+    rc = lib().oracle_conv3d_fwd_naive(code, epilogue, _params(params), inp.ctypes.data, wei.ctypes.data,
+                                       out.ctypes.data, pb, pr, N, K, C, Di, Hi, Wi, Z, Y, X, Do, Ho, Wo, *stride,
+                                       *dilation, *pad, threads or hardware_concurrency())
+    if rc != 0:
+        raise RuntimeError(f"oracle conv3d failed rc={rc}")
+    return out
+
+
+def conv1d_fwd(inp: np.ndarray, wei: np.ndarray, stride=1, dilation=1, pad=0, pad_right=None, **kw) -> np.ndarray:
+    """NWC input (N,Wi,C), KXC weights (K,X,C) -> NWK output (N,Wo,K): the 3-D convolution with depth = height = 1."""
+    pr = pad if pad_right is None else pad_right
+    out = conv3d_fwd(inp[:, None, None], wei[:, None, None], (1, 1, stride), (1, 1, dilation), (0, 0, pad),
+                     (0, 0, pr), **kw)
+    return out[:, 0, 0]
 
 
 def conv2d_fwd_f32(inp: np.ndarray, wei: np.ndarray, stride=(1, 1), dilation=(1, 1), pad=(0, 0),

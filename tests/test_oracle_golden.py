@@ -202,3 +202,32 @@ def test_int8_conv_matches_exact_integer_arithmetic():
                              params=[0.03, 1.0])
     expect = np.clip(np.trunc(np.float32(1.0) * np.maximum(np.float32(0.03) * ref.astype(np.float32), 0)), -128, 127)
     np.testing.assert_array_equal(relu, expect.astype(np.int8))
+
+
+def test_reference_conv_1d_3d_golden_vectors():
+    """The reference's own golden vectors for its 1-D and 3-D CPU convolution
+    (tests/golden/reference_conv_fwd_1d_3d.json, made by tests/golden/make_convnd_golden.py)."""
+    import json
+    import os
+    fx = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "reference_conv_fwd_1d_3d.json")))
+    assert len(fx["cases"]) == 4
+    for case in fx["cases"]:
+        g = case["geometry"]
+        nd, N, K, C = g["nd"], g["N"], g["K"], g["C"]
+        sp = g["in_sp"]
+        step = np.float32(case["input_step"])
+        count = N * C * int(np.prod(sp))
+        seq = (np.arange(count, dtype=np.float32) * step).astype(np.float32)
+        if nd == 1:  # NWC in memory
+            inp = seq.reshape(N, sp[0], C)
+            wei = np.full((K, g["filt"][0], C), 0.5, np.float32)
+            out = oracle.conv1d_fwd(inp, wei, g["stride"][0], g["dil"][0], g["pad"][0])
+            got = out.ravel()  # N, W, K order
+        else:        # NCDHW in memory -> the oracle's NDHWC
+            inp = np.ascontiguousarray(seq.reshape(N, C, *sp).transpose(0, 2, 3, 4, 1))
+            wei = np.full((K, *g["filt"], C), 0.5, np.float32)
+            out = oracle.conv3d_fwd(inp, wei, tuple(g["stride"]), tuple(g["dil"]), tuple(g["pad"]))
+            got = out.transpose(0, 4, 1, 2, 3).ravel()  # N, K, D, H, W order
+        assert list(out.shape[1:1 + nd]) == case["output_spatial"]
+        np.testing.assert_allclose(got, np.array(case["expected"], np.float32), rtol=1e-5, atol=1e-6)
+        np.testing.assert_allclose(got, np.array(case["derived"]), rtol=1e-5, atol=1e-6)
