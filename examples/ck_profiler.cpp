@@ -8,6 +8,8 @@
 //   ck_profiler gemm_add_add_fastgelu <dtype 1> <layout 1> <verify> <init> <log> <time> M N K StrideA StrideB StrideD0 StrideD1 StrideE
 //   ck_profiler grouped_gemm          <dtype 1> <layout 1> <verify> <init> <log> <time> Ms Ns Ks          (comma separated lists)
 //   ck_profiler conv_fwd_bias_relu    <dtype 1> <verify> <init> <log> <time> N K C Y X Hi Wi Sy Sx Dy Dx LeftPy LeftPx RightPy RightPx
+//   ck_profiler conv_fwd              <dtype 1 fp16|2 bf16|3 int8> <layout 1 NHWC> <verify> <init> <log> <time> <nd 1|2|3> N K C
+//                                     <filter> <input> <strides> <dilations> <left pads> <right pads>   (nd values each)
 // gemm takes the reference's four matrix layouts (0: mk_kn, 1: mk_nk, 2: km_kn, 3: km_nk); the fused and grouped
 // sub-commands take layout 1.
 #include <cstring>
@@ -25,7 +27,9 @@
 #include "ck/library/tensor_operation_instance/gpu/grouped_gemm.hpp"
 #include "ck/library/utility/check_err.hpp"
 #include "ck/library/utility/conv_util.hpp"
+#include "ck/library/reference_tensor_operation/cpu/reference_conv_fwd.hpp"
 #include "ck/tensor_operation/gpu/device/device_conv2d_fwd_xdl_c_shuffle_bias_activation_nhwc_kyxc_nhwk.hpp"
+#include "ck/tensor_operation/gpu/device/device_convnd_fwd_xdl_nhwc_kyxc_nhwk.hpp"
 
 namespace inst = ck::tensor_operation::device::instance;
 namespace dev  = ck::tensor_operation::device;
@@ -380,6 +384,94 @@ int profile_conv_fwd_bias_relu(int argc, char* argv[])
     return pass && !best.name.empty() ? 0 : 1;
 }
 
+template <int ND, typename T>
+bool profile_convnd_typed(const ck::utils::conv::ConvParams& p, bool verify, int init, bool time)
+{
+    namespace conv_util = ck::utils::conv;
+    // clang-format off
+    using Conv = dev::DeviceConvNDFwdXdl_Input_N_Hi_Wi_C_Weight_K_Y_X_C_Output_N_Ho_Wo_K<
+        T, T, T, float, PassThrough, PassThrough, PassThrough, dev::ConvolutionForwardSpecialization::Default, ND,
+        256, 128, 256, 4, 8, 32, 32, 2, 4, inst::S<4, 64, 1>, inst::S<1, 0, 2>, inst::S<1, 0, 2>, 2, 8, 8, true,
+        inst::S<4, 64, 1>, inst::S<1, 0, 2>, inst::S<1, 0, 2>, 2, 8, 8, true, 7, 1>;
+    // clang-format on
+    const auto out_sp = p.GetOutputSpatialLengths();
+    std::vector<std::size_t> in_dims{std::size_t(p.N_), std::size_t(p.C_)}, wei_dims{std::size_t(p.K_), std::size_t(p.C_)},
+        out_dims{std::size_t(p.N_), std::size_t(p.K_)};
+    for(int i = 0; i < ND; ++i)
+    {
+        in_dims.push_back(p.input_spatial_lengths_[i]);
+        wei_dims.push_back(p.filter_spatial_lengths_[i]);
+        out_dims.push_back(out_sp[i]);
+    }
+    Tensor<T> in(conv_util::get_input_host_tensor_descriptor(in_dims, ND));
+    Tensor<T> wei(conv_util::get_filters_host_tensor_descriptor(wei_dims, ND));
+    Tensor<T> out_h(conv_util::get_output_host_tensor_descriptor(out_dims, ND)), out_d(out_h.mDesc);
+    init_tensor(in, init, false);
+    init_tensor(wei, init, true);
+    DeviceMem in_buf(sizeof(T) * in.mDesc.GetElementSpace()), wei_buf(sizeof(T) * wei.mDesc.GetElementSpace()),
+        out_buf(sizeof(T) * out_d.mDesc.GetElementSpace());
+    in_buf.ToDevice(in.mData.data());
+    wei_buf.ToDevice(wei.mData.data());
+    std::vector<std::unique_ptr<dev::DeviceConvFwd<PassThrough, PassThrough, PassThrough>>> ops;
+    ops.push_back(std::make_unique<Conv>());
+    Best best;
+    bool pass = true;
+    for(auto& op : ops)
+    {
+        auto arg = op->MakeArgumentPointer(in_buf.GetDeviceBuffer(), wei_buf.GetDeviceBuffer(), out_buf.GetDeviceBuffer(),
+                                           p.N_, p.K_, p.C_, p.input_spatial_lengths_, p.filter_spatial_lengths_, out_sp,
+                                           p.conv_filter_strides_, p.conv_filter_dilations_, p.input_left_pads_,
+                                           p.input_right_pads_, {}, {}, {});
+        if(!op->IsSupportedArgument(arg.get()))
+        {
+            std::cout << op->GetTypeString() << " does not support this problem" << std::endl;
+            continue;
+        }
+        const float ms = op->MakeInvokerPointer()->Run(arg.get(), StreamConfig{nullptr, time});
+        if(time)
+            best.offer(op->GetTypeString(), ms, conv_util::get_flops(p.N_, p.C_, p.K_, p.filter_spatial_lengths_, out_sp),
+                       conv_util::get_btype<T, T, T>(p.N_, p.C_, p.K_, p.input_spatial_lengths_,
+                                                     p.filter_spatial_lengths_, out_sp));
+        else
+            best.name = op->GetTypeString();
+        if(verify)
+        {
+            out_buf.FromDevice(out_d.mData.data());
+            using Ref = ck::tensor_operation::host::ReferenceConvFwd<T, T, T, PassThrough, PassThrough, PassThrough, ND>;
+            auto rarg = Ref::MakeArgument(in, wei, out_h, p.conv_filter_strides_, p.conv_filter_dilations_,
+                                          p.input_left_pads_, p.input_right_pads_, {}, {}, {});
+            Ref::MakeInvoker().Run(rarg);
+            pass = pass && ck::utils::check_err(out_d.mData, out_h.mData);
+        }
+    }
+    best.report("conv_fwd");
+    return pass && !best.name.empty();
+}
+
+int profile_convnd_fwd(int argc, char* argv[])
+{
+    const int nd = argc > 8 ? std::stoi(argv[8]) : 0;
+    if(nd < 1 || nd > 3 || argc != 9 + 3 + 6 * nd || std::stoi(argv[3]) != 1)
+    {
+        std::printf("conv_fwd <dtype 1 fp16|2 bf16|3 int8> <layout 1: NHWC> verify init log time <nd 1|2|3> N K C "
+                    "<filter> <input> <strides> <dilations> <left pads> <right pads>\n");
+        return 1;
+    }
+    const int dtype = std::stoi(argv[2]);
+    const bool verify = std::stoi(argv[4]), time = std::stoi(argv[7]);
+    const int init = std::stoi(argv[5]);
+    const auto p   = ck::utils::conv::parse_conv_params(nd, 9, argv);
+    auto by_type   = [&](auto ndc) {
+        constexpr int ND = decltype(ndc)::value;
+        return dtype == 1 ? profile_convnd_typed<ND, ck::half_t>(p, verify, init, time)
+                          : dtype == 2 ? profile_convnd_typed<ND, ck::bhalf_t>(p, verify, init, time)
+                                       : dtype == 3 ? profile_convnd_typed<ND, int8_t>(p, verify, init, time) : false;
+    };
+    const bool ok = nd == 1 ? by_type(std::integral_constant<int, 1>{})
+                            : nd == 2 ? by_type(std::integral_constant<int, 2>{}) : by_type(std::integral_constant<int, 3>{});
+    return ok ? 0 : 1;
+}
+
 int main(int argc, char* argv[])
 {
     if(argc >= 2)
@@ -392,10 +484,13 @@ int main(int argc, char* argv[])
             return profile_grouped_gemm(argc, argv);
         if(std::strcmp(argv[1], "conv_fwd_bias_relu") == 0)
             return profile_conv_fwd_bias_relu(argc, argv);
+        if(std::strcmp(argv[1], "conv_fwd") == 0)
+            return profile_convnd_fwd(argc, argv);
     }
     std::printf("arg1: tensor operation (gemm: GEMM\n"
                 "                        gemm_add_add_fastgelu: GEMM+Add+Add+FastGeLU\n"
                 "                        grouped_gemm: Grouped GEMM\n"
-                "                        conv_fwd_bias_relu: ForwardConvolution+Bias+ReLU)\n");
+                "                        conv_fwd_bias_relu: ForwardConvolution+Bias+ReLU\n"
+                "                        conv_fwd: ForwardConvolution 1-D / 2-D / 3-D)\n");
     return 0;
 }

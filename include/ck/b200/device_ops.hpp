@@ -416,22 +416,27 @@ struct GroupedGemmInvoker : dev::BaseInvoker
     }
 };
 
-// -------- conv2d forward --------
+// -------- convolution forward (1-D, 2-D, 3-D) --------
 struct ConvArgument : dev::BaseArgument
 {
-    ckb_conv2d_fwd_desc desc{};
+    ckb_conv2d_fwd_desc desc{};  // 1-D (as a 2-D problem of height 1) and 2-D
+    ckb_conv3d_fwd_desc desc3{}; // 3-D
+    bool is_3d   = false;
     bool host_ok = true;
 };
+
+inline bool conv_supported(const ConvArgument& a);
 
 struct ConvInvoker : dev::BaseInvoker
 {
     float Run(const ConvArgument& arg, const StreamConfig& stream_config = StreamConfig{})
     {
-        if(!arg.host_ok || ckb_conv2d_fwd_supported(&arg.desc) != CKB_OK)
+        if(!conv_supported(arg))
             throw_invalid_setting();
-        float ms = 0.f;
-        check_runtime(ckb_conv2d_fwd_run(&arg.desc, stream_config.stream_id_,
-                                         stream_config.time_kernel_ ? kTimedRepeats : 0, &ms));
+        float ms      = 0.f;
+        const int rep = stream_config.time_kernel_ ? kTimedRepeats : 0;
+        check_runtime(arg.is_3d ? ckb_conv3d_fwd_run(&arg.desc3, stream_config.stream_id_, rep, &ms)
+                                : ckb_conv2d_fwd_run(&arg.desc, stream_config.stream_id_, rep, &ms));
         return ms;
     }
     float Run(const dev::BaseArgument* p_arg, const StreamConfig& stream_config = StreamConfig{}) override
@@ -440,6 +445,8 @@ struct ConvInvoker : dev::BaseInvoker
     }
 };
 
+// The spatial vectors decide the dimensionality (the reference's NumDimSpatial); a 1-D problem is passed on as a
+// 2-D one of height 1.
 template <typename InDataType, typename InOp, typename WeiOp, typename OutOp>
 ConvArgument make_conv_argument(const void* p_in, const void* p_wei, void* p_out, const void* p_bias,
                                 const void* p_resi, index_t N, index_t K, index_t C,
@@ -449,36 +456,60 @@ ConvArgument make_conv_argument(const void* p_in, const void* p_wei, void* p_out
                                 const std::vector<index_t>& rpads, const OutOp& op)
 {
     ConvArgument a;
-    ckb_conv2d_fwd_desc& d = a.desc;
-    const bool two_d       = in_sp.size() == 2 && filt_sp.size() == 2 && out_sp.size() == 2 && strides.size() == 2 &&
-                       dilations.size() == 2 && lpads.size() == 2 && rpads.size() == 2;
-    a.host_ok = two_d && is_passthrough<InOp>::value && is_passthrough<WeiOp>::value &&
+    const std::size_t nd = in_sp.size();
+    const bool same_nd   = filt_sp.size() == nd && out_sp.size() == nd && strides.size() == nd &&
+                         dilations.size() == nd && lpads.size() == nd && rpads.size() == nd;
+    a.host_ok = same_nd && nd >= 1 && nd <= 3 && is_passthrough<InOp>::value && is_passthrough<WeiOp>::value &&
                 EpilogueTraits<OutOp, ctx_conv>::kind >= 0;
-    d.dtype    = dtype_of<InDataType>::value;
-    d.epilogue = EpilogueTraits<OutOp, ctx_conv>::kind;
-    EpilogueTraits<OutOp, ctx_conv>::params(op, d.epi_params);
-    d.N = N;
-    d.K = K;
-    d.C = C;
-    if(two_d)
+    a.is_3d = nd == 3;
+    auto fill_common = [&](auto& d) {
+        d.dtype    = dtype_of<InDataType>::value;
+        d.epilogue = EpilogueTraits<OutOp, ctx_conv>::kind;
+        EpilogueTraits<OutOp, ctx_conv>::params(op, d.epi_params);
+        d.N      = N;
+        d.K      = K;
+        d.C      = C;
+        d.p_in   = p_in;
+        d.p_wei  = p_wei;
+        d.p_out  = p_out;
+        d.p_bias = p_bias;
+        d.p_resi = p_resi;
+    };
+    fill_common(a.desc);
+    fill_common(a.desc3);
+    if(!same_nd)
+        return a;
+    if(nd == 3)
     {
-        d.Hi = in_sp[0], d.Wi = in_sp[1];
-        d.Y = filt_sp[0], d.X = filt_sp[1];
-        d.Ho = out_sp[0], d.Wo = out_sp[1];
-        d.stride_h = strides[0], d.stride_w = strides[1];
-        d.dilation_h = dilations[0], d.dilation_w = dilations[1];
-        d.pad_h = lpads[0], d.pad_w = lpads[1];
-        d.pad_h_right = rpads[0], d.pad_w_right = rpads[1];
+        ckb_conv3d_fwd_desc& d = a.desc3;
+        d.Di = in_sp[0], d.Hi = in_sp[1], d.Wi = in_sp[2];
+        d.Z = filt_sp[0], d.Y = filt_sp[1], d.X = filt_sp[2];
+        d.Do = out_sp[0], d.Ho = out_sp[1], d.Wo = out_sp[2];
+        d.stride_d = strides[0], d.stride_h = strides[1], d.stride_w = strides[2];
+        d.dilation_d = dilations[0], d.dilation_h = dilations[1], d.dilation_w = dilations[2];
+        d.pad_d = lpads[0], d.pad_h = lpads[1], d.pad_w = lpads[2];
+        d.pad_d_right = rpads[0], d.pad_h_right = rpads[1], d.pad_w_right = rpads[2];
     }
-    d.p_in   = p_in;
-    d.p_wei  = p_wei;
-    d.p_out  = p_out;
-    d.p_bias = p_bias;
-    d.p_resi = p_resi;
+    else if(nd == 2 || nd == 1)
+    {
+        ckb_conv2d_fwd_desc& d = a.desc;
+        const std::size_t w    = nd - 1; // index of the innermost (width) dimension
+        d.Hi = nd == 2 ? in_sp[0] : 1, d.Wi = in_sp[w];
+        d.Y = nd == 2 ? filt_sp[0] : 1, d.X = filt_sp[w];
+        d.Ho = nd == 2 ? out_sp[0] : 1, d.Wo = out_sp[w];
+        d.stride_h = nd == 2 ? strides[0] : 1, d.stride_w = strides[w];
+        d.dilation_h = nd == 2 ? dilations[0] : 1, d.dilation_w = dilations[w];
+        d.pad_h = nd == 2 ? lpads[0] : 0, d.pad_w = lpads[w];
+        d.pad_h_right = nd == 2 ? rpads[0] : 0, d.pad_w_right = rpads[w];
+    }
     return a;
 }
 
-inline bool conv_supported(const ConvArgument& a) { return a.host_ok && ckb_conv2d_fwd_supported(&a.desc) == CKB_OK; }
+inline bool conv_supported(const ConvArgument& a)
+{
+    return a.host_ok &&
+           (a.is_3d ? ckb_conv3d_fwd_supported(&a.desc3) : ckb_conv2d_fwd_supported(&a.desc)) == CKB_OK;
+}
 
 } // namespace b200
 
@@ -783,7 +814,7 @@ struct DeviceGroupedGemmXdl
     }
 };
 
-// device_convnd_fwd_xdl_nhwc_kyxc_nhwk.hpp:42-75 (2-D only here)
+// device_convnd_fwd_xdl_nhwc_kyxc_nhwk.hpp:42-75 (NumDimSpatial = 1, 2 or 3: NWC, NHWC, NDHWC tensors)
 template <typename InDataType, typename WeiDataType, typename OutDataType, typename AccDataType,
           typename InElementwiseOperation, typename WeiElementwiseOperation, typename OutElementwiseOperation,
           ConvolutionForwardSpecialization ConvForwardSpecialization, index_t NumDimSpatial, index_t BlockSize,
@@ -808,8 +839,8 @@ struct DeviceConvNDFwdXdl_Input_N_Hi_Wi_C_Weight_K_Y_X_C_Output_N_Ho_Wo_K
             p_in, p_wei, p_out, nullptr, nullptr, N, K, C, input_spatial_lengths, filter_spatial_lengths,
             output_spatial_lengths, conv_filter_strides, conv_filter_dilations, input_left_pads, input_right_pads,
             out_element_op);
-        arg.host_ok = arg.host_ok && NumDimSpatial == 2 && std::is_same<InDataType, WeiDataType>::value &&
-                      std::is_same<InDataType, OutDataType>::value;
+        arg.host_ok = arg.host_ok && static_cast<std::size_t>(NumDimSpatial) == input_spatial_lengths.size() &&
+                      std::is_same<InDataType, WeiDataType>::value && std::is_same<InDataType, OutDataType>::value;
         return arg;
     }
     static auto MakeInvoker() { return Invoker{}; }

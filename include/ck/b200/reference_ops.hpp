@@ -76,12 +76,14 @@ struct ReferenceGemm : public device::BaseOperator
     std::string GetTypeString() const override { return "ReferenceGemm"; }
 };
 
-// 2-D only: tensors carry NCHW-ordered lengths (any strides), see conv_util host descriptors.
+// 1-D, 2-D and 3-D (reference_conv_fwd.hpp:84-254): tensors carry channel-first ordered lengths {N, C, spatial...}
+// ({K, C, filter...}, {N, K, out spatial...}) with the strides of any memory layout, see the conv_util host
+// descriptors.  Accumulation in float over c, then the filter positions outermost dimension first.
 template <typename InDataType, typename WeiDataType, typename OutDataType, typename InElementwiseOperation,
           typename WeiElementwiseOperation, typename OutElementwiseOperation, index_t NumDimSpatial = 2>
 struct ReferenceConvFwd : public device::BaseOperator
 {
-    static_assert(NumDimSpatial == 2, "only the 2-D convolution is on the B200 path");
+    static_assert(NumDimSpatial >= 1 && NumDimSpatial <= 3, "1-D, 2-D and 3-D convolutions");
     struct Argument : public device::BaseArgument
     {
         Argument(const Tensor<InDataType>& input, const Tensor<WeiDataType>& weight, Tensor<OutDataType>& output,
@@ -106,39 +108,108 @@ struct ReferenceConvFwd : public device::BaseOperator
 
     struct Invoker : public device::BaseInvoker
     {
+        // input coordinate of output position `o` and filter position `f` along spatial dimension `dim`
+        static long_index_t in_pos(const Argument& arg, std::size_t o, std::size_t f, int dim)
+        {
+            return static_cast<long_index_t>(o * arg.conv_strides_[dim]) +
+                   static_cast<long_index_t>(f * arg.conv_dilations_[dim]) -
+                   static_cast<long_index_t>(arg.in_left_pads_[dim]);
+        }
+        static bool inside(long_index_t p, std::size_t len) { return p >= 0 && static_cast<std::size_t>(p) < len; }
+        template <typename... Idx>
+        static void mac(const Argument& arg, float& v_acc, std::size_t n, std::size_t k, std::size_t c, Idx... sp_and_f)
+        {
+            // sp_and_f = input positions..., filter positions...
+            float v_in, v_wei;
+            const std::size_t v[] = {static_cast<std::size_t>(sp_and_f)...};
+            if constexpr(NumDimSpatial == 1)
+            {
+                arg.in_element_op_(v_in, type_convert<float>(arg.input_(n, c, v[0])));
+                arg.wei_element_op_(v_wei, type_convert<float>(arg.weight_(k, c, v[1])));
+            }
+            else if constexpr(NumDimSpatial == 2)
+            {
+                arg.in_element_op_(v_in, type_convert<float>(arg.input_(n, c, v[0], v[1])));
+                arg.wei_element_op_(v_wei, type_convert<float>(arg.weight_(k, c, v[2], v[3])));
+            }
+            else
+            {
+                arg.in_element_op_(v_in, type_convert<float>(arg.input_(n, c, v[0], v[1], v[2])));
+                arg.wei_element_op_(v_wei, type_convert<float>(arg.weight_(k, c, v[3], v[4], v[5])));
+            }
+            v_acc += v_in * v_wei;
+        }
+        template <typename... Out>
+        static void store(const Argument& arg, float v_acc, std::size_t n, std::size_t k, Out... o)
+        {
+            float v_out;
+            arg.out_element_op_(v_out, v_acc);
+            arg.output_(n, k, o...) = type_convert<OutDataType>(v_out);
+        }
+
         float Run(const Argument& arg)
         {
-            const auto& wl = arg.weight_.mDesc.GetLengths(); // K, C, Y, X
-            const auto& il = arg.input_.mDesc.GetLengths();  // N, C, Hi, Wi
-            auto f_nchw    = [&](auto n, auto k, auto ho, auto wo) {
-                float v_acc = 0;
-                for(std::size_t c = 0; c < wl[1]; ++c)
-                    for(std::size_t y = 0; y < wl[2]; ++y)
-                    {
-                        const long_index_t hi = static_cast<long_index_t>(ho * arg.conv_strides_[0]) +
-                                                static_cast<long_index_t>(y * arg.conv_dilations_[0]) -
-                                                static_cast<long_index_t>(arg.in_left_pads_[0]);
-                        for(std::size_t x = 0; x < wl[3]; ++x)
+            const auto& wl = arg.weight_.mDesc.GetLengths(); // K, C, filter...
+            const auto& il = arg.input_.mDesc.GetLengths();  // N, C, spatial...
+            const auto& ol = arg.output_.mDesc.GetLengths(); // N, K, out spatial...
+            const unsigned threads = std::thread::hardware_concurrency();
+            if constexpr(NumDimSpatial == 1)
+            {
+                auto f = [&](auto n, auto k, auto wo) {
+                    float v_acc = 0;
+                    for(std::size_t c = 0; c < wl[1]; ++c)
+                        for(std::size_t x = 0; x < wl[2]; ++x)
                         {
-                            const long_index_t wi = static_cast<long_index_t>(wo * arg.conv_strides_[1]) +
-                                                    static_cast<long_index_t>(x * arg.conv_dilations_[1]) -
-                                                    static_cast<long_index_t>(arg.in_left_pads_[1]);
-                            if(hi >= 0 && static_cast<std::size_t>(hi) < il[2] && wi >= 0 &&
-                               static_cast<std::size_t>(wi) < il[3])
+                            const long_index_t wi = in_pos(arg, wo, x, 0);
+                            if(inside(wi, il[2]))
+                                mac(arg, v_acc, n, k, c, wi, x);
+                        }
+                    store(arg, v_acc, n, k, wo);
+                };
+                make_ParallelTensorFunctor(f, ol[0], ol[1], ol[2])(threads);
+            }
+            else if constexpr(NumDimSpatial == 2)
+            {
+                auto f = [&](auto n, auto k, auto ho, auto wo) {
+                    float v_acc = 0;
+                    for(std::size_t c = 0; c < wl[1]; ++c)
+                        for(std::size_t y = 0; y < wl[2]; ++y)
+                        {
+                            const long_index_t hi = in_pos(arg, ho, y, 0);
+                            for(std::size_t x = 0; x < wl[3]; ++x)
                             {
-                                float v_in, v_wei;
-                                arg.in_element_op_(v_in, type_convert<float>(arg.input_(n, c, hi, wi)));
-                                arg.wei_element_op_(v_wei, type_convert<float>(arg.weight_(k, c, y, x)));
-                                v_acc += v_in * v_wei;
+                                const long_index_t wi = in_pos(arg, wo, x, 1);
+                                if(inside(hi, il[2]) && inside(wi, il[3]))
+                                    mac(arg, v_acc, n, k, c, hi, wi, y, x);
                             }
                         }
-                    }
-                float v_out;
-                arg.out_element_op_(v_out, v_acc);
-                arg.output_(n, k, ho, wo) = type_convert<OutDataType>(v_out);
-            };
-            const auto& ol = arg.output_.mDesc.GetLengths();
-            make_ParallelTensorFunctor(f_nchw, ol[0], ol[1], ol[2], ol[3])(std::thread::hardware_concurrency());
+                    store(arg, v_acc, n, k, ho, wo);
+                };
+                make_ParallelTensorFunctor(f, ol[0], ol[1], ol[2], ol[3])(threads);
+            }
+            else
+            {
+                auto f = [&](auto n, auto k, auto od, auto ho, auto wo) {
+                    float v_acc = 0;
+                    for(std::size_t c = 0; c < wl[1]; ++c)
+                        for(std::size_t z = 0; z < wl[2]; ++z)
+                        {
+                            const long_index_t di = in_pos(arg, od, z, 0);
+                            for(std::size_t y = 0; y < wl[3]; ++y)
+                            {
+                                const long_index_t hi = in_pos(arg, ho, y, 1);
+                                for(std::size_t x = 0; x < wl[4]; ++x)
+                                {
+                                    const long_index_t wi = in_pos(arg, wo, x, 2);
+                                    if(inside(di, il[2]) && inside(hi, il[3]) && inside(wi, il[4]))
+                                        mac(arg, v_acc, n, k, c, di, hi, wi, z, y, x);
+                                }
+                            }
+                        }
+                    store(arg, v_acc, n, k, od, ho, wo);
+                };
+                make_ParallelTensorFunctor(f, ol[0], ol[1], ol[2], ol[3], ol[4])(threads);
+            }
             return 0;
         }
         float Run(const device::BaseArgument* p_arg, const StreamConfig& = StreamConfig{}) override

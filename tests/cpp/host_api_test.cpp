@@ -1,6 +1,7 @@
 // Host-only checks of the Composable-Kernel-compatible C++ headers (no GPU call is made):
 // descriptors, ConvParams, check_err, the CPU reference operators against the reference's golden
 // vectors, functor semantics, epilogue-trait mapping, IsSupportedArgument and type strings.
+#include <cmath>
 #include <cstdio>
 #include <iostream>
 #include <string>
@@ -19,6 +20,7 @@
 #include "ck/library/utility/conv_util.hpp"
 #include "ck/library/utility/fill.hpp"
 #include "ck/tensor_operation/gpu/device/device_conv2d_fwd_xdl_c_shuffle_bias_activation_nhwc_kyxc_nhwk.hpp"
+#include "ck/tensor_operation/gpu/device/device_convnd_fwd_xdl_nhwc_kyxc_nhwk.hpp"
 #include "ck/tensor_operation/gpu/device/device_batched_gemm_xdl.hpp"
 #include "ck/tensor_operation/gpu/device/device_gemm_multiple_d_xdl_cshuffle.hpp"
 #include "ck/tensor_operation/gpu/device/device_gemm_xdl_cshuffle.hpp"
@@ -364,8 +366,74 @@ static void test_batched_gemm_host_side()
     EXPECT(base->IsSupportedArgument(parg.get()));
 }
 
+// 1-D and 3-D: the reference's golden vectors for its CPU operator (test/reference_conv_fwd/reference_conv_fwd.cpp:
+// Conv1DNWC, Conv1DNWCStridesDilationsPadding, Conv3DNCDHW) and the NumDimSpatial = 1 / 3 device operations.
+static void test_convnd_host_side()
+{
+    namespace host = ck::tensor_operation::host;
+    {
+        using Ref = host::ReferenceConvFwd<float, float, float, ew::PassThrough, ew::PassThrough, ew::PassThrough, 1>;
+        Tensor<float> in(ck::utils::conv::get_input_host_tensor_descriptor(std::vector<std::size_t>{1, 2, 6}));
+        Tensor<float> wei(ck::utils::conv::get_filters_host_tensor_descriptor(std::vector<std::size_t>{1, 2, 3}));
+        Tensor<float> out(ck::utils::conv::get_output_host_tensor_descriptor(std::vector<std::size_t>{1, 1, 4}));
+        ck::utils::FillMonotonicSeq<float>{}(in.begin(), in.end());
+        ck::utils::FillConstant<float>{0.5f}(wei.begin(), wei.end());
+        auto arg = Ref::MakeArgument(in, wei, out, {1}, {1}, {0}, {0}, {}, {}, {});
+        Ref::MakeInvoker().Run(arg);
+        EXPECT(ck::utils::check_err(out.mData, std::vector<float>{7.5, 13.5, 19.5, 25.5}));
+    }
+    {
+        using Ref = host::ReferenceConvFwd<float, float, float, ew::PassThrough, ew::PassThrough, ew::PassThrough, 1>;
+        Tensor<float> in(ck::utils::conv::get_input_host_tensor_descriptor(std::vector<std::size_t>{1, 2, 12}));
+        Tensor<float> wei(ck::utils::conv::get_filters_host_tensor_descriptor(std::vector<std::size_t>{2, 2, 3}));
+        Tensor<float> out(ck::utils::conv::get_output_host_tensor_descriptor(std::vector<std::size_t>{1, 2, 5}));
+        ck::utils::FillMonotonicSeq<float>{}(in.begin(), in.end());
+        ck::utils::FillConstant<float>{0.5f}(wei.begin(), wei.end());
+        auto arg = Ref::MakeArgument(in, wei, out, {2}, {2}, {1}, {1}, {}, {}, {});
+        Ref::MakeInvoker().Run(arg);
+        EXPECT(ck::utils::check_err(out.mData, std::vector<float>{9., 9., 19.5, 19.5, 31.5, 31.5, 43.5, 43.5, 55.5, 55.5}));
+    }
+    {
+        // NCDHW in memory (packed channel-first descriptor), output NKDHW, input 0, 0.1, 0.2, ...
+        using Ref = host::ReferenceConvFwd<float, float, float, ew::PassThrough, ew::PassThrough, ew::PassThrough, 3>;
+        Tensor<float> in(HostTensorDescriptor(std::vector<std::size_t>{1, 2, 6, 6, 6}));
+        Tensor<float> wei(HostTensorDescriptor(std::vector<std::size_t>{1, 2, 3, 3, 3}));
+        Tensor<float> out(HostTensorDescriptor(std::vector<std::size_t>{1, 1, 4, 4, 4}));
+        ck::utils::FillMonotonicSeq<float>{0.f, 0.1f}(in.begin(), in.end());
+        ck::utils::FillConstant<float>{0.5f}(wei.begin(), wei.end());
+        auto arg = Ref::MakeArgument(in, wei, out, {1, 1, 1}, {1, 1, 1}, {0, 0, 0}, {0, 0, 0}, {}, {}, {});
+        Ref::MakeInvoker().Run(arg);
+        EXPECT(out.mData.size() == 64);
+        EXPECT(std::abs(out.mData[0] - 407.7f) < 1e-2f && std::abs(out.mData[1] - 410.4f) < 1e-2f &&
+               std::abs(out.mData[16] - 504.9f) < 1e-2f && std::abs(out.mData[63] - 756.f) < 1e-2f);
+    }
+    // clang-format off
+    using Conv1d = dev::DeviceConvNDFwdXdl_Input_N_Hi_Wi_C_Weight_K_Y_X_C_Output_N_Ho_Wo_K<
+        F16, F16, F16, float, ew::PassThrough, ew::PassThrough, ew::PassThrough, dev::ConvolutionForwardSpecialization::Default, 1,
+        256, 128, 256, 4, 8, 32, 32, 2, 4, S<4, 64, 1>, S<1, 0, 2>, S<1, 0, 2>, 2, 8, 8, true,
+        S<4, 64, 1>, S<1, 0, 2>, S<1, 0, 2>, 2, 8, 8, true, 7, 1>;
+    using Conv3d = dev::DeviceConvNDFwdXdl_Input_N_Hi_Wi_C_Weight_K_Y_X_C_Output_N_Ho_Wo_K<
+        F16, F16, F16, float, ew::PassThrough, ew::PassThrough, ew::PassThrough, dev::ConvolutionForwardSpecialization::Default, 3,
+        256, 128, 256, 4, 8, 32, 32, 2, 4, S<4, 64, 1>, S<1, 0, 2>, S<1, 0, 2>, 2, 8, 8, true,
+        S<4, 64, 1>, S<1, 0, 2>, S<1, 0, 2>, 2, 8, 8, true, 7, 1>;
+    // clang-format on
+    const F16* pa = reinterpret_cast<const F16*>(0x1000);
+    F16* pc       = reinterpret_cast<F16*>(0x3000);
+    // test/convnd_fwd/conv1d_fwd.cpp:73-74 and conv3d_fwd.cpp:76-77
+    auto a1 = Conv1d::MakeArgument(pa, pa, pc, 4, 256, 64, {71}, {3}, {36}, {2}, {2}, {2}, {2}, {}, {}, {});
+    EXPECT(Conv1d::IsSupportedArgument(a1));
+    auto a3 = Conv3d::MakeArgument(pa, pa, pc, 4, 256, 64, {28, 28, 28}, {3, 3, 3}, {14, 14, 14}, {2, 2, 2}, {2, 2, 2},
+                                   {2, 2, 2}, {2, 2, 2}, {}, {}, {});
+    EXPECT(Conv3d::IsSupportedArgument(a3));
+    auto mismatch = Conv3d::MakeArgument(pa, pa, pc, 4, 256, 64, {28, 28}, {3, 3}, {14, 14}, {2, 2}, {2, 2}, {2, 2},
+                                         {2, 2}, {}, {}, {});
+    EXPECT(!Conv3d::IsSupportedArgument(mismatch)); // a 2-D problem handed to the 3-D instance
+    EXPECT(Conv3d{}.GetTypeString().find("DeviceConv3DFwdXdl") == 0);
+}
+
 int main()
 {
+    test_convnd_host_side();
     test_batched_gemm_host_side();
     test_instance_factory();
     test_descriptors();

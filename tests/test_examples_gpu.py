@@ -82,3 +82,16 @@ def test_profiler_driver_walks_instance_lists(examples_built):
     assert "Best Perf for grouped_gemm" in out
     out = run_example("ck_profiler", "conv_fwd_bias_relu", 1, 1, 2, 0, 1, 4, 64, 64, 3, 3, 17, 17, 2, 2, 1, 1, 1, 1, 1, 1)
     assert "Best Perf for conv_fwd_bias_relu" in out
+
+
+def test_profiler_driver_convnd(examples_built):
+    """conv_fwd sub-command (profiler/src/profile_convnd_fwd.cpp:60-115): 1-D, 2-D and 3-D channels-last problems of
+    the reference's device tests, verified against the N-D ReferenceConvFwd of the compat headers."""
+    # conv_fwd dtype layout verify init log time nd N K C <filter> <input> <strides> <dilations> <lpads> <rpads>
+    out = run_example("ck_profiler", "conv_fwd", 1, 1, 1, 1, 0, 1, 1, 4, 256, 64, 3, 71, 2, 2, 2, 2)
+    assert "Best Perf for conv_fwd" in out and "DeviceConv1DFwdXdl" in out
+    out = run_example("ck_profiler", "conv_fwd", 3, 1, 1, 1, 0, 1, 2, 4, 64, 64, 3, 3, 17, 17, 2, 2, 1, 1, 1, 1, 1, 1)
+    assert "DeviceConv2DFwdXdl" in out
+    out = run_example("ck_profiler", "conv_fwd", 1, 1, 1, 1, 0, 1, 3, 2, 64, 32, 3, 3, 3, 10, 10, 10, 1, 1, 1, 2, 2, 2,
+                      2, 2, 2, 2, 2, 2)
+    assert "Best Perf for conv_fwd" in out and "DeviceConv3DFwdXdl" in out
