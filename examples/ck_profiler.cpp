@@ -8,6 +8,8 @@
 //   ck_profiler gemm_add_add_fastgelu <dtype 1> <layout 1> <verify> <init> <log> <time> M N K StrideA StrideB StrideD0 StrideD1 StrideE
 //   ck_profiler grouped_gemm          <dtype 1> <layout 1> <verify> <init> <log> <time> Ms Ns Ks          (comma separated lists)
 //   ck_profiler conv_fwd_bias_relu    <dtype 1> <verify> <init> <log> <time> N K C Y X Hi Wi Sy Sx Dy Dx LeftPy LeftPx RightPy RightPx
+//   ck_profiler batched_gemm          <dtype 1 fp16|2 bf16|3 int8> <layout 0..3> <verify> <init> <log> <time> M N K StrideA StrideB StrideC
+//                                     BatchStrideA BatchStrideB BatchStrideC BatchCount
 //   ck_profiler conv_fwd              <dtype 1 fp16|2 bf16|3 int8> <layout 1 NHWC> <verify> <init> <log> <time> <nd 1|2|3> N K C
 //                                     <filter> <input> <strides> <dilations> <left pads> <right pads>   (nd values each)
 // gemm takes the reference's four matrix layouts (0: mk_kn, 1: mk_nk, 2: km_kn, 3: km_nk); the fused and grouped
@@ -27,7 +29,9 @@
 #include "ck/library/tensor_operation_instance/gpu/grouped_gemm.hpp"
 #include "ck/library/utility/check_err.hpp"
 #include "ck/library/utility/conv_util.hpp"
+#include "ck/library/reference_tensor_operation/cpu/reference_batched_gemm.hpp"
 #include "ck/library/reference_tensor_operation/cpu/reference_conv_fwd.hpp"
+#include "ck/tensor_operation/gpu/device/device_batched_gemm_xdl.hpp"
 #include "ck/tensor_operation/gpu/device/device_conv2d_fwd_xdl_c_shuffle_bias_activation_nhwc_kyxc_nhwk.hpp"
 #include "ck/tensor_operation/gpu/device/device_convnd_fwd_xdl_nhwc_kyxc_nhwk.hpp"
 
@@ -384,6 +388,91 @@ int profile_conv_fwd_bias_relu(int argc, char* argv[])
     return pass && !best.name.empty() ? 0 : 1;
 }
 
+template <typename T, typename ALayout, typename BLayout>
+bool profile_batched_gemm_typed(bool verify, int init, bool time, int M, int N, int K, int sa, int sb, int sc, int bsa,
+                                int bsb, int bsc, int G)
+{
+    // clang-format off
+    using Op = dev::DeviceBatchedGemmXdl<T, T, T, float, ALayout, BLayout, Row, PassThrough, PassThrough, PassThrough,
+        256, 256, 128, 4, 8, 32, 32, 4, 2, inst::S<4, 64, 1>, inst::S<1, 0, 2>, inst::S<1, 0, 2>, 2, 8, 8, true,
+        inst::S<4, 64, 1>, inst::S<1, 0, 2>, inst::S<1, 0, 2>, 2, 8, 8, true, 7, 1>;
+    // clang-format on
+    auto desc3 = [](std::size_t g, std::size_t row, std::size_t col, std::size_t stride, std::size_t bstride, auto layout) {
+        const bool row_major = std::is_same<decltype(layout), Row>::value;
+        return HostTensorDescriptor(std::vector<std::size_t>{g, row, col},
+                                    row_major ? std::vector<std::size_t>{bstride, stride, 1}
+                                              : std::vector<std::size_t>{bstride, 1, stride});
+    };
+    Tensor<T> a(desc3(G, M, K, sa, bsa, ALayout{})), b(desc3(G, K, N, sb, bsb, BLayout{}));
+    Tensor<T> c_host(desc3(G, M, N, sc, bsc, Row{})), c_dev(desc3(G, M, N, sc, bsc, Row{}));
+    init_tensor(a, init, false);
+    init_tensor(b, init, true);
+    DeviceMem a_buf(sizeof(T) * a.mDesc.GetElementSpace()), b_buf(sizeof(T) * b.mDesc.GetElementSpace()),
+        c_buf(sizeof(T) * c_dev.mDesc.GetElementSpace());
+    a_buf.ToDevice(a.mData.data());
+    b_buf.ToDevice(b.mData.data());
+    c_buf.SetZero();
+    Op op;
+    auto arg = op.MakeArgumentPointer(a_buf.GetDeviceBuffer(), b_buf.GetDeviceBuffer(), c_buf.GetDeviceBuffer(), M, N, K,
+                                      sa, sb, sc, bsa, bsb, bsc, G, {}, {}, {});
+    Best best;
+    if(!op.IsSupportedArgument(arg.get()))
+    {
+        best.report("batched_gemm");
+        return false;
+    }
+    const float ms = op.MakeInvokerPointer()->Run(arg.get(), StreamConfig{nullptr, time});
+    if(time)
+        best.offer(op.GetTypeString(), ms, std::size_t(2) * G * M * N * K,
+                   sizeof(T) * G * (std::size_t(M) * K + std::size_t(K) * N + std::size_t(M) * N));
+    else
+        best.name = op.GetTypeString();
+    bool pass = true;
+    if(verify)
+    {
+        using Ref = ck::tensor_operation::host::ReferenceBatchedGemm<T, T, T, PassThrough, PassThrough, PassThrough>;
+        auto rarg = Ref::MakeArgument(a, b, c_host, {}, {}, {});
+        Ref::MakeInvoker().Run(rarg);
+        c_buf.FromDevice(c_dev.mData.data());
+        pass = ck::utils::check_err(c_dev.mData, c_host.mData);
+    }
+    best.report("batched_gemm");
+    return pass;
+}
+
+int profile_batched_gemm(int argc, char* argv[])
+{
+    if(argc != 18)
+    {
+        std::printf("batched_gemm <dtype 1|2|3> <layout 0..3> verify init log time M N K StrideA StrideB StrideC "
+                    "BatchStrideA BatchStrideB BatchStrideC BatchCount\n");
+        return 1;
+    }
+    const int dtype = std::stoi(argv[2]), layout = std::stoi(argv[3]);
+    const bool verify = std::stoi(argv[4]), time = std::stoi(argv[7]);
+    const int init = std::stoi(argv[5]);
+    int v[10];
+    for(int i = 0; i < 10; ++i)
+        v[i] = std::stoi(argv[8 + i]);
+    if(layout < 0 || layout > 3 || dtype < 1 || dtype > 3)
+        return 1;
+    auto run = [&](auto t, auto la, auto lb) {
+        return profile_batched_gemm_typed<decltype(t), decltype(la), decltype(lb)>(verify, init, time, v[0], v[1], v[2],
+                                                                                   v[3], v[4], v[5], v[6], v[7], v[8], v[9]);
+    };
+    auto by_layout = [&](auto t) {
+        switch(layout)
+        {
+        case 0: return run(t, Row{}, Row{});
+        case 1: return run(t, Row{}, Col{});
+        case 2: return run(t, Col{}, Row{});
+        default: return run(t, Col{}, Col{});
+        }
+    };
+    const bool ok = dtype == 1 ? by_layout(ck::half_t{}) : dtype == 2 ? by_layout(ck::bhalf_t{}) : by_layout(int8_t{});
+    return ok ? 0 : 1;
+}
+
 template <int ND, typename T>
 bool profile_convnd_typed(const ck::utils::conv::ConvParams& p, bool verify, int init, bool time)
 {
@@ -486,11 +575,14 @@ int main(int argc, char* argv[])
             return profile_conv_fwd_bias_relu(argc, argv);
         if(std::strcmp(argv[1], "conv_fwd") == 0)
             return profile_convnd_fwd(argc, argv);
+        if(std::strcmp(argv[1], "batched_gemm") == 0)
+            return profile_batched_gemm(argc, argv);
     }
     std::printf("arg1: tensor operation (gemm: GEMM\n"
                 "                        gemm_add_add_fastgelu: GEMM+Add+Add+FastGeLU\n"
                 "                        grouped_gemm: Grouped GEMM\n"
                 "                        conv_fwd_bias_relu: ForwardConvolution+Bias+ReLU\n"
-                "                        conv_fwd: ForwardConvolution 1-D / 2-D / 3-D)\n");
+                "                        conv_fwd: ForwardConvolution 1-D / 2-D / 3-D\n"
+                "                        batched_gemm: Batched GEMM)\n");
     return 0;
 }

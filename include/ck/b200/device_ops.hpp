@@ -157,6 +157,21 @@ struct DeviceGemmMultipleD : public BaseOperator
 template <typename... Ts>
 using DeviceGemmMultipleDPtr = std::unique_ptr<DeviceGemmMultipleD<Ts...>>;
 
+// device_gemm_splitk.hpp:15-42
+template <typename ALayout, typename BLayout, typename CLayout, typename ADataType, typename BDataType,
+          typename CDataType, typename AElementwiseOperation, typename BElementwiseOperation,
+          typename CElementwiseOperation>
+struct DeviceGemmSplitK : public BaseOperator
+{
+    virtual std::unique_ptr<BaseArgument>
+    MakeArgumentPointer(const void* p_a, const void* p_b, void* p_c, index_t M, index_t N, index_t K, index_t StrideA,
+                        index_t StrideB, index_t StrideC, AElementwiseOperation a_element_op,
+                        BElementwiseOperation b_element_op, CElementwiseOperation c_element_op, index_t KBatch) = 0;
+    virtual std::unique_ptr<BaseInvoker> MakeInvokerPointer()                                                   = 0;
+};
+template <typename... Ts>
+using DeviceGemmSplitKPtr = std::unique_ptr<DeviceGemmSplitK<Ts...>>;
+
 // device_batched_gemm.hpp:15-52
 template <typename ALayout, typename BLayout, typename CLayout, typename ADataType, typename BDataType,
           typename CDataType, typename AElementwiseOperation, typename BElementwiseOperation,
@@ -615,6 +630,59 @@ struct DeviceGemmXdl : public DeviceGemm<ALayout, BLayout, CLayout, ADataType, B
         s << "DeviceGemmXdl<" << BlockSize << ", " << MPerBlock << ", " << NPerBlock << ", " << K0PerBlock << ", " << K1
           << ", " << MPerXDL << ", " << NPerXDL << ", " << MXdlPerWave << ", " << NXdlPerWave
           << "> on B200 tcgen05 (tuning parameters ignored)";
+        return s.str();
+    }
+};
+
+// device_gemm_xdl_splitk_c_shuffle.hpp:23-60.  KBatch is the reference's tuning knob for how many ways the K loop
+// is cut (partial sums added atomically into a zero-initialised C); here the result is written once and the library
+// decides by itself where cutting K pays (the tail wave), so the value only has to be >= 1.
+template <typename ADataType, typename BDataType, typename CDataType, typename AccDataType, typename ALayout,
+          typename BLayout, typename CLayout, typename AElementwiseOperation, typename BElementwiseOperation,
+          typename CElementwiseOperation, GemmSpecialization GemmSpec, index_t BlockSize, index_t MPerBlock,
+          index_t NPerBlock, index_t K0PerBlock, index_t K1, index_t MPerXDL, index_t NPerXDL, index_t MXdlPerWave,
+          index_t NXdlPerWave, CKB_XFER(ABlockTransfer), CKB_XFER(BBlockTransfer), index_t CShuffleMRepeatPerShuffle,
+          index_t CShuffleNRepeatPerShuffle, typename CBlockTransferClusterLengths,
+          index_t CBlockTransferScalarPerVector>
+struct DeviceGemmXdlSplitKCShuffle : public DeviceGemmSplitK<ALayout, BLayout, CLayout, ADataType, BDataType, CDataType,
+                                                             AElementwiseOperation, BElementwiseOperation,
+                                                             CElementwiseOperation>
+{
+    using Argument = b200::GemmArgument;
+    using Invoker  = b200::GemmInvoker;
+
+    static auto MakeArgument(const ADataType* p_a, const BDataType* p_b, CDataType* p_c, index_t M, index_t N,
+                             index_t K, index_t StrideA, index_t StrideB, index_t StrideC, AElementwiseOperation,
+                             BElementwiseOperation, CElementwiseOperation c_element_op, index_t KBatch)
+    {
+        auto arg = b200::make_gemm_argument<ALayout, BLayout, CLayout, ADataType, BDataType, CDataType,
+                                            AElementwiseOperation, BElementwiseOperation, CElementwiseOperation,
+                                            b200::ctx_gemm_c, 0>(p_a, p_b, {}, p_c, M, N, K, StrideA, StrideB, {},
+                                                                 StrideC, c_element_op);
+        arg.host_ok = arg.host_ok && KBatch >= 1;
+        return arg;
+    }
+    static auto MakeInvoker() { return Invoker{}; }
+    static bool IsSupportedArgument(const Argument& arg) { return b200::gemm_supported(arg); }
+    bool IsSupportedArgument(const BaseArgument* p_arg) override
+    {
+        return IsSupportedArgument(b200::argument_cast<Argument>(p_arg));
+    }
+    std::unique_ptr<BaseArgument> MakeArgumentPointer(const void* p_a, const void* p_b, void* p_c, index_t M, index_t N,
+                                                      index_t K, index_t StrideA, index_t StrideB, index_t StrideC,
+                                                      AElementwiseOperation a_op, BElementwiseOperation b_op,
+                                                      CElementwiseOperation c_op, index_t KBatch) override
+    {
+        return std::make_unique<Argument>(MakeArgument(static_cast<const ADataType*>(p_a),
+                                                       static_cast<const BDataType*>(p_b), static_cast<CDataType*>(p_c),
+                                                       M, N, K, StrideA, StrideB, StrideC, a_op, b_op, c_op, KBatch));
+    }
+    std::unique_ptr<BaseInvoker> MakeInvokerPointer() override { return std::make_unique<Invoker>(); }
+    std::string GetTypeString() const override
+    {
+        std::ostringstream s;
+        s << "DeviceGemmXdlSplitKCShuffle<" << BlockSize << ", " << MPerBlock << ", " << NPerBlock << ", " << K0PerBlock
+          << "> on B200 tcgen05 (tuning parameters and KBatch ignored)";
         return s.str();
     }
 };

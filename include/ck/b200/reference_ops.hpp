@@ -76,6 +76,66 @@ struct ReferenceGemm : public device::BaseOperator
     std::string GetTypeString() const override { return "ReferenceGemm"; }
 };
 
+// C[g,m,n] = c_op( sum_k a_op(A[g,m,k]) * b_op(B[g,k,n]) ), float accumulation
+// (reference_batched_gemm.hpp:21-135); tensors are 3-D with any strides.
+template <typename ADataType, typename BDataType, typename CDataType, typename AElementwiseOperation,
+          typename BElementwiseOperation, typename CElementwiseOperation>
+struct ReferenceBatchedGemm : public device::BaseOperator
+{
+    struct Argument : public device::BaseArgument
+    {
+        Argument(const Tensor<ADataType>& a_g_m_k, const Tensor<BDataType>& b_g_k_n, Tensor<CDataType>& c_g_m_n,
+                 AElementwiseOperation a_element_op, BElementwiseOperation b_element_op,
+                 CElementwiseOperation c_element_op)
+            : a_g_m_k_{a_g_m_k}, b_g_k_n_{b_g_k_n}, c_g_m_n_{c_g_m_n}, a_element_op_{a_element_op},
+              b_element_op_{b_element_op}, c_element_op_{c_element_op}
+        {
+        }
+        const Tensor<ADataType>& a_g_m_k_;
+        const Tensor<BDataType>& b_g_k_n_;
+        Tensor<CDataType>& c_g_m_n_;
+        AElementwiseOperation a_element_op_;
+        BElementwiseOperation b_element_op_;
+        CElementwiseOperation c_element_op_;
+    };
+    struct Invoker : public device::BaseInvoker
+    {
+        float Run(const Argument& arg)
+        {
+            auto f = [&](auto g, auto m, auto n) {
+                const std::size_t K = arg.a_g_m_k_.mDesc.GetLengths()[2];
+                float v_acc         = 0;
+                for(std::size_t k = 0; k < K; ++k)
+                {
+                    ADataType v_a;
+                    BDataType v_b;
+                    arg.a_element_op_(v_a, arg.a_g_m_k_(g, m, k));
+                    arg.b_element_op_(v_b, arg.b_g_k_n_(g, k, n));
+                    v_acc += type_convert<float>(v_a) * type_convert<float>(v_b);
+                }
+                float v_c;
+                arg.c_element_op_(v_c, v_acc);
+                arg.c_g_m_n_(g, m, n) = type_convert<CDataType>(v_c);
+            };
+            const auto& l = arg.c_g_m_n_.mDesc.GetLengths();
+            make_ParallelTensorFunctor(f, l[0], l[1], l[2])(std::thread::hardware_concurrency());
+            return 0;
+        }
+        float Run(const device::BaseArgument* p_arg, const StreamConfig& = StreamConfig{}) override
+        {
+            return Run(*dynamic_cast<const Argument*>(p_arg));
+        }
+    };
+    bool IsSupportedArgument(const device::BaseArgument*) override { return true; }
+    static auto MakeArgument(const Tensor<ADataType>& a, const Tensor<BDataType>& b, Tensor<CDataType>& c,
+                             AElementwiseOperation a_op, BElementwiseOperation b_op, CElementwiseOperation c_op)
+    {
+        return Argument{a, b, c, a_op, b_op, c_op};
+    }
+    static auto MakeInvoker() { return Invoker{}; }
+    std::string GetTypeString() const override { return "ReferenceBatchedGemm"; }
+};
+
 // 1-D, 2-D and 3-D (reference_conv_fwd.hpp:84-254): tensors carry channel-first ordered lengths {N, C, spatial...}
 // ({K, C, filter...}, {N, K, out spatial...}) with the strides of any memory layout, see the conv_util host
 // descriptors.  Accumulation in float over c, then the filter positions outermost dimension first.

@@ -24,6 +24,7 @@
 #include "ck/tensor_operation/gpu/device/device_batched_gemm_xdl.hpp"
 #include "ck/tensor_operation/gpu/device/device_gemm_multiple_d_xdl_cshuffle.hpp"
 #include "ck/tensor_operation/gpu/device/device_gemm_xdl_cshuffle.hpp"
+#include "ck/tensor_operation/gpu/device/device_gemm_xdl_splitk_c_shuffle.hpp"
 #include "ck/tensor_operation/gpu/device/device_grouped_gemm_xdl.hpp"
 #include "ck/tensor_operation/gpu/element/element_wise_operation.hpp"
 
@@ -361,6 +362,17 @@ static void test_batched_gemm_host_side()
     auto none = op.MakeArgument(pa, pa, pc, 256, 256, 64, 64, 64, 256, 256 * 64, 256 * 64, 256 * 256, 0, {}, {}, {});
     EXPECT(!op.IsSupportedArgument(none));
     EXPECT(op.GetTypeString().find("DeviceBatchedGemmXdl<256, 256, 128, 4>") == 0);
+    // clang-format off
+    using SplitK = dev::DeviceGemmXdlSplitKCShuffle<F16, F16, F16, float, Row, Col, Row, ew::PassThrough, ew::PassThrough, ew::PassThrough, GemmDefault,
+        256, 256, 128, 4, 8, 32, 32, 4, 2, S<1, 4, 64, 1>, S<0, 2, 1, 3>, S<0, 2, 1, 3>, 3, 8, 8, true,
+        S<1, 4, 64, 1>, S<0, 1, 3, 2>, S<0, 1, 3, 2>, 3, 8, 8, true, 1, 1, S<1, 32, 1, 8>, 8>;
+    // clang-format on
+    SplitK sk;
+    dev::DeviceGemmSplitK<Row, Col, Row, F16, F16, F16, ew::PassThrough, ew::PassThrough, ew::PassThrough>* sk_base = &sk;
+    auto sk_arg = sk_base->MakeArgumentPointer(pa, pa, pc, 256, 256, 512, 512, 512, 256, {}, {}, {}, 4);
+    EXPECT(sk_base->IsSupportedArgument(sk_arg.get()));
+    auto sk_bad = sk_base->MakeArgumentPointer(pa, pa, pc, 256, 256, 512, 512, 512, 256, {}, {}, {}, 0);
+    EXPECT(!sk_base->IsSupportedArgument(sk_bad.get()));
     dev::DeviceBatchedGemm<Row, Col, Row, F16, F16, F16, ew::PassThrough, ew::PassThrough, ew::PassThrough>* base = &op;
     auto parg = base->MakeArgumentPointer(pa, pa, pc, 256, 256, 64, 64, 64, 256, 256 * 64, 256 * 64, 256 * 256, 8, {}, {}, {});
     EXPECT(base->IsSupportedArgument(parg.get()));

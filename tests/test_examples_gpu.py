@@ -95,3 +95,14 @@ def test_profiler_driver_convnd(examples_built):
     out = run_example("ck_profiler", "conv_fwd", 1, 1, 1, 1, 0, 1, 3, 2, 64, 32, 3, 3, 3, 10, 10, 10, 1, 1, 1, 2, 2, 2,
                       2, 2, 2, 2, 2, 2)
     assert "Best Perf for conv_fwd" in out and "DeviceConv3DFwdXdl" in out
+
+
+def test_profiler_driver_batched_gemm(examples_built):
+    """batched_gemm sub-command (profiler/src/profile_batched_gemm.cpp:27-60), verified against ReferenceBatchedGemm."""
+    # dtype layout verify init log time M N K StrideA StrideB StrideC BatchStrideA BatchStrideB BatchStrideC BatchCount
+    out = run_example("ck_profiler", "batched_gemm", 1, 1, 1, 1, 0, 1, 256, 384, 128, 128, 128, 384,
+                      256 * 128, 384 * 128, 256 * 384, 8)
+    assert "Best Perf for batched_gemm" in out and "DeviceBatchedGemmXdl" in out
+    out = run_example("ck_profiler", "batched_gemm", 3, 2, 1, 1, 0, 0, 256, 384, 128, 256, 384, 384,
+                      256 * 128, 384 * 128, 256 * 384, 3)  # int8, A[g,k,m] * B[g,k,n]
+    assert "Best Perf for batched_gemm" in out
