@@ -110,3 +110,23 @@ def test_ksplit_on_two_streams_at_once(cuda_device):
     assert ck.device_status() == 0
     for e, (a, bt) in zip(outs, ins):
         np.testing.assert_array_equal(e.cpu().numpy(), oracle.gemm(a, bt.T))
+
+
+def test_ksplit_tail_of_a_batched_gemm_spans_batches(cuda_device):
+    """Batched GEMM whose tail tiles belong to different batches: 40 batches of 512 x 512 x 512 are 160 pair tiles on
+    74 pairs (148 whole, 12 tail tiles cut in four along K)."""
+    rng = np.random.default_rng(17)
+    G, M, N, K = 40, 512, 512, 512
+    a, bt = ints(rng, (G, M, K)), ints(rng, (G, N, K))
+    da, db = torch.from_numpy(a).cuda(), torch.from_numpy(bt).cuda()
+    e = torch.zeros((G, M, N), dtype=torch.float16, device="cuda")
+    op = ck.DeviceBatchedGemm(capi.CKB_F16)
+    arg = op.MakeArgument(da.data_ptr(), db.data_ptr(), e.data_ptr(), M, N, K, K, K, N, M * K, N * K, M * N, G)
+    assert op.IsSupportedArgument(arg), capi.last_error()
+    op.MakeInvoker().Run(arg)
+    op.MakeInvoker().Run(arg)
+    torch.cuda.synchronize()
+    assert ck.device_status() == 0
+    out = e.cpu().numpy()
+    for g in range(G):
+        np.testing.assert_array_equal(out[g], oracle.gemm(a[g], bt[g].T))
