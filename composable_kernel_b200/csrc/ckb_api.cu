@@ -235,6 +235,30 @@ int encode_mnmajor_2d(CUtensorMap* tm, int dtype, const void* ptr, int64_t mn, i
     return CKB_OK;
 }
 
+// E (M x N row-major, pitch `lde` elements) as the (columns, rows[, batch]) map of the epilogue's staged stores:
+// 32 x 32 box whose rows are 64 bytes (16-bit E, 64-byte swizzle) or 32 bytes (int8 E, 32-byte swizzle).
+// Only encoded when E allows 16-byte accesses (base and pitch multiples of 16 bytes).
+int encode_e_map(CUtensorMap* tm, int dtype, const void* ptr, int64_t m, int64_t n, int64_t lde, int64_t batch = 0,
+                 int64_t batch_stride = 0)
+{
+    load_entry_points();
+    if(!g_encode_tiled)
+        return fail(CKB_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+    const int eb          = elem_bytes(dtype);
+    cuuint64_t dims[3]    = {static_cast<cuuint64_t>(n), static_cast<cuuint64_t>(m), static_cast<cuuint64_t>(batch)};
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(lde) * eb, static_cast<cuuint64_t>(batch_stride) * eb};
+    cuuint32_t box[3]     = {32, 32, 1};
+    cuuint32_t estr[3]    = {1, 1, 1};
+    CUresult r = g_encode_tiled(tm, tm_dtype(dtype), batch >= 1 ? 3 : 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                eb == 1 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B,
+                                CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if(r != CUDA_SUCCESS)
+        return fail(CKB_ERR_CUDA, "cuTensorMapEncodeTiled (E) failed (CUresult %d) m=%lld n=%lld lde=%lld",
+                    static_cast<int>(r), (long long)m, (long long)n, (long long)lde);
+    return CKB_OK;
+}
+
 // A is M x K: row-major = K-major, column-major = M-major.  B is K x N: column-major = K-major,
 // row-major = N-major.
 bool a_is_mn_major(const ckb_gemm_desc* d) { return d->a_layout == CKB_COL_MAJOR; }
@@ -668,6 +692,12 @@ static int gemm_run_impl(const ckb_gemm_desc* d, const BatchInfo& bi, void* stre
     p.tiles_n       = static_cast<int32_t>(tiles_n);
     p.num_kb        = num_kb;
     p.vec_ok        = gemm_vec_ok(d) && bi.vec_ok ? 1 : 0;
+    if(p.vec_ok)
+    {
+        rc = encode_e_map(&p.tm_e, d->e_dtype, d->p_e, d->M, d->N, d->lde, bi.batch, bi.stride_e);
+        if(rc)
+            return rc;
+    }
     p.wait_limit_ns = wait_limit_ns();
     p.status        = dev->status;
     LaunchFn fn     = find_launch(MODE_GEMM, kind_of(d->ab_dtype), d->epilogue);
@@ -827,6 +857,12 @@ static int fill_group_table(const ckb_grouped_gemm_desc* g, const GroupedPlan& g
         ge.tile_start = static_cast<int32_t>(tile_start);
         ge.num_kb     = static_cast<int32_t>((d.K + bk - 1) / bk);
         ge.vec_ok     = gemm_vec_ok(&d) ? 1 : 0;
+        if(ge.vec_ok)
+        {
+            rc = encode_e_map(&ge.tm_e, dtype, d.p_e, d.M, d.N, d.lde);
+            if(rc)
+                return rc;
+        }
         ge.e          = d.p_e;
         ge.d0         = d.n_ds > 0 ? d.p_ds[0] : nullptr;
         ge.d1         = d.n_ds > 1 ? d.p_ds[1] : nullptr;
@@ -899,7 +935,7 @@ int ckb_grouped_gemm_run(const ckb_grouped_gemm_desc* g, void* workspace, size_t
 // the device address comes from cudaGetSymbolAddress (looked up once per device, with that device
 // current) and that pointer is what the kernel receives.
 static __device__ __align__(256) unsigned char g_noalloc_group_table[CKB_NOALLOC_MAX_GROUPS * sizeof(GroupEntry)];
-static_assert(sizeof(GroupEntry) == 512, "the documented size of the fixed table assumes 512-byte entries");
+static_assert(sizeof(GroupEntry) == 640, "the documented size of the fixed table assumes 640-byte entries");
 
 static GroupEntry* g_noalloc_dev_ptr[64] = {};
 static GroupEntry g_noalloc_host_table[CKB_NOALLOC_MAX_GROUPS]; // host staging, fixed size
@@ -1193,6 +1229,12 @@ static int run_conv(const ConvProblem& c, void* stream, int n_rep, float* avg_ms
     p.conv.pad_w    = c.pw;
     p.num_kb        = static_cast<int32_t>(taps * p.conv.c_blocks);
     p.vec_ok        = vec ? 1 : 0;
+    if(vec)
+    {
+        rc = encode_e_map(&p.tm_e, c.dtype, c.p_out, gm, c.K, c.K);
+        if(rc)
+            return rc;
+    }
     p.wait_limit_ns = wait_limit_ns();
     p.status        = dev->status;
     LaunchFn fn = find_launch(MODE_CONV, kind_of(c.dtype), c.epilogue);

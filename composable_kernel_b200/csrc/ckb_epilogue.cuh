@@ -9,6 +9,7 @@
 #include <stdint.h>
 
 #include "../../include/ckb200.h"
+#include "ckb_ptx.cuh"
 
 namespace ckb {
 
@@ -182,13 +183,13 @@ __device__ __forceinline__ void epi_prefetch_d(const EpilogueArgs& ea, int64_t m
     }
 }
 
-// Full 32-column segment, 128-bit accesses; the last D tensor is already in registers.
+// Full 32-column segment of one row: the functor applied to 32 accumulators, packed as 4 x 128 bits of E.
+// 128-bit D accesses; the last D tensor is already in registers.
 template <int EPI, typename T>
-__device__ __forceinline__ void epi_store_vec_f(const uint32_t (&v)[32], const DChunk& dc,
-                                                const EpilogueArgs& ea, int64_t m, int64_t n0)
+__device__ __forceinline__ void epi_compute_vec_f(uint4 (&out)[4], const uint32_t (&v)[32], const DChunk& dc,
+                                                  const EpilogueArgs& ea, int64_t m, int64_t n0)
 {
     constexpr int ND = epi_num_d(EPI);
-    T* e_row         = static_cast<T*>(ea.e) + m * ea.lde + n0;
     const uint4* d0p = ND >= 2 ? reinterpret_cast<const uint4*>(static_cast<const T*>(ea.d0) + m * ea.ldd0 + n0)
                                : nullptr;
 #pragma unroll
@@ -199,12 +200,10 @@ __device__ __forceinline__ void epi_store_vec_f(const uint32_t (&v)[32], const D
             q0 = __ldg(d0p + j);
         const T* h0 = reinterpret_cast<const T*>(&q0);
         const T* h1 = reinterpret_cast<const T*>(&q1);
-        uint4 out;
-        T* ho = reinterpret_cast<T*>(&out);
+        T* ho       = reinterpret_cast<T*>(&out[j]);
 #pragma unroll
         for(int i = 0; i < 8; ++i)
             ho[i] = epi_apply_f<EPI, T>(__uint_as_float(v[j * 8 + i]), h0[i], h1[i], ea.p);
-        reinterpret_cast<uint4*>(e_row)[j] = out;
     }
 }
 
@@ -232,40 +231,86 @@ __device__ __forceinline__ void epi_store_scalar_f(const uint32_t (&v)[32], cons
     }
 }
 
+// int8: full 32-column segment of one row packed as 2 x 128 bits of E.
 template <int EPI>
-__device__ __forceinline__ void epi_store_row_i8(const uint32_t (&v)[32], const EpilogueArgs& ea,
-                                                 int64_t m, int64_t n0, int ncols, bool vec_ok)
+__device__ __forceinline__ void epi_compute_vec_i8(uint4 (&out)[2], const uint32_t (&v)[32], const EpilogueArgs& ea)
+{
+#pragma unroll
+    for(int j = 0; j < 2; ++j) // 2 x 16 elements = 2 x 128-bit
+    {
+        uint32_t w[4];
+#pragma unroll
+        for(int k = 0; k < 4; ++k)
+        {
+            uint32_t packed = 0;
+#pragma unroll
+            for(int i = 0; i < 4; ++i)
+            {
+                const int32_t r = epi_apply_i8<EPI>(static_cast<int32_t>(v[j * 16 + k * 4 + i]), ea.p);
+                packed |= (static_cast<uint32_t>(r) & 0xFFu) << (8 * i);
+            }
+            w[k] = packed;
+        }
+        out[j] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
+// int8: ragged or unaligned segment, element by element.
+template <int EPI>
+__device__ __forceinline__ void epi_store_scalar_i8(const uint32_t (&v)[32], const EpilogueArgs& ea, int64_t m,
+                                                    int64_t n0, int ncols)
 {
     int8_t* e_row = static_cast<int8_t*>(ea.e) + m * ea.lde + n0;
-    if(ncols == 32 && vec_ok)
+#pragma unroll
+    for(int i = 0; i < 32; ++i)
+        if(i < ncols)
+            e_row[i] = static_cast<int8_t>(epi_apply_i8<EPI>(static_cast<int32_t>(v[i]), ea.p));
+}
+
+// ---- staged stores --------------------------------------------------------------------------------
+// A full segment (32 rows of one warp x 32 columns) is written to a per-warp shared-memory tile and
+// leaves through one TMA store, so that E is written in whole row pieces by the copy unit instead
+// of 32 scattered 16-byte pieces per instruction; rows and columns beyond the tensor are clipped by the
+// tensor map.  The tile is laid out the way a TMA box with the matching swizzle mode reads it (rows of 64
+// bytes with CU_TENSOR_MAP_SWIZZLE_64B: 16-byte chunk index ^= (row >> 1) & 3; rows of 32 bytes with
+// SWIZZLE_32B: chunk index ^= (row >> 2) & 1), which also makes the 128-bit shared-memory writes of a warp
+// free of bank conflicts.  Two tiles per warp alternate.
+struct StoreStage
+{
+    uint32_t buf;            // shared-memory address of this warp's two tiles (2 x 2 KiB, 1 KiB aligned)
+    uint32_t count;          // segments stored so far by this warp
+    const CUtensorMap* tm_e; // E as (columns, rows[, batch]) with a 32 x 32 box
+    int batch;               // >= 0: third coordinate of a batched E map; < 0: 2-D map
+};
+
+template <int ROW_BYTES> // 64: 16-bit E, 32: int8 E
+__device__ __forceinline__ void stage_and_store(StoreStage& st, const uint4* out, int lane, int col0, int row0)
+{
+    constexpr int CHUNKS = ROW_BYTES / 16;
+    const uint32_t tile  = st.buf + (st.count & 1u) * 2048u;
+    // the store issued two segments ago has to be done reading this tile
+    if(lane == 0)
+        bulk_wait_group_read<1>();
+    __syncwarp();
+#pragma unroll
+    for(int c = 0; c < CHUNKS; ++c)
     {
-#pragma unroll
-        for(int j = 0; j < 2; ++j) // 2 x 16 elements = 2 x 128-bit
-        {
-            uint32_t w[4];
-#pragma unroll
-            for(int k = 0; k < 4; ++k)
-            {
-                uint32_t packed = 0;
-#pragma unroll
-                for(int i = 0; i < 4; ++i)
-                {
-                    const int32_t r =
-                        epi_apply_i8<EPI>(static_cast<int32_t>(v[j * 16 + k * 4 + i]), ea.p);
-                    packed |= (static_cast<uint32_t>(r) & 0xFFu) << (8 * i);
-                }
-                w[k] = packed;
-            }
-            reinterpret_cast<uint4*>(e_row)[j] = make_uint4(w[0], w[1], w[2], w[3]);
-        }
+        const int sw = ROW_BYTES == 64 ? (c ^ ((lane >> 1) & 3)) : (c ^ ((lane >> 2) & 1));
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(tile + lane * ROW_BYTES + sw * 16), "r"(out[c].x),
+                     "r"(out[c].y), "r"(out[c].z), "r"(out[c].w)
+                     : "memory");
     }
-    else
+    fence_proxy_async_smem(); // generic-proxy writes -> visible to the copy unit
+    __syncwarp();
+    if(lane == 0)
     {
-#pragma unroll
-        for(int i = 0; i < 32; ++i)
-            if(i < ncols)
-                e_row[i] = static_cast<int8_t>(epi_apply_i8<EPI>(static_cast<int32_t>(v[i]), ea.p));
+        if(st.batch >= 0)
+            tma_store_3d(st.tm_e, tile, col0, row0, st.batch);
+        else
+            tma_store_2d(st.tm_e, tile, col0, row0);
+        bulk_commit_group();
     }
+    ++st.count;
 }
 
 } // namespace ckb

@@ -94,6 +94,7 @@ struct alignas(128) GroupEntry
     CUtensorMap tm_a;       // 128 B
     CUtensorMap tm_b;       // box of BN rows
     CUtensorMap tm_b_split; // box of BN/split rows (tail slices)
+    CUtensorMap tm_e;       // E as (N, M), 32 x 32 box, for the staged stores of the epilogue
     int32_t M, N, K;
     int32_t tiles_n;
     int32_t tile_start; // first global tile index of this group
@@ -120,6 +121,7 @@ struct KernelParams
     CUtensorMap tm_a;       // GEMM: A (K, M[, batch]).  CONV: im2col map over the NHWC input
     CUtensorMap tm_b;       // GEMM: B^T (K, N[, batch]). CONV: weights as (C, Y*X, K); box of BN rows
     CUtensorMap tm_b_split; // same tensor, box of BN/split rows
+    CUtensorMap tm_e;       // E as (N, M[, batch]), 32 x 32 box (valid when vec_ok; GROUPED: in the group entry)
     EpilogueArgs epi;       // GROUPED: e/d/ld fields come from the group entry instead
     const GroupEntry* groups;
     int32_t group_count;
@@ -159,7 +161,10 @@ struct SmemLayout
     static constexpr int A_BYTES     = KSUB * A_SUB_BYTES;
     static constexpr int B_BYTES     = KSUB * B_SUB_BYTES;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int BAR_OFFSET  = STAGES * STAGE_BYTES;
+    // staging tiles of the epilogue's TMA stores: two 2 KiB tiles per epilogue warp
+    static constexpr int EPI_OFFSET     = STAGES * STAGE_BYTES;
+    static constexpr int EPI_WARP_BYTES = 2 * 2048;
+    static constexpr int BAR_OFFSET     = EPI_OFFSET + NUM_EPI_WARPS * EPI_WARP_BYTES;
     // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], drain
     static constexpr int NUM_BARS    = 2 * STAGES + 5;
     static constexpr int MISC_OFFSET = BAR_OFFSET + NUM_BARS * 8;
@@ -456,10 +461,9 @@ __device__ __forceinline__ void reduce_chunk(uint32_t (&v)[32], const uint32_t* 
 // REDUCE = true: the accumulator comes from the parked K slices (`parked` = this warp's block in slice 0)
 // instead of tensor memory.
 template <int EPI, int KIND, bool REDUCE = false>
-__device__ __forceinline__ void epilogue_span(uint32_t tmem_addr, const EpilogueArgs& ea, int64_t m,
-                                              bool row_ok, int64_t n_begin, int64_t n_end, bool vec_ok,
-                                              const uint32_t* parked = nullptr, int lane = 0, int ks = 0,
-                                              int64_t slice_stride = 0)
+__device__ __forceinline__ void epilogue_span(uint32_t tmem_addr, const EpilogueArgs& ea, StoreStage& st, int lane,
+                                              int64_t m, bool row_ok, int64_t n_begin, int64_t n_end, bool vec_ok,
+                                              const uint32_t* parked = nullptr, int ks = 0, int64_t slice_stride = 0)
 {
     using T          = typename std::conditional<KIND == KIND_BF16, __nv_bfloat16, __half>::type;
     constexpr int ND = (KIND == KIND_I8) ? 0 : epi_num_d(EPI);
@@ -487,17 +491,30 @@ __device__ __forceinline__ void epilogue_span(uint32_t tmem_addr, const Epilogue
             tmem_ld_32x32b_x32(tmem_addr + c * 32, v);
             tmem_ld_wait();
         }
-        if(row_ok)
+        if(vec_ok && ncols == 32) // warp-uniform: a whole segment leaves through the staged TMA store
         {
+            const int row0 = static_cast<int>(m) - lane;
             if constexpr(KIND == KIND_I8)
-                epi_store_row_i8<EPI>(v, ea, m, n0, ncols, vec_ok);
+            {
+                uint4 out[2] = {};
+                if(row_ok)
+                    epi_compute_vec_i8<EPI>(out, v, ea);
+                stage_and_store<32>(st, out, lane, static_cast<int>(n0), row0);
+            }
             else
             {
-                if(vec_ok && ncols == 32)
-                    epi_store_vec_f<EPI, T>(v, cur, ea, m, n0);
-                else
-                    epi_store_scalar_f<EPI, T>(v, ea, m, n0, ncols);
+                uint4 out[4] = {};
+                if(row_ok)
+                    epi_compute_vec_f<EPI, T>(out, v, cur, ea, m, n0);
+                stage_and_store<64>(st, out, lane, static_cast<int>(n0), row0);
             }
+        }
+        else if(row_ok)
+        {
+            if constexpr(KIND == KIND_I8)
+                epi_store_scalar_i8<EPI>(v, ea, m, n0, ncols);
+            else
+                epi_store_scalar_f<EPI, T>(v, ea, m, n0, ncols);
         }
         if constexpr(ND > 0)
             cur = nxt;
@@ -893,6 +910,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
         const int half    = (warp - 2) >> 2; // which half of the item's columns
         int iter          = 0;
         bool ok           = true;
+        StoreStage st;
+        st.buf   = base_addr + L::EPI_OFFSET + (warp - 2) * L::EPI_WARP_BYTES;
+        st.count = 0;
+        st.tm_e  = &P.tm_e;
+        st.batch = -1;
+        if(MODE != MODE_GROUPED && P.vec_ok != 0 && lane == 0)
+            tma_prefetch_desc(&P.tm_e);
         CKB_TR(long long tr_wait = 0; const long long tr_start = clock64();)
         for(int slot = 0; ok && slot < P.num_slots; ++slot)
         {
@@ -908,6 +932,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                 Mdim                = G->M;
                 Ndim                = G->N;
                 vec_ok              = G->vec_ok != 0;
+                st.tm_e             = &G->tm_e;
                 ea.e                = G->e;
                 ea.d0               = G->d0;
                 ea.d1               = G->d1;
@@ -917,6 +942,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
             }
             if constexpr(MODE == MODE_GEMM)
             {
+                if(P.batch_tiles > 0)
+                    st.batch = wi.batch; // batched E map: third coordinate
                 if(wi.batch != 0)
                 {
                     constexpr int EB = (KIND == KIND_I8) ? 1 : 2;
@@ -963,7 +990,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                     ok                    = __all_sync(0xffffffffu, ok);
                     if(!ok)
                         break;
-                    epilogue_span<EPI, KIND, true>(0, ea, m, row_ok, n_begin, n_end, vec_ok, parked, lane, P.ksplit,
+                    epilogue_span<EPI, KIND, true>(0, ea, st, lane, m, row_ok, n_begin, n_end, vec_ok, parked, P.ksplit,
                                                    static_cast<int64_t>(TILE_M) * BN);
                     // the last of the reducing warps leaves the counter at zero for the next launch
                     __syncwarp();
@@ -987,7 +1014,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
             if(KSPLIT && wi.kind == ITEM_KSLICE)
                 park_span(tmem_addr, const_cast<uint32_t*>(parked) + static_cast<int64_t>(wi.slice) * TILE_M * BN, span, lane);
             else
-                epilogue_span<EPI, KIND>(tmem_addr, ea, m, row_ok, n_begin, n_end, vec_ok);
+                epilogue_span<EPI, KIND>(tmem_addr, ea, st, lane, m, row_ok, n_begin, n_end, vec_ok);
             // Release the accumulator: all of this warp's tcgen05.ld have completed.
             tc_fence_before_sync();
             __syncwarp();
@@ -1053,6 +1080,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                 }
             }
         }
+        // the staged stores read this CTA's shared memory: they must be done before it goes away
+        if(lane == 0)
+            bulk_wait_group<0>();
         CKB_TR(if(P.trace && warp == 2 && lane == 0) {
             P.trace[blockIdx.x * 16 + 5] = tr_wait;
             P.trace[blockIdx.x * 16 + 6] = clock64() - tr_start;

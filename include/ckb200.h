@@ -186,7 +186,7 @@ int ckb_grouped_gemm_run(const ckb_grouped_gemm_desc* desc, void* workspace,
  *
  * Limits and rules
  *   - at most CKB_NOALLOC_MAX_GROUPS groups; more is rejected with CKB_ERR_LIMIT and a message.
- *     The array costs CKB_NOALLOC_MAX_GROUPS * 512 bytes (128 KiB) of device memory on every
+ *     The array costs CKB_NOALLOC_MAX_GROUPS * 640 bytes (160 KiB) of device memory on every
  *     GPU that loads the library, until the process exits.
  *   - the FIRST call on a device looks up the array's device address (cudaGetSymbolAddress with
  *     that device current) and sets the kernel's shared-memory attribute.  Make that first call
