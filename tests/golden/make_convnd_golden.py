@@ -16,7 +16,7 @@ import re
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = "/root/reference/test/reference_conv_fwd/reference_conv_fwd.cpp"
+REF_TEST = os.path.join("test", "reference_conv_fwd", "reference_conv_fwd.cpp")  # inside the reference checkout
 
 
 def ref_data_of(text, test_name):
@@ -74,9 +74,9 @@ CASES = [
 
 
 def main():
-    if not os.path.exists(REF):
-        sys.exit("the reference checkout is needed to (re)make this fixture: " + REF)
-    text = open(REF).read()
+    if len(sys.argv) != 2 or not os.path.exists(os.path.join(sys.argv[1], REF_TEST)):
+        sys.exit("usage: make_convnd_golden.py <root of the reference checkout>   (needs " + REF_TEST + ")")
+    text = open(os.path.join(sys.argv[1], REF_TEST)).read()
     cases = []
     for name, geom, channel_first, (num, den) in CASES:
         expected = ref_data_of(text, name)

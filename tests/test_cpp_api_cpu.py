@@ -28,5 +28,5 @@ def test_example_drivers_build():
     res = subprocess.run(["make", "-C", os.path.join(ROOT, "examples"), "-j4"], capture_output=True, text=True)
     assert res.returncode == 0, res.stderr[-3000:]
     for name in ("gemm_xdl_fp16", "gemm_add_add_fastgelu_xdl_fp16", "gemm_xdl_requant_relu_requant_int8",
-                 "grouped_gemm_xdl_fp16", "conv2d_fwd_xdl_bias_relu", "ck_profiler"):
+                 "grouped_gemm_xdl_fp16", "conv2d_fwd_xdl_bias_relu", "ck_profiler", "convnd_fwd_instance_engine"):
         assert os.path.exists(os.path.join(ROOT, "examples", "bin", name))

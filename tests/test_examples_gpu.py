@@ -106,3 +106,11 @@ def test_profiler_driver_batched_gemm(examples_built):
     out = run_example("ck_profiler", "batched_gemm", 3, 2, 1, 1, 0, 0, 256, 384, 128, 256, 384, 384,
                       256 * 128, 384 * 128, 256 * 384, 3)  # int8, A[g,k,m] * B[g,k,n]
     assert "Best Perf for batched_gemm" in out
+
+
+@pytest.mark.parametrize("nd", [1, 2, 3])
+def test_op_instance_run_engine_conv(examples_built, nd):
+    """ConvFwdOpInstance + OpInstanceRunEngine (library/include/ck/library/utility/op_instance_engine.hpp:72-246,
+    conv_util.hpp:399-570) in the style of test/convnd_fwd/conv{1,2,3}d_fwd.cpp: Test() then Profile()."""
+    out = run_example("convnd_fwd_instance_engine", nd)
+    assert "SUCCESS" in out and "PASSED" in out and "Perf:" in out
