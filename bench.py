@@ -264,7 +264,7 @@ class GroupedWorkload:
 # ------------------------------------------------------------------------------------------------
 def time_steps(torch, sets, steps, warmup, stream_cfg, dist_barrier):
     """W warm-up steps, then K timed steps bracketed by barrier + synchronize.  Returns
-    (total_ms over the K steps, [per-launch ms])."""
+    (total_ms over the K steps, [mean launch ms] * K)."""
     n = len(sets)
     for i in range(warmup):
         s = sets[i % n]
@@ -272,18 +272,19 @@ def time_steps(torch, sets, steps, warmup, stream_cfg, dist_barrier):
     torch.cuda.synchronize()
     dist_barrier()
     torch.cuda.synchronize()
-    evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
-    evs[0].record()
+    # Two events around the K launches: nothing sits between consecutive kernels in the stream (a launch may
+    # begin its start-up while the one before it drains), and the mean launch duration is total / K.
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
     for i in range(steps):
         s = sets[i % n]
         s["inv"].Run(s["arg"], stream_cfg)
-        evs[i + 1].record()
+    stop.record()
     torch.cuda.synchronize()
     dist_barrier()
     torch.cuda.synchronize()
-    total = evs[0].elapsed_time(evs[steps])
-    per = [evs[i].elapsed_time(evs[i + 1]) for i in range(steps)]
-    return total, per
+    total = start.elapsed_time(stop)
+    return total, [total / steps] * steps
 
 
 def metric_name(unit):

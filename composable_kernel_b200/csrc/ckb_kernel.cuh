@@ -601,6 +601,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
         __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = misc[0];
+    // Everything above (barriers, tensor memory) touched no global memory and may overlap the tail of the previous
+    // kernel of the stream; from here on its results (and the K-split scratch it may still use) are needed.
+    grid_dependency_wait();
+    grid_launch_dependents();
 
     WaitCtx wc{&misc[1], P.wait_limit_ns, P.status};
 

@@ -1,6 +1,8 @@
 // Launch helpers.  launch_epi<MODE, KIND, EPI> is explicitly instantiated in the generated
 // ckb_inst_*.cu files (so that they compile in parallel); find_launch() maps runtime ids to them.
 #pragma once
+#include <cstdlib>
+
 #include "ckb_kernel.cuh"
 
 namespace ckb {
@@ -27,6 +29,16 @@ struct StagesFor
     static constexpr int value = CG == 2 ? pair_stages : BN == 256 ? 4 : BN == 128 ? (conv ? 6 : 3) : (conv ? 8 : 4);
 };
 
+// CKB_NO_PDL=1 turns programmatic dependent launch off (plain stream order).
+inline bool programmatic_launch_enabled()
+{
+    static const bool on = [] {
+        const char* s = getenv("CKB_NO_PDL");
+        return !(s && atoi(s) != 0);
+    }();
+    return on;
+}
+
 template <int MODE, int KIND, int EPI, int BN, int CG>
 cudaError_t launch_one(const KernelParams& p, int grid, cudaStream_t stream)
 {
@@ -48,27 +60,32 @@ cudaError_t launch_one(const KernelParams& p, int grid, cudaStream_t stream)
         if(dev >= 0 && dev < 64)
             attr_done[dev] = true;
     }
-    if constexpr(CG == 1)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim            = dim3(grid, 1, 1); // CG = 2: a multiple of the cluster size
+    cfg.blockDim           = dim3(NUM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes   = SMEM;
+    cfg.stream             = stream;
+    cudaLaunchAttribute attr[2];
+    int n_attr = 0;
+    if constexpr(CG == 2)
     {
-        kern<<<grid, NUM_THREADS, SMEM, stream>>>(p);
-        return cudaGetLastError();
+        attr[n_attr].id               = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = CG;
+        attr[n_attr].val.clusterDim.y = 1;
+        attr[n_attr].val.clusterDim.z = 1;
+        ++n_attr;
     }
-    else
+    if(programmatic_launch_enabled())
     {
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim            = dim3(grid, 1, 1); // a multiple of the cluster size
-        cfg.blockDim           = dim3(NUM_THREADS, 1, 1);
-        cfg.dynamicSmemBytes   = SMEM;
-        cfg.stream             = stream;
-        cudaLaunchAttribute attr[1];
-        attr[0].id               = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = CG;
-        attr[0].val.clusterDim.y = 1;
-        attr[0].val.clusterDim.z = 1;
-        cfg.attrs                = attr;
-        cfg.numAttrs             = 1;
-        return cudaLaunchKernelEx(&cfg, kern, p);
+        // the start-up of this kernel (barrier set-up, tensor-memory allocation) may overlap the tail of the kernel
+        // before it in the stream; the kernel waits (griddepcontrol.wait) before it touches global memory
+        attr[n_attr].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attr;
     }
+    cfg.attrs    = attr;
+    cfg.numAttrs = n_attr;
+    return cudaLaunchKernelEx(&cfg, kern, p);
 }
 
 // cg = CTAs per tile (1 or 2; 2 is instantiated for bn = 256 only).

@@ -111,6 +111,14 @@ __device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const void* tma
         : "memory");
 }
 
+// ---- programmatic dependent launch ---------------------------------------------------------------
+// A kernel launched with the programmatic-stream-serialization attribute may start while the kernel before it in
+// the stream is still running; griddepcontrol.wait blocks until that kernel has completed and its memory
+// operations are visible, launch_dependents lets the NEXT kernel of the stream begin its own start-up early.
+// Both are no-ops for a launch without the attribute.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- TMA stores (shared -> global) of the epilogue ----------------------------------------------
 // Tiled store of one box; completion is tracked by the issuing thread's bulk async-group.
 __device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src, int c0, int c1)
