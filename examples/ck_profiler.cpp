@@ -10,6 +10,8 @@
 //   ck_profiler conv_fwd_bias_relu    <dtype 1> <verify> <init> <log> <time> N K C Y X Hi Wi Sy Sx Dy Dx LeftPy LeftPx RightPy RightPx
 //   ck_profiler batched_gemm          <dtype 1 fp16|2 bf16|3 int8> <layout 0..3> <verify> <init> <log> <time> M N K StrideA StrideB StrideC
 //                                     BatchStrideA BatchStrideB BatchStrideC BatchCount
+//   ck_profiler gemm_bilinear         <dtype 1> <layout 0..3> <verify> <init> <log> <time> M N K StrideA StrideB StrideD StrideE alpha beta
+//   ck_profiler gemm_splitk           <dtype 1> <layout 0..3> <verify> <init> <log> <time> M N K StrideA StrideB StrideC KBatch
 //   ck_profiler conv_fwd              <dtype 1 fp16|2 bf16|3 int8> <layout 1 NHWC> <verify> <init> <log> <time> <nd 1|2|3> N K C
 //                                     <filter> <input> <strides> <dilations> <left pads> <right pads>   (nd values each)
 // gemm takes the reference's four matrix layouts (0: mk_kn, 1: mk_nk, 2: km_kn, 3: km_nk); the fused and grouped
@@ -32,6 +34,8 @@
 #include "ck/library/reference_tensor_operation/cpu/reference_batched_gemm.hpp"
 #include "ck/library/reference_tensor_operation/cpu/reference_conv_fwd.hpp"
 #include "ck/tensor_operation/gpu/device/device_batched_gemm_xdl.hpp"
+#include "ck/tensor_operation/gpu/device/device_gemm_multiple_d_xdl_cshuffle.hpp"
+#include "ck/tensor_operation/gpu/device/device_gemm_xdl_splitk_c_shuffle.hpp"
 #include "ck/tensor_operation/gpu/device/device_conv2d_fwd_xdl_c_shuffle_bias_activation_nhwc_kyxc_nhwk.hpp"
 #include "ck/tensor_operation/gpu/device/device_convnd_fwd_xdl_nhwc_kyxc_nhwk.hpp"
 
@@ -473,6 +477,111 @@ int profile_batched_gemm(int argc, char* argv[])
     return ok ? 0 : 1;
 }
 
+// E = alpha * A * B + beta * D (profiler/src/profile_gemm_bilinear.cpp:29-43) and C = A * B with a KBatch argument
+// (profile_gemm_splitk.cpp:29-42); fp16, the four layouts.
+template <typename ALayout, typename BLayout>
+bool profile_gemm_bilinear_or_splitk(bool bilinear, bool verify, int init, bool time, int M, int N, int K, int sa, int sb,
+                                     int sd, int se, float alpha, float beta, int kbatch)
+{
+    using F16      = ck::half_t;
+    using Bilinear = ck::tensor_operation::element_wise::Bilinear;
+    // clang-format off
+    using BilinearOp = dev::DeviceGemmMultipleD_Xdl_CShuffle<ALayout, BLayout, Row, F16, F16, float, float, ck::Tuple<F16>, F16, PassThrough, PassThrough, Bilinear, dev::GemmSpecialization::MNKPadding,
+        1, 256, 256, 128, 32, 8, 8, 32, 32, 4, 2, inst::S<4, 64, 1>, inst::S<1, 0, 2>, inst::S<1, 0, 2>, 2, 8, 8, 1,
+        inst::S<4, 64, 1>, inst::S<1, 0, 2>, inst::S<1, 0, 2>, 2, 8, 8, 1, 1, 1, inst::S<1, 32, 1, 8>, 8>;
+    using SplitKOp = dev::DeviceGemmXdlSplitKCShuffle<F16, F16, F16, float, ALayout, BLayout, Row, PassThrough, PassThrough, PassThrough, dev::GemmSpecialization::MNKPadding,
+        256, 256, 128, 4, 8, 32, 32, 4, 2, inst::S<1, 4, 64, 1>, inst::S<0, 2, 1, 3>, inst::S<0, 2, 1, 3>, 3, 8, 8, true,
+        inst::S<1, 4, 64, 1>, inst::S<0, 1, 3, 2>, inst::S<0, 1, 3, 2>, 3, 8, 8, true, 1, 1, inst::S<1, 32, 1, 8>, 8>;
+    // clang-format on
+    Tensor<F16> a(example::matrix_descriptor(M, K, sa, ALayout{})), b(example::matrix_descriptor(K, N, sb, BLayout{}));
+    Tensor<F16> d(example::matrix_descriptor(M, N, sd, Row{}));
+    Tensor<F16> e_host(example::matrix_descriptor(M, N, se, Row{})), e_dev(example::matrix_descriptor(M, N, se, Row{}));
+    init_tensor(a, init, false);
+    init_tensor(b, init, true);
+    init_tensor(d, init, false);
+    DeviceMem a_buf(2 * a.mDesc.GetElementSpace()), b_buf(2 * b.mDesc.GetElementSpace()),
+        d_buf(2 * d.mDesc.GetElementSpace()), e_buf(2 * e_dev.mDesc.GetElementSpace());
+    a_buf.ToDevice(a.mData.data());
+    b_buf.ToDevice(b.mData.data());
+    d_buf.ToDevice(d.mData.data());
+    e_buf.SetZero();
+    const Bilinear op_fn{alpha, beta};
+    std::string name;
+    float ms = 0;
+    if(bilinear)
+    {
+        BilinearOp op;
+        auto arg = op.MakeArgumentPointer(a_buf.GetDeviceBuffer(), b_buf.GetDeviceBuffer(),
+                                          std::array<const void*, 1>{d_buf.GetDeviceBuffer()}, e_buf.GetDeviceBuffer(), M, N,
+                                          K, sa, sb, std::array<ck::index_t, 1>{sd}, se, {}, {}, op_fn);
+        if(!op.IsSupportedArgument(arg.get()))
+            return false;
+        ms   = op.MakeInvokerPointer()->Run(arg.get(), StreamConfig{nullptr, time});
+        name = op.GetTypeString();
+    }
+    else
+    {
+        SplitKOp op;
+        auto arg = op.MakeArgumentPointer(a_buf.GetDeviceBuffer(), b_buf.GetDeviceBuffer(), e_buf.GetDeviceBuffer(), M, N, K,
+                                          sa, sb, se, {}, {}, {}, kbatch);
+        if(!op.IsSupportedArgument(arg.get()))
+            return false;
+        ms   = op.MakeInvokerPointer()->Run(arg.get(), StreamConfig{nullptr, time});
+        name = op.GetTypeString();
+    }
+    Best best;
+    if(time)
+        best.offer(name, ms, std::size_t(2) * M * N * K,
+                   2 * (std::size_t(M) * K + std::size_t(K) * N + (bilinear ? 2 : 1) * std::size_t(M) * N));
+    else
+        best.name = name;
+    bool pass = true;
+    if(verify)
+    {
+        Tensor<float> c(HostTensorDescriptor(std::vector<std::size_t>{std::size_t(M), std::size_t(N)}));
+        using Ref = ck::tensor_operation::host::ReferenceGemm<F16, F16, float, float, PassThrough, PassThrough, PassThrough>;
+        auto rarg = Ref::MakeArgument(a, b, c, {}, {}, {});
+        Ref::MakeInvoker().Run(rarg);
+        for(int m = 0; m < M; ++m)
+            for(int n = 0; n < N; ++n)
+            {
+                if(bilinear)
+                    op_fn(e_host(m, n), c(m, n), d(m, n));
+                else
+                    e_host(m, n) = ck::type_convert<F16>(c(m, n));
+            }
+        e_buf.FromDevice(e_dev.mData.data());
+        pass = ck::utils::check_err(e_dev.mData, e_host.mData);
+    }
+    best.report(bilinear ? "gemm_bilinear" : "gemm_splitk");
+    return pass;
+}
+
+int profile_gemm_bilinear_splitk(int argc, char* argv[], bool bilinear)
+{
+    if(argc != (bilinear ? 17 : 15) || std::stoi(argv[2]) != 1)
+    {
+        std::printf("gemm_bilinear 1 <layout 0..3> verify init log time M N K StrideA StrideB StrideD StrideE alpha beta\n"
+                    "gemm_splitk   1 <layout 0..3> verify init log time M N K StrideA StrideB StrideC KBatch\n");
+        return 1;
+    }
+    const int layout  = std::stoi(argv[3]);
+    const bool verify = std::stoi(argv[4]), time = std::stoi(argv[7]);
+    const int init = std::stoi(argv[5]);
+    const int M = std::stoi(argv[8]), N = std::stoi(argv[9]), K = std::stoi(argv[10]);
+    const int sa = std::stoi(argv[11]), sb = std::stoi(argv[12]);
+    const int sd = bilinear ? std::stoi(argv[13]) : N, se = std::stoi(argv[bilinear ? 14 : 13]);
+    const float alpha = bilinear ? std::stof(argv[15]) : 1.f, beta = bilinear ? std::stof(argv[16]) : 0.f;
+    const int kbatch = bilinear ? 1 : std::stoi(argv[14]);
+    auto run         = [&](auto la, auto lb) {
+        return profile_gemm_bilinear_or_splitk<decltype(la), decltype(lb)>(bilinear, verify, init, time, M, N, K, sa, sb, sd,
+                                                                           se, alpha, beta, kbatch);
+    };
+    const bool ok = layout == 0 ? run(Row{}, Row{}) : layout == 1 ? run(Row{}, Col{}) : layout == 2 ? run(Col{}, Row{})
+                                                                                                     : run(Col{}, Col{});
+    return ok ? 0 : 1;
+}
+
 template <int ND, typename T>
 bool profile_convnd_typed(const ck::utils::conv::ConvParams& p, bool verify, int init, bool time)
 {
@@ -577,12 +686,18 @@ int main(int argc, char* argv[])
             return profile_convnd_fwd(argc, argv);
         if(std::strcmp(argv[1], "batched_gemm") == 0)
             return profile_batched_gemm(argc, argv);
+        if(std::strcmp(argv[1], "gemm_bilinear") == 0)
+            return profile_gemm_bilinear_splitk(argc, argv, true);
+        if(std::strcmp(argv[1], "gemm_splitk") == 0)
+            return profile_gemm_bilinear_splitk(argc, argv, false);
     }
     std::printf("arg1: tensor operation (gemm: GEMM\n"
                 "                        gemm_add_add_fastgelu: GEMM+Add+Add+FastGeLU\n"
                 "                        grouped_gemm: Grouped GEMM\n"
                 "                        conv_fwd_bias_relu: ForwardConvolution+Bias+ReLU\n"
                 "                        conv_fwd: ForwardConvolution 1-D / 2-D / 3-D\n"
-                "                        batched_gemm: Batched GEMM)\n");
+                "                        batched_gemm: Batched GEMM\n"
+                "                        gemm_bilinear: GEMM+Bilinear\n"
+                "                        gemm_splitk: Split-K GEMM)\n");
     return 0;
 }

@@ -114,3 +114,12 @@ def test_op_instance_run_engine_conv(examples_built, nd):
     conv_util.hpp:399-570) in the style of test/convnd_fwd/conv{1,2,3}d_fwd.cpp: Test() then Profile()."""
     out = run_example("convnd_fwd_instance_engine", nd)
     assert "SUCCESS" in out and "PASSED" in out and "Perf:" in out
+
+
+def test_profiler_driver_bilinear_and_splitk(examples_built):
+    """gemm_bilinear (profile_gemm_bilinear.cpp:29-43) and gemm_splitk (profile_gemm_splitk.cpp:29-42)."""
+    out = run_example("ck_profiler", "gemm_bilinear", 1, 1, 1, 2, 0, 1, 384, 512, 256, 256, 256, 512, 512, 0.5, 1.5)
+    assert "Best Perf for gemm_bilinear" in out
+    out = run_example("ck_profiler", "gemm_bilinear", 1, 2, 1, 1, 0, 0, 384, 512, 256, 384, 512, 512, 512, 2.0, -1.0)
+    out = run_example("ck_profiler", "gemm_splitk", 1, 1, 1, 1, 0, 1, 256, 256, 2048, 2048, 2048, 256, 4)
+    assert "Best Perf for gemm_splitk" in out and "DeviceGemmXdlSplitKCShuffle" in out
