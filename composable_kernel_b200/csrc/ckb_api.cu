@@ -1037,6 +1037,22 @@ static ConvProblem problem_of_3d(const ckb_conv3d_fwd_desc* d)
     return c;
 }
 
+// Multiply-high / shift constants of ckb::FastDiv for the divisor d (1 <= d < 2^31).
+static FastDiv make_fast_div(uint32_t d)
+{
+    FastDiv f{0, 0, d, 0};
+    if(d > 1)
+    {
+        uint32_t log2_ceil = 0;
+        while((1ull << log2_ceil) < d)
+            ++log2_ceil;
+        const uint32_t p = 31 + log2_ceil;
+        f.mul            = static_cast<uint32_t>(((1ull << p) + d - 1) / d);
+        f.shr            = p - 32;
+    }
+    return f;
+}
+
 static int out_len(int in, int pad_l, int pad_r, int filt, int dil, int stride)
 {
     return (in + pad_l + pad_r - ((filt - 1) * dil + 1)) / stride + 1;
@@ -1214,6 +1230,9 @@ static int run_conv(const ConvProblem& c, void* stream, int n_rep, float* avg_ms
     p.conv.Wo       = c.Wo;
     p.conv.HoWo     = c.Ho * c.Wo;
     p.conv.DoHoWo   = c.Do * c.Ho * c.Wo;
+    p.conv.div_wo     = make_fast_div(static_cast<uint32_t>(c.Wo));
+    p.conv.div_howo   = make_fast_div(static_cast<uint32_t>(c.Ho) * c.Wo);
+    p.conv.div_dohowo = make_fast_div(static_cast<uint32_t>(c.Do) * c.Ho * c.Wo);
     p.conv.Z        = c.Z;
     p.conv.Y        = c.Y;
     p.conv.X        = c.X;

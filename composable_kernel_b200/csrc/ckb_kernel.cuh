@@ -107,6 +107,17 @@ struct alignas(128) GroupEntry
     int64_t lde, ldd0, ldd1;
 };
 
+// Division of a 31-bit unsigned number by a run-time constant as multiply-high and shift (host-computed:
+// p = 31 + ceil(log2 d), mul = ceil(2^p / d), shr = p - 32; quotient = umulhi(n, mul) >> shr; d = 1 is passed through).
+struct FastDiv
+{
+    uint32_t mul, shr, d, pad_;
+};
+__device__ __forceinline__ uint32_t fast_div(uint32_t n, const FastDiv& f)
+{
+    return f.d == 1 ? n : __umulhi(n, f.mul) >> f.shr;
+}
+
 struct ConvGeom
 {
     int32_t Ho, Wo, HoWo;
@@ -114,6 +125,7 @@ struct ConvGeom
     int32_t stride_h, stride_w, dil_h, dil_w, pad_h, pad_w;
     // 3-D convolution (nd3 != 0): depth extents; a 2-D problem has Do = Z = 1
     int32_t nd3, Do, DoHoWo, Z, stride_d, dil_d, pad_d, pad_;
+    FastDiv div_wo, div_howo, div_dohowo; // the producer splits a row index into (n, do, ho, wo) once per tile
 };
 
 struct KernelParams
@@ -663,31 +675,59 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                 (is_b ? L::A_BYTES + box_j * L::B_SUB_BYTES : box_j * L::A_SUB_BYTES) + box_i * ATOM_BYTES;
             const int box_row         = (is_b ? b_row0 : a_row0) + box_i * BK_ELEMS;
             const CUtensorMap* box_tm = is_b ? tm_b : tm_a;
-            // CONV: first output pixel of this CTA's rows in (n, ho, wo)
+            // CONV: first output pixel of this CTA's rows in (n, do, ho, wo), as input coordinates
             int cv_n = 0, cv_d = 0, cv_h = 0, cv_w = 0;
             if constexpr(MODE == MODE_CONV)
             {
-                const int m0 = a_row0;
-                cv_n         = m0 / P.conv.DoHoWo;
-                int rem      = m0 - cv_n * P.conv.DoHoWo;
-                const int od = rem / P.conv.HoWo;
-                rem -= od * P.conv.HoWo;
-                const int ho = rem / P.conv.Wo;
-                const int wo = rem - ho * P.conv.Wo;
-                cv_d         = od * P.conv.stride_d - P.conv.pad_d;
-                cv_h         = ho * P.conv.stride_h - P.conv.pad_h;
-                cv_w         = wo * P.conv.stride_w - P.conv.pad_w;
+                uint32_t rem = static_cast<uint32_t>(a_row0);
+                if(P.conv.nd3 != 0)
+                {
+                    cv_n = fast_div(rem, P.conv.div_dohowo);
+                    rem -= cv_n * P.conv.DoHoWo;
+                    const uint32_t od = fast_div(rem, P.conv.div_howo);
+                    rem -= od * P.conv.HoWo;
+                    cv_d = od * P.conv.stride_d - P.conv.pad_d;
+                }
+                else
+                {
+                    cv_n = fast_div(rem, P.conv.div_howo);
+                    rem -= cv_n * P.conv.HoWo;
+                }
+                const uint32_t ho = fast_div(rem, P.conv.div_wo);
+                const uint32_t wo = rem - ho * P.conv.Wo;
+                cv_h              = ho * P.conv.stride_h - P.conv.pad_h;
+                cv_w              = wo * P.conv.stride_w - P.conv.pad_w;
             }
-            // CONV: filter tap (z, y, x) and channel block of this lane's k block (advanced by KSUB per stage)
-            int cv_z = 0, cv_y = 0, cv_x = 0, cv_cb = 0;
-            if constexpr(MODE == MODE_CONV)
+            // CONV: running state of this lane's k block: channel coordinate, filter tap index and the tap's
+            // offsets (tap position x dilation); stepped by KSUB blocks per stage without multiplications
+            int cv_c = 0, cv_cb = 0, cv_x = 0, cv_y = 0, cv_tap = 0;
+            uint32_t off_w = 0, off_h = 0, off_d = 0;
+            auto conv_step = [&]() {
+                cv_c += BK_ELEMS;
+                if(++cv_cb == P.conv.c_blocks)
+                {
+                    cv_cb = 0;
+                    cv_c  = 0;
+                    ++cv_tap;
+                    off_w += P.conv.dil_w;
+                    if(++cv_x == P.conv.X)
+                    {
+                        cv_x  = 0;
+                        off_w = 0;
+                        off_h += P.conv.dil_h;
+                        if(++cv_y == P.conv.Y)
+                        {
+                            cv_y  = 0;
+                            off_h = 0;
+                            off_d += P.conv.dil_d;
+                        }
+                    }
+                }
+            };
+            if constexpr(MODE == MODE_CONV && KSUB > 1)
             {
-                int taps = box_j / P.conv.c_blocks;
-                cv_cb    = box_j - taps * P.conv.c_blocks;
-                cv_x     = taps % P.conv.X;
-                taps /= P.conv.X;
-                cv_y = taps % P.conv.Y;
-                cv_z = taps / P.conv.Y;
+                for(int i = 0; i < box_j && i < KSUB; ++i) // lanes of the later k blocks of a stage start further on
+                    conv_step();
             }
             for(int kb = 0; kb < wi.num_kb; kb += KSUB)
             {
@@ -706,32 +746,28 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                 {
                     if constexpr(MODE == MODE_CONV)
                     {
-                        const uint16_t off_w = static_cast<uint16_t>(cv_x * P.conv.dil_w);
-                        const uint16_t off_h = static_cast<uint16_t>(cv_y * P.conv.dil_h);
+                        const uint16_t ow = static_cast<uint16_t>(off_w), oh = static_cast<uint16_t>(off_h);
                         if(!is_b && P.conv.nd3 == 0)
                         {
                             if constexpr(CG == 2)
-                                tma_load_im2col_4d_pair(dst, box_tm, bar, cv_cb * BK_ELEMS, cv_w, cv_h, cv_n, off_w, off_h);
+                                tma_load_im2col_4d_pair(dst, box_tm, bar, cv_c, cv_w, cv_h, cv_n, ow, oh);
                             else
-                                tma_load_im2col_4d(dst, box_tm, bar, cv_cb * BK_ELEMS, cv_w, cv_h, cv_n, off_w, off_h);
+                                tma_load_im2col_4d(dst, box_tm, bar, cv_c, cv_w, cv_h, cv_n, ow, oh);
                         }
                         else if(!is_b)
                         {
-                            const uint16_t off_d = static_cast<uint16_t>(cv_z * P.conv.dil_d);
+                            const uint16_t od = static_cast<uint16_t>(off_d);
                             if constexpr(CG == 2)
-                                tma_load_im2col_5d_pair(dst, box_tm, bar, cv_cb * BK_ELEMS, cv_w, cv_h, cv_d, cv_n, off_w,
-                                                        off_h, off_d);
+                                tma_load_im2col_5d_pair(dst, box_tm, bar, cv_c, cv_w, cv_h, cv_d, cv_n, ow, oh, od);
                             else
-                                tma_load_im2col_5d(dst, box_tm, bar, cv_cb * BK_ELEMS, cv_w, cv_h, cv_d, cv_n, off_w, off_h,
-                                                   off_d);
+                                tma_load_im2col_5d(dst, box_tm, bar, cv_c, cv_w, cv_h, cv_d, cv_n, ow, oh, od);
                         }
                         else
                         {
-                            const int tap = (cv_z * P.conv.Y + cv_y) * P.conv.X + cv_x;
                             if constexpr(CG == 2)
-                                tma_load_3d_pair(dst, box_tm, bar, cv_cb * BK_ELEMS, tap, b_row0);
+                                tma_load_3d_pair(dst, box_tm, bar, cv_c, cv_tap, b_row0);
                             else
-                                tma_load_3d(dst, box_tm, bar, cv_cb * BK_ELEMS, tap, wi.n_start);
+                                tma_load_3d(dst, box_tm, bar, cv_c, cv_tap, wi.n_start);
                         }
                     }
                     else
@@ -743,21 +779,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                 }
                 if constexpr(MODE == MODE_CONV)
                 {
-                    // advance this lane's (tap, channel block) by KSUB k blocks
-                    cv_cb += KSUB;
-                    while(cv_cb >= P.conv.c_blocks)
-                    {
-                        cv_cb -= P.conv.c_blocks;
-                        if(++cv_x == P.conv.X)
-                        {
-                            cv_x = 0;
-                            if(++cv_y == P.conv.Y)
-                            {
-                                cv_y = 0;
-                                ++cv_z;
-                            }
-                        }
-                    }
+#pragma unroll
+                    for(int i = 0; i < KSUB; ++i)
+                        conv_step();
                 }
                 ++loads;
                 if(++stage == STAGES)
