@@ -434,11 +434,20 @@ unsigned long long* trace_buffer()
 #endif
 }
 
+// CKB_STORE_DIRECT=1 makes every kernel write E with 128-bit global stores instead of the staged TMA stores.
+int store_direct_forced()
+{
+    const char* s = getenv("CKB_STORE_DIRECT");
+    return s ? atoi(s) : -1;
+}
+
 int run_timed(LaunchFn fn, int bn, int cg, const KernelParams& p_in, int grid, cudaStream_t stream, int n_rep,
               float* avg_ms)
 {
     KernelParams p = p_in;
     p.trace        = trace_buffer();
+    if(store_direct_forced() >= 0)
+        p.store_direct = store_direct_forced();
     if(avg_ms)
         *avg_ms = 0.f;
     if(n_rep <= 0)

@@ -155,7 +155,7 @@ struct KernelParams
     int32_t ks_full;     // tiles that run whole (a multiple of the number of units); tail tiles follow
     int32_t ks_rem;      // tail tiles
     int32_t num_slots;   // work slots per unit
-    int32_t pad2_;
+    int32_t store_direct; // full segments of E: 0 = staged TMA stores, 1 = 128-bit global stores
     uint32_t* ks_partials; // [tail tile][slice][TILE_M rows][BN columns] raw 32-bit accumulators
     uint32_t* ks_counters; // one per tail tile, zero between launches
     ConvGeom conv;
@@ -511,14 +511,29 @@ __device__ __forceinline__ void epilogue_span(uint32_t tmem_addr, const Epilogue
                 uint4 out[2] = {};
                 if(row_ok)
                     epi_compute_vec_i8<EPI>(out, v, ea);
-                stage_and_store<32>(st, out, lane, static_cast<int>(n0), row0);
+                if(!st.direct)
+                    stage_and_store<32>(st, out, lane, static_cast<int>(n0), row0);
+                else if(row_ok)
+                {
+                    uint4* e_row = reinterpret_cast<uint4*>(static_cast<int8_t*>(ea.e) + m * ea.lde + n0);
+                    e_row[0]     = out[0];
+                    e_row[1]     = out[1];
+                }
             }
             else
             {
                 uint4 out[4] = {};
                 if(row_ok)
                     epi_compute_vec_f<EPI, T>(out, v, cur, ea, m, n0);
-                stage_and_store<64>(st, out, lane, static_cast<int>(n0), row0);
+                if(!st.direct)
+                    stage_and_store<64>(st, out, lane, static_cast<int>(n0), row0);
+                else if(row_ok)
+                {
+                    uint4* e_row = reinterpret_cast<uint4*>(static_cast<T*>(ea.e) + m * ea.lde + n0);
+#pragma unroll
+                    for(int j = 0; j < 4; ++j)
+                        e_row[j] = out[j];
+                }
             }
         }
         else if(row_ok)
@@ -941,8 +956,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
         StoreStage st;
         st.buf   = base_addr + L::EPI_OFFSET + (warp - 2) * L::EPI_WARP_BYTES;
         st.count = 0;
-        st.tm_e  = &P.tm_e;
-        st.batch = -1;
+        st.tm_e   = &P.tm_e;
+        st.batch  = -1;
+        st.direct = P.store_direct != 0;
         if(MODE != MODE_GROUPED && P.vec_ok != 0 && lane == 0)
             tma_prefetch_desc(&P.tm_e);
         CKB_TR(long long tr_wait = 0; const long long tr_start = clock64();)
