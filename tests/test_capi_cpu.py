@@ -38,9 +38,11 @@ def test_struct_layout_matches_header():
     #include "ckb200.h"
     #include <stdio.h>
     #include <stddef.h>
-    int main(){ printf("%zu %zu %zu %zu %zu %zu\n", sizeof(ckb_gemm_desc), sizeof(ckb_conv2d_fwd_desc),
+    int main(){ printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\n", sizeof(ckb_gemm_desc), sizeof(ckb_conv2d_fwd_desc),
       sizeof(ckb_grouped_gemm_desc), offsetof(ckb_gemm_desc, p_e), offsetof(ckb_gemm_desc, epi_params),
-      offsetof(ckb_conv2d_fwd_desc, p_in)); return 0; }'''
+      offsetof(ckb_conv2d_fwd_desc, p_in), sizeof(ckb_batched_gemm_desc), offsetof(ckb_batched_gemm_desc, batch),
+      offsetof(ckb_batched_gemm_desc, batch_stride_d), sizeof(ckb_conv3d_fwd_desc),
+      offsetof(ckb_conv3d_fwd_desc, p_in)); return 0; }'''
     with tempfile.TemporaryDirectory() as td:
         c = os.path.join(td, "t.c")
         open(c, "w").write(src)
@@ -48,7 +50,10 @@ def test_struct_layout_matches_header():
         subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), c, "-o", exe], check=True)
         out = subprocess.run([exe], capture_output=True, text=True, check=True).stdout.split()
     want = [ctypes.sizeof(capi.GemmDesc), ctypes.sizeof(capi.Conv2dFwdDesc), ctypes.sizeof(capi.GroupedGemmDesc),
-            capi.GemmDesc.p_e.offset, capi.GemmDesc.epi_params.offset, capi.Conv2dFwdDesc.p_in.offset]
+            capi.GemmDesc.p_e.offset, capi.GemmDesc.epi_params.offset, capi.Conv2dFwdDesc.p_in.offset,
+            ctypes.sizeof(capi.BatchedGemmDesc), capi.BatchedGemmDesc.batch.offset,
+            capi.BatchedGemmDesc.batch_stride_d.offset, ctypes.sizeof(capi.Conv3dFwdDesc),
+            capi.Conv3dFwdDesc.p_in.offset]
     assert [int(x) for x in out] == want
 
 
