@@ -9,15 +9,20 @@
 //                             TMEM accumulators (2 x BN columns) and commits to mbarriers
 //   warps 2-9  epilogue     : tcgen05.ld the finished accumulator (two warps per TMEM lane
 //                             quarter, each half of the columns), apply the fused epilogue with
-//                             the D values prefetched one segment ahead, store E with 128-bit stores
+//                             the D values prefetched one segment ahead, write each 32 x 32 segment
+//                             of E to a per-warp shared-memory tile and send it off with a TMA store
 // The second accumulator lets the epilogue of item i overlap the main loop of item i+1.
+//
+// Start-up (barrier initialisation, tensor-memory allocation, cluster sync) touches no global memory: the
+// kernel then executes griddepcontrol.wait, so that under programmatic dependent launch the start-up
+// overlaps the tail of the previous kernel of the stream.
 //
 // Work items.  The output is cut into 128 x BN tiles.  With G CTAs, the first floor(T/G)*G tiles
 // are whole-tile items; the R = T mod G tiles of the last, partial wave are each cut into
 // `split` column slices of BN/split columns (R*split <= G), so that the tail occupies all SMs
 // instead of R of them.
 //
-// K-split tail (MODE_GEMM with a scratch buffer).  Column slices of a tail tile cost almost as much as a whole
+// K-split tail (16-bit MODE_GEMM kernels without D tensors, with a scratch buffer).  Column slices of a tail tile cost almost as much as a whole
 // tile, because the MMA role is bound by the number of instructions it issues, not by their width.  When
 // KernelParams::ksplit > 1 the R tail tiles are cut along K instead: after its first whole tile every unit runs
 // one K slice of a tail tile (full-width MMAs over 1/ksplit of the k blocks) and parks the raw accumulator in the
@@ -42,8 +47,8 @@
 // tensor memory and runs its own epilogue.  All loads post their bytes on the LEADER's "full"
 // barrier; the leader's tcgen05.commit fans the "empty" / "accumulator full" arrivals out to both
 // CTAs; the epilogue warps of both CTAs release the accumulator on the leader's barrier.
-// Compared with CG = 1 a stage holds half the B tile, so the ring is 6 deep instead of 4 and
-// every SM pulls a third less operand traffic through L2.
+// Compared with CG = 1 a k block holds half the B tile (32 KB instead of 48 KB), and every SM pulls a
+// third less operand traffic through L2.
 //
 // Every wait is bounded: after `wait_limit_ns` the waiting thread records a code in the status
 // word, raises the CTA's abort flag, and all roles drain and leave through the common exit,
