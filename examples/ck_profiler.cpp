@@ -8,6 +8,7 @@
 //   ck_profiler gemm_add_add_fastgelu <dtype 1> <layout 1> <verify> <init> <log> <time> M N K StrideA StrideB StrideD0 StrideD1 StrideE
 //   ck_profiler grouped_gemm          <dtype 1> <layout 1> <verify> <init> <log> <time> Ms Ns Ks          (comma separated lists)
 //   ck_profiler conv_fwd_bias_relu    <dtype 1> <verify> <init> <log> <time> N K C Y X Hi Wi Sy Sx Dy Dx LeftPy LeftPx RightPy RightPx
+//   ck_profiler conv_fwd_bias_relu_add  (same arguments; adds a residual tensor after the ReLU)
 //   ck_profiler batched_gemm          <dtype 1 fp16|2 bf16|3 int8> <layout 0..3> <verify> <init> <log> <time> M N K StrideA StrideB StrideC
 //                                     BatchStrideA BatchStrideB BatchStrideC BatchCount
 //   ck_profiler gemm_bilinear         <dtype 1> <layout 0..3> <verify> <init> <log> <time> M N K StrideA StrideB StrideD StrideE alpha beta
@@ -392,6 +393,79 @@ int profile_conv_fwd_bias_relu(int argc, char* argv[])
     return pass && !best.name.empty() ? 0 : 1;
 }
 
+int profile_conv_fwd_bias_relu_add(int argc, char* argv[])
+{
+    if(argc != 22 || std::stoi(argv[2]) != 1)
+    {
+        std::printf("conv_fwd_bias_relu_add 1 verify init log time N K C Y X Hi Wi Sy Sx Dy Dx LeftPy LeftPx RightPy RightPx\n");
+        return 1;
+    }
+    using F16 = ck::half_t;
+    const bool verify = std::stoi(argv[3]), time = std::stoi(argv[6]);
+    const int init = std::stoi(argv[4]);
+    const ck::utils::conv::ConvParams p = ck::utils::conv::parse_conv_params(2, 7, argv);
+    const auto out_sp                   = p.GetOutputSpatialLengths();
+    using AddReluAdd = ck::tensor_operation::element_wise::AddReluAdd;
+    // clang-format off
+    using Conv = dev::DeviceConv2dFwdXdl_C_Shuffle_Bias_Activation_Add_Input_N_Hi_Wi_C_Weight_K_Y_X_C_Output_N_Ho_Wo_K<
+        F16, F16, F16, float, PassThrough, PassThrough, AddReluAdd, dev::ConvolutionForwardSpecialization::Default,
+        256, 128, 256, 4, 8, 32, 32, 2, 4, inst::S<4, 64, 1>, inst::S<1, 0, 2>, inst::S<1, 0, 2>, 2, 8, 8, true,
+        inst::S<4, 64, 1>, inst::S<1, 0, 2>, inst::S<1, 0, 2>, 2, 8, 8, true, 1, 1, inst::S<1, 1, 32, 1, 1, 8>, 8>;
+    // clang-format on
+    const std::size_t N = p.N_, K = p.K_, C = p.C_;
+    Tensor<F16> in(ck::utils::conv::get_input_host_tensor_descriptor(
+        {N, C, std::size_t(p.input_spatial_lengths_[0]), std::size_t(p.input_spatial_lengths_[1])}));
+    Tensor<F16> wei(ck::utils::conv::get_filters_host_tensor_descriptor(
+        {K, C, std::size_t(p.filter_spatial_lengths_[0]), std::size_t(p.filter_spatial_lengths_[1])}));
+    Tensor<F16> out_h(ck::utils::conv::get_output_host_tensor_descriptor({N, K, std::size_t(out_sp[0]), std::size_t(out_sp[1])}));
+    Tensor<F16> out_d(out_h.mDesc), resi(out_h.mDesc), bias(HostTensorDescriptor(std::vector<std::size_t>{K}));
+    init_tensor(in, init, false);
+    init_tensor(wei, init, true);
+    init_tensor(bias, init, false);
+    init_tensor(resi, init, false);
+    DeviceMem in_buf(2 * in.mDesc.GetElementSpace()), wei_buf(2 * wei.mDesc.GetElementSpace()),
+        out_buf(2 * out_d.mDesc.GetElementSpace()), bias_buf(2 * K), resi_buf(2 * resi.mDesc.GetElementSpace());
+    in_buf.ToDevice(in.mData.data());
+    wei_buf.ToDevice(wei.mData.data());
+    bias_buf.ToDevice(bias.mData.data());
+    resi_buf.ToDevice(resi.mData.data());
+    std::vector<std::unique_ptr<dev::DeviceConvFwdBiasActivationAdd<PassThrough, PassThrough, AddReluAdd>>> ops;
+    ops.push_back(std::make_unique<Conv>());
+    Best best;
+    bool pass = true;
+    for(auto& op : ops)
+    {
+        auto arg = op->MakeArgumentPointer(in_buf.GetDeviceBuffer(), wei_buf.GetDeviceBuffer(), out_buf.GetDeviceBuffer(),
+                                           bias_buf.GetDeviceBuffer(), resi_buf.GetDeviceBuffer(), p.N_, p.K_, p.C_, p.input_spatial_lengths_,
+                                           p.filter_spatial_lengths_, out_sp, p.conv_filter_strides_, p.conv_filter_dilations_,
+                                           p.input_left_pads_, p.input_right_pads_, {}, {}, {});
+        if(!op->IsSupportedArgument(arg.get()))
+        {
+            std::cout << op->GetTypeString() << " does not support this problem" << std::endl;
+            continue;
+        }
+        const float ms = op->MakeInvokerPointer()->Run(arg.get(), StreamConfig{nullptr, time});
+        if(time)
+            best.offer(op->GetTypeString(), ms, ck::utils::conv::get_flops(p.N_, p.C_, p.K_, p.filter_spatial_lengths_, out_sp),
+                       ck::utils::conv::get_btype<F16, F16, F16>(p.N_, p.C_, p.K_, p.input_spatial_lengths_,
+                                                                 p.filter_spatial_lengths_, out_sp) + 2 * K +
+                           2 * resi.mDesc.GetElementSpace());
+        else
+            best.name = op->GetTypeString();
+        if(verify)
+        {
+            out_buf.FromDevice(out_d.mData.data());
+            using Ref = ck::tensor_operation::host::ReferenceConvFwd_Bias_Activation_Add<F16, F16, F16, PassThrough, PassThrough, AddReluAdd>;
+            auto rarg = Ref::MakeArgument(in, wei, out_h, bias, resi, p.conv_filter_strides_, p.conv_filter_dilations_,
+                                          p.input_left_pads_, p.input_right_pads_, {}, {}, {});
+            Ref::MakeInvoker().Run(rarg);
+            pass = pass && ck::utils::check_err(out_d.mData, out_h.mData);
+        }
+    }
+    best.report("conv_fwd_bias_relu_add");
+    return pass && !best.name.empty() ? 0 : 1;
+}
+
 template <typename T, typename ALayout, typename BLayout>
 bool profile_batched_gemm_typed(bool verify, int init, bool time, int M, int N, int K, int sa, int sb, int sc, int bsa,
                                 int bsb, int bsc, int G)
@@ -682,6 +756,8 @@ int main(int argc, char* argv[])
             return profile_grouped_gemm(argc, argv);
         if(std::strcmp(argv[1], "conv_fwd_bias_relu") == 0)
             return profile_conv_fwd_bias_relu(argc, argv);
+        if(std::strcmp(argv[1], "conv_fwd_bias_relu_add") == 0)
+            return profile_conv_fwd_bias_relu_add(argc, argv);
         if(std::strcmp(argv[1], "conv_fwd") == 0)
             return profile_convnd_fwd(argc, argv);
         if(std::strcmp(argv[1], "batched_gemm") == 0)
@@ -695,6 +771,7 @@ int main(int argc, char* argv[])
                 "                        gemm_add_add_fastgelu: GEMM+Add+Add+FastGeLU\n"
                 "                        grouped_gemm: Grouped GEMM\n"
                 "                        conv_fwd_bias_relu: ForwardConvolution+Bias+ReLU\n"
+                "                        conv_fwd_bias_relu_add: ForwardConvolution+Bias+ReLU+Add\n"
                 "                        conv_fwd: ForwardConvolution 1-D / 2-D / 3-D\n"
                 "                        batched_gemm: Batched GEMM\n"
                 "                        gemm_bilinear: GEMM+Bilinear\n"

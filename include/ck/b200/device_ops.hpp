@@ -305,6 +305,39 @@ const Derived& argument_cast(const Base* p)
     return *d;
 }
 
+// What a GemmSpecialization means for IsSupportedArgument.  The reference pads the dimensions a specialisation
+// names up to the block tile (device_gemm_xdl_cshuffle.hpp:84-346) and then demands M % MPerBlock == 0 &&
+// N % NPerBlock == 0 && K % KPerBlock == 0 of the padded problem (gridwise_gemm_xdl_cshuffle_v1.hpp:222-226): an
+// instance therefore rejects a ragged dimension its specialisation does not pad.  The kernel behind these headers
+// handles ragged edges by itself (TMA zero fill, predicated stores), so this rule is kept only so that an instance
+// answers as the reference's instance would; define CK_B200_RELAXED_GEMM_SPECIALIZATION to accept every shape.
+constexpr bool pads_m(dev::GemmSpecialization s)
+{
+    return s == dev::GemmSpecialization::MPadding || s == dev::GemmSpecialization::MNPadding ||
+           s == dev::GemmSpecialization::MKPadding || s == dev::GemmSpecialization::MNKPadding;
+}
+constexpr bool pads_n(dev::GemmSpecialization s)
+{
+    return s == dev::GemmSpecialization::NPadding || s == dev::GemmSpecialization::MNPadding ||
+           s == dev::GemmSpecialization::NKPadding || s == dev::GemmSpecialization::MNKPadding;
+}
+constexpr bool pads_k(dev::GemmSpecialization s)
+{
+    return s == dev::GemmSpecialization::KPadding || s == dev::GemmSpecialization::MKPadding ||
+           s == dev::GemmSpecialization::NKPadding || s == dev::GemmSpecialization::MNKPadding;
+}
+template <dev::GemmSpecialization Spec, index_t MPerBlock, index_t NPerBlock, index_t KPerBlock>
+inline bool specialization_accepts(index_t M, index_t N, index_t K)
+{
+#ifdef CK_B200_RELAXED_GEMM_SPECIALIZATION
+    (void)M, (void)N, (void)K;
+    return true;
+#else
+    return (pads_m(Spec) || M % MPerBlock == 0) && (pads_n(Spec) || N % NPerBlock == 0) &&
+           (pads_k(Spec) || K % KPerBlock == 0);
+#endif
+}
+
 // -------- GEMM (single C op or multiple D) --------
 struct GemmArgument : dev::BaseArgument
 {
@@ -520,6 +553,28 @@ ConvArgument make_conv_argument(const void* p_in, const void* p_wei, void* p_out
     return a;
 }
 
+// device_convnd_fwd_xdl_nhwc_kyxc_nhwk.hpp:894-919: an instance built for a 1x1 filter specialisation rejects every
+// other geometry (Default and OddC accept all).
+template <dev::ConvolutionForwardSpecialization Spec>
+inline bool conv_specialization_accepts(const std::vector<index_t>& filt_sp, const std::vector<index_t>& strides,
+                                        const std::vector<index_t>& lpads, const std::vector<index_t>& rpads)
+{
+    constexpr bool one_by_one = Spec == dev::ConvolutionForwardSpecialization::Filter1x1Pad0 ||
+                                Spec == dev::ConvolutionForwardSpecialization::Filter1x1Stride1Pad0;
+    if(!one_by_one)
+        return true;
+    if(strides.size() != filt_sp.size() || lpads.size() != filt_sp.size() || rpads.size() != filt_sp.size())
+        return false;
+    for(std::size_t i = 0; i < filt_sp.size(); ++i)
+    {
+        if(!(filt_sp[i] == 1 && lpads[i] == 0 && rpads[i] == 0))
+            return false;
+        if(Spec == dev::ConvolutionForwardSpecialization::Filter1x1Stride1Pad0 && strides[i] != 1)
+            return false;
+    }
+    return true;
+}
+
 inline bool conv_supported(const ConvArgument& a)
 {
     return a.host_ok &&
@@ -556,10 +611,12 @@ struct DeviceGemm_Xdl_CShuffle : public DeviceGemm<ALayout, BLayout, CLayout, AD
                              index_t K, index_t StrideA, index_t StrideB, index_t StrideC, AElementwiseOperation,
                              BElementwiseOperation, CElementwiseOperation c_element_op)
     {
-        return b200::make_gemm_argument<ALayout, BLayout, CLayout, ADataType, BDataType, CDataType,
-                                        AElementwiseOperation, BElementwiseOperation, CElementwiseOperation,
-                                        b200::ctx_gemm_c, 0>(p_a, p_b, {}, p_c, M, N, K, StrideA, StrideB, {}, StrideC,
-                                                             c_element_op);
+        auto arg = b200::make_gemm_argument<ALayout, BLayout, CLayout, ADataType, BDataType, CDataType,
+                                            AElementwiseOperation, BElementwiseOperation, CElementwiseOperation,
+                                            b200::ctx_gemm_c, 0>(p_a, p_b, {}, p_c, M, N, K, StrideA, StrideB, {},
+                                                                 StrideC, c_element_op);
+        arg.host_ok = arg.host_ok && b200::specialization_accepts<GemmSpec, MPerBlock, NPerBlock, KPerBlock>(M, N, K);
+        return arg;
     }
     static auto MakeInvoker() { return Invoker{}; }
     static bool IsSupportedArgument(const Argument& arg) { return b200::gemm_supported(arg); }
@@ -603,10 +660,12 @@ struct DeviceGemmXdl : public DeviceGemm<ALayout, BLayout, CLayout, ADataType, B
                              index_t K, index_t StrideA, index_t StrideB, index_t StrideC, AElementwiseOperation,
                              BElementwiseOperation, CElementwiseOperation c_element_op)
     {
-        return b200::make_gemm_argument<ALayout, BLayout, CLayout, ADataType, BDataType, CDataType,
-                                        AElementwiseOperation, BElementwiseOperation, CElementwiseOperation,
-                                        b200::ctx_gemm_c, 0>(p_a, p_b, {}, p_c, M, N, K, StrideA, StrideB, {}, StrideC,
-                                                             c_element_op);
+        auto arg = b200::make_gemm_argument<ALayout, BLayout, CLayout, ADataType, BDataType, CDataType,
+                                            AElementwiseOperation, BElementwiseOperation, CElementwiseOperation,
+                                            b200::ctx_gemm_c, 0>(p_a, p_b, {}, p_c, M, N, K, StrideA, StrideB, {},
+                                                                 StrideC, c_element_op);
+        arg.host_ok = arg.host_ok && b200::specialization_accepts<GemmSpec, MPerBlock, NPerBlock, K0PerBlock * K1>(M, N, K);
+        return arg;
     }
     static auto MakeInvoker() { return Invoker{}; }
     static bool IsSupportedArgument(const Argument& arg) { return b200::gemm_supported(arg); }
@@ -659,7 +718,9 @@ struct DeviceGemmXdlSplitKCShuffle : public DeviceGemmSplitK<ALayout, BLayout, C
                                             AElementwiseOperation, BElementwiseOperation, CElementwiseOperation,
                                             b200::ctx_gemm_c, 0>(p_a, p_b, {}, p_c, M, N, K, StrideA, StrideB, {},
                                                                  StrideC, c_element_op);
-        arg.host_ok = arg.host_ok && KBatch >= 1;
+        // device_gemm_xdl_splitk_c_shuffle.hpp pads K to a multiple of KBatch * K0PerBlock * K1 whatever the
+        // specialisation; M and N follow the usual rule
+        arg.host_ok = arg.host_ok && KBatch >= 1 && b200::specialization_accepts<GemmSpec, MPerBlock, NPerBlock, 1>(M, N, K);
         return arg;
     }
     static auto MakeInvoker() { return Invoker{}; }
@@ -770,10 +831,12 @@ struct DeviceGemmMultipleD_Xdl_CShuffle
                              std::array<index_t, NumDTensor> StrideDs, index_t StrideE, AElementwiseOperation,
                              BElementwiseOperation, CDEElementwiseOperation cde_element_op)
     {
-        return b200::make_gemm_argument<ALayout, BLayout, DELayout, ADataType, BDataType, EDataType,
-                                        AElementwiseOperation, BElementwiseOperation, CDEElementwiseOperation,
-                                        b200::ctx_gemm_cde, NumDTensor>(p_a, p_b, p_ds, p_e, M, N, K, StrideA, StrideB,
-                                                                        StrideDs, StrideE, cde_element_op);
+        auto arg = b200::make_gemm_argument<ALayout, BLayout, DELayout, ADataType, BDataType, EDataType,
+                                            AElementwiseOperation, BElementwiseOperation, CDEElementwiseOperation,
+                                            b200::ctx_gemm_cde, NumDTensor>(p_a, p_b, p_ds, p_e, M, N, K, StrideA,
+                                                                            StrideB, StrideDs, StrideE, cde_element_op);
+        arg.host_ok = arg.host_ok && b200::specialization_accepts<GemmSpec, MPerBlock, NPerBlock, KPerBlock>(M, N, K);
+        return arg;
     }
     static auto MakeInvoker() { return Invoker{}; }
     static bool IsSupportedArgument(const Argument& arg) { return b200::gemm_supported(arg); }
@@ -843,7 +906,10 @@ struct DeviceGroupedGemmXdl
                                                 b200::ctx_gemm_cde, NumDTensor>(
                 p_a[i], p_b[i], ds, p_e[i], gemm_descs[i].M_, gemm_descs[i].N_, gemm_descs[i].K_, gemm_descs[i].stride_A_,
                 gemm_descs[i].stride_B_, sds, gemm_descs[i].stride_C_, c_element_op);
-            arg.host_ok = arg.host_ok && one.host_ok;
+            // device_grouped_gemm_xdl.hpp:586-628: a group the instance cannot run makes the argument unsupported
+            arg.host_ok = arg.host_ok && one.host_ok &&
+                          b200::specialization_accepts<GemmSpec, MPerBlock, NPerBlock, KPerBlock>(
+                              gemm_descs[i].M_, gemm_descs[i].N_, gemm_descs[i].K_);
             arg.groups.push_back(one.desc);
         }
         return arg;
@@ -908,7 +974,9 @@ struct DeviceConvNDFwdXdl_Input_N_Hi_Wi_C_Weight_K_Y_X_C_Output_N_Ho_Wo_K
             output_spatial_lengths, conv_filter_strides, conv_filter_dilations, input_left_pads, input_right_pads,
             out_element_op);
         arg.host_ok = arg.host_ok && static_cast<std::size_t>(NumDimSpatial) == input_spatial_lengths.size() &&
-                      std::is_same<InDataType, WeiDataType>::value && std::is_same<InDataType, OutDataType>::value;
+                      std::is_same<InDataType, WeiDataType>::value && std::is_same<InDataType, OutDataType>::value &&
+                      b200::conv_specialization_accepts<ConvForwardSpecialization>(
+                          filter_spatial_lengths, conv_filter_strides, input_left_pads, input_right_pads);
         return arg;
     }
     static auto MakeInvoker() { return Invoker{}; }
@@ -970,7 +1038,9 @@ struct DeviceConv2dFwdXdl_C_Shuffle_Bias_Activation_Input_N_Hi_Wi_C_Weight_K_Y_X
             output_spatial_lengths, conv_filter_strides, conv_filter_dilations, input_left_pads, input_right_pads,
             out_element_op);
         arg.host_ok = arg.host_ok && OutGlobalMemoryDataOperation == InMemoryDataOperationEnum::Set &&
-                      std::is_same<InDataType, WeiDataType>::value && std::is_same<InDataType, OutDataType>::value;
+                      std::is_same<InDataType, WeiDataType>::value && std::is_same<InDataType, OutDataType>::value &&
+                      b200::conv_specialization_accepts<ConvForwardSpecialization>(
+                          filter_spatial_lengths, conv_filter_strides, input_left_pads, input_right_pads);
         return arg;
     }
     static auto MakeInvoker() { return Invoker{}; }
@@ -1031,7 +1101,9 @@ struct DeviceConv2dFwdXdl_C_Shuffle_Bias_Activation_Add_Input_N_Hi_Wi_C_Weight_K
             output_spatial_lengths, conv_filter_strides, conv_filter_dilations, input_left_pads, input_right_pads,
             out_element_op);
         arg.host_ok = arg.host_ok && std::is_same<InDataType, WeiDataType>::value &&
-                      std::is_same<InDataType, OutDataType>::value;
+                      std::is_same<InDataType, OutDataType>::value &&
+                      b200::conv_specialization_accepts<ConvForwardSpecialization>(
+                          filter_spatial_lengths, conv_filter_strides, input_left_pads, input_right_pads);
         return arg;
     }
     static auto MakeInvoker() { return Invoker{}; }

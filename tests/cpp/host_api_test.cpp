@@ -52,6 +52,9 @@ static constexpr auto GemmDefault = dev::GemmSpecialization::Default;
 template <typename AL, typename BL, typename T, typename COp>
 using Gemm = dev::DeviceGemm_Xdl_CShuffle<AL, BL, Row, T, T, T, float, float, ew::PassThrough, ew::PassThrough, COp, GemmDefault,
     1, 256, 256, 128, 32, 8, 8, 32, 32, 4, 2, S<4, 64, 1>, S<1, 0, 2>, S<1, 0, 2>, 2, 8, 8, 1, S<4, 64, 1>, S<1, 0, 2>, S<1, 0, 2>, 2, 8, 8, 1, 1, 1, S<1, 32, 1, 8>, 8>;
+template <dev::GemmSpecialization Spec>
+using GemmSpec = dev::DeviceGemm_Xdl_CShuffle<Row, Col, Row, F16, F16, F16, float, float, ew::PassThrough, ew::PassThrough, ew::PassThrough, Spec,
+    1, 256, 256, 128, 32, 8, 8, 32, 32, 4, 2, S<4, 64, 1>, S<1, 0, 2>, S<1, 0, 2>, 2, 8, 8, 1, S<4, 64, 1>, S<1, 0, 2>, S<1, 0, 2>, 2, 8, 8, 1, 1, 1, S<1, 32, 1, 8>, 8>;
 template <typename CDEOp, typename Ds>
 using GemmMultiD = dev::DeviceGemmMultipleD_Xdl_CShuffle<Row, Col, Row, F16, F16, float, float, Ds, F16, ew::PassThrough, ew::PassThrough, CDEOp, GemmDefault,
     1, 256, 256, 128, 32, 8, 8, 32, 32, 4, 2, S<4, 64, 1>, S<1, 0, 2>, S<1, 0, 2>, 2, 8, 8, 1, S<4, 64, 1>, S<1, 0, 2>, S<1, 0, 2>, 2, 8, 8, 1, 1, 1, S<1, 32, 1, 8>, 8>;
@@ -199,14 +202,26 @@ static void test_traits_and_support()
     auto ok = gemm.MakeArgument(pa, pb, pc, 3840, 4096, 4096, 4096, 4096, 4096, {}, {}, {});
     EXPECT(gemm.IsSupportedArgument(ok));
     EXPECT(gemm.IsSupportedArgument(&ok)); // polymorphic overload
-    auto ragged = gemm.MakeArgument(pa, pb, pc, 100, 37, 72, 72, 72, 37, {}, {}, {});
-    EXPECT(gemm.IsSupportedArgument(ragged));
-    auto bad = gemm.MakeArgument(pa, pb, pc, 100, 37, 70, 70, 70, 37, {}, {}, {});
-    EXPECT(!gemm.IsSupportedArgument(bad));
+    // A dimension the specialisation does not pad must divide the instance's block tile (256 x 128 x 32 here),
+    // as in gridwise_gemm_xdl_cshuffle_v1.hpp:222-226 over the descriptors of device_gemm_xdl_cshuffle.hpp:84-346.
+    auto ragged_default = gemm.MakeArgument(pa, pb, pc, 100, 40, 72, 72, 72, 40, {}, {}, {});
+    EXPECT(!gemm.IsSupportedArgument(ragged_default));
+    GemmSpec<dev::GemmSpecialization::MNKPadding> padded;
+    auto ragged = padded.MakeArgument(pa, pb, pc, 100, 40, 72, 72, 72, 40, {}, {}, {});
+    EXPECT(padded.IsSupportedArgument(ragged));
+    GemmSpec<dev::GemmSpecialization::MNPadding> mn_padded;
+    EXPECT(!mn_padded.IsSupportedArgument(mn_padded.MakeArgument(pa, pb, pc, 100, 40, 72, 72, 72, 40, {}, {}, {})));
+    EXPECT(mn_padded.IsSupportedArgument(mn_padded.MakeArgument(pa, pb, pc, 100, 40, 96, 96, 96, 40, {}, {}, {})));
+    GemmSpec<dev::GemmSpecialization::KPadding> k_padded;
+    EXPECT(k_padded.IsSupportedArgument(k_padded.MakeArgument(pa, pb, pc, 512, 256, 72, 72, 72, 256, {}, {}, {})));
+    EXPECT(!k_padded.IsSupportedArgument(k_padded.MakeArgument(pa, pb, pc, 500, 256, 72, 72, 72, 256, {}, {}, {})));
+    // strides that TMA cannot address are refused whatever the specialisation
+    auto bad = padded.MakeArgument(pa, pb, pc, 100, 40, 70, 70, 70, 40, {}, {}, {});
+    EXPECT(!padded.IsSupportedArgument(bad));
     bool threw = false;
     try
     {
-        gemm.MakeInvoker().Run(bad);
+        padded.MakeInvoker().Run(bad);
     }
     catch(const std::runtime_error& e)
     {
@@ -284,6 +299,24 @@ static void test_traits_and_support()
                                 {35, 36}, p.conv_filter_strides_, p.conv_filter_dilations_, p.input_left_pads_,
                                 p.input_right_pads_, {}, {}, {});
     EXPECT(!conv.IsSupportedArgument(cb));
+
+    // an instance specialised for 1x1 filters refuses every other geometry
+    // (device_conv2d_fwd_xdl_c_shuffle_bias_activation_nhwc_kyxc_nhwk.hpp IsSupportedArgument, same rule as
+    // device_convnd_fwd_xdl_nhwc_kyxc_nhwk.hpp:894-919)
+    // clang-format off
+    using Conv1x1 = dev::DeviceConv2dFwdXdl_C_Shuffle_Bias_Activation_Input_N_Hi_Wi_C_Weight_K_Y_X_C_Output_N_Ho_Wo_K<
+        F16, F16, F16, float, ew::PassThrough, ew::PassThrough, ew::AddRelu, ck::InMemoryDataOperationEnum::Set,
+        dev::ConvolutionForwardSpecialization::Filter1x1Stride1Pad0, 256, 128, 256, 4, 8, 32, 32, 2, 4, S<4, 64, 1>, S<1, 0, 2>, S<1, 0, 2>, 2, 8, 8, true,
+        S<4, 64, 1>, S<1, 0, 2>, S<1, 0, 2>, 2, 8, 8, true, 1, 1, S<1, 1, 32, 1, 1, 8>, 8>;
+    // clang-format on
+    Conv1x1 conv1x1;
+    EXPECT(!conv1x1.IsSupportedArgument(conv1x1.MakeArgument(
+        pa, pb, pc, pa, p.N_, p.K_, p.C_, p.input_spatial_lengths_, p.filter_spatial_lengths_, p.GetOutputSpatialLengths(),
+        p.conv_filter_strides_, p.conv_filter_dilations_, p.input_left_pads_, p.input_right_pads_, {}, {}, {})));
+    EXPECT(conv1x1.IsSupportedArgument(conv1x1.MakeArgument(pa, pb, pc, pa, 4, 64, 64, {20, 20}, {1, 1}, {20, 20}, {1, 1},
+                                                            {1, 1}, {0, 0}, {0, 0}, {}, {}, {})));
+    EXPECT(!conv1x1.IsSupportedArgument(conv1x1.MakeArgument(pa, pb, pc, pa, 4, 64, 64, {20, 20}, {1, 1}, {10, 10}, {2, 2},
+                                                             {1, 1}, {0, 0}, {0, 0}, {}, {}, {})));
 }
 
 // The instance lists a profiler-style client walks: non-empty for the kernels that exist, each instance

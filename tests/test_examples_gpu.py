@@ -29,11 +29,17 @@ def test_gemm_fp16_example(examples_built):
     # verify=1, integer init, timed; both reference instances (DeviceGemmXdl, DeviceGemm_Xdl_CShuffle)
     out = run_example("gemm_xdl_fp16", 1, 1, 1, 512, 768, 256, 256, 256, 768)
     assert out.count("Perf:") == 2 and "TFlops" in out
-    run_example("gemm_xdl_fp16", 1, 2, 0, 300, 200, 136, 136, 136, 200)  # ragged, decimal init
+    run_example("gemm_xdl_fp16", 1, 2, 0, 768, 384, 160, 160, 160, 384)  # decimal init
+    # The example's instances use GemmSpecialization::Default: a shape that does not divide the 256 x 128 x 32 block
+    # tile is refused, as by the reference (gridwise_gemm_xdl_cshuffle_v1.hpp:222-226); the MNKPadding instances of
+    # the factory take it (test_profiler_driver).
+    res = subprocess.run([os.path.join(BIN, "gemm_xdl_fp16"), "1", "2", "0", "300", "200", "136", "136", "136", "200"],
+                         capture_output=True, text=True, timeout=300)
+    assert res.returncode != 0 and "does not support" in res.stdout + res.stderr
 
 
 def test_gemm_add_add_fastgelu_example(examples_built):
-    out = run_example("gemm_add_add_fastgelu_xdl_fp16", 1, 2, 1, 384, 512, 256, 256, 256, 0, 512, 512)
+    out = run_example("gemm_add_add_fastgelu_xdl_fp16", 1, 2, 1, 512, 512, 256, 256, 256, 0, 512, 512)
     assert "DeviceGemmMultipleD_Xdl_CShuffle" in out
 
 
@@ -72,6 +78,8 @@ def test_profiler_driver_walks_instance_lists(examples_built):
     for dtype in (1, 2, 3):  # fp16, bf16, int8
         out = run_example("ck_profiler", "gemm", dtype, 1, 1, 1, 0, 1, 512, 768, 256, 256, 256, 768)
         assert "Best Perf for gemm" in out and "DeviceGemm_Xdl_CShuffle" in out
+    out = run_example("ck_profiler", "gemm", 1, 1, 1, 2, 0, 1, 300, 200, 136, 136, 136, 200)  # ragged: MNKPadding instances
+    assert "Best Perf for gemm" in out
     # the other three matrix layouts of profile_gemm.cpp (0: mk_kn, 2: km_kn, 3: km_nk); M N K = 512 768 256
     for layout, sa, sb in ((0, 256, 768), (2, 512, 768), (3, 512, 256)):
         out = run_example("ck_profiler", "gemm", 1, layout, 1, 1, 0, 1, 512, 768, 256, sa, sb, 768)
@@ -82,6 +90,10 @@ def test_profiler_driver_walks_instance_lists(examples_built):
     assert "Best Perf for grouped_gemm" in out
     out = run_example("ck_profiler", "conv_fwd_bias_relu", 1, 1, 2, 0, 1, 4, 64, 64, 3, 3, 17, 17, 2, 2, 1, 1, 1, 1, 1, 1)
     assert "Best Perf for conv_fwd_bias_relu" in out
+    # profile_conv_fwd_bias_relu_add.cpp: the same problem with a residual tensor added after the ReLU
+    out = run_example("ck_profiler", "conv_fwd_bias_relu_add", 1, 1, 2, 0, 1, 4, 64, 64, 3, 3, 17, 17, 2, 2, 1, 1, 1, 1,
+                      1, 1)
+    assert "Best Perf for conv_fwd_bias_relu_add" in out
 
 
 def test_profiler_driver_convnd(examples_built):
