@@ -645,7 +645,11 @@ static int gemm_run_impl(const ckb_gemm_desc* d, const BatchInfo& bi, void* stre
     // Measured on 3840 x 4096 x 4096: +5 % for 16-bit operands with a D-less epilogue; a loss for int8 (tiles
     // half as long) and for epilogues that read D tensors, where the epilogue warps have no slack for the
     // parking and the reduction - those keep the column slices.
+#ifdef CKB_KSPLIT_WITH_D
+    const bool ks_pays = d->ab_dtype != CKB_I8;
+#else
     const bool ks_pays = d->ab_dtype != CKB_I8 && d->n_ds == 0;
+#endif
     if(ks_pays && rem > 0 && ful > 0 && rem * 2 <= G && rem <= 1024 && !(no_ks && atoi(no_ks) != 0))
     {
         // 4 or 2 slices; the reduction is shared out in column parts of bn / ksplit >= 64 columns

@@ -263,7 +263,11 @@ struct WorkItem
 template <int MODE, int KIND, int EPI>
 struct HasKSplit
 {
+#ifdef CKB_KSPLIT_WITH_D
+    static constexpr bool value = MODE == MODE_GEMM && KIND != KIND_I8;
+#else
     static constexpr bool value = MODE == MODE_GEMM && KIND != KIND_I8 && epi_num_d(EPI) == 0;
+#endif
 };
 
 template <int MODE, int BN, bool KSPLIT = false>
@@ -430,8 +434,9 @@ __device__ __forceinline__ void park_span(uint32_t tmem_addr, uint32_t* block, i
     }
 }
 
-// Reduction side: v = sum over the slices, in slice order, of chunk `c` of this lane's row.
-template <int KIND>
+// Reduction side: v = sum over the slices, in slice order, of chunk `c` of this lane's row.  QUADS columns quads
+// (of 4 columns) of all slices are in flight together: 2 normally, 1 where the epilogue also holds D values.
+template <int KIND, int QUADS>
 __device__ __forceinline__ void reduce_chunk(uint32_t (&v)[32], const uint32_t* block, int c, int lane, int ks,
                                              int64_t slice_stride)
 {
@@ -442,20 +447,20 @@ __device__ __forceinline__ void reduce_chunk(uint32_t (&v)[32], const uint32_t* 
             return __float_as_uint(__uint_as_float(a) + __uint_as_float(b));
     };
 #pragma unroll
-    for(int h = 0; h < 4; ++h) // 8 columns at a time: all slices of a quarter chunk are in flight together
+    for(int h = 0; h < 8 / QUADS; ++h)
     {
-        uint4 t[4][2];
+        uint4 t[4][QUADS];
 #pragma unroll
         for(int sl = 0; sl < 4; ++sl)
             if(sl < ks)
             {
                 const uint4* src = reinterpret_cast<const uint4*>(block + sl * slice_stride) + lane;
 #pragma unroll
-                for(int q = 0; q < 2; ++q)
-                    t[sl][q] = __ldcg(src + (c * 8 + h * 2 + q) * 32);
+                for(int q = 0; q < QUADS; ++q)
+                    t[sl][q] = __ldcg(src + (c * 8 + h * QUADS + q) * 32);
             }
 #pragma unroll
-        for(int q = 0; q < 2; ++q)
+        for(int q = 0; q < QUADS; ++q)
         {
             uint4 a = t[0][q];
 #pragma unroll
@@ -467,10 +472,10 @@ __device__ __forceinline__ void reduce_chunk(uint32_t (&v)[32], const uint32_t* 
                     a.z = add(a.z, t[sl][q].z);
                     a.w = add(a.w, t[sl][q].w);
                 }
-            v[h * 8 + q * 4 + 0] = a.x;
-            v[h * 8 + q * 4 + 1] = a.y;
-            v[h * 8 + q * 4 + 2] = a.z;
-            v[h * 8 + q * 4 + 3] = a.w;
+            v[(h * QUADS + q) * 4 + 0] = a.x;
+            v[(h * QUADS + q) * 4 + 1] = a.y;
+            v[(h * QUADS + q) * 4 + 2] = a.z;
+            v[(h * QUADS + q) * 4 + 3] = a.w;
         }
     }
 }
@@ -485,8 +490,11 @@ __device__ __forceinline__ void epilogue_span(uint32_t tmem_addr, const Epilogue
     using T          = typename std::conditional<KIND == KIND_BF16, __nv_bfloat16, __half>::type;
     constexpr int ND = (KIND == KIND_I8) ? 0 : epi_num_d(EPI);
     const int nchunks = n_end > n_begin ? static_cast<int>((n_end - n_begin + 31) / 32) : 0;
+    // D values of the next chunk are fetched while this one is computed; the reduction path, whose registers hold
+    // the parked slices, fetches the chunk's own D values together with them instead.
+    constexpr bool PREFETCH_D = ND > 0 && !REDUCE;
     DChunk cur, nxt;
-    if constexpr(ND > 0)
+    if constexpr(PREFETCH_D)
     {
         if(row_ok && vec_ok && n_end - n_begin >= 32)
             epi_load_d<EPI, T>(cur, ea, m, n_begin);
@@ -495,14 +503,19 @@ __device__ __forceinline__ void epilogue_span(uint32_t tmem_addr, const Epilogue
     {
         const int64_t n0 = n_begin + c * 32;
         const int ncols  = static_cast<int>(n_end - n0 < 32 ? n_end - n0 : 32);
-        if constexpr(ND > 0)
+        if constexpr(PREFETCH_D)
         {
             if(row_ok && vec_ok && n_end - (n0 + 32) >= 32)
                 epi_load_d<EPI, T>(nxt, ea, m, n0 + 32);
         }
+        else if constexpr(ND > 0)
+        {
+            if(row_ok && vec_ok && ncols == 32)
+                epi_load_d<EPI, T>(cur, ea, m, n0);
+        }
         uint32_t v[32];
         if constexpr(REDUCE)
-            reduce_chunk<KIND>(v, parked, c, lane, ks, slice_stride);
+            reduce_chunk<KIND, (ND > 0) ? 1 : 2>(v, parked, c, lane, ks, slice_stride);
         else
         {
             tmem_ld_32x32b_x32(tmem_addr + c * 32, v);
@@ -548,9 +561,21 @@ __device__ __forceinline__ void epilogue_span(uint32_t tmem_addr, const Epilogue
             else
                 epi_store_scalar_f<EPI, T>(v, ea, m, n0, ncols);
         }
-        if constexpr(ND > 0)
+        if constexpr(PREFETCH_D)
             cur = nxt;
     }
+}
+
+// The reduction epilogue of kernels whose functor reads D tensors, as a function of its own: inlined, its parked
+// slices and D values together push the whole kernel over the register budget (spills in every epilogue path);
+// called, the caller's live registers are saved once per tail tile instead.  Returns the updated segment count.
+template <int EPI, int KIND>
+__device__ __noinline__ uint32_t reduce_epilogue_call(EpilogueArgs ea, StoreStage st, int lane, int64_t m, bool row_ok,
+                                                      int64_t n_begin, int64_t n_end, bool vec_ok,
+                                                      const uint32_t* parked, int ks, int64_t slice_stride)
+{
+    epilogue_span<EPI, KIND, true>(0, ea, st, lane, m, row_ok, n_begin, n_end, vec_ok, parked, ks, slice_stride);
+    return st.count;
 }
 
 // EPI (the fused epilogue functor) is a template parameter: one functor per kernel keeps the
@@ -1039,8 +1064,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                     ok                    = __all_sync(0xffffffffu, ok);
                     if(!ok)
                         break;
-                    epilogue_span<EPI, KIND, true>(0, ea, st, lane, m, row_ok, n_begin, n_end, vec_ok, parked, P.ksplit,
-                                                   static_cast<int64_t>(TILE_M) * BN);
+                    if constexpr(epi_num_d(EPI) > 0)
+                        st.count = reduce_epilogue_call<EPI, KIND>(ea, st, lane, m, row_ok, n_begin, n_end, vec_ok, parked,
+                                                                   P.ksplit, static_cast<int64_t>(TILE_M) * BN);
+                    else
+                        epilogue_span<EPI, KIND, true>(0, ea, st, lane, m, row_ok, n_begin, n_end, vec_ok, parked,
+                                                       P.ksplit, static_cast<int64_t>(TILE_M) * BN);
                     // the last of the reducing warps leaves the counter at zero for the next launch
                     __syncwarp();
                     if(lane == 0 && atomicAdd(counter, 1u) + 1u == 2u * target)

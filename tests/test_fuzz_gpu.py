@@ -129,3 +129,137 @@ def test_random_convolution(cuda_device, seed):
     ref = oracle.conv3d_fwd(inp.reshape(N, *lead, *in_sp, C), wei.reshape(K, *lead, *filt, C), tuple(lead + stride),
                             tuple(lead + dil), tuple([0] * (3 - nd) + pad))
     np.testing.assert_array_equal(res.reshape(ref.shape), ref, err_msg=str((nd, dtype, N, C, K, filt, in_sp, stride, dil, pad)))
+
+
+def _typed(x, dtype):
+    """Integer-valued float array -> the numpy form the oracle takes for `dtype`."""
+    if dtype == capi.CKB_I8:
+        return x.astype(np.int8)
+    if dtype == capi.CKB_BF16:
+        return oracle.to_bf16(x.astype(np.float32))
+    return x.astype(np.float16)
+
+
+def _dev_image(x, col_major, ldim):
+    src = x.T if col_major else x
+    buf = np.zeros((src.shape[0], ldim), dtype=x.dtype)
+    buf[:, :src.shape[1]] = src
+    return torch.from_numpy(buf.view(np.int16) if buf.dtype == np.uint16 else buf).cuda()
+
+
+_TORCH = {capi.CKB_I8: torch.int8, capi.CKB_F16: torch.float16, capi.CKB_BF16: torch.int16}
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_random_multi_d_gemm(cuda_device, seed):
+    """Epilogues that read D tensors (DeviceGemmMultipleD): random functor, layout, shape and D strides (0 = one row
+    broadcast over M, N, or a padded pitch).  Integer inputs: the functors without a transcendental are bit exact."""
+    rng = np.random.default_rng(20000 + seed)
+    dtype = [capi.CKB_F16, capi.CKB_BF16][rng.integers(0, 2)]
+    ops = [ck.Add(), ck.AddRelu(), ck.AddHardswish(), ck.Bilinear(0.5, 2.0), ck.AddAddFastGelu(), ck.AddReluAdd()]
+    if dtype == capi.CKB_BF16:
+        ops = [ck.AddRelu(), ck.AddHardswish(), ck.AddReluAdd()]
+    op = ops[rng.integers(0, len(ops))]
+    big = seed % 4 == 0
+    M, N = (int(rng.integers(1500, 4000)), int(rng.integers(1500, 4000))) if big else (
+        int(rng.integers(1, 600)), int(rng.integers(1, 600)))
+    K = int(rng.integers(1, 24)) * 16
+    a_layout, b_layout = [ROW, COL][rng.integers(0, 2)], [ROW, COL][rng.integers(0, 2)]
+    a, b = _typed(rng.integers(-5, 6, (M, K)), dtype), _typed(rng.integers(-5, 6, (K, N)), dtype)
+    lda = ((K if a_layout == ROW else M) + 7) // 8 * 8
+    ldb = ((K if b_layout == COL else N) + 7) // 8 * 8
+    da, db = _dev_image(a, a_layout == COL, lda), _dev_image(b, b_layout == COL, ldb)
+    n_d = capi.EPI_NUM_D[op.kind]
+    d_np, d_dev, ldds = [], [], []
+    for i in range(n_d):
+        mode = int(rng.integers(0, 3))  # 0: broadcast row, 1: packed, 2: padded pitch
+        if mode == 0:
+            row = _typed(rng.integers(-5, 6, (N,)), dtype)
+            d_np.append(np.broadcast_to(row, (M, N)))
+            d_dev.append(torch.from_numpy(row.view(np.int16) if row.dtype == np.uint16 else row).cuda())
+            ldds.append(0)
+        else:
+            full = _typed(rng.integers(-5, 6, (M, N)), dtype)
+            ldd = N if mode == 1 else N + 8 * int(rng.integers(1, 3))
+            d_np.append(full)
+            d_dev.append(_dev_image(full, False, ldd))
+            ldds.append(ldd)
+    e = torch.zeros((M, N), dtype=_TORCH[dtype], device="cuda")
+    gemm = ck.DeviceGemmMultipleD(dtype, a_layout, b_layout)
+    arg = gemm.MakeArgument(da.data_ptr(), db.data_ptr(), [t.data_ptr() for t in d_dev], e.data_ptr(), M, N, K, lda, ldb,
+                            ldds, N, None, None, op)
+    assert gemm.IsSupportedArgument(arg), capi.last_error()
+    gemm.MakeInvoker().Run(arg)
+    torch.cuda.synchronize()
+    assert ck.device_status() == 0
+    out = e.cpu().numpy()
+    out = out.view(np.uint16) if dtype == capi.CKB_BF16 else out
+    ref = oracle.gemm(a, b, op.kind, op.params, d_np[0] if n_d > 0 else None, d_np[1] if n_d > 1 else None)
+    what = (seed, dtype, op.kind, M, N, K, a_layout, b_layout, ldds)
+    if op.kind in (capi.CKB_EPI_ADD_ADD_FASTGELU, capi.CKB_EPI_ADD_HARDSWISH):
+        if dtype == capi.CKB_BF16:
+            o, r = oracle.from_bf16(out), oracle.from_bf16(ref)
+            assert np.all(np.abs(o - r) <= np.abs(r) * 2.0 ** -7 + 1e-3), what
+        else:
+            bad, max_err = oracle.check_err(np.ascontiguousarray(out), ref, 1e-3, 1e-3)
+            assert bad == 0, (what, bad, max_err)
+    else:
+        np.testing.assert_array_equal(out, ref, err_msg=str(what))
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_random_grouped_gemm(cuda_device, seed):
+    """Grouped GEMM (DeviceGroupedGemm): 1 to 12 groups of unrelated shapes in one launch, random layout and type."""
+    rng = np.random.default_rng(30000 + seed)
+    dtype = [capi.CKB_F16, capi.CKB_BF16, capi.CKB_I8][rng.integers(0, 3)]
+    per16 = 16 if dtype == capi.CKB_I8 else 8
+    a_layout, b_layout = [ROW, COL][rng.integers(0, 2)], [ROW, COL][rng.integers(0, 2)]
+    groups = int(rng.integers(1, 13))
+    keep, p_a, p_b, p_e, descs, refs, outs = [], [], [], [], [], [], []
+    for g in range(groups):
+        M, N = int(rng.integers(1, 900)), int(rng.integers(1, 900))
+        K = int(rng.integers(1, 20)) * 16
+        a, b = _typed(rng.integers(-5, 6, (M, K)), dtype), _typed(rng.integers(-5, 6, (K, N)), dtype)
+        lda = ((K if a_layout == ROW else M) + per16 - 1) // per16 * per16
+        ldb = ((K if b_layout == COL else N) + per16 - 1) // per16 * per16
+        lde = (N + per16 - 1) // per16 * per16
+        da, db = _dev_image(a, a_layout == COL, lda), _dev_image(b, b_layout == COL, ldb)
+        e = torch.zeros((M, lde), dtype=_TORCH[dtype], device="cuda")
+        keep += [da, db]
+        outs.append((e, N))
+        p_a.append(da.data_ptr())
+        p_b.append(db.data_ptr())
+        p_e.append(e.data_ptr())
+        descs.append(ck.GemmDescHost(M, N, K, lda, ldb, lde, []))
+        refs.append(oracle.gemm(a, b))
+    op = ck.DeviceGroupedGemm(dtype, a_layout, b_layout)
+    arg = op.MakeArgument(p_a, p_b, [[] for _ in range(groups)], p_e, descs, None, None, ck.PassThrough())
+    ws = torch.empty(max(op.GetWorkSpaceSize(arg), 1), dtype=torch.uint8, device="cuda")
+    op.SetWorkSpacePointer(arg, ws.data_ptr())
+    assert op.IsSupportedArgument(arg), capi.last_error()
+    op.MakeInvoker().Run(arg)
+    torch.cuda.synchronize()
+    assert ck.device_status() == 0
+    for g, ((e, N), ref) in enumerate(zip(outs, refs)):
+        out = e.cpu().numpy()[:, :N]
+        out = out.view(np.uint16) if dtype == capi.CKB_BF16 else out
+        np.testing.assert_array_equal(out, ref, err_msg=str((seed, g, dtype, a_layout, b_layout, ref.shape)))
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_random_batched_gemm(cuda_device, seed):
+    """Batched GEMM (DeviceBatchedGemm): random batch count, shape, layout, type and batch-stride padding."""
+    from tests.test_batched_gpu import inputs, oracle_batched, run_batched
+
+    rng = np.random.default_rng(40000 + seed)
+    dtype = [capi.CKB_F16, capi.CKB_BF16, capi.CKB_I8][rng.integers(0, 3)]
+    per16 = 16 if dtype == capi.CKB_I8 else 8
+    G = int(rng.integers(1, 20))
+    # run_batched packs the matrices (leading dimension = contiguous extent): keep those TMA-addressable
+    M, N = per16 * int(rng.integers(1, 40)), per16 * int(rng.integers(1, 40))
+    K = per16 * int(rng.integers(1, 24))
+    layouts = ([ROW, COL][rng.integers(0, 2)], [ROW, COL][rng.integers(0, 2)])
+    pad = per16 * int(rng.integers(0, 4))
+    a, b = inputs(rng, dtype, G, M, N, K)
+    out = run_batched(dtype, layouts[0], layouts[1], a, b, pad)
+    np.testing.assert_array_equal(out, oracle_batched(a, b), err_msg=str((seed, dtype, G, M, N, K, layouts, pad)))
