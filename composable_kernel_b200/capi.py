@@ -107,6 +107,7 @@ SYMBOLS = {
     "ckb_memcpy_d2h": (c_int, [c_void_p, c_void_p, c_size_t]),
     "ckb_memset": (c_int, [c_void_p, c_int, c_size_t]),
     "ckb_device_synchronize": (c_int, []),
+    "ckb_release_scratch": (c_int, [c_void_p, c_int]),
     "ckb_gemm_supported": (c_int, [POINTER(GemmDesc)]),
     "ckb_gemm_run": (c_int, [POINTER(GemmDesc), c_void_p, c_int, POINTER(c_float)]),
     "ckb_batched_gemm_supported": (c_int, [POINTER(BatchedGemmDesc)]),

@@ -128,6 +128,18 @@ int current_device(DeviceInfo** out)
     return CKB_OK;
 }
 
+// True while `stream` records into a CUDA graph (a failed query counts as capturing: nothing is allocated then).
+bool stream_is_capturing(cudaStream_t stream)
+{
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    if(cudaStreamIsCapturing(stream, &st) != cudaSuccess)
+    {
+        cudaGetLastError();
+        return true;
+    }
+    return st != cudaStreamCaptureStatusNone;
+}
+
 constexpr size_t kScratchCounterBytes = 4096; // 1024 tail-tile counters at the front of a scratch buffer
 
 // Grow-only scratch of `stream` with room for `bytes` after the counters; nullptr when the device has no memory
@@ -138,6 +150,11 @@ void* scratch_for(DeviceInfo* dev, cudaStream_t stream, size_t bytes)
     std::lock_guard<std::mutex> lock(g_dev_mutex);
     Scratch& sc       = dev->scratch[stream];
     const size_t need = kScratchCounterBytes + bytes;
+    // A launch that is being captured into a graph gets no scratch: the graph may be replayed on any stream,
+    // next to other launches that use this stream's buffer, and a capture must not see an allocation either.
+    // The caller then keeps the plan that needs none.
+    if(stream_is_capturing(stream))
+        return nullptr;
     if(sc.bytes >= need)
         return sc.ptr;
     if(sc.ptr)
@@ -599,6 +616,27 @@ int ckb_device_synchronize(void)
     CKB_CUDA(cudaDeviceSynchronize());
     return CKB_OK;
 }
+int ckb_release_scratch(void* stream, int all_streams)
+{
+    DeviceInfo* dev = nullptr;
+    int rc          = current_device(&dev);
+    if(rc)
+        return rc;
+    CKB_CUDA(cudaDeviceSynchronize());
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    for(auto it = dev->scratch.begin(); it != dev->scratch.end();)
+    {
+        if(all_streams || it->first == static_cast<cudaStream_t>(stream))
+        {
+            if(it->second.ptr)
+                cudaFree(it->second.ptr);
+            it = dev->scratch.erase(it);
+        }
+        else
+            ++it;
+    }
+    return CKB_OK;
+}
 
 // ---- GEMM ---------------------------------------------------------------------------------------
 int ckb_gemm_supported(const ckb_gemm_desc* desc) { return check_gemm(desc, false); }
@@ -920,6 +958,9 @@ int ckb_grouped_gemm_run(const ckb_grouped_gemm_desc* g, void* workspace, size_t
     if(rc)
         return rc;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if(stream_is_capturing(stream))
+        return fail(CKB_ERR_UNSUPPORTED, "grouped GEMM copies its group table from host memory at every launch and "
+                                         "cannot be captured into a graph");
     GroupedPlan gp;
     rc = plan_grouped(g, dev, &gp);
     if(rc)
@@ -983,6 +1024,9 @@ int ckb_grouped_gemm_run_noalloc(const ckb_grouped_gemm_desc* g, void* stream_)
     GroupEntry* d_table = g_noalloc_dev_ptr[ordinal];
 
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if(stream_is_capturing(stream))
+        return fail(CKB_ERR_UNSUPPORTED, "grouped GEMM copies its group table from host memory at every launch and "
+                                         "cannot be captured into a graph");
     GroupedPlan gp;
     rc = plan_grouped(g, dev, &gp);
     if(rc)

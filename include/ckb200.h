@@ -131,7 +131,15 @@ int ckb_gemm_supported(const ckb_gemm_desc* desc);
  * n_rep > 0: the reference's timing protocol - one warm-up launch, then n_rep
  * launches between two events, device-synchronised; *avg_ms = mean per launch
  * (include/ck/device_utility/kernel_launch.hpp:12-74 uses n_rep = 10).
- * Replaces DeviceGemm_Xdl_CShuffle::Invoker::Run (device_gemm_xdl_cshuffle.hpp:456-563). */
+ * Replaces DeviceGemm_Xdl_CShuffle::Invoker::Run (device_gemm_xdl_cshuffle.hpp:456-563).
+ *
+ * Scratch memory: a 16-bit GEMM whose last wave of tiles is partial may cut those tiles along K, which needs
+ * device scratch (4 bytes per accumulator of the tail tiles, at most a few tens of MB).  The library allocates it
+ * once per stream on the first such call, grows it on demand and keeps it until ckb_release_scratch.
+ * CUDA graphs: with n_rep = 0 the GEMM, batched-GEMM and convolution launches can be captured into a graph (call
+ * the library once on the device outside a capture first); a captured launch never uses the scratch, so a graph
+ * may be replayed on any stream.  The grouped-GEMM entry points copy a table from host memory at every launch and
+ * refuse a capturing stream. */
 int ckb_gemm_run(const ckb_gemm_desc* desc, void* stream, int n_rep, float* avg_ms);
 
 /* ---- batched GEMM: E[g] = epilogue(A[g]*B[g], D0[g], D1[g]), g = 0..batch-1 -------------- */
@@ -268,6 +276,9 @@ int ckb_memcpy_h2d(void* dev_dst, const void* host_src, size_t bytes);
 int ckb_memcpy_d2h(void* host_dst, const void* dev_src, size_t bytes);
 int ckb_memset(void* dev_ptr, int value, size_t bytes);
 int ckb_device_synchronize(void);
+/* Frees the scratch memory this library holds for `stream` on the current device (all streams of the device when
+ * `all_streams` is non-zero).  Synchronises the device first.  For callers that create and destroy streams. */
+int ckb_release_scratch(void* stream, int all_streams);
 
 /* ---- diagnostics ------------------------------------------------------------- */
 /* Message of the last failing call made by this thread ("" if none). */

@@ -1,0 +1,117 @@
+"""GPU tests of the library under CUDA graph capture and of the scratch-memory entry point.
+
+A captured launch must not allocate, free or synchronise, and its result must not depend on state that another stream
+can touch while the graph replays: GEMM, batched GEMM and convolution launches are captured with n_rep = 0 and replayed
+with fresh inputs; the grouped-GEMM entry points (which copy a host table at every launch) must refuse a capturing
+stream without breaking the capture."""
+import numpy as np
+import pytest
+import torch
+
+import composable_kernel_b200 as ck
+from composable_kernel_b200 import capi
+from oracle import ck_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def _ints(rng, shape, dtype=np.float16):
+    return rng.integers(-5, 6, shape).astype(dtype)
+
+
+def test_gemm_and_conv_replay_from_a_graph(cuda_device):
+    rng = np.random.default_rng(77)
+    M, N, K = 3840, 4096, 1024  # partial last wave: the eager plan cuts its tiles along K and owns scratch
+    a, bt = _ints(rng, (M, K)), _ints(rng, (N, K))
+    da, db = torch.from_numpy(a).cuda(), torch.from_numpy(bt).cuda()
+    e = torch.zeros((M, N), dtype=torch.float16, device="cuda")
+    gemm = ck.DeviceGemm(capi.CKB_F16)
+    garg = gemm.MakeArgument(da.data_ptr(), db.data_ptr(), e.data_ptr(), M, N, K, K, K, N, None, None, ck.PassThrough())
+    assert gemm.IsSupportedArgument(garg), capi.last_error()
+
+    Nb, C, Kc, H = 8, 64, 96, 19
+    inp, wei = _ints(rng, (Nb, H, H, C)), _ints(rng, (Kc, 3, 3, C))
+    di, dw = torch.from_numpy(inp).cuda(), torch.from_numpy(wei).cuda()
+    Ho = oracle.conv_out_len(H, 3, 2, 1, 1, 1)
+    out = torch.zeros((Nb, Ho, Ho, Kc), dtype=torch.float16, device="cuda")
+    conv = ck.DeviceConvFwd(capi.CKB_F16)
+    carg = conv.MakeArgument(di.data_ptr(), dw.data_ptr(), out.data_ptr(), Nb, Kc, C, [H, H], [3, 3], [Ho, Ho], [2, 2],
+                             [1, 1], [1, 1], [1, 1])
+    assert conv.IsSupportedArgument(carg), capi.last_error()
+
+    # eager warm-up on the side stream the capture will use (first-use initialisation happens here)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        gemm.MakeInvoker().Run(garg, ck.StreamConfig(side.cuda_stream, False))
+        conv.MakeInvoker().Run(carg, ck.StreamConfig(side.cuda_stream, False))
+    side.synchronize()
+    np.testing.assert_array_equal(e.cpu().numpy(), oracle.gemm(a, bt.T))
+    launches_before = ck.launch_count()
+
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        s = torch.cuda.current_stream().cuda_stream
+        gemm.MakeInvoker().Run(garg, ck.StreamConfig(s, False))
+        conv.MakeInvoker().Run(carg, ck.StreamConfig(s, False))
+    assert ck.launch_count() == launches_before + 2
+
+    for rep in range(2):  # new operand values in the same buffers, then replay
+        a, bt = _ints(rng, (M, K)), _ints(rng, (N, K))
+        inp, wei = _ints(rng, (Nb, H, H, C)), _ints(rng, (Kc, 3, 3, C))
+        da.copy_(torch.from_numpy(a))
+        db.copy_(torch.from_numpy(bt))
+        di.copy_(torch.from_numpy(inp))
+        dw.copy_(torch.from_numpy(wei))
+        e.zero_()
+        out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert ck.device_status() == 0
+        np.testing.assert_array_equal(e.cpu().numpy(), oracle.gemm(a, bt.T))
+        np.testing.assert_array_equal(out.cpu().numpy(), oracle.conv2d_fwd(inp, wei, (2, 2), (1, 1), (1, 1)))
+
+
+def test_grouped_gemm_refuses_a_capturing_stream(cuda_device):
+    rng = np.random.default_rng(78)
+    M, N, K = 256, 128, 64
+    a, bt = _ints(rng, (M, K)), _ints(rng, (N, K))
+    da, db = torch.from_numpy(a).cuda(), torch.from_numpy(bt).cuda()
+    e = torch.zeros((M, N), dtype=torch.float16, device="cuda")
+    op = ck.DeviceGroupedGemm(capi.CKB_F16)
+    arg = op.MakeArgument([da.data_ptr()], [db.data_ptr()], [[]], [e.data_ptr()], [ck.GemmDescHost(M, N, K, K, K, N, [])],
+                          None, None, ck.PassThrough())
+    ws = torch.empty(max(op.GetWorkSpaceSize(arg), 1), dtype=torch.uint8, device="cuda")
+    op.SetWorkSpacePointer(arg, ws.data_ptr())
+    op.MakeInvoker().Run(arg)  # eager: fine
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(e.cpu().numpy(), oracle.gemm(a, bt.T))
+
+    side = torch.cuda.Stream()
+    marker = torch.zeros(4, device="cuda")
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        s = torch.cuda.current_stream().cuda_stream
+        with pytest.raises(capi.CkbError) as err:
+            op.MakeInvoker().Run(arg, ck.StreamConfig(s, False))
+        assert "graph" in str(err.value)
+        marker += 1  # the capture is still alive and records this
+    graph.replay()
+    torch.cuda.synchronize()
+    assert marker.cpu().tolist() == [1.0] * 4
+
+
+def test_release_scratch_and_run_again(cuda_device):
+    rng = np.random.default_rng(79)
+    M, N, K = 2048, 2560, 512
+    a, bt = _ints(rng, (M, K)), _ints(rng, (N, K))
+    da, db = torch.from_numpy(a).cuda(), torch.from_numpy(bt).cuda()
+    ref = oracle.gemm(a, bt.T)
+    gemm = ck.DeviceGemm(capi.CKB_F16)
+    for round_ in range(3):
+        e = torch.zeros((M, N), dtype=torch.float16, device="cuda")
+        arg = gemm.MakeArgument(da.data_ptr(), db.data_ptr(), e.data_ptr(), M, N, K, K, K, N, None, None, ck.PassThrough())
+        gemm.MakeInvoker().Run(arg)
+        torch.cuda.synchronize()
+        np.testing.assert_array_equal(e.cpu().numpy(), ref)
+        capi.check(capi.lib().ckb_release_scratch(None, 1 if round_ else 0))
+    assert ck.device_status() == 0
