@@ -10,6 +10,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <map>
+#include <memory>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -520,6 +521,13 @@ LaunchFn find_launch(int mode, int kind, int epi)
 }
 } // namespace ckb
 
+namespace ckb {
+// Group tables of grouped-GEMM launches that were captured into graphs (see ckb_grouped_gemm_run).
+std::mutex g_captured_mutex;
+std::map<void*, std::unique_ptr<std::vector<GroupEntry>>> g_captured_tables;
+std::vector<std::unique_ptr<std::vector<GroupEntry>>> g_retired_tables;
+} // namespace ckb
+
 extern "C" {
 
 int ckb_abi_version(void) { return CKB_ABI_VERSION; }
@@ -634,6 +642,12 @@ int ckb_release_scratch(void* stream, int all_streams)
         }
         else
             ++it;
+    }
+    if(all_streams)
+    {
+        std::lock_guard<std::mutex> tables(g_captured_mutex);
+        g_captured_tables.clear();
+        g_retired_tables.clear();
     }
     return CKB_OK;
 }
@@ -958,22 +972,40 @@ int ckb_grouped_gemm_run(const ckb_grouped_gemm_desc* g, void* workspace, size_t
     if(rc)
         return rc;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    if(stream_is_capturing(stream))
-        return fail(CKB_ERR_UNSUPPORTED, "grouped GEMM copies its group table from host memory at every launch and "
-                                         "cannot be captured into a graph");
     GroupedPlan gp;
     rc = plan_grouped(g, dev, &gp);
     if(rc)
         return rc;
-    std::vector<GroupEntry> table(g->group_count);
-    rc = fill_group_table(g, gp, table.data());
-    if(rc)
-        return rc;
     uintptr_t ws_addr = (reinterpret_cast<uintptr_t>(workspace) + 127u) & ~static_cast<uintptr_t>(127u);
     GroupEntry* d_table = reinterpret_cast<GroupEntry*>(ws_addr);
-    // Pageable source: the runtime stages the bytes before returning, so `table` may go out of scope.
-    CKB_CUDA(cudaMemcpyAsync(d_table, table.data(), table.size() * sizeof(GroupEntry),
-                             cudaMemcpyHostToDevice, stream));
+    if(stream_is_capturing(stream))
+    {
+        // The copy node of a graph reads its host source again at every replay: the table is kept alive in the
+        // library, one per workspace, until the next captured launch with the same workspace replaces it.
+        std::lock_guard<std::mutex> lock(g_captured_mutex);
+        auto held = std::make_unique<std::vector<GroupEntry>>(g->group_count);
+        rc        = fill_group_table(g, gp, held->data());
+        if(rc)
+            return rc;
+        CKB_CUDA(cudaMemcpyAsync(d_table, held->data(), held->size() * sizeof(GroupEntry), cudaMemcpyHostToDevice,
+                                 stream));
+        // a table that an earlier graph captured for this workspace stays readable: it is retired, not freed
+        // (ckb_release_scratch with all_streams set drops them all)
+        auto& slot = g_captured_tables[workspace];
+        if(slot)
+            g_retired_tables.push_back(std::move(slot));
+        slot = std::move(held);
+    }
+    else
+    {
+        std::vector<GroupEntry> table(g->group_count);
+        rc = fill_group_table(g, gp, table.data());
+        if(rc)
+            return rc;
+        // Pageable source: the runtime stages the bytes before returning, so `table` may go out of scope.
+        CKB_CUDA(cudaMemcpyAsync(d_table, table.data(), table.size() * sizeof(GroupEntry), cudaMemcpyHostToDevice,
+                                 stream));
+    }
 
     KernelParams p;
     fill_grouped_params(p, g, gp, d_table, dev);

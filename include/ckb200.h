@@ -138,8 +138,9 @@ int ckb_gemm_supported(const ckb_gemm_desc* desc);
  * once per stream on the first such call, grows it on demand and keeps it until ckb_release_scratch.
  * CUDA graphs: with n_rep = 0 the GEMM, batched-GEMM and convolution launches can be captured into a graph (call
  * the library once on the device outside a capture first); a captured launch never uses the scratch, so a graph
- * may be replayed on any stream.  The grouped-GEMM entry points copy a table from host memory at every launch and
- * refuse a capturing stream. */
+ * may be replayed on any stream.  ckb_grouped_gemm_run copies a table from host memory at every launch; when it is
+ * captured the library keeps that table alive for the graph's copy node (until ckb_release_scratch with all_streams
+ * set).  ckb_grouped_gemm_run_noalloc refuses a capturing stream: its host table is shared by all calls. */
 int ckb_gemm_run(const ckb_gemm_desc* desc, void* stream, int n_rep, float* avg_ms);
 
 /* ---- batched GEMM: E[g] = epilogue(A[g]*B[g], D0[g], D1[g]), g = 0..batch-1 -------------- */
@@ -277,7 +278,8 @@ int ckb_memcpy_d2h(void* host_dst, const void* dev_src, size_t bytes);
 int ckb_memset(void* dev_ptr, int value, size_t bytes);
 int ckb_device_synchronize(void);
 /* Frees the scratch memory this library holds for `stream` on the current device (all streams of the device when
- * `all_streams` is non-zero).  Synchronises the device first.  For callers that create and destroy streams. */
+ * `all_streams` is non-zero; that also drops the host tables kept for captured grouped-GEMM launches, whose graphs
+ * must not be replayed afterwards).  Synchronises the device first.  For callers that create and destroy streams. */
 int ckb_release_scratch(void* stream, int all_streams);
 
 /* ---- diagnostics ------------------------------------------------------------- */
