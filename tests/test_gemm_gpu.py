@@ -192,3 +192,26 @@ def test_run_returns_zero_without_timing_and_counts_launches(cuda_device):
     assert ms == 0.0 and ck.launch_count() == before + 1
     _, ms = H.run_gemm(a, bt, time_kernel=True)  # 1 warm-up + 10 timed (kernel_launch.hpp:32-61)
     assert ms > 0.0 and ck.launch_count() == before + 12
+
+
+def test_output_offsets_beyond_2_gib(cuda_device):
+    """E of 140 000 x 8192 halves is 2.29 GB: row offsets pass 2^31 bytes, so every address computation of the
+    epilogue (staged tile stores and the scalar path of the ragged last rows) has to be 64-bit.  Row blocks at the
+    start, around the 2 GiB mark and at the ragged end are compared bit-exactly with the oracle."""
+    rng = np.random.default_rng(4242)
+    M, N, K = 140_000, 8192, 32
+    a = rng.integers(-5, 6, (M, K)).astype(np.float16)
+    bt = rng.integers(-5, 6, (N, K)).astype(np.float16)
+    da, db = torch.from_numpy(a).cuda(), torch.from_numpy(bt).cuda()
+    e = torch.zeros((M, N), dtype=torch.float16, device="cuda")
+    gemm = ck.DeviceGemm(capi.CKB_F16)
+    arg = gemm.MakeArgument(da.data_ptr(), db.data_ptr(), e.data_ptr(), M, N, K, K, K, N, None, None, ck.PassThrough())
+    assert gemm.IsSupportedArgument(arg), capi.last_error()
+    gemm.MakeInvoker().Run(arg)
+    torch.cuda.synchronize()
+    assert ck.device_status() == 0
+    mark = (1 << 31) // (2 * N)  # first row whose byte offset is past 2 GiB
+    for lo, hi in [(0, 256), (mark - 200, mark + 200), (M - 300, M)]:
+        np.testing.assert_array_equal(e[lo:hi].cpu().numpy(), oracle.gemm(a[lo:hi], bt.T), err_msg=f"rows {lo}:{hi}")
+    # nothing outside the ragged edge was left unwritten: every row has a non-zero element with these inputs
+    assert bool((e != 0).any(dim=1).all())
