@@ -662,6 +662,53 @@ struct BatchInfo
     bool vec_ok; // every batch of E / D keeps the 16-byte alignment of the first
 };
 
+// Whole-problem K split.  A GEMM with few output tiles and a long K leaves most SMs idle whatever the tile shape;
+// cutting every tile's K loop into 2 or 4 slices (the machinery of the K-split tail, with no whole tiles before
+// it) puts 2-8 times as many SMs to work on full-width MMAs.  Cycle estimates per k block, fitted to timings of
+// 1024 x 1024 x K and 512 x 512 x K with and without the split: 590 for 256 accumulator columns, 340 for 128,
+// 315 for 64 (the narrow ones are bound by the issue rate of the single MMA thread, not by the tensor pipe);
+// parking and summing the slices costs about 9100 cycles (5.5 us), most of it the exposed latency of the
+// reduction's loads.
+struct WholeSplit
+{
+    int bn = 0, cg = 0, ksplit = 0;
+};
+
+int kb_cycles(int width) { return width >= 256 ? 590 : width >= 128 ? 340 : 315; }
+
+WholeSplit consider_whole_split(int64_t M, int64_t N, int num_kb, int sm_count, int b_min, int64_t est_current)
+{
+    WholeSplit best;
+    int64_t best_est = est_current - est_current / 8; // has to beat the plan without it by an eighth
+    const int cand[3][2] = {{256, 2}, {256, 1}, {128, 1}};
+    for(const auto& c : cand)
+    {
+        const int bn = c[0], cg = c[1];
+        if(bn / cg < b_min || (cg == 2 && M <= BM)) // a pair tile with one half of its rows empty pays for nothing
+            continue;
+        const int64_t G     = sm_count / cg;
+        const int64_t tiles = ((M + BM * cg - 1) / (BM * cg)) * ((N + bn - 1) / bn);
+        for(int ks = bn / 32; ks >= 2; ks /= 2) // column parts of the reduction are whole 32-column chunks
+        {
+            if(tiles * ks > G)
+                continue;
+            int ks_kb = (num_kb + ks - 1) / ks;
+            ks_kb     = (ks_kb + 1) & ~1;
+            if(ks_kb < 4 || static_cast<int64_t>(ks - 1) * ks_kb >= num_kb)
+                continue;
+            const int64_t est = static_cast<int64_t>(ks_kb) * kb_cycles(bn) + 9100 + (ks > 4 ? 1500 : 0);
+            if(est < best_est)
+            {
+                best_est    = est;
+                best.bn     = bn;
+                best.cg     = cg;
+                best.ksplit = ks;
+            }
+        }
+    }
+    return best;
+}
+
 static int gemm_run_impl(const ckb_gemm_desc* d, const BatchInfo& bi, void* stream, int n_rep, float* avg_ms)
 {
     int rc = CKB_OK;
@@ -671,7 +718,7 @@ static int gemm_run_impl(const ckb_gemm_desc* d, const BatchInfo& bi, void* stre
         return rc;
     const bool a_mn  = a_is_mn_major(d), b_mn = b_is_mn_major(d);
     const int b_min  = min_b_rows(d->ab_dtype, b_mn);
-    const int bn     = pick_bn(d->M, d->N, dev->sm_count, b_min);
+    int bn           = pick_bn(d->M, d->N, dev->sm_count, b_min);
     const int eb     = elem_bytes(d->ab_dtype);
     KernelParams p;
     memset(&p, 0, sizeof(p));
@@ -679,9 +726,42 @@ static int gemm_run_impl(const ckb_gemm_desc* d, const BatchInfo& bi, void* stre
     if(rc)
         return rc;
     fill_epilogue(p.epi, d);
-    const int64_t tiles_n = (d->N + bn - 1) / bn;
     const int64_t nb      = bi.batch > 0 ? bi.batch : 1;
-    const int cg          = pick_cg(((d->M + BM - 1) / BM) * tiles_n * nb, bn, dev->sm_count);
+    int cg                = pick_cg(((d->M + BM - 1) / BM) * ((d->N + bn - 1) / bn) * nb, bn, dev->sm_count);
+    const int bk          = BK_BYTES / eb;
+    const int num_kb      = static_cast<int>((d->K + bk - 1) / bk);
+    const char* no_ks     = getenv("CKB_NO_SPLITK");
+    const bool ks_allowed = !(no_ks && atoi(no_ks) != 0);
+    // Measured on 3840 x 4096 x 4096: +5 % for 16-bit operands with a D-less epilogue; a loss for int8 (tiles
+    // half as long) and for epilogues that read D tensors (bound by power: parking the partials through L2 costs
+    // more energy than the narrow MMAs it removes) - those keep the column slices.
+#ifdef CKB_KSPLIT_WITH_D
+    const bool ks_pays = d->ab_dtype != CKB_I8;
+#else
+    const bool ks_pays = d->ab_dtype != CKB_I8 && d->n_ds == 0;
+#endif
+    int whole_ksplit = 0;
+    if(ks_pays && ks_allowed && bi.batch == 0 && forced_bn() == 0 && !getenv("CKB_FORCE_CG") &&
+       !stream_is_capturing(static_cast<cudaStream_t>(stream)))
+    {
+        // only where the plan without it runs a single, partly filled wave
+        const int64_t t0 = ((d->M + BM * cg - 1) / (BM * cg)) * ((d->N + bn - 1) / bn);
+        const int64_t G0 = dev->sm_count / cg;
+        if(t0 * 2 <= G0)
+        {
+            const WorkPlan w0 = plan_work(t0, static_cast<int>(G0), bn, cg, b_min);
+            const WholeSplit ws =
+                consider_whole_split(d->M, d->N, num_kb, dev->sm_count, b_min,
+                                     static_cast<int64_t>(num_kb) * kb_cycles(bn / w0.split));
+            if(ws.ksplit >= 2)
+            {
+                bn           = ws.bn;
+                cg           = ws.cg;
+                whole_ksplit = ws.ksplit;
+            }
+        }
+    }
+    const int64_t tiles_n = (d->N + bn - 1) / bn;
     const int64_t tiles_m = (d->M + BM * cg - 1) / (BM * cg);
     const int64_t all_tiles = tiles_m * tiles_n * nb;
     if(all_tiles > 0x3FFFFFFFll)
@@ -689,25 +769,14 @@ static int gemm_run_impl(const ckb_gemm_desc* d, const BatchInfo& bi, void* stre
     WorkPlan plan = plan_work(all_tiles, dev->sm_count / cg, bn, cg, b_min);
     // K-split tail: with whole waves before it and a tail of at most half the units, cut the tail tiles along K
     // (see "K-split tail" in ckb_kernel.cuh); needs scratch, else the column-slice plan above stands.
-    const int bk      = BK_BYTES / eb;
-    const int num_kb  = static_cast<int>((d->K + bk - 1) / bk);
     const int64_t G   = dev->sm_count / cg;
     const int64_t ful = (all_tiles / G) * G, rem = all_tiles - ful;
-    const char* no_ks = getenv("CKB_NO_SPLITK");
-    // Measured on 3840 x 4096 x 4096: +5 % for 16-bit operands with a D-less epilogue; a loss for int8 (tiles
-    // half as long) and for epilogues that read D tensors, where the epilogue warps have no slack for the
-    // parking and the reduction - those keep the column slices.
-#ifdef CKB_KSPLIT_WITH_D
-    const bool ks_pays = d->ab_dtype != CKB_I8;
-#else
-    const bool ks_pays = d->ab_dtype != CKB_I8 && d->n_ds == 0;
-#endif
-    if(ks_pays && rem > 0 && ful > 0 && rem * 2 <= G && rem <= 1024 && !(no_ks && atoi(no_ks) != 0))
+    if(ks_pays && ks_allowed && rem > 0 && (ful > 0 || whole_ksplit >= 2) && rem * 2 <= G && rem <= 1024)
     {
-        // 4 or 2 slices; the reduction is shared out in column parts of bn / ksplit >= 64 columns
-        int ksplit = (G / rem >= 4 && bn >= 256) ? 4 : (bn >= 128 ? 2 : 0);
+        // tail: 4 or 2 slices, reduction in column parts of bn / ksplit >= 64 columns; whole problem: up to 8
+        int ksplit = whole_ksplit >= 2 ? whole_ksplit : (G / rem >= 4 && bn >= 256) ? 4 : (bn >= 128 ? 2 : 0);
         int ks_kb  = 0;
-        for(; ksplit >= 2; ksplit -= 2)
+        for(; ksplit >= 2; ksplit /= 2)
         {
             ks_kb = (num_kb + ksplit - 1) / ksplit;
             ks_kb = (ks_kb + 1) & ~1; // slices start on a stage boundary (at most two k blocks per stage)

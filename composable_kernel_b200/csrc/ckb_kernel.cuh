@@ -449,33 +449,45 @@ __device__ __forceinline__ void reduce_chunk(uint32_t (&v)[32], const uint32_t* 
 #pragma unroll
     for(int h = 0; h < 8 / QUADS; ++h)
     {
-        uint4 t[4][QUADS];
+        uint4 acc[QUADS];
 #pragma unroll
-        for(int sl = 0; sl < 4; ++sl)
-            if(sl < ks)
+        for(int base = 0; base < 8; base += 4) // up to 8 slices, four in flight at a time, summed in slice order
+        {
+            if(base >= ks)
+                break;
+            uint4 t[4][QUADS];
+#pragma unroll
+            for(int sl = 0; sl < 4; ++sl)
+                if(base + sl < ks)
+                {
+                    const uint4* src = reinterpret_cast<const uint4*>(block + (base + sl) * slice_stride) + lane;
+#pragma unroll
+                    for(int q = 0; q < QUADS; ++q)
+                        t[sl][q] = __ldcg(src + (c * 8 + h * QUADS + q) * 32);
+                }
+#pragma unroll
+            for(int q = 0; q < QUADS; ++q)
             {
-                const uint4* src = reinterpret_cast<const uint4*>(block + sl * slice_stride) + lane;
+                uint4 a = base == 0 ? t[0][q] : acc[q];
 #pragma unroll
-                for(int q = 0; q < QUADS; ++q)
-                    t[sl][q] = __ldcg(src + (c * 8 + h * QUADS + q) * 32);
+                for(int sl = 0; sl < 4; ++sl)
+                    if((base > 0 || sl > 0) && base + sl < ks)
+                    {
+                        a.x = add(a.x, t[sl][q].x);
+                        a.y = add(a.y, t[sl][q].y);
+                        a.z = add(a.z, t[sl][q].z);
+                        a.w = add(a.w, t[sl][q].w);
+                    }
+                acc[q] = a;
             }
+        }
 #pragma unroll
         for(int q = 0; q < QUADS; ++q)
         {
-            uint4 a = t[0][q];
-#pragma unroll
-            for(int sl = 1; sl < 4; ++sl)
-                if(sl < ks)
-                {
-                    a.x = add(a.x, t[sl][q].x);
-                    a.y = add(a.y, t[sl][q].y);
-                    a.z = add(a.z, t[sl][q].z);
-                    a.w = add(a.w, t[sl][q].w);
-                }
-            v[(h * QUADS + q) * 4 + 0] = a.x;
-            v[(h * QUADS + q) * 4 + 1] = a.y;
-            v[(h * QUADS + q) * 4 + 2] = a.z;
-            v[(h * QUADS + q) * 4 + 3] = a.w;
+            v[(h * QUADS + q) * 4 + 0] = acc[q].x;
+            v[(h * QUADS + q) * 4 + 1] = acc[q].y;
+            v[(h * QUADS + q) * 4 + 2] = acc[q].z;
+            v[(h * QUADS + q) * 4 + 3] = acc[q].w;
         }
     }
 }
@@ -1028,12 +1040,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                         ea.d1 = static_cast<const char*>(ea.d1) + wi.batch * P.batch_stride_d1 * EB;
                 }
             }
-            const int span          = wi.width >> 1; // columns per epilogue warp (>= 32)
+            // columns per epilogue warp (>= 32); a 32-column part (reduction of an 8-way K split) is handled by
+            // the warps of column half 0 alone, those of half 1 get an empty range
+            const int span          = wi.width >= 64 ? wi.width >> 1 : wi.width;
             const int64_t m =
                 static_cast<int64_t>(wi.m_blk) * TILE_M + cta_rank * BM + quarter * 32 + lane;
             const bool row_ok       = m < Mdim;
             const int64_t n_begin   = static_cast<int64_t>(wi.n_start) + half * span;
-            const int64_t n_end_raw = n_begin + span;
+            const int64_t n_end_raw = (wi.width >= 64 || half == 0) ? n_begin + span : n_begin;
             const int64_t n_end     = n_end_raw < Ndim ? n_end_raw : Ndim;
 
             // K-split tail: this warp's block of the tail tile in slice 0 of the scratch buffer

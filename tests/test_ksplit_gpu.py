@@ -130,3 +130,51 @@ def test_ksplit_tail_of_a_batched_gemm_spans_batches(cuda_device):
     out = e.cpu().numpy()
     for g in range(G):
         np.testing.assert_array_equal(out[g], oracle.gemm(a[g], bt[g].T))
+
+
+@pytest.mark.parametrize("M,N,K", [
+    (512, 512, 8192),     # 4 pair tiles x 4 slices
+    (1024, 1024, 4096),   # 16 pair tiles x 4 slices
+    (256, 256, 16384),    # one pair tile, 4 slices of 64 k blocks
+    (128, 384, 6144),     # a single row of tiles: M fills half a pair tile
+    (1000, 700, 5000),    # ragged M, N (scalar stores) and K (last slice shorter than the others)
+    (1536, 2048, 2048),   # 2 slices only: 48 pair tiles on 74 pairs would not take 4
+    (192, 128, 3072),     # narrow N: the 128-wide tile, 2 slices
+])
+def test_whole_problem_k_split_bit_exact(cuda_device, M, N, K):
+    """Few output tiles and a long K: every tile's K loop is cut (no whole tiles before the slices)."""
+    rng = np.random.default_rng(M * 3 + N * 5 + K)
+    a, bt = ints(rng, (M, K)), ints(rng, (N, K))
+    out = run(a, bt, reps=2)
+    np.testing.assert_array_equal(out, oracle.gemm(a, bt.T))
+
+
+def test_whole_problem_k_split_bf16_layouts_and_functor(cuda_device):
+    from tests.test_layouts_gpu import COL, ROW, make_inputs, run_layout
+
+    rng = np.random.default_rng(4321)
+    M, N, K = 640, 768, 6144
+    for dtype in (capi.CKB_F16, capi.CKB_BF16):
+        a, b = make_inputs(rng, dtype, M, N, K)
+        ref = oracle.gemm(a, b)
+        for layouts in ((ROW, COL), (ROW, ROW), (COL, ROW), (COL, COL)):
+            np.testing.assert_array_equal(run_layout(dtype, layouts[0], layouts[1], a, b), ref, err_msg=str((dtype, layouts)))
+    a, b = make_inputs(rng, capi.CKB_F16, M, N, K, kind="real")
+    op = ck.FastGelu()
+    out = run_layout(capi.CKB_F16, ROW, COL, a, b, op=op)
+    bad, max_err = oracle.check_err(out, oracle.gemm(a, b, op.kind, op.params), 1e-3, 1e-3)
+    assert bad == 0, (bad, max_err)
+
+
+def test_whole_problem_k_split_matches_the_unsplit_plan(cuda_device):
+    """Same problem with the K split switched off: the column-slice plan.  Integer inputs: identical bits."""
+    rng = np.random.default_rng(99)
+    a, bt = ints(rng, (768, 8192)), ints(rng, (512, 8192))
+    split = run(a, bt)
+    os.environ["CKB_NO_SPLITK"] = "1"
+    try:
+        plain = run(a, bt)
+    finally:
+        del os.environ["CKB_NO_SPLITK"]
+    np.testing.assert_array_equal(split, plain)
+    np.testing.assert_array_equal(split, oracle.gemm(a, bt.T))
