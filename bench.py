@@ -229,17 +229,17 @@ class ConvWorkload:
 class GroupedWorkload:
     """C5: 64 groups, M_g = 256*(1 + g mod 16), N = K = 4096; groups partitioned over ranks by LPT."""
 
-    def __init__(self, torch, ck, capi, rank, world):
+    def __init__(self, torch, ck, capi, rank, world, groups=64):
         self.name, self.torch, self.ck, self.capi = "grouped", torch, ck, capi
         self.N = self.K = 4096
-        all_m = [256 * (1 + g % 16) for g in range(64)]
+        all_m = [256 * (1 + g % 16) for g in range(groups)]
         self.mine = grouped_gemm_shard(all_m, rank, world)
         self.Ms = [all_m[g] for g in self.mine]
         self.flop_total = sum(2 * m * self.N * self.K for m in all_m)
         self.flop = sum(2 * m * self.N * self.K for m in self.Ms)
         self.bytes = sum(2 * (m * self.K + self.K * self.N + m * self.N) for m in self.Ms)
         self.dtype, self.unit = "f16", "TFLOPS"
-        self.desc = (f"fp16 grouped GEMM, 64 groups M_g=256*(1+g%16) N=K=4096, "
+        self.desc = (f"fp16 grouped GEMM, {groups} groups M_g=256*(1+g%16) N=K=4096, "
                      f"{len(self.mine)} groups on this GPU (FLOP-balanced LPT)")
 
     def make_set(self, host=None):
@@ -383,6 +383,9 @@ def main():
     ap.add_argument("--workload", default="gemm_fp16",
                     choices=["gemm_fp16", "gemm_int8", "gemm_fastgelu", "conv", "grouped"])
     ap.add_argument("--no-extra", action="store_true", help="skip the other workloads / e2e / cpu baseline")
+    ap.add_argument("--groups", type=int, default=64,
+                    help="grouped workload: number of groups (64 = the benchmark; 16, one period of the group "
+                         "sizes and about 1.1 GB, is the case small enough for a multi-pass profiler capture)")
     ap.add_argument("--role-cycles", action="store_true",
                     help="with a -DCKB_TRACE build of the library (CKB200_LIB): print the per-role cycle counters "
                          "of the last launch of the workload on stderr")
@@ -431,7 +434,7 @@ def main():
         if name == "conv":
             return ConvWorkload(torch, ck, capi, rank, world)
         if name == "grouped":
-            return GroupedWorkload(torch, ck, capi, rank, world)
+            return GroupedWorkload(torch, ck, capi, rank, world, args.groups)
         return GemmWorkload(name, torch, ck, capi)
 
     def measure(name, steps, warmup, sample_clocks=False):
