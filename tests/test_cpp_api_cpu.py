@@ -28,5 +28,8 @@ def test_example_drivers_build():
     res = subprocess.run(["make", "-C", os.path.join(ROOT, "examples"), "-j4"], capture_output=True, text=True)
     assert res.returncode == 0, res.stderr[-3000:]
     for name in ("gemm_xdl_fp16", "gemm_add_add_fastgelu_xdl_fp16", "gemm_xdl_requant_relu_requant_int8",
-                 "grouped_gemm_xdl_fp16", "conv2d_fwd_xdl_bias_relu", "ck_profiler", "convnd_fwd_instance_engine"):
+                 "grouped_gemm_xdl_fp16", "conv2d_fwd_xdl_bias_relu", "ck_profiler", "convnd_fwd_instance_engine",
+                 "gemm_bilinear_xdl_fp16", "gemm_bias_relu_xdl_fp16", "grouped_gemm_bias_xdl_fp16",
+                 "convnd_fwd_xdl_fp16", "convnd_fwd_xdl_int8", "client_gemm",
+                 "client_gemm_add_add_fastgelu"):
         assert os.path.exists(os.path.join(ROOT, "examples", "bin", name))

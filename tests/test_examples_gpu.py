@@ -43,6 +43,49 @@ def test_gemm_add_add_fastgelu_example(examples_built):
     assert "DeviceGemmMultipleD_Xdl_CShuffle" in out
 
 
+def test_gemm_bilinear_example(examples_built):
+    # example-local AlphaBetaAdd functor mapped to the library's bilinear epilogue by one trait specialisation
+    # M N K StrideA StrideB StrideD StrideE alpha beta
+    out = run_example("gemm_bilinear_xdl_fp16", 1, 1, 1, 512, 768, 256, 256, 256, 768, 768, 2.0, 0.5)
+    assert "DeviceGemmMultipleD_Xdl_CShuffle" in out
+    run_example("gemm_bilinear_xdl_fp16", 1, 2, 0, 256, 384, 192, 192, 192, 400, 392, 0.75, -1.25)  # padded D and E
+
+
+def test_gemm_bias_relu_example(examples_built):
+    # example-local binary16 AddRelu functor, bias row with stride 0, MNKPadding instance: ragged sizes are accepted
+    out = run_example("gemm_bias_relu_xdl_fp16", 1, 1, 1, 512, 768, 256, 256, 256, 768)
+    assert "DeviceGemmMultipleD_Xdl_CShuffle" in out
+    # Integer init throughout: the functor adds in binary16 after the accumulator has been rounded to binary16, so
+    # with decimal inputs a last-bit difference of the fp32 sum (summation order) can grow to two binary16 spacings
+    # of the result, beyond check_err's 1e-3 bounds; integer inputs give exact sums.
+    run_example("gemm_bias_relu_xdl_fp16", 1, 1, 0, 300, 200, 136, 136, 136, 200)
+
+
+def test_grouped_gemm_bias_example(examples_built):
+    out = run_example("grouped_gemm_bias_xdl_fp16", 1, 1, 1)
+    assert "DeviceGroupedGemmXdl" in out
+    run_example("grouped_gemm_bias_xdl_fp16", 1, 1, 0, 7)  # integer init: binary16 functor, see the bias + ReLU test
+
+
+def test_convnd_fwd_example(examples_built):
+    # verify init time nd N K C <filter> <input> <strides> <dilations> <left pads> <right pads>
+    out = run_example("convnd_fwd_xdl_fp16", 1, 1, 1, 1, 4, 64, 32, 3, 71, 2, 1, 1, 1)
+    assert "Perf:" in out and "DeviceConv1DFwdXdl" in out
+    run_example("convnd_fwd_xdl_fp16", 1, 2, 0, 2, 4, 64, 64, 3, 3, 17, 19, 2, 1, 1, 2, 1, 2, 1, 2)
+    run_example("convnd_fwd_xdl_fp16", 1, 1, 0, 3, 2, 32, 16, 3, 3, 3, 9, 10, 11, 1, 2, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1)
+    # the int8 instance list of the same example (int32 accumulation, bit-exact)
+    run_example("convnd_fwd_xdl_int8", 1, 1, 0, 2, 4, 64, 64, 3, 3, 17, 19, 2, 1, 1, 2, 1, 2, 1, 2)
+    run_example("convnd_fwd_xdl_int8", 1, 1, 0, 1, 4, 64, 32, 3, 71, 2, 1, 1, 1)
+
+
+def test_client_examples_walk_the_instance_factory(examples_built):
+    """Client-style programs: device-operation interface + instance list only, best instance re-run at the end."""
+    out = run_example("client_gemm", 512, 768, 256, 256, 256, 768)
+    assert "found 1 instances" in out and "Best Perf:" in out and out.rstrip().endswith("Done")
+    out = run_example("client_gemm_add_add_fastgelu", 512, 768, 256, 256, 256, 0, 768, 768)
+    assert "Best Perf:" in out and "DeviceGemmMultipleD_Xdl_CShuffle" in out and out.rstrip().endswith("Done")
+
+
 def test_int8_requant_example_both_roundings(examples_built):
     run_example("gemm_xdl_requant_relu_requant_int8", 1, 1, 0, 512, 512, 1024, 1024, 1024, 512)
     run_example("gemm_xdl_requant_relu_requant_int8", 1, 1, 0, 512, 512, 1024, 1024, 1024, 512, 1)
