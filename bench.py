@@ -188,6 +188,7 @@ class ConvWorkload:
         self.Nloc = b1 - b0
         self.flop_total = 2 * self.Ntot * self.K * self.Ho * self.Wo * self.C * 9
         self.flop = 2 * self.Nloc * self.K * self.Ho * self.Wo * self.C * 9
+        self.traffic_scale = self.Nloc / self.Ntot  # the ncu summary states the 128-image launch
         self.bytes = 2 * (self.Nloc * self.C * self.Hi * self.Wi + self.K * self.C * 9 +
                           self.Nloc * self.K * self.Ho * self.Wo) + 2 * self.K
         self.dtype, self.unit = "f16", "TFLOPS"
@@ -237,6 +238,8 @@ class GroupedWorkload:
         self.Ms = [all_m[g] for g in self.mine]
         self.flop_total = sum(2 * m * self.N * self.K for m in all_m)
         self.flop = sum(2 * m * self.N * self.K for m in self.Ms)
+        # share of the 64-group benchmark launch (whose DRAM traffic the ncu summary states) that this GPU runs
+        self.traffic_scale = self.flop / sum(2 * 256 * (1 + g % 16) * self.N * self.K for g in range(64))
         self.bytes = sum(2 * (m * self.K + self.K * self.N + m * self.N) for m in self.Ms)
         self.dtype, self.unit = "f16", "TFLOPS"
         self.desc = (f"fp16 grouped GEMM, {groups} groups M_g=256*(1+g%16) N=K=4096, "
@@ -465,11 +468,15 @@ def main():
         long_region = total_ms >= 100.0 and "bf16_tflops_sustained" in peaks
         regime = "sustained" if long_region else "burst"
         peak = peaks["bf16_tflops_sustained" if long_region else "bf16_tflops"] * (2.0 if wl.dtype == "i8" else 1.0)
+        # the ncu figure is for the whole workload on one GPU; a shard's launch moves its share of it
+        traffic = ncu_traffic(name)
+        if traffic is not None:
+            traffic *= getattr(wl, "traffic_scale", 1.0)
         res = {
             "workload": wl.desc, "value": value, "unit": wl.unit, "ms_per_step": total_ms / steps,
             "scaling": "strong" if sharded else "weak",
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s" if wl.dtype == "i8" else "TFLOP/s",
-                         "frac": achieved / peak, "traffic": ncu_traffic(name),
+                         "frac": achieved / peak, "traffic": traffic,
                          "peak_source": f"{peak_kind} bf16 {regime}" + (" x2 (int8)" if wl.dtype == "i8" else ""),
                          "kernel_ms": kern_ms, "hbm_gbs_algorithmic": wl.bytes / (kern_ms * 1e-3) / 1e9},
             "gpu_launches": launches,
