@@ -31,5 +31,5 @@ def test_example_drivers_build():
                  "grouped_gemm_xdl_fp16", "conv2d_fwd_xdl_bias_relu", "ck_profiler", "convnd_fwd_instance_engine",
                  "gemm_bilinear_xdl_fp16", "gemm_bias_relu_xdl_fp16", "grouped_gemm_bias_xdl_fp16",
                  "convnd_fwd_xdl_fp16", "convnd_fwd_xdl_int8", "client_gemm",
-                 "client_gemm_add_add_fastgelu"):
+                 "client_gemm_add_add_fastgelu", "test_gemm_instances"):
         assert os.path.exists(os.path.join(ROOT, "examples", "bin", name))

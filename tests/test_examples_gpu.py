@@ -86,6 +86,14 @@ def test_client_examples_walk_the_instance_factory(examples_built):
     assert "Best Perf:" in out and "DeviceGemmMultipleD_Xdl_CShuffle" in out and out.rstrip().endswith("Done")
 
 
+def test_reference_style_gemm_instance_tests(examples_built):
+    """The reference's test/gemm programs: every factory instance, four layouts, fp16 / bf16 / int8, 1024^3."""
+    out = run_example("test_gemm_instances")
+    for name in ("fp16", "bf16", "int8"):
+        assert f"TestGemm {name} ..... SUCCESS" in out
+    assert "FAILURE" not in out
+
+
 def test_int8_requant_example_both_roundings(examples_built):
     run_example("gemm_xdl_requant_relu_requant_int8", 1, 1, 0, 512, 512, 1024, 1024, 1024, 512)
     run_example("gemm_xdl_requant_relu_requant_int8", 1, 1, 0, 512, 512, 1024, 1024, 1024, 512, 1)
