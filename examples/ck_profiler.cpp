@@ -250,15 +250,14 @@ static std::vector<int> parse_list(const char* s)
     return v;
 }
 
-int profile_grouped_gemm(int argc, char* argv[])
+// layout: the reference's GemmMatrixLayout (profiler/src/profile_grouped_gemm.cpp:15-25): 0 MK_KN_MN, 1 MK_NK_MN,
+// 2 KM_KN_MN, 3 KM_NK_MN; leading dimensions are the packed ones of each layout.
+template <typename ALayout, typename BLayout>
+int profile_grouped_gemm_layout(char* argv[])
 {
-    if(argc != 11 || std::stoi(argv[2]) != 1 || std::stoi(argv[3]) != 1)
-    {
-        std::printf("grouped_gemm 1 1 verify init log time Ms Ns Ks   (comma separated lists, e.g. 256,512 128,256 64,128)\n");
-        return 1;
-    }
     using F16      = ck::half_t;
-    using DeviceOp = dev::DeviceGroupedGemm<Row, Col, Row, F16, F16, inst::EMPTY_TUPLE, F16, PassThrough, PassThrough, PassThrough>;
+    using DeviceOp = dev::DeviceGroupedGemm<ALayout, BLayout, Row, F16, F16, inst::EMPTY_TUPLE, F16, PassThrough, PassThrough, PassThrough>;
+    constexpr bool a_row = std::is_same<ALayout, Row>::value, b_row = std::is_same<BLayout, Row>::value;
     const bool verify = std::stoi(argv[4]), time = std::stoi(argv[7]);
     const int init = std::stoi(argv[5]);
     const auto Ms = parse_list(argv[8]), Ns = parse_list(argv[9]), Ks = parse_list(argv[10]);
@@ -274,9 +273,10 @@ int profile_grouped_gemm(int argc, char* argv[])
     std::size_t flop = 0, bytes = 0;
     for(std::size_t i = 0; i < G; ++i)
     {
-        descs.push_back({Ms[i], Ns[i], Ks[i], Ks[i], Ks[i], Ns[i], {}});
-        As.emplace_back(example::matrix_descriptor(Ms[i], Ks[i], Ks[i], Row{}));
-        Bs.emplace_back(example::matrix_descriptor(Ks[i], Ns[i], Ks[i], Col{}));
+        const int lda = a_row ? Ks[i] : Ms[i], ldb = b_row ? Ns[i] : Ks[i];
+        descs.push_back({Ms[i], Ns[i], Ks[i], lda, ldb, Ns[i], {}});
+        As.emplace_back(example::matrix_descriptor(Ms[i], Ks[i], lda, ALayout{}));
+        Bs.emplace_back(example::matrix_descriptor(Ks[i], Ns[i], ldb, BLayout{}));
         Ch.emplace_back(example::matrix_descriptor(Ms[i], Ns[i], Ns[i], Row{}));
         Cd.emplace_back(example::matrix_descriptor(Ms[i], Ns[i], Ns[i], Row{}));
         init_tensor(As[i], init, false);
@@ -321,6 +321,21 @@ int profile_grouped_gemm(int argc, char* argv[])
     }
     best.report("grouped_gemm");
     return pass && !best.name.empty() ? 0 : 1;
+}
+
+int profile_grouped_gemm(int argc, char* argv[])
+{
+    const int layout = argc == 11 ? std::stoi(argv[3]) : -1;
+    if(argc != 11 || std::stoi(argv[2]) != 1 || layout < 0 || layout > 3)
+    {
+        std::printf("grouped_gemm 1 <layout 0 MK_KN | 1 MK_NK | 2 KM_KN | 3 KM_NK> verify init log time Ms Ns Ks   "
+                    "(comma separated lists, e.g. 256,512 128,256 64,128)\n");
+        return 1;
+    }
+    return layout == 0 ? profile_grouped_gemm_layout<Row, Row>(argv)
+                       : layout == 1 ? profile_grouped_gemm_layout<Row, Col>(argv)
+                                     : layout == 2 ? profile_grouped_gemm_layout<Col, Row>(argv)
+                                                   : profile_grouped_gemm_layout<Col, Col>(argv);
 }
 
 int profile_conv_fwd_bias_relu(int argc, char* argv[])

@@ -94,6 +94,20 @@ def test_reference_style_gemm_instance_tests(examples_built):
     assert "FAILURE" not in out
 
 
+def test_grouped_gemm_random_groups_four_layouts(examples_built):
+    """The reference's test/grouped_gemm/grouped_gemm_fp16.cpp: 1-10 groups with M, N in 256..2560 and K in
+    128..1280 (multiples of 256 / 128), all four A/B layouts, verified against the CPU reference (seeded here)."""
+    import random
+    rnd = random.Random(11939)
+    for layout in (0, 1, 2, 3):
+        g = rnd.randrange(10) + 1
+        ms = ",".join(str(256 + 256 * rnd.randrange(10)) for _ in range(g))
+        ns = ",".join(str(256 + 256 * rnd.randrange(10)) for _ in range(g))
+        ks = ",".join(str(128 + 128 * rnd.randrange(10)) for _ in range(g))
+        out = run_example("ck_profiler", "grouped_gemm", 1, layout, 1, 1, 0, 1, ms, ns, ks)
+        assert "Best Perf for grouped_gemm" in out
+
+
 def test_int8_requant_example_both_roundings(examples_built):
     run_example("gemm_xdl_requant_relu_requant_int8", 1, 1, 0, 512, 512, 1024, 1024, 1024, 512)
     run_example("gemm_xdl_requant_relu_requant_int8", 1, 1, 0, 512, 512, 1024, 1024, 1024, 512, 1)
