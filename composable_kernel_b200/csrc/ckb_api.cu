@@ -290,9 +290,17 @@ int encode_operand(CUtensorMap* tm, int dtype, const void* ptr, int64_t mn, int6
                     : encode_kmajor_2d(tm, dtype, ptr, mn, k, ld, box_mn, batch, batch_stride);
 }
 
-// Narrowest B slice one CTA can load: 64 rows of a K-major tile, one whole swizzle atom (128 bytes of N
-// positions) of an N-major one.
-int min_b_rows(int dtype, bool b_mn) { return b_mn ? BK_BYTES / elem_bytes(dtype) : 64; }
+// Narrowest B slice one CTA loads: 32 rows of a K-major tile (a CTA pair can then cut a 256-wide tail tile into
+// four 64-column slices: +1.7 % on the int8 3840 x 4096 x 4096 GEMM against two 128-column slices, which leave
+// half of the pairs idle during the tail), one whole swizzle atom (128 bytes of N positions) of an N-major one.
+// CKB_MIN_B_ROWS=64 restores the wider minimum for A/B runs.
+int min_b_rows(int dtype, bool b_mn)
+{
+    if(b_mn)
+        return BK_BYTES / elem_bytes(dtype);
+    const char* s = getenv("CKB_MIN_B_ROWS");
+    return (s && atoi(s) == 64) ? 64 : 32;
+}
 
 int pick_bn(int64_t M, int64_t N, int sm_count, int min_bn = 64)
 {
