@@ -111,6 +111,32 @@ def test_gemm_int8_bit_exact(cuda_device, M, N, K):
         np.testing.assert_array_equal(out, H.oracle_gemm(a, bt, op), err_msg=type(op).__name__)
 
 
+@pytest.mark.parametrize("kind", ["int8", "f16"])
+def test_pair_tail_cut_into_four_ragged_column_slices(cuda_device, kind):
+    """2560 x 2000: 80 pair tiles of 256 x 256 on 74 CTA pairs leave 6 tail tiles, each cut into four 64-column
+    slices (32 B rows per CTA); the last column tile has 208 valid columns, so its fourth slice holds 16 of them.
+    A column of canaries beside E (leading dimension 2008) must survive."""
+    rng = np.random.default_rng(2560)
+    M, N, K = 2560, 2000, 320
+    if kind == "int8":
+        a = rng.integers(-5, 6, (M, K)).astype(np.int8)
+        bt = rng.integers(-5, 6, (N, K)).astype(np.int8)
+        op = ck.RequantReluRequantRne(0.03, 14.0)
+        d0 = None
+    else:
+        # a functor that reads a D tensor keeps the column-slice tail (D-less 16-bit GEMMs cut their tail along K)
+        a, bt = H.rand_f16(rng, (M, K), "int"), H.rand_f16(rng, (N, K), "int")
+        op, d0 = ck.AddRelu(), H.rand_f16(rng, (N,), "int")
+    out, _ = H.run_gemm(a, bt, op, d0=d0, lde=N + 8)
+    ref = H.oracle_gemm(a, bt, op, d0=d0)
+    if kind == "int8":
+        np.testing.assert_array_equal(out[:, :N], ref)
+        assert (out[:, N:] == -77).all()
+    else:
+        np.testing.assert_array_equal(out[:, :N].view(np.uint16), ref.view(np.uint16))
+        assert np.isnan(out[:, N:]).all()
+
+
 def test_gemm_int8_full_range_inputs(cuda_device):
     """Full int8 range: accumulators exceed 2^24, PassThrough keeps the low byte of the int32 sum."""
     rng = np.random.default_rng(9)
