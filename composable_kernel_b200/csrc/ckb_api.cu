@@ -782,7 +782,12 @@ static int gemm_run_impl(const ckb_gemm_desc* d, const BatchInfo& bi, void* stre
     if(ks_pays && ks_allowed && rem > 0 && (ful > 0 || whole_ksplit >= 2) && rem * 2 <= G && rem <= 1024)
     {
         // tail: 4 or 2 slices, reduction in column parts of bn / ksplit >= 64 columns; whole problem: up to 8
-        int ksplit = whole_ksplit >= 2 ? whole_ksplit : (G / rem >= 4 && bn >= 256) ? 4 : (bn >= 128 ? 2 : 0);
+        // A 256-wide tail tile is cut four ways along K where a quarter of the units suffice; with more tail tiles only
+        // two K halves fit, and those beat two 128-column slices only for a long K (parking and reduction cost the
+        // same whatever K is, a column slice costs per k block): measured break-even near 78 k blocks
+        // (4096^3: 78.8 us with the K halves, 77.5 us with column slices; 4096 x 4096 x 8192: 160.2 against 165.0 us).
+        int ksplit = whole_ksplit >= 2 ? whole_ksplit
+                                       : (G / rem >= 4 && bn >= 256) ? 4 : ((bn == 128 || (bn >= 256 && num_kb >= 80)) ? 2 : 0);
         int ks_kb  = 0;
         for(; ksplit >= 2; ksplit /= 2)
         {

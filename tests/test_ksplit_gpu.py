@@ -40,7 +40,8 @@ def ints(rng, shape):
 
 @pytest.mark.parametrize("M,N,K,env", [
     (2048, 2560, 1024, {}),                       # 80 pair tiles on 74 pairs: 6 tail tiles, 4 slices
-    (2048, 3328, 512, {}),                        # 104 pair tiles: 30 tail tiles, 2 slices
+    (2048, 3328, 5120, {}),                       # 104 pair tiles: 30 tail tiles, 2 K halves (80 k blocks)
+    (2048, 3328, 512, {}),                        # same tiles, short K: the tail stays with column slices
     (2000, 2500, 1000, {}),                       # ragged M, N (scalar stores) and K
     (2048, 2560, 1024, {"CKB_FORCE_CG": "1"}),    # 160 single-CTA tiles on 148 SMs
     (2048, 2560, 512, {"CKB_FORCE_BN": "128"}),   # 128-wide tiles: 2 slices
