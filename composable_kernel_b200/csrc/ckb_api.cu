@@ -786,8 +786,13 @@ static int gemm_run_impl(const ckb_gemm_desc* d, const BatchInfo& bi, void* stre
         // two K halves fit, and those beat two 128-column slices only for a long K (parking and reduction cost the
         // same whatever K is, a column slice costs per k block): measured break-even near 78 k blocks
         // (4096^3: 78.8 us with the K halves, 77.5 us with column slices; 4096 x 4096 x 8192: 160.2 against 165.0 us).
+        // The four-way cut itself needs a K loop long enough to pay for parking and reduction: 3840 x 4096 x K
+        // with K = 1024 / 2048 / 3072 / 4096 / 6144 took 29.9 / 43.7 / 57.4 / 73.6 / 110.6 us with it and
+        // 25.3 / 42.3 / 58.9 / 76.4 / 115.8 us with four column slices: taken from 40 k blocks on (48 for the
+        // two halves of a 128-wide tile, by the same cost model).
         int ksplit = whole_ksplit >= 2 ? whole_ksplit
-                                       : (G / rem >= 4 && bn >= 256) ? 4 : ((bn == 128 || (bn >= 256 && num_kb >= 80)) ? 2 : 0);
+                     : (G / rem >= 4 && bn >= 256) ? (num_kb >= 40 ? 4 : 0)
+                     : ((bn == 128 && num_kb >= 48) || (bn >= 256 && num_kb >= 80)) ? 2 : 0;
         int ks_kb  = 0;
         for(; ksplit >= 2; ksplit /= 2)
         {

@@ -39,13 +39,14 @@ def ints(rng, shape):
 
 
 @pytest.mark.parametrize("M,N,K,env", [
-    (2048, 2560, 1024, {}),                       # 80 pair tiles on 74 pairs: 6 tail tiles, 4 slices
+    (2048, 2560, 2560, {}),                       # 80 pair tiles on 74 pairs: 6 tail tiles, 4 slices (40 k blocks)
+    (2048, 2560, 1024, {}),                       # same tiles, 16 k blocks: too short for the K split, column slices
     (2048, 3328, 5120, {}),                       # 104 pair tiles: 30 tail tiles, 2 K halves (80 k blocks)
     (2048, 3328, 512, {}),                        # same tiles, short K: the tail stays with column slices
-    (2000, 2500, 1000, {}),                       # ragged M, N (scalar stores) and K
-    (2048, 2560, 1024, {"CKB_FORCE_CG": "1"}),    # 160 single-CTA tiles on 148 SMs
-    (2048, 2560, 512, {"CKB_FORCE_BN": "128"}),   # 128-wide tiles: 2 slices
-    (4096, 4864, 768, {}),                        # several whole waves before the tail
+    (2000, 2500, 2600, {}),                       # ragged M, N (scalar stores) and K
+    (2048, 2560, 2560, {"CKB_FORCE_CG": "1"}),    # 160 single-CTA tiles on 148 SMs
+    (2048, 2560, 3072, {"CKB_FORCE_BN": "128"}),  # 128-wide tiles: 2 slices (48 k blocks)
+    (4096, 4864, 2560, {}),                       # several whole waves before the tail
 ])
 def test_ksplit_tail_bit_exact(cuda_device, M, N, K, env):
     rng = np.random.default_rng(M + N + K)
@@ -61,7 +62,7 @@ def test_ksplit_tail_bit_exact(cuda_device, M, N, K, env):
 
 def test_ksplit_matches_column_slices_and_oracle_on_real_inputs(cuda_device):
     rng = np.random.default_rng(7)
-    M, N, K = 2048, 2560, 1024
+    M, N, K = 2048, 2560, 2560
     a = rng.uniform(-1, 1, (M, K)).astype(np.float16)
     bt = rng.uniform(-1, 1, (N, K)).astype(np.float16)
     op = ck.Relu()
@@ -82,7 +83,7 @@ def test_ksplit_matches_column_slices_and_oracle_on_real_inputs(cuda_device):
 
 def test_ksplit_bf16(cuda_device):
     rng = np.random.default_rng(11)
-    M, N, K = 2048, 2560, 1024
+    M, N, K = 2048, 2560, 2560
     a = oracle.to_bf16(rng.integers(-5, 6, (M, K)).astype(np.float32))
     bt = oracle.to_bf16(rng.integers(-5, 6, (N, K)).astype(np.float32))
     out = run(a, bt, dtype=capi.CKB_BF16)
@@ -92,7 +93,7 @@ def test_ksplit_bf16(cuda_device):
 def test_ksplit_on_two_streams_at_once(cuda_device):
     """Each stream has its own scratch: interleaved launches of two different problems stay correct."""
     rng = np.random.default_rng(13)
-    shapes = [(2048, 2560, 1024), (2048, 3328, 512)]
+    shapes = [(2048, 2560, 2560), (2048, 3328, 5120)]
     streams = [torch.cuda.Stream(), torch.cuda.Stream()]
     ins = [(ints(rng, (M, K)), ints(rng, (N, K))) for M, N, K in shapes]
     keep, outs, args = [], [], []
@@ -114,10 +115,10 @@ def test_ksplit_on_two_streams_at_once(cuda_device):
 
 
 def test_ksplit_tail_of_a_batched_gemm_spans_batches(cuda_device):
-    """Batched GEMM whose tail tiles belong to different batches: 40 batches of 512 x 512 x 512 are 160 pair tiles on
-    74 pairs (148 whole, 12 tail tiles cut in four along K)."""
+    """Batched GEMM whose tail tiles belong to different batches: 40 batches of 512 x 512 x 2560 are 160 pair tiles on
+    74 pairs (148 whole, 12 tail tiles cut in four along K: 40 k blocks, the shortest K loop that takes the split)."""
     rng = np.random.default_rng(17)
-    G, M, N, K = 40, 512, 512, 512
+    G, M, N, K = 40, 512, 512, 2560
     a, bt = ints(rng, (G, M, K)), ints(rng, (G, N, K))
     da, db = torch.from_numpy(a).cuda(), torch.from_numpy(bt).cuda()
     e = torch.zeros((G, M, N), dtype=torch.float16, device="cuda")
