@@ -25,6 +25,12 @@ CKB_ROW_MAJOR, CKB_COL_MAJOR = 0, 1
  CKB_EPI_ADD_HARDSWISH) = range(13)
 CKB_MAX_DS = 2
 CKB_NOALLOC_MAX_GROUPS = 256
+CKB_ABI_VERSION = 2
+
+
+def tile_config(bn: int = 0, cg: int = 0, no_ksplit: int = 0) -> int:
+    """CKB_TILE_CONFIG(bn, cg, no_ksplit) of include/ckb200.h; 0 = the library's own choice."""
+    return bn | (cg << 12) | (no_ksplit << 16)
 
 EPI_NUM_D = {CKB_EPI_ADD: 1, CKB_EPI_ADD_RELU_F16: 1, CKB_EPI_BILINEAR: 1, CKB_EPI_ADD_RELU: 1,
              CKB_EPI_ADD_HARDSWISH: 1, CKB_EPI_ADD_ADD_FASTGELU: 2, CKB_EPI_ADD_RELU_ADD: 2}
@@ -35,7 +41,7 @@ class GemmDesc(Structure):
     _fields_ = [
         ("ab_dtype", c_int32), ("e_dtype", c_int32),
         ("a_layout", c_int32), ("b_layout", c_int32), ("e_layout", c_int32),
-        ("epilogue", c_int32), ("n_ds", c_int32), ("reserved0", c_int32),
+        ("epilogue", c_int32), ("n_ds", c_int32), ("tile_config", c_int32),
         ("M", c_int64), ("N", c_int64), ("K", c_int64),
         ("lda", c_int64), ("ldb", c_int64), ("lde", c_int64),
         ("ldd", c_int64 * CKB_MAX_DS),
@@ -54,7 +60,7 @@ class BatchedGemmDesc(Structure):
 
 class GroupedGemmDesc(Structure):
     """struct ckb_grouped_gemm_desc"""
-    _fields_ = [("group_count", c_int32), ("reserved0", c_int32), ("groups", POINTER(GemmDesc))]
+    _fields_ = [("group_count", c_int32), ("tile_config", c_int32), ("groups", POINTER(GemmDesc))]
 
 
 class Conv2dFwdDesc(Structure):
@@ -68,7 +74,7 @@ class Conv2dFwdDesc(Structure):
         ("dilation_h", c_int32), ("dilation_w", c_int32),
         ("pad_h", c_int32), ("pad_w", c_int32),
         ("pad_h_right", c_int32), ("pad_w_right", c_int32),
-        ("reserved0", c_int32),
+        ("tile_config", c_int32),
         ("p_in", c_void_p), ("p_wei", c_void_p), ("p_out", c_void_p),
         ("p_bias", c_void_p), ("p_resi", c_void_p),
         ("epi_params", c_float * 4),
@@ -87,7 +93,7 @@ class Conv3dFwdDesc(Structure):
         ("dilation_d", c_int32), ("dilation_h", c_int32), ("dilation_w", c_int32),
         ("pad_d", c_int32), ("pad_h", c_int32), ("pad_w", c_int32),
         ("pad_d_right", c_int32), ("pad_h_right", c_int32), ("pad_w_right", c_int32),
-        ("reserved0", c_int32),
+        ("tile_config", c_int32),
         ("p_in", c_void_p), ("p_wei", c_void_p), ("p_out", c_void_p),
         ("p_bias", c_void_p), ("p_resi", c_void_p),
         ("epi_params", c_float * 4),

@@ -113,6 +113,15 @@ int current_device(DeviceInfo** out)
         cudaDeviceProp prop;
         CKB_CUDA(cudaGetDeviceProperties(&prop, dev));
         d.sm_count = prop.multiProcessorCount;
+        // A process that may use only part of the GPU (an MPS active-thread percentage, a green context) says so
+        // with CKB_SM_LIMIT: the K-split plans let units wait for one another, so every unit of a launch has to be
+        // resident at the same time, and the runtime reports the whole device whatever the partition is.
+        if(const char* lim = getenv("CKB_SM_LIMIT"))
+        {
+            const int n = atoi(lim) & ~1;
+            if(n >= 2 && n < d.sm_count)
+                d.sm_count = n;
+        }
         d.cc_major = prop.major;
         d.cc_minor = prop.minor;
         if(prop.major != 10)
@@ -121,9 +130,8 @@ int current_device(DeviceInfo** out)
                         prop.name, prop.major, prop.minor);
         void* sym = nullptr;
         CKB_CUDA(cudaGetSymbolAddress(&sym, g_status_word));
-        d.status = static_cast<uint32_t*>(sym);
-        CKB_CUDA(cudaMemset(d.status, 0, sizeof(uint32_t)));
-        d.ready = true;
+        d.status = static_cast<uint32_t*>(sym); // a __device__ variable: zero when the module is loaded
+        d.ready  = true;
     }
     *out = &d;
     return CKB_OK;
@@ -141,24 +149,27 @@ bool stream_is_capturing(cudaStream_t stream)
     return st != cudaStreamCaptureStatusNone;
 }
 
-constexpr size_t kScratchCounterBytes = 4096; // 1024 tail-tile counters at the front of a scratch buffer
+constexpr size_t kScratchCounterBytes = kMaxTailTiles * sizeof(uint32_t); // tail-tile counters at the front
 
-// Grow-only scratch of `stream` with room for `bytes` after the counters; nullptr when the device has no memory
-// left for it (the caller then falls back to a plan that needs none).  The counters are zero on return the
-// first time and are left at zero by every kernel that uses them.
+// Scratch of `stream` for the K-split plans; nullptr when the device has no memory left for it or the stream is
+// capturing (the caller then keeps a plan that needs none).  Every K-split plan parks at most one accumulator tile
+// per unit (tail tiles x slices <= units), so the buffer is sized once for that worst case - counters + SMs x 128
+// KiB, 19 MB on a B200 - and never grows: no later call frees or allocates.  The counters are zeroed on the stream
+// that will use them (ordered before the first kernel that reads them, also on non-blocking streams) and are left
+// at zero by every kernel.
 void* scratch_for(DeviceInfo* dev, cudaStream_t stream, size_t bytes)
 {
     std::lock_guard<std::mutex> lock(g_dev_mutex);
-    Scratch& sc       = dev->scratch[stream];
-    const size_t need = kScratchCounterBytes + bytes;
     // A launch that is being captured into a graph gets no scratch: the graph may be replayed on any stream,
     // next to other launches that use this stream's buffer, and a capture must not see an allocation either.
-    // The caller then keeps the plan that needs none.
     if(stream_is_capturing(stream))
         return nullptr;
+    Scratch& sc            = dev->scratch[stream];
+    const size_t worst     = static_cast<size_t>(dev->sm_count) * BM * 256 * sizeof(uint32_t);
+    const size_t need      = kScratchCounterBytes + (bytes > worst ? bytes : worst);
     if(sc.bytes >= need)
         return sc.ptr;
-    if(sc.ptr)
+    if(sc.ptr) // only reachable if a plan ever parks more than one tile per unit
     {
         cudaFree(sc.ptr); // synchronises: no kernel is still using the old buffer
         sc.ptr   = nullptr;
@@ -170,8 +181,9 @@ void* scratch_for(DeviceInfo* dev, cudaStream_t stream, size_t bytes)
         cudaGetLastError();
         return nullptr;
     }
-    if(cudaMemset(ptr, 0, kScratchCounterBytes) != cudaSuccess)
+    if(cudaMemsetAsync(ptr, 0, kScratchCounterBytes, stream) != cudaSuccess)
     {
+        cudaGetLastError();
         cudaFree(ptr);
         return nullptr;
     }
@@ -192,10 +204,45 @@ uint64_t wait_limit_ns()
     return v;
 }
 
-int forced_bn()
+// Test hook: CKB_TEST_KSLICE_WAIT_EXTRA=n makes the reductions of the K-split plans wait for n arrivals more than
+// will ever come, so that the bounded wait runs out (with a short CKB_WAIT_LIMIT_MS) and the give-up path executes.
+uint32_t test_kslice_wait_extra()
 {
+    const char* s = getenv("CKB_TEST_KSLICE_WAIT_EXTRA");
+    return s ? static_cast<uint32_t>(atoi(s)) : 0u;
+}
+
+// Tile configuration of a call: the descriptor's tile_config field when it is set, else the environment overrides
+// CKB_FORCE_BN / CKB_FORCE_CG / CKB_NO_SPLITK (read at every call), else all zero = the library decides.
+int check_tile_config(int32_t tc)
+{
+    const int bn = tc & 0xFFF, cg = (tc >> 12) & 0xF, rest = tc >> 17;
+    if(tc < 0 || rest != 0 || !(bn == 0 || bn == 64 || bn == 128 || bn == 256) || cg > 2)
+        return fail(CKB_ERR_INVALID, "tile_config 0x%x is not a CKB_TILE_CONFIG(bn, cg, no_ksplit) value", tc);
+    if(cg == 2 && bn != 256 && bn != 0)
+        return fail(CKB_ERR_UNSUPPORTED, "a CTA pair (cg = 2) works on 256-wide tiles only");
+    return CKB_OK;
+}
+
+TileConfig tile_config_of(int32_t tc)
+{
+    TileConfig t;
+    if(tc != 0)
+    {
+        t.bn        = tc & 0xFFF;
+        t.cg        = (tc >> 12) & 0xF;
+        t.no_ksplit = (tc >> 16) & 1;
+        return t;
+    }
     const char* s = getenv("CKB_FORCE_BN");
-    return s ? atoi(s) : 0;
+    const int bn  = s ? atoi(s) : 0;
+    t.bn          = (bn == 64 || bn == 128 || bn == 256) ? bn : 0;
+    s             = getenv("CKB_FORCE_CG");
+    const int cg  = s ? atoi(s) : 0;
+    t.cg          = (cg == 1 || cg == 2) ? cg : 0;
+    s             = getenv("CKB_NO_SPLITK");
+    t.no_ksplit   = (s && atoi(s) != 0) ? 1 : 0;
+    return t;
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -209,26 +256,75 @@ CUtensorMapDataType tm_dtype(int dtype)
                                                : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
 }
 
+// cuTensorMapEncodeTiled behind a small per-thread cache.  A tensor map is a pure function of the arguments below,
+// and callers launch the same problem again and again (a timing loop, a layer executed every step): a hit copies
+// 128 bytes instead of calling into the driver (about a microsecond per map, four maps per GEMM).
+struct TiledKey
+{
+    const void* ptr;
+    uint64_t dims[3], strides[2];
+    uint32_t box[3];
+    int32_t dtype, rank, swizzle, promo;
+};
+struct TiledEntry
+{
+    TiledKey key;
+    CUtensorMap map;
+    bool used;
+};
+constexpr int kTiledCacheSize = 32;
+thread_local TiledEntry t_tiled_cache[kTiledCacheSize];
+thread_local int t_tiled_next = 0;
+
+int encode_tiled(CUtensorMap* tm, int dtype, int rank, const void* ptr, const cuuint64_t* dims, const cuuint64_t* strides,
+                 const cuuint32_t* box, CUtensorMapSwizzle swizzle, CUtensorMapL2promotion promo, const char* what)
+{
+    load_entry_points();
+    if(!g_encode_tiled)
+        return fail(CKB_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+    TiledKey key;
+    memset(&key, 0, sizeof(key));
+    key.ptr = ptr;
+    for(int i = 0; i < rank; ++i)
+    {
+        key.dims[i] = dims[i];
+        key.box[i]  = box[i];
+        if(i + 1 < rank)
+            key.strides[i] = strides[i];
+    }
+    key.dtype = dtype, key.rank = rank, key.swizzle = swizzle, key.promo = promo;
+    for(const TiledEntry& e : t_tiled_cache)
+        if(e.used && memcmp(&e.key, &key, sizeof(key)) == 0)
+        {
+            *tm = e.map;
+            return CKB_OK;
+        }
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = g_encode_tiled(tm, tm_dtype(dtype), rank, const_cast<void*>(ptr), dims, strides, box, estr,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if(r != CUDA_SUCCESS)
+        return fail(CKB_ERR_CUDA, "cuTensorMapEncodeTiled (%s) failed (CUresult %d): dims %llu x %llu x %llu, pitch %llu B",
+                    what, static_cast<int>(r), (unsigned long long)key.dims[0], (unsigned long long)key.dims[1],
+                    (unsigned long long)key.dims[2], (unsigned long long)key.strides[0]);
+    TiledEntry& slot = t_tiled_cache[t_tiled_next];
+    t_tiled_next     = (t_tiled_next + 1) % kTiledCacheSize;
+    slot.key         = key;
+    slot.map         = *tm;
+    slot.used        = true;
+    return CKB_OK;
+}
+
 // K-major matrix [rows][k] with row pitch `ld` elements -> 2-D map, box = 128 bytes x box_rows.
 // batch >= 1 adds a third dimension of `batch` matrices `batch_stride` elements apart (box extent 1).
 int encode_kmajor_2d(CUtensorMap* tm, int dtype, const void* ptr, int64_t rows, int64_t k,
                      int64_t ld, int box_rows, int64_t batch = 0, int64_t batch_stride = 0)
 {
-    load_entry_points();
-    if(!g_encode_tiled)
-        return fail(CKB_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
     const int eb          = elem_bytes(dtype);
     cuuint64_t dims[3]    = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(batch)};
     cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * eb, static_cast<cuuint64_t>(batch_stride) * eb};
     cuuint32_t box[3]     = {static_cast<cuuint32_t>(BK_BYTES / eb), static_cast<cuuint32_t>(box_rows), 1};
-    cuuint32_t estr[3]    = {1, 1, 1};
-    CUresult r            = g_encode_tiled(tm, tm_dtype(dtype), batch >= 1 ? 3 : 2, const_cast<void*>(ptr), dims, strides,
-                                box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if(r != CUDA_SUCCESS)
-        return fail(CKB_ERR_CUDA, "cuTensorMapEncodeTiled failed (CUresult %d) rows=%lld k=%lld ld=%lld",
-                    static_cast<int>(r), (long long)rows, (long long)k, (long long)ld);
-    return CKB_OK;
+    return encode_tiled(tm, dtype, batch >= 1 ? 3 : 2, ptr, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, "K-major operand");
 }
 
 // MN-major matrix (the M or N index contiguous, pitch `ld` elements between consecutive k) -> 2-D map
@@ -236,21 +332,12 @@ int encode_kmajor_2d(CUtensorMap* tm, int dtype, const void* ptr, int64_t rows, 
 int encode_mnmajor_2d(CUtensorMap* tm, int dtype, const void* ptr, int64_t mn, int64_t k, int64_t ld,
                       int64_t batch = 0, int64_t batch_stride = 0)
 {
-    load_entry_points();
-    if(!g_encode_tiled)
-        return fail(CKB_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
     const int eb          = elem_bytes(dtype);
     cuuint64_t dims[3]    = {static_cast<cuuint64_t>(mn), static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(batch)};
     cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * eb, static_cast<cuuint64_t>(batch_stride) * eb};
     cuuint32_t box[3]     = {static_cast<cuuint32_t>(BK_BYTES / eb), static_cast<cuuint32_t>(BK_BYTES / eb), 1};
-    cuuint32_t estr[3]    = {1, 1, 1};
-    CUresult r            = g_encode_tiled(tm, tm_dtype(dtype), batch >= 1 ? 3 : 2, const_cast<void*>(ptr), dims, strides,
-                                box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if(r != CUDA_SUCCESS)
-        return fail(CKB_ERR_CUDA, "cuTensorMapEncodeTiled failed (CUresult %d) mn=%lld k=%lld ld=%lld",
-                    static_cast<int>(r), (long long)mn, (long long)k, (long long)ld);
-    return CKB_OK;
+    return encode_tiled(tm, dtype, batch >= 1 ? 3 : 2, ptr, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, "MN-major operand");
 }
 
 // E (M x N row-major, pitch `lde` elements) as the (columns, rows[, batch]) map of the epilogue's staged stores:
@@ -259,22 +346,13 @@ int encode_mnmajor_2d(CUtensorMap* tm, int dtype, const void* ptr, int64_t mn, i
 int encode_e_map(CUtensorMap* tm, int dtype, const void* ptr, int64_t m, int64_t n, int64_t lde, int64_t batch = 0,
                  int64_t batch_stride = 0)
 {
-    load_entry_points();
-    if(!g_encode_tiled)
-        return fail(CKB_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
     const int eb          = elem_bytes(dtype);
     cuuint64_t dims[3]    = {static_cast<cuuint64_t>(n), static_cast<cuuint64_t>(m), static_cast<cuuint64_t>(batch)};
     cuuint64_t strides[2] = {static_cast<cuuint64_t>(lde) * eb, static_cast<cuuint64_t>(batch_stride) * eb};
     cuuint32_t box[3]     = {32, 32, 1};
-    cuuint32_t estr[3]    = {1, 1, 1};
-    CUresult r = g_encode_tiled(tm, tm_dtype(dtype), batch >= 1 ? 3 : 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                                CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                eb == 1 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B,
-                                CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if(r != CUDA_SUCCESS)
-        return fail(CKB_ERR_CUDA, "cuTensorMapEncodeTiled (E) failed (CUresult %d) m=%lld n=%lld lde=%lld",
-                    static_cast<int>(r), (long long)m, (long long)n, (long long)lde);
-    return CKB_OK;
+    return encode_tiled(tm, dtype, batch >= 1 ? 3 : 2, ptr, dims, strides, box,
+                        eb == 1 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                        "E");
 }
 
 // A is M x K: row-major = K-major, column-major = M-major.  B is K x N: column-major = K-major,
@@ -293,72 +371,7 @@ int encode_operand(CUtensorMap* tm, int dtype, const void* ptr, int64_t mn, int6
 // Narrowest B slice one CTA loads: 32 rows of a K-major tile (a CTA pair can then cut a 256-wide tail tile into
 // four 64-column slices: +1.7 % on the int8 3840 x 4096 x 4096 GEMM against two 128-column slices, which leave
 // half of the pairs idle during the tail), one whole swizzle atom (128 bytes of N positions) of an N-major one.
-// CKB_MIN_B_ROWS=64 restores the wider minimum for A/B runs.
-int min_b_rows(int dtype, bool b_mn)
-{
-    if(b_mn)
-        return BK_BYTES / elem_bytes(dtype);
-    const char* s = getenv("CKB_MIN_B_ROWS");
-    return (s && atoi(s) == 64) ? 64 : 32;
-}
-
-int pick_bn(int64_t M, int64_t N, int sm_count, int min_bn = 64)
-{
-    const int f = forced_bn();
-    if((f == 256 || f == 128 || f == 64) && f >= min_bn)
-        return f;
-    if(N <= 64 && min_bn <= 64)
-        return 64;
-    if(N <= 128)
-        return 128;
-    // Prefer the 256-wide tile (lowest shared-memory traffic per flop) unless it leaves most of
-    // the machine idle.
-    const int64_t tiles256 = ((M + BM - 1) / BM) * ((N + 255) / 256);
-    if(tiles256 < sm_count / 2)
-        return 128;
-    return 256;
-}
-
-// Splits the last, partial wave of tiles into column slices so that it occupies every SM
-// (see "Work items" in ckb_kernel.cuh).  Slices are at least 64 columns wide.
-struct WorkPlan
-{
-    int32_t split_start, split, total_work, grid;
-};
-
-// `units` = CTAs (one CTA per tile) or CTA pairs (cg = 2) that run concurrently.
-WorkPlan plan_work(int64_t total_tiles, int units, int bn, int cg, int min_rows = 64)
-{
-    WorkPlan w;
-    const int64_t G    = units;
-    const int64_t full = (total_tiles / G) * G;
-    const int64_t rem  = total_tiles - full;
-    int split          = 1;
-    const char* env    = getenv("CKB_NO_TAIL_SPLIT");
-    if(rem > 0 && !(env && atoi(env) != 0))
-    {
-        // slices of >= 64 columns whose per-CTA share is >= min_rows: K-major 256 -> 4, 128 -> 2, 64 -> 1
-        const int min_width = min_rows * cg > 64 ? min_rows * cg : 64;
-        const int max_split = bn / min_width;
-        while(split * 2 <= max_split && rem * split * 2 <= G)
-            split *= 2;
-    }
-    w.split       = split;
-    w.split_start = static_cast<int32_t>(split > 1 ? full : total_tiles);
-    w.total_work  = static_cast<int32_t>(split > 1 ? full + rem * split : total_tiles);
-    w.grid        = static_cast<int32_t>((w.total_work < G ? w.total_work : G) * cg);
-    return w;
-}
-
-// CTAs per tile: pairs (256 x 256 tiles, tcgen05 cta_group::2) once the problem fills the machine
-// with 128 x 256 tiles at least once; single CTAs for small problems.
-int pick_cg(int64_t tiles_128, int bn, int sm_count)
-{
-    const char* s = getenv("CKB_FORCE_CG");
-    if(s && (atoi(s) == 1 || atoi(s) == 2))
-        return bn == 256 ? atoi(s) : 1;
-    return (bn == 256 && tiles_128 >= sm_count) ? 2 : 1;
-}
+int min_b_rows(int dtype, bool b_mn) { return b_mn ? BK_BYTES / elem_bytes(dtype) : 32; }
 
 int kind_of(int dtype) { return dtype == CKB_I8 ? KIND_I8 : dtype == CKB_BF16 ? KIND_BF16 : KIND_F16; }
 
@@ -375,8 +388,9 @@ bool epilogue_valid_for(int epi, int ab_dtype)
     return epi != CKB_EPI_REQUANT_RELU_REQUANT && epi != CKB_EPI_REQUANT_RELU_REQUANT_RNE;
 }
 
-// Shared validation of one GEMM problem.  `why` receives the reason on failure.
-int check_gemm(const ckb_gemm_desc* d, bool need_pointers)
+// Shared validation of one GEMM problem.  strict_tma: A and B must be readable by TMA in place (16-byte aligned
+// base and pitch) - the rule of the batched and grouped entry points; the plain GEMM copies such operands first.
+int check_gemm(const ckb_gemm_desc* d, bool need_pointers, bool strict_tma)
 {
     if(!d)
         return fail(CKB_ERR_INVALID, "null descriptor");
@@ -401,8 +415,10 @@ int check_gemm(const ckb_gemm_desc* d, bool need_pointers)
     const int eb = elem_bytes(d->ab_dtype);
     if(d->lda < (a_is_mn_major(d) ? d->M : d->K) || d->ldb < (b_is_mn_major(d) ? d->N : d->K) || d->lde < d->N)
         return fail(CKB_ERR_INVALID, "leading dimension smaller than the row length");
-    if((d->lda * eb) % 16 != 0 || (d->ldb * eb) % 16 != 0)
+    if(strict_tma && ((d->lda * eb) % 16 != 0 || (d->ldb * eb) % 16 != 0))
         return fail(CKB_ERR_UNSUPPORTED, "lda and ldb must be multiples of 16 bytes (TMA row pitch)");
+    if(int rc = check_tile_config(d->tile_config))
+        return rc;
     for(int i = 0; i < d->n_ds; ++i)
         if(d->ldd[i] != 0 && d->ldd[i] < d->N)
             return fail(CKB_ERR_INVALID, "ldd[%d] smaller than N", i);
@@ -410,8 +426,10 @@ int check_gemm(const ckb_gemm_desc* d, bool need_pointers)
     {
         if(!d->p_a || !d->p_b || !d->p_e)
             return fail(CKB_ERR_INVALID, "null tensor pointer");
-        if(!aligned16(d->p_a) || !aligned16(d->p_b))
+        if(strict_tma && (!aligned16(d->p_a) || !aligned16(d->p_b)))
             return fail(CKB_ERR_UNSUPPORTED, "A and B must be 16-byte aligned");
+        if((reinterpret_cast<uintptr_t>(d->p_a) | reinterpret_cast<uintptr_t>(d->p_b)) % eb != 0)
+            return fail(CKB_ERR_INVALID, "A or B is not aligned to its element size");
         for(int i = 0; i < d->n_ds; ++i)
             if(!d->p_ds[i])
                 return fail(CKB_ERR_INVALID, "null D%d pointer", i);
@@ -460,30 +478,82 @@ unsigned long long* trace_buffer()
 #endif
 }
 
-// CKB_STORE_DIRECT=1 makes every kernel write E with 128-bit global stores instead of the staged TMA stores.
-int store_direct_forced()
+// Work that has to run on the stream before the contraction kernel of the same call: pitch-fixing copies of
+// operands that TMA cannot read in place (see repack_pitch_kernel).  Part of every timed repetition.
+struct Repack
 {
-    const char* s = getenv("CKB_STORE_DIRECT");
-    return s ? atoi(s) : -1;
+    const void* src;
+    void* dst;
+    int64_t outer, inner, ld_src, ld_dst;
+    int elem_bytes;
+};
+
+// Copies an [outer][inner] matrix with pitch ld_src (any alignment) into one with pitch ld_dst (a multiple of 16
+// bytes, base 16-byte aligned) and writes zeros into the padding.  One thread per 16 bytes of the destination.
+template <typename T>
+__global__ void repack_pitch_kernel(const T* __restrict__ src, T* __restrict__ dst, int64_t outer, int64_t inner,
+                                    int64_t ld_src, int64_t ld_dst)
+{
+    constexpr int PER = 16 / sizeof(T);
+    const int64_t vec_per_row = ld_dst / PER;
+    const int64_t total       = outer * vec_per_row;
+    for(int64_t v = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; v < total;
+        v += static_cast<int64_t>(gridDim.x) * blockDim.x)
+    {
+        const int64_t row = v / vec_per_row, col0 = (v - row * vec_per_row) * PER;
+        alignas(16) T tmp[PER];
+#pragma unroll
+        for(int i = 0; i < PER; ++i)
+            tmp[i] = col0 + i < inner ? src[row * ld_src + col0 + i] : T(0);
+        *reinterpret_cast<uint4*>(dst + row * ld_dst + col0) = *reinterpret_cast<const uint4*>(tmp);
+    }
 }
 
+cudaError_t launch_repack(const Repack& r, cudaStream_t stream)
+{
+    const int64_t vecs = r.outer * (r.ld_dst * r.elem_bytes / 16);
+    if(vecs <= 0)
+        return cudaSuccess;
+    const int threads = 256;
+    const int64_t want = (vecs + threads - 1) / threads;
+    const int blocks   = static_cast<int>(want < 148 * 16 ? want : 148 * 16);
+    if(r.elem_bytes == 1)
+        repack_pitch_kernel<int8_t><<<blocks, threads, 0, stream>>>(static_cast<const int8_t*>(r.src),
+                                                                    static_cast<int8_t*>(r.dst), r.outer, r.inner,
+                                                                    r.ld_src, r.ld_dst);
+    else
+        repack_pitch_kernel<uint16_t><<<blocks, threads, 0, stream>>>(static_cast<const uint16_t*>(r.src),
+                                                                      static_cast<uint16_t*>(r.dst), r.outer, r.inner,
+                                                                      r.ld_src, r.ld_dst);
+    return cudaGetLastError();
+}
+
+// One launch, or the reference timing protocol (kernel_launch.hpp:12-74): a warm-up launch, then n_rep launches
+// between two events.  `pre` / `n_pre`: copies that belong to the call and run before the kernel every time.
 int run_timed(LaunchFn fn, int bn, int cg, const KernelParams& p_in, int grid, cudaStream_t stream, int n_rep,
-              float* avg_ms)
+              float* avg_ms, const Repack* pre = nullptr, int n_pre = 0)
 {
     KernelParams p = p_in;
     p.trace        = trace_buffer();
-    if(store_direct_forced() >= 0)
-        p.store_direct = store_direct_forced();
     if(avg_ms)
         *avg_ms = 0.f;
+    auto once = [&]() -> cudaError_t {
+        for(int i = 0; i < n_pre; ++i)
+        {
+            cudaError_t e = launch_repack(pre[i], stream);
+            if(e != cudaSuccess)
+                return e;
+        }
+        return fn(bn, cg, p, grid, stream);
+    };
     if(n_rep <= 0)
     {
-        CKB_CUDA(fn(bn, cg, p, grid, stream));
-        g_launches.fetch_add(1);
+        CKB_CUDA(once());
+        g_launches.fetch_add(1 + n_pre);
         return CKB_OK;
     }
-    CKB_CUDA(fn(bn, cg, p, grid, stream)); // warm-up
-    g_launches.fetch_add(1);
+    CKB_CUDA(once()); // warm-up
+    g_launches.fetch_add(1 + n_pre);
     cudaEvent_t start, stop;
     CKB_CUDA(cudaEventCreate(&start));
     CKB_CUDA(cudaEventCreate(&stop));
@@ -491,7 +561,7 @@ int run_timed(LaunchFn fn, int bn, int cg, const KernelParams& p_in, int grid, c
     CKB_CUDA(cudaEventRecord(start, stream));
     for(int i = 0; i < n_rep; ++i)
     {
-        cudaError_t e = fn(bn, cg, p, grid, stream);
+        cudaError_t e = once();
         if(e != cudaSuccess)
         {
             cudaEventDestroy(start);
@@ -499,7 +569,7 @@ int run_timed(LaunchFn fn, int bn, int cg, const KernelParams& p_in, int grid, c
             return fail(CKB_ERR_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
         }
     }
-    g_launches.fetch_add(n_rep);
+    g_launches.fetch_add(static_cast<uint64_t>(n_rep) * (1 + n_pre));
     CKB_CUDA(cudaEventRecord(stop, stream));
     CKB_CUDA(cudaEventSynchronize(stop));
     float total = 0.f;
@@ -510,6 +580,21 @@ int run_timed(LaunchFn fn, int bn, int cg, const KernelParams& p_in, int grid, c
         *avg_ms = total / n_rep;
     return CKB_OK;
 }
+
+// Stream-ordered temporary for repacked operands: allocated and freed on the call's stream (cudaMallocAsync /
+// cudaFreeAsync from the device's default pool), so neither end synchronises the device.
+struct StreamTemp
+{
+    void* ptr = nullptr;
+    cudaStream_t stream = nullptr;
+    ~StreamTemp()
+    {
+        if(ptr)
+            cudaFreeAsync(ptr, stream);
+    }
+};
+
+bool tma_readable(const void* p, int64_t ld, int eb) { return aligned16(p) && (ld * eb) % 16 == 0; }
 
 } // namespace
 
@@ -587,10 +672,14 @@ int ckb_device_status(uint32_t* word)
     {
         CKB_CUDA(cudaMemset(dev->status, 0, sizeof(w)));
         // a kernel that gave up may have left tail-tile counters of the K-split scratch half way
-        std::lock_guard<std::mutex> lock(g_dev_mutex);
-        for(auto& kv : dev->scratch)
-            if(kv.second.ptr)
-                cudaMemset(kv.second.ptr, 0, kScratchCounterBytes);
+        {
+            std::lock_guard<std::mutex> lock2(g_dev_mutex);
+            for(auto& kv : dev->scratch)
+                if(kv.second.ptr)
+                    cudaMemset(kv.second.ptr, 0, kScratchCounterBytes);
+        }
+        // the zeroing above runs on the legacy default stream: finish it before the caller launches on any other
+        CKB_CUDA(cudaDeviceSynchronize());
     }
     if(word)
         *word = w;
@@ -661,7 +750,7 @@ int ckb_release_scratch(void* stream, int all_streams)
 }
 
 // ---- GEMM ---------------------------------------------------------------------------------------
-int ckb_gemm_supported(const ckb_gemm_desc* desc) { return check_gemm(desc, false); }
+int ckb_gemm_supported(const ckb_gemm_desc* desc) { return check_gemm(desc, false, false); }
 
 // Strides between the matrices of a batch (elements); batch = 0 for a plain GEMM.
 struct BatchInfo
@@ -670,179 +759,112 @@ struct BatchInfo
     bool vec_ok; // every batch of E / D keeps the 16-byte alignment of the first
 };
 
-// Whole-problem K split.  A GEMM with few output tiles and a long K leaves most SMs idle whatever the tile shape;
-// cutting every tile's K loop into 2 or 4 slices (the machinery of the K-split tail, with no whole tiles before
-// it) puts 2-8 times as many SMs to work on full-width MMAs.  Cycle estimates per k block, fitted to timings of
-// 1024 x 1024 x K and 512 x 512 x K with and without the split: 590 for 256 accumulator columns, 340 for 128,
-// 315 for 64 (the narrow ones are bound by the issue rate of the single MMA thread, not by the tensor pipe);
-// parking and summing the slices costs about 9100 cycles (5.5 us), most of it the exposed latency of the
-// reduction's loads.
-struct WholeSplit
-{
-    int bn = 0, cg = 0, ksplit = 0;
-};
-
-int kb_cycles(int width) { return width >= 256 ? 590 : width >= 128 ? 340 : 315; }
-
-WholeSplit consider_whole_split(int64_t M, int64_t N, int num_kb, int sm_count, int b_min, int64_t est_current)
-{
-    WholeSplit best;
-    int64_t best_est = est_current - est_current / 8; // has to beat the plan without it by an eighth
-    const int cand[3][2] = {{256, 2}, {256, 1}, {128, 1}};
-    for(const auto& c : cand)
-    {
-        const int bn = c[0], cg = c[1];
-        if(bn / cg < b_min || (cg == 2 && M <= BM)) // a pair tile with one half of its rows empty pays for nothing
-            continue;
-        const int64_t G     = sm_count / cg;
-        const int64_t tiles = ((M + BM * cg - 1) / (BM * cg)) * ((N + bn - 1) / bn);
-        for(int ks = bn / 32; ks >= 2; ks /= 2) // column parts of the reduction are whole 32-column chunks
-        {
-            if(tiles * ks > G)
-                continue;
-            int ks_kb = (num_kb + ks - 1) / ks;
-            ks_kb     = (ks_kb + 1) & ~1;
-            if(ks_kb < 4 || static_cast<int64_t>(ks - 1) * ks_kb >= num_kb)
-                continue;
-            const int64_t est = static_cast<int64_t>(ks_kb) * kb_cycles(bn) + 9100 + (ks > 4 ? 1500 : 0);
-            if(est < best_est)
-            {
-                best_est    = est;
-                best.bn     = bn;
-                best.cg     = cg;
-                best.ksplit = ks;
-            }
-        }
-    }
-    return best;
-}
-
-static int gemm_run_impl(const ckb_gemm_desc* d, const BatchInfo& bi, void* stream, int n_rep, float* avg_ms)
+static int gemm_run_impl(const ckb_gemm_desc* d_in, const BatchInfo& bi, void* stream_, int n_rep, float* avg_ms)
 {
     int rc = CKB_OK;
     DeviceInfo* dev = nullptr;
     rc              = current_device(&dev);
     if(rc)
         return rc;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    ckb_gemm_desc dd    = *d_in;
+    const ckb_gemm_desc* d = &dd;
     const bool a_mn  = a_is_mn_major(d), b_mn = b_is_mn_major(d);
-    const int b_min  = min_b_rows(d->ab_dtype, b_mn);
-    int bn           = pick_bn(d->M, d->N, dev->sm_count, b_min);
     const int eb     = elem_bytes(d->ab_dtype);
-    KernelParams p;
-    memset(&p, 0, sizeof(p));
-    rc = encode_operand(&p.tm_a, d->ab_dtype, d->p_a, d->M, d->K, d->lda, a_mn, BM, bi.batch, bi.stride_a);
-    if(rc)
-        return rc;
-    fill_epilogue(p.epi, d);
-    const int64_t nb      = bi.batch > 0 ? bi.batch : 1;
-    int cg                = pick_cg(((d->M + BM - 1) / BM) * ((d->N + bn - 1) / bn) * nb, bn, dev->sm_count);
-    const int bk          = BK_BYTES / eb;
-    const int num_kb      = static_cast<int>((d->K + bk - 1) / bk);
-    const char* no_ks     = getenv("CKB_NO_SPLITK");
-    const bool ks_allowed = !(no_ks && atoi(no_ks) != 0);
+    const bool capturing = stream_is_capturing(stream);
+
+    // Operands whose base or pitch is not a multiple of 16 bytes cannot be read by TMA in place: they are copied
+    // into a stream-ordered temporary with a padded pitch first (the reference serves such problems with its
+    // scalar-load instances, ABlockTransferSrcScalarPerVector = 1).  The copy is part of the call and of its timing.
+    Repack pre[2];
+    int n_pre = 0;
+    StreamTemp temp;
+    temp.stream = stream;
+    {
+        const bool a_bad = !tma_readable(d->p_a, d->lda, eb), b_bad = !tma_readable(d->p_b, d->ldb, eb);
+        if(a_bad || b_bad)
+        {
+            if(bi.batch > 0)
+                return fail(CKB_ERR_UNSUPPORTED, "batched GEMM needs 16-byte aligned operands and pitches");
+            if(capturing)
+                return fail(CKB_ERR_UNSUPPORTED, "operands that need a pitch-fixing copy cannot be captured into a graph");
+            const int64_t per16   = 16 / eb;
+            const int64_t a_outer = a_mn ? d->K : d->M, a_inner = a_mn ? d->M : d->K;
+            const int64_t b_outer = b_mn ? d->K : d->N, b_inner = b_mn ? d->N : d->K;
+            const int64_t lda_p = (a_inner + per16 - 1) / per16 * per16, ldb_p = (b_inner + per16 - 1) / per16 * per16;
+            const size_t a_bytes = a_bad ? (static_cast<size_t>(a_outer) * lda_p * eb + 255) & ~size_t(255) : 0;
+            const size_t b_bytes = b_bad ? (static_cast<size_t>(b_outer) * ldb_p * eb + 255) & ~size_t(255) : 0;
+            CKB_CUDA(cudaMallocAsync(&temp.ptr, a_bytes + b_bytes, stream));
+            if(a_bad)
+            {
+                pre[n_pre++] = Repack{d->p_a, temp.ptr, a_outer, a_inner, d->lda, lda_p, eb};
+                dd.p_a       = temp.ptr;
+                dd.lda       = lda_p;
+            }
+            if(b_bad)
+            {
+                void* dst    = static_cast<char*>(temp.ptr) + a_bytes;
+                pre[n_pre++] = Repack{d->p_b, dst, b_outer, b_inner, d->ldb, ldb_p, eb};
+                dd.p_b       = dst;
+                dd.ldb       = ldb_p;
+            }
+        }
+    }
+
+    GemmPlanInput in;
+    in.M          = d->M;
+    in.N          = d->N;
+    in.num_kb     = static_cast<int>((d->K + BK_BYTES / eb - 1) / (BK_BYTES / eb));
+    in.batch      = bi.batch;
+    in.sm_count   = dev->sm_count;
+    in.b_min      = min_b_rows(d->ab_dtype, b_mn);
+    in.force      = tile_config_of(d->tile_config);
     // Measured on 3840 x 4096 x 4096: +5 % for 16-bit operands with a D-less epilogue; a loss for int8 (tiles
     // half as long) and for epilogues that read D tensors (bound by power: parking the partials through L2 costs
     // more energy than the narrow MMAs it removes) - those keep the column slices.
-#ifdef CKB_KSPLIT_WITH_D
-    const bool ks_pays = d->ab_dtype != CKB_I8;
-#else
-    const bool ks_pays = d->ab_dtype != CKB_I8 && d->n_ds == 0;
-#endif
-    int whole_ksplit = 0;
-    if(ks_pays && ks_allowed && bi.batch == 0 && forced_bn() == 0 && !getenv("CKB_FORCE_CG") &&
-       !stream_is_capturing(static_cast<cudaStream_t>(stream)))
-    {
-        // only where the plan without it runs a single, partly filled wave
-        const int64_t t0 = ((d->M + BM * cg - 1) / (BM * cg)) * ((d->N + bn - 1) / bn);
-        const int64_t G0 = dev->sm_count / cg;
-        if(t0 * 2 <= G0)
-        {
-            const WorkPlan w0 = plan_work(t0, static_cast<int>(G0), bn, cg, b_min);
-            const WholeSplit ws =
-                consider_whole_split(d->M, d->N, num_kb, dev->sm_count, b_min,
-                                     static_cast<int64_t>(num_kb) * kb_cycles(bn / w0.split));
-            if(ws.ksplit >= 2)
-            {
-                bn           = ws.bn;
-                cg           = ws.cg;
-                whole_ksplit = ws.ksplit;
-            }
-        }
-    }
-    const int64_t tiles_n = (d->N + bn - 1) / bn;
-    const int64_t tiles_m = (d->M + BM * cg - 1) / (BM * cg);
-    const int64_t all_tiles = tiles_m * tiles_n * nb;
-    if(all_tiles > 0x3FFFFFFFll)
+    in.ks_pays    = d->ab_dtype != CKB_I8 && d->n_ds == 0;
+    in.ks_allowed = !capturing;
+    GemmPlan gp;
+    if(!plan_gemm(in, &gp))
         return fail(CKB_ERR_UNSUPPORTED, "too many tiles");
-    WorkPlan plan = plan_work(all_tiles, dev->sm_count / cg, bn, cg, b_min);
-    // K-split tail: with whole waves before it and a tail of at most half the units, cut the tail tiles along K
-    // (see "K-split tail" in ckb_kernel.cuh); needs scratch, else the column-slice plan above stands.
-    const int64_t G   = dev->sm_count / cg;
-    const int64_t ful = (all_tiles / G) * G, rem = all_tiles - ful;
-    if(ks_pays && ks_allowed && rem > 0 && (ful > 0 || whole_ksplit >= 2) && rem * 2 <= G && rem <= 1024)
+    KernelParams p;
+    memset(&p, 0, sizeof(p));
+    if(gp.pp.ksplit >= 2)
     {
-        // tail: 4 or 2 slices, reduction in column parts of bn / ksplit >= 64 columns; whole problem: up to 8
-        // A 256-wide tail tile is cut four ways along K where a quarter of the units suffice; with more tail tiles only
-        // two K halves fit, and those beat two 128-column slices only for a long K (parking and reduction cost the
-        // same whatever K is, a column slice costs per k block): measured break-even near 78 k blocks
-        // (4096^3: 78.8 us with the K halves, 77.5 us with column slices; 4096 x 4096 x 8192: 160.2 against 165.0 us).
-        // The four-way cut itself needs a K loop long enough to pay for parking and reduction: 3840 x 4096 x K
-        // with K = 1024 / 2048 / 3072 / 4096 / 6144 took 29.9 / 43.7 / 57.4 / 73.6 / 110.6 us with it and
-        // 25.3 / 42.3 / 58.9 / 76.4 / 115.8 us with four column slices: taken from 40 k blocks on (48 for the
-        // two halves of a 128-wide tile, by the same cost model).
-        int ksplit = whole_ksplit >= 2 ? whole_ksplit
-                     : (G / rem >= 4 && bn >= 256) ? (num_kb >= 40 ? 4 : 0)
-                     : ((bn == 128 && num_kb >= 48) || (bn >= 256 && num_kb >= 80)) ? 2 : 0;
-        int ks_kb  = 0;
-        for(; ksplit >= 2; ksplit /= 2)
+        // the K split needs scratch; without it the column-slice plan stands
+        void* sc = scratch_for(dev, stream, gp.partial_bytes);
+        if(sc)
         {
-            ks_kb = (num_kb + ksplit - 1) / ksplit;
-            ks_kb = (ks_kb + 1) & ~1; // slices start on a stage boundary (at most two k blocks per stage)
-            if(ks_kb >= 4 && static_cast<int64_t>(ksplit - 1) * ks_kb < num_kb)
-                break;
+            p.ks_counters   = static_cast<uint32_t*>(sc);
+            p.ks_partials   = reinterpret_cast<uint32_t*>(static_cast<char*>(sc) + kScratchCounterBytes);
+            p.ks_wait_extra = test_kslice_wait_extra();
         }
-        if(ksplit >= 2)
+        else
         {
-            const size_t part_bytes = static_cast<size_t>(rem) * ksplit * (BM * cg) * bn * sizeof(uint32_t);
-            void* sc                = scratch_for(dev, static_cast<cudaStream_t>(stream), part_bytes);
-            if(sc)
-            {
-                p.ksplit      = ksplit;
-                p.ks_kb       = ks_kb;
-                p.ks_full     = static_cast<int32_t>(ful);
-                p.ks_rem      = static_cast<int32_t>(rem);
-                p.ks_counters = static_cast<uint32_t*>(sc);
-                p.ks_partials = reinterpret_cast<uint32_t*>(static_cast<char*>(sc) + kScratchCounterBytes);
-                p.num_slots   = static_cast<int32_t>(ful / G + 2 < 4 ? 4 : ful / G + 2);
-                plan.split    = 1;
-                plan.split_start = static_cast<int32_t>(all_tiles);
-                plan.total_work  = static_cast<int32_t>(all_tiles);
-                plan.grid        = static_cast<int32_t>(G * cg);
-            }
+            in.ks_allowed = false;
+            if(!plan_gemm(in, &gp))
+                return fail(CKB_ERR_UNSUPPORTED, "too many tiles");
         }
     }
-    if(p.ksplit < 2)
-        p.num_slots = static_cast<int32_t>((plan.total_work + G - 1) / G);
+    const int bn = gp.bn, cg = gp.cg;
+    rc = encode_operand(&p.tm_a, d->ab_dtype, d->p_a, d->M, d->K, d->lda, a_mn, BM, bi.batch, bi.stride_a);
+    if(rc)
+        return rc;
     rc = encode_operand(&p.tm_b, d->ab_dtype, d->p_b, d->N, d->K, d->ldb, b_mn, bn / cg, bi.batch, bi.stride_b);
     if(rc)
         return rc;
-    rc = encode_operand(&p.tm_b_split, d->ab_dtype, d->p_b, d->N, d->K, d->ldb, b_mn, bn / plan.split / cg, bi.batch,
+    rc = encode_operand(&p.tm_b_split, d->ab_dtype, d->p_b, d->N, d->K, d->ldb, b_mn, gp.b_split_rows, bi.batch,
                         bi.stride_b);
     if(rc)
         return rc;
-    p.batch_tiles     = bi.batch > 0 ? static_cast<int32_t>(tiles_m * tiles_n) : 0;
+    fill_epilogue(p.epi, d);
+    p.plan            = gp.pp;
     p.batch_stride_e  = bi.stride_e;
     p.batch_stride_d0 = bi.stride_d[0];
     p.batch_stride_d1 = bi.stride_d[1];
     p.mn_major      = (a_mn ? 1 : 0) | (b_mn ? 2 : 0);
-    p.split_start   = plan.split_start;
-    p.split         = plan.split;
-    p.total_work    = plan.total_work;
-    p.total_tiles   = static_cast<int32_t>(all_tiles);
     p.M             = static_cast<int32_t>(d->M);
     p.N             = static_cast<int32_t>(d->N);
-    p.tiles_n       = static_cast<int32_t>(tiles_n);
-    p.num_kb        = num_kb;
     p.vec_ok        = gemm_vec_ok(d) && bi.vec_ok ? 1 : 0;
     if(p.vec_ok)
     {
@@ -855,12 +877,12 @@ static int gemm_run_impl(const ckb_gemm_desc* d, const BatchInfo& bi, void* stre
     LaunchFn fn     = find_launch(MODE_GEMM, kind_of(d->ab_dtype), d->epilogue);
     if(!fn)
         return fail(CKB_ERR_UNSUPPORTED, "no kernel instance for epilogue %d", d->epilogue);
-    return run_timed(fn, bn, cg, p, plan.grid, static_cast<cudaStream_t>(stream), n_rep, avg_ms);
+    return run_timed(fn, bn, cg, p, gp.grid, stream, n_rep, avg_ms, pre, n_pre);
 }
 
 int ckb_gemm_run(const ckb_gemm_desc* d, void* stream, int n_rep, float* avg_ms)
 {
-    int rc = check_gemm(d, true);
+    int rc = check_gemm(d, true, false);
     if(rc)
         return rc;
     BatchInfo bi{0, 0, 0, 0, {0, 0}, true}; // batch 0: 2-D operand maps
@@ -872,7 +894,7 @@ static int check_batched(const ckb_batched_gemm_desc* b, bool need_pointers)
 {
     if(!b)
         return fail(CKB_ERR_INVALID, "null descriptor");
-    int rc = check_gemm(&b->gemm, need_pointers);
+    int rc = check_gemm(&b->gemm, need_pointers, true);
     if(rc)
         return rc;
     if(b->batch < 1 || b->batch > 0x7FFFFFFFll)
@@ -914,11 +936,13 @@ static int check_grouped(const ckb_grouped_gemm_desc* g, bool need_pointers)
 {
     if(!g || g->group_count < 1 || !g->groups)
         return fail(CKB_ERR_INVALID, "grouped descriptor needs at least one group");
+    if(int rc = check_tile_config(g->tile_config))
+        return rc;
     const ckb_gemm_desc& g0 = g->groups[0];
     for(int i = 0; i < g->group_count; ++i)
     {
         const ckb_gemm_desc& gi = g->groups[i];
-        int rc                  = check_gemm(&gi, need_pointers);
+        int rc                  = check_gemm(&gi, need_pointers, true);
         if(rc)
         {
             std::string msg = "group " + std::to_string(i) + ": " + t_last_error;
@@ -943,50 +967,41 @@ int ckb_grouped_gemm_workspace_size(const ckb_grouped_gemm_desc* desc, size_t* b
     return CKB_OK;
 }
 
-// Tile shape, CTA grouping and work plan of a grouped problem, and its device table entries.
-struct GroupedPlan
+// Tile shape, CTA grouping and work plan of a grouped problem (plan_grouped of ckb_plan.h), and its device table.
+struct GroupedLaunch
 {
-    int bn, cg, mn_major;
-    WorkPlan plan;
-    int64_t total_tiles;
+    GroupedPlan plan;
+    int mn_major      = 0;
+    GroupTiles* tiles = nullptr; // one per group, caller-provided
 };
 
-static int plan_grouped(const ckb_grouped_gemm_desc* g, const DeviceInfo* dev, GroupedPlan* gp)
+// `shapes` and `tiles`: caller-provided arrays of group_count elements (the allocation-free entry point hands in
+// fixed arrays).
+static int plan_grouped_call(const ckb_grouped_gemm_desc* g, const DeviceInfo* dev, int64_t (*shapes)[3],
+                             GroupTiles* tiles, GroupedLaunch* gl)
 {
     const int dtype = g->groups[0].ab_dtype;
     const bool a_mn = a_is_mn_major(&g->groups[0]), b_mn = b_is_mn_major(&g->groups[0]);
-    const int b_min = min_b_rows(dtype, b_mn);
-    int64_t max_n = 0, sum_m = 0;
+    const int bk    = BK_BYTES / elem_bytes(dtype);
     for(int i = 0; i < g->group_count; ++i)
     {
-        max_n = max_n > g->groups[i].N ? max_n : g->groups[i].N;
-        sum_m += g->groups[i].M;
+        shapes[i][0] = g->groups[i].M;
+        shapes[i][1] = g->groups[i].N;
+        shapes[i][2] = (g->groups[i].K + bk - 1) / bk;
     }
-    const int bn      = pick_bn(sum_m, max_n, dev->sm_count, b_min);
-    int64_t tiles_128 = 0;
-    for(int i = 0; i < g->group_count; ++i)
-        tiles_128 += ((g->groups[i].M + BM - 1) / BM) * ((g->groups[i].N + bn - 1) / bn);
-    const int cg      = pick_cg(tiles_128, bn, dev->sm_count);
-    int64_t all_tiles = 0;
-    for(int i = 0; i < g->group_count; ++i)
-        all_tiles += ((g->groups[i].M + BM * cg - 1) / (BM * cg)) * ((g->groups[i].N + bn - 1) / bn);
-    if(all_tiles > 0x3FFFFFFFll)
+    gl->tiles    = tiles;
+    gl->mn_major = (a_mn ? 1 : 0) | (b_mn ? 2 : 0);
+    if(!plan_grouped(shapes, g->group_count, dev->sm_count, min_b_rows(dtype, b_mn), tile_config_of(g->tile_config),
+                     tiles, &gl->plan))
         return fail(CKB_ERR_UNSUPPORTED, "too many tiles");
-    gp->bn          = bn;
-    gp->cg          = cg;
-    gp->mn_major    = (a_mn ? 1 : 0) | (b_mn ? 2 : 0);
-    gp->plan        = plan_work(all_tiles, dev->sm_count / cg, bn, cg, b_min);
-    gp->total_tiles = all_tiles;
     return CKB_OK;
 }
 
-static int fill_group_table(const ckb_grouped_gemm_desc* g, const GroupedPlan& gp, GroupEntry* table)
+static int fill_group_table(const ckb_grouped_gemm_desc* g, const GroupedLaunch& gl, GroupEntry* table)
 {
     const int dtype = g->groups[0].ab_dtype;
-    const int bk    = BK_BYTES / elem_bytes(dtype);
-    const bool a_mn = (gp.mn_major & 1) != 0, b_mn = (gp.mn_major & 2) != 0;
-    const int bn = gp.bn, cg = gp.cg;
-    int64_t tile_start = 0;
+    const bool a_mn = (gl.mn_major & 1) != 0, b_mn = (gl.mn_major & 2) != 0;
+    const int bn = gl.plan.bn, cg = gl.plan.cg;
     for(int i = 0; i < g->group_count; ++i)
     {
         const ckb_gemm_desc& d = g->groups[i];
@@ -998,16 +1013,17 @@ static int fill_group_table(const ckb_grouped_gemm_desc* g, const GroupedPlan& g
         rc = encode_operand(&ge.tm_b, dtype, d.p_b, d.N, d.K, d.ldb, b_mn, bn / cg);
         if(rc)
             return rc;
-        rc = encode_operand(&ge.tm_b_split, dtype, d.p_b, d.N, d.K, d.ldb, b_mn, bn / gp.plan.split / cg);
+        rc = encode_operand(&ge.tm_b_split, dtype, d.p_b, d.N, d.K, d.ldb, b_mn, gl.plan.b_split_rows);
         if(rc)
             return rc;
-        const int64_t tm = (d.M + BM * cg - 1) / (BM * cg), tn = (d.N + bn - 1) / bn;
         ge.M          = static_cast<int32_t>(d.M);
         ge.N          = static_cast<int32_t>(d.N);
         ge.K          = static_cast<int32_t>(d.K);
-        ge.tiles_n    = static_cast<int32_t>(tn);
-        ge.tile_start = static_cast<int32_t>(tile_start);
-        ge.num_kb     = static_cast<int32_t>((d.K + bk - 1) / bk);
+        ge.tiles_m    = gl.tiles[i].tiles_m;
+        ge.tiles_n    = gl.tiles[i].tiles_n;
+        ge.tile_start = gl.tiles[i].tile_start;
+        ge.num_kb     = gl.tiles[i].num_kb;
+        ge.m_fastest  = gl.tiles[i].m_fastest;
         ge.vec_ok     = gemm_vec_ok(&d) ? 1 : 0;
         if(ge.vec_ok)
         {
@@ -1021,24 +1037,18 @@ static int fill_group_table(const ckb_grouped_gemm_desc* g, const GroupedPlan& g
         ge.lde        = d.lde;
         ge.ldd0       = d.n_ds > 0 ? d.ldd[0] : 0;
         ge.ldd1       = d.n_ds > 1 ? d.ldd[1] : 0;
-        tile_start += tm * tn;
     }
     return CKB_OK;
 }
 
-static void fill_grouped_params(KernelParams& p, const ckb_grouped_gemm_desc* g, const GroupedPlan& gp,
+static void fill_grouped_params(KernelParams& p, const ckb_grouped_gemm_desc* g, const GroupedLaunch& gl,
                                 const GroupEntry* d_table, const DeviceInfo* dev)
 {
     memset(&p, 0, sizeof(p));
     fill_epilogue(p.epi, &g->groups[0]);
     p.groups        = d_table;
-    p.group_count   = g->group_count;
-    p.total_tiles   = static_cast<int32_t>(gp.total_tiles);
-    p.split_start   = gp.plan.split_start;
-    p.split         = gp.plan.split;
-    p.total_work    = gp.plan.total_work;
-    p.num_slots     = (gp.plan.total_work + gp.plan.grid / gp.cg - 1) / (gp.plan.grid / gp.cg);
-    p.mn_major      = gp.mn_major;
+    p.plan          = gl.plan.pp;
+    p.mn_major      = gl.mn_major;
     p.wait_limit_ns = wait_limit_ns();
     p.status        = dev->status;
 }
@@ -1059,8 +1069,10 @@ int ckb_grouped_gemm_run(const ckb_grouped_gemm_desc* g, void* workspace, size_t
     if(rc)
         return rc;
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    GroupedPlan gp;
-    rc = plan_grouped(g, dev, &gp);
+    GroupedLaunch gp;
+    std::vector<int64_t> shapes(static_cast<size_t>(g->group_count) * 3);
+    std::vector<GroupTiles> tiles(g->group_count);
+    rc = plan_grouped_call(g, dev, reinterpret_cast<int64_t(*)[3]>(shapes.data()), tiles.data(), &gp);
     if(rc)
         return rc;
     uintptr_t ws_addr = (reinterpret_cast<uintptr_t>(workspace) + 127u) & ~static_cast<uintptr_t>(127u);
@@ -1099,7 +1111,7 @@ int ckb_grouped_gemm_run(const ckb_grouped_gemm_desc* g, void* workspace, size_t
     LaunchFn fn = find_launch(MODE_GROUPED, kind_of(g->groups[0].ab_dtype), g->groups[0].epilogue);
     if(!fn)
         return fail(CKB_ERR_UNSUPPORTED, "no kernel instance for epilogue %d", g->groups[0].epilogue);
-    return run_timed(fn, gp.bn, gp.cg, p, gp.plan.grid, stream, n_rep, avg_ms);
+    return run_timed(fn, gp.plan.bn, gp.plan.cg, p, gp.plan.grid, stream, n_rep, avg_ms);
 }
 
 // ---- grouped GEMM without allocation ----------------------------------------------------------------
@@ -1112,6 +1124,8 @@ static_assert(sizeof(GroupEntry) == 640, "the documented size of the fixed table
 
 static GroupEntry* g_noalloc_dev_ptr[64] = {};
 static GroupEntry g_noalloc_host_table[CKB_NOALLOC_MAX_GROUPS]; // host staging, fixed size
+static int64_t g_noalloc_shapes[CKB_NOALLOC_MAX_GROUPS][3];      // planner input / output, fixed size
+static GroupTiles g_noalloc_tiles[CKB_NOALLOC_MAX_GROUPS];
 static std::mutex g_noalloc_mutex;
 
 int ckb_grouped_gemm_run_noalloc(const ckb_grouped_gemm_desc* g, void* stream_)
@@ -1146,8 +1160,8 @@ int ckb_grouped_gemm_run_noalloc(const ckb_grouped_gemm_desc* g, void* stream_)
     if(stream_is_capturing(stream))
         return fail(CKB_ERR_UNSUPPORTED, "grouped GEMM copies its group table from host memory at every launch and "
                                          "cannot be captured into a graph");
-    GroupedPlan gp;
-    rc = plan_grouped(g, dev, &gp);
+    GroupedLaunch gp;
+    rc = plan_grouped_call(g, dev, g_noalloc_shapes, g_noalloc_tiles, &gp);
     if(rc)
         return rc;
     rc = fill_group_table(g, gp, g_noalloc_host_table);
@@ -1165,7 +1179,7 @@ int ckb_grouped_gemm_run_noalloc(const ckb_grouped_gemm_desc* g, void* stream_)
     if(!fn)
         return fail(CKB_ERR_UNSUPPORTED, "no kernel instance for epilogue %d", g->groups[0].epilogue);
     p.trace = trace_buffer();
-    CKB_CUDA(fn(gp.bn, gp.cg, p, gp.plan.grid, stream));
+    CKB_CUDA(fn(gp.plan.bn, gp.plan.cg, p, gp.plan.grid, stream));
     g_launches.fetch_add(1);
     return CKB_OK;
 }
@@ -1175,6 +1189,7 @@ int ckb_grouped_gemm_run_noalloc(const ckb_grouped_gemm_desc* g, void* stream_)
 struct ConvProblem
 {
     int dtype, epilogue, nd; // nd = 2 (4-D im2col map) or 3 (5-D)
+    int tile_config;
     int N, K, C;
     int Di, Hi, Wi, Z, Y, X, Do, Ho, Wo;
     int sd, sh, sw, dd, dh, dw;
@@ -1187,7 +1202,7 @@ struct ConvProblem
 static ConvProblem problem_of_2d(const ckb_conv2d_fwd_desc* d)
 {
     ConvProblem c{};
-    c.dtype = d->dtype, c.epilogue = d->epilogue, c.nd = 2;
+    c.dtype = d->dtype, c.epilogue = d->epilogue, c.nd = 2, c.tile_config = d->tile_config;
     c.N = d->N, c.K = d->K, c.C = d->C;
     c.Di = 1, c.Hi = d->Hi, c.Wi = d->Wi, c.Z = 1, c.Y = d->Y, c.X = d->X, c.Do = 1, c.Ho = d->Ho, c.Wo = d->Wo;
     c.sd = 1, c.sh = d->stride_h, c.sw = d->stride_w, c.dd = 1, c.dh = d->dilation_h, c.dw = d->dilation_w;
@@ -1200,7 +1215,7 @@ static ConvProblem problem_of_2d(const ckb_conv2d_fwd_desc* d)
 static ConvProblem problem_of_3d(const ckb_conv3d_fwd_desc* d)
 {
     ConvProblem c{};
-    c.dtype = d->dtype, c.epilogue = d->epilogue, c.nd = 3;
+    c.dtype = d->dtype, c.epilogue = d->epilogue, c.nd = 3, c.tile_config = d->tile_config;
     c.N = d->N, c.K = d->K, c.C = d->C;
     c.Di = d->Di, c.Hi = d->Hi, c.Wi = d->Wi, c.Z = d->Z, c.Y = d->Y, c.X = d->X;
     c.Do = d->Do, c.Ho = d->Ho, c.Wo = d->Wo;
@@ -1261,8 +1276,8 @@ static int check_conv(const ConvProblem& c, bool need_pointers)
     if(dd != c.Do || ho != c.Ho || wo != c.Wo || dd < 1 || ho < 1 || wo < 1)
         return fail(CKB_ERR_INVALID, "Do/Ho/Wo (%d,%d,%d) do not match the convolution geometry (%d,%d,%d)", c.Do,
                     c.Ho, c.Wo, dd, ho, wo);
-    if(c.C % (16 / eb) != 0)
-        return fail(CKB_ERR_UNSUPPORTED, "C must be a multiple of %d (16-byte pixel pitch for TMA)", 16 / eb);
+    if(int rc = check_tile_config(c.tile_config))
+        return rc;
     // Limits of the im2col tensor map: traversal stride <= 8, box corners within [-128, 127] (4-D maps) or
     // [-16, 15] (5-D maps).
     if(c.sd > 8 || c.sh > 8 || c.sw > 8)
@@ -1287,8 +1302,8 @@ static int check_conv(const ConvProblem& c, bool need_pointers)
     {
         if(!c.p_in || !c.p_wei || !c.p_out)
             return fail(CKB_ERR_INVALID, "null tensor pointer");
-        if(!aligned16(c.p_in) || !aligned16(c.p_wei))
-            return fail(CKB_ERR_UNSUPPORTED, "input and weights must be 16-byte aligned");
+        if((reinterpret_cast<uintptr_t>(c.p_in) | reinterpret_cast<uintptr_t>(c.p_wei)) % eb != 0)
+            return fail(CKB_ERR_INVALID, "input or weights not aligned to the element size");
         if(nd >= 1 && !c.p_bias)
             return fail(CKB_ERR_INVALID, "epilogue needs a bias pointer");
         if(nd >= 2 && !c.p_resi)
@@ -1297,9 +1312,9 @@ static int check_conv(const ConvProblem& c, bool need_pointers)
     return CKB_OK;
 }
 
-static int run_conv(const ConvProblem& c, void* stream, int n_rep, float* avg_ms)
+static int run_conv(const ConvProblem& c_in, void* stream_, int n_rep, float* avg_ms)
 {
-    int rc = check_conv(c, true);
+    int rc = check_conv(c_in, true);
     if(rc)
         return rc;
     DeviceInfo* dev = nullptr;
@@ -1309,10 +1324,50 @@ static int run_conv(const ConvProblem& c, void* stream, int n_rep, float* avg_ms
     load_entry_points();
     if(!g_encode_im2col || !g_encode_tiled)
         return fail(CKB_ERR_CUDA, "tensor-map entry points not available");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    ConvProblem c       = c_in;
+    const int eb        = elem_bytes(c.dtype);
+    const int bk        = BK_BYTES / eb; // channels per k block
+
+    // A channel count whose pixel pitch is not a multiple of 16 bytes (the reference's OddC instances,
+    // device_convnd_fwd_xdl_nhwc_kyxc_nhwk.hpp:921-933, e.g. C = 3) or an unaligned base cannot be read by TMA in
+    // place: input and weights are copied into a stream-ordered temporary with the channels zero-padded to the next
+    // multiple of 16 bytes, and the problem runs with that channel count (zero channels add nothing to any sum).
+    Repack pre[2];
+    int n_pre = 0;
+    StreamTemp temp;
+    temp.stream = stream;
+    if(c.C % (16 / eb) != 0 || !aligned16(c.p_in) || !aligned16(c.p_wei))
+    {
+        if(stream_is_capturing(stream))
+            return fail(CKB_ERR_UNSUPPORTED, "tensors that need a channel-padding copy cannot be captured into a graph");
+        const int64_t per16 = 16 / eb;
+        const int64_t c_pad = (c.C + per16 - 1) / per16 * per16;
+        const int64_t pixels = static_cast<int64_t>(c.N) * c.Di * c.Hi * c.Wi;
+        const int64_t wrows  = static_cast<int64_t>(c.K) * c.Z * c.Y * c.X;
+        const size_t in_bytes  = (static_cast<size_t>(pixels) * c_pad * eb + 255) & ~size_t(255);
+        const size_t wei_bytes = (static_cast<size_t>(wrows) * c_pad * eb + 255) & ~size_t(255);
+        CKB_CUDA(cudaMallocAsync(&temp.ptr, in_bytes + wei_bytes, stream));
+        void* wei_dst = static_cast<char*>(temp.ptr) + in_bytes;
+        pre[n_pre++]  = Repack{c.p_in, temp.ptr, pixels, c.C, c.C, c_pad, eb};
+        pre[n_pre++]  = Repack{c.p_wei, wei_dst, wrows, c.C, c.C, c_pad, eb};
+        c.p_in        = temp.ptr;
+        c.p_wei       = wei_dst;
+        c.C           = static_cast<int>(c_pad);
+    }
     const int64_t gm = static_cast<int64_t>(c.N) * c.Do * c.Ho * c.Wo;
-    const int bn     = pick_bn(gm, c.K, dev->sm_count);
-    const int eb     = elem_bytes(c.dtype);
-    const int bk     = BK_BYTES / eb; // channels per k block
+    const int64_t taps = static_cast<int64_t>(c.Z) * c.Y * c.X;
+    GemmPlanInput in;
+    in.M        = gm;
+    in.N        = c.K;
+    in.num_kb   = static_cast<int>(taps * ((c.C + bk - 1) / bk));
+    in.sm_count = dev->sm_count;
+    in.b_min    = 64;
+    in.force    = tile_config_of(c.tile_config);
+    GemmPlan gp;
+    if(!plan_gemm(in, &gp))
+        return fail(CKB_ERR_UNSUPPORTED, "too many tiles");
+    const int bn = gp.bn, cg = gp.cg;
 
     KernelParams p;
     memset(&p, 0, sizeof(p));
@@ -1354,27 +1409,17 @@ static int run_conv(const ConvProblem& c, void* stream, int n_rep, float* avg_ms
         if(g_driver_version <= 13010 && in_bytes < 131072)
             reinterpret_cast<uint64_t*>(&p.tm_a)[1] &= ~(1ull << 21);
     }
-    const int64_t tiles_n = (c.K + bn - 1) / bn;
-    const int cg          = pick_cg(((gm + BM - 1) / BM) * tiles_n, bn, dev->sm_count);
-    const int64_t tiles_m = (gm + BM * cg - 1) / (BM * cg);
-    if(tiles_m * tiles_n > 0x3FFFFFFFll)
-        return fail(CKB_ERR_UNSUPPORTED, "too many tiles");
-    const WorkPlan plan = plan_work(tiles_m * tiles_n, dev->sm_count / cg, bn, cg);
-    const int64_t taps  = static_cast<int64_t>(c.Z) * c.Y * c.X;
     for(int which = 0; which < 2; ++which)
     {
         // Weights K[Z]YXC as (C, taps, K): a box never crosses a filter tap, channels beyond C read 0.
         cuuint64_t dims[3]    = {static_cast<cuuint64_t>(c.C), static_cast<cuuint64_t>(taps), static_cast<cuuint64_t>(c.K)};
         cuuint64_t strides[2] = {static_cast<cuuint64_t>(c.C) * eb, static_cast<cuuint64_t>(taps) * c.C * eb};
         cuuint32_t box[3]     = {static_cast<cuuint32_t>(bk), 1,
-                             static_cast<cuuint32_t>((which == 0 ? bn : bn / plan.split) / cg)};
-        cuuint32_t estr[3]    = {1, 1, 1};
-        CUresult r = g_encode_tiled(which == 0 ? &p.tm_b : &p.tm_b_split, tm_dtype(c.dtype), 3,
-                                    const_cast<void*>(c.p_wei), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if(r != CUDA_SUCCESS)
-            return fail(CKB_ERR_CUDA, "cuTensorMapEncodeTiled (weights) failed (CUresult %d)", static_cast<int>(r));
+                             static_cast<cuuint32_t>(which == 0 ? bn / cg : gp.b_split_rows)};
+        rc = encode_tiled(which == 0 ? &p.tm_b : &p.tm_b_split, c.dtype, 3, c.p_wei, dims, strides, box,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, "weights");
+        if(rc)
+            return rc;
     }
     const int nd = epi_num_d(c.epilogue);
     p.epi.kind   = c.epilogue;
@@ -1392,14 +1437,9 @@ static int run_conv(const ConvProblem& c, void* stream, int n_rep, float* avg_ms
         vec = vec && aligned16(c.p_bias);
     if(nd >= 2)
         vec = vec && aligned16(c.p_resi);
-    p.total_tiles   = static_cast<int32_t>(tiles_m * tiles_n);
-    p.split_start   = plan.split_start;
-    p.split         = plan.split;
-    p.total_work    = plan.total_work;
-    p.num_slots     = (plan.total_work + plan.grid / cg - 1) / (plan.grid / cg);
+    p.plan          = gp.pp;
     p.M             = static_cast<int32_t>(gm);
     p.N             = c.K;
-    p.tiles_n       = static_cast<int32_t>(tiles_n);
     p.conv.nd3      = c.nd == 3 ? 1 : 0;
     p.conv.Do       = c.Do;
     p.conv.Ho       = c.Ho;
@@ -1422,7 +1462,6 @@ static int run_conv(const ConvProblem& c, void* stream, int n_rep, float* avg_ms
     p.conv.pad_d    = c.pd;
     p.conv.pad_h    = c.ph;
     p.conv.pad_w    = c.pw;
-    p.num_kb        = static_cast<int32_t>(taps * p.conv.c_blocks);
     p.vec_ok        = vec ? 1 : 0;
     if(vec)
     {
@@ -1435,7 +1474,7 @@ static int run_conv(const ConvProblem& c, void* stream, int n_rep, float* avg_ms
     LaunchFn fn = find_launch(MODE_CONV, kind_of(c.dtype), c.epilogue);
     if(!fn)
         return fail(CKB_ERR_UNSUPPORTED, "no kernel instance for epilogue %d", c.epilogue);
-    return run_timed(fn, bn, cg, p, plan.grid, static_cast<cudaStream_t>(stream), n_rep, avg_ms);
+    return run_timed(fn, bn, cg, p, gp.grid, stream, n_rep, avg_ms, pre, n_pre);
 }
 
 int ckb_conv2d_fwd_supported(const ckb_conv2d_fwd_desc* desc)

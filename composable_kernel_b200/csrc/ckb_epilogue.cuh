@@ -281,7 +281,6 @@ struct StoreStage
     uint32_t count;          // segments stored so far by this warp
     const CUtensorMap* tm_e; // E as (columns, rows[, batch]) with a 32 x 32 box
     int batch;               // >= 0: third coordinate of a batched E map; < 0: 2-D map
-    bool direct;             // write the segment with 128-bit global stores instead (no staging)
 };
 
 template <int ROW_BYTES> // 64: 16-bit E, 32: int8 E

@@ -57,6 +57,7 @@
 #include <type_traits>
 
 #include "ckb_epilogue.cuh"
+#include "ckb_plan.h"
 #include "ckb_ptx.cuh"
 
 // Cycle counters of the three roles, compiled in only with -DCKB_TRACE (a profiling build): per CTA
@@ -74,10 +75,8 @@
 
 namespace ckb {
 
-enum { MODE_GEMM = 0, MODE_GROUPED = 1, MODE_CONV = 2 };
 enum { KIND_F16 = 0, KIND_BF16 = 1, KIND_I8 = 2 };
 
-constexpr int BM            = 128; // rows of an output tile = TMEM lanes
 constexpr int BK_BYTES      = 128; // bytes of K per stage row = one swizzle span
 constexpr int NUM_EPI_WARPS = 8;
 constexpr int NUM_THREADS   = 64 + 32 * NUM_EPI_WARPS;
@@ -105,7 +104,9 @@ struct alignas(128) GroupEntry
     int32_t tile_start; // first global tile index of this group
     int32_t num_kb;
     int32_t vec_ok;
-    int32_t pad_;
+    int32_t tiles_m;
+    int32_t m_fastest;  // tile order inside the group (see tile_position)
+    int32_t pad_[3];
     void* e;
     const void* d0;
     const void* d1;
@@ -141,28 +142,15 @@ struct KernelParams
     CUtensorMap tm_e;       // E as (N, M[, batch]), 32 x 32 box (valid when vec_ok; GROUPED: in the group entry)
     EpilogueArgs epi;       // GROUPED: e/d/ld fields come from the group entry instead
     const GroupEntry* groups;
-    int32_t group_count;
-    int32_t total_tiles; // T: 128 x BN tiles over all groups
-    int32_t split_start; // first tile index whose tile is cut into column slices (= T if none)
-    int32_t split;       // slices per tail tile (1, 2 or 4)
-    int32_t total_work;  // split_start + (T - split_start) * split
+    PlanParams plan;     // which unit runs which tile / slice in which slot (ckb_plan.h)
     int32_t M, N;        // GEMM / CONV problem (CONV: M = N*Ho*Wo, N = K_out)
-    int32_t tiles_n;
-    int32_t num_kb;      // k blocks per tile (GEMM / CONV)
     int32_t vec_ok;      // 128-bit epilogue access allowed
     int32_t mn_major;    // bit 0: A is M-contiguous (column-major A); bit 1: B is N-contiguous (row-major B)
-    int32_t batch_tiles; // batched GEMM: tiles per batch (0 = not batched)
-    int32_t pad_;
     int64_t batch_stride_e, batch_stride_d0, batch_stride_d1; // elements between batches of E / D0 / D1
-    // K-split tail (0 / 1 = off): see "K-split tail" above
-    int32_t ksplit;      // K slices per tail tile
-    int32_t ks_kb;       // k blocks per slice (a multiple of the k blocks per stage)
-    int32_t ks_full;     // tiles that run whole (a multiple of the number of units); tail tiles follow
-    int32_t ks_rem;      // tail tiles
-    int32_t num_slots;   // work slots per unit
-    int32_t store_direct; // full segments of E: 0 = staged TMA stores, 1 = 128-bit global stores
     uint32_t* ks_partials; // [tail tile][slice][TILE_M rows][BN columns] raw 32-bit accumulators
     uint32_t* ks_counters; // one per tail tile, zero between launches
+    uint32_t ks_wait_extra; // test hook: added to the arrival count a reduction waits for, so that the wait runs out
+    uint32_t pad_;
     ConvGeom conv;
     uint64_t wait_limit_ns;
     uint32_t* status; // device status word
@@ -188,6 +176,11 @@ struct SmemLayout
     static constexpr int TOTAL       = MISC_OFFSET + 16;
     static constexpr int DYN_BYTES   = TOTAL + 1024; // slack to align the base to 1024 B
 };
+
+// The exit path waits for copies and MMAs in flight with a limit of its own: the caller's limit may be short (it
+// decides how soon a role gives up on another role), but a CTA must not leave while a bulk copy may still write
+// its shared memory or an MMA may still write its tensor memory.
+constexpr uint64_t kDrainLimitNs = 2000000000ull;
 
 struct WaitCtx
 {
@@ -222,144 +215,13 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, cons
     }
 }
 
-// Finds g with tile_start[g] <= tile < tile_start[g+1].
-__device__ __forceinline__ int find_group(const GroupEntry* groups, int group_count, int tile)
-{
-    int lo = 0, hi = group_count - 1;
-    while(lo < hi)
-    {
-        const int mid = (lo + hi + 1) >> 1;
-        if(groups[mid].tile_start <= tile)
-            lo = mid;
-        else
-            hi = mid - 1;
-    }
-    return lo;
-}
-
-// What one work item covers.
-enum { ITEM_NONE = 0, ITEM_TILE = 1, ITEM_KSLICE = 2, ITEM_REDUCE = 3 };
-struct WorkItem
-{
-    int kind;    // ITEM_*: TILE runs all roles; KSLICE is a TILE over part of K whose accumulator is parked;
-                 // REDUCE is epilogue-only
-    int m_blk;   // row tile
-    int n_start; // first output column
-    int width;   // columns of this item (BN, or BN/split for a tail slice)
-    int kb_begin, num_kb;    // k blocks [kb_begin, kb_begin + num_kb)
-    const GroupEntry* group; // MODE_GROUPED only
-    int batch;               // MODE_GEMM: batch index (0 unless batched)
-    int tail;                // KSLICE / REDUCE: index of the tail tile
-    int slice;               // KSLICE: which K slice; REDUCE: which column part (of width BN / ksplit)
-    bool is_slice;           // a column slice of a tail tile
-};
-
-// Item of `unit` (CTA or CTA pair) in its work slot `slot`.
-//   plain / column-slice plan: item w = unit + slot * num_units of the list described under "Work items"
-//   K-split plan             : whole tile, K slice, whole tile, reduction of one column part of the tail tile,
-//                              then the remaining whole tiles (parking and reduction both overlap a main loop)
 // Kernel instances that carry the K-split tail: 16-bit GEMMs whose epilogue reads no D tensor (the host enables
 // it only for those; leaving the code out of the others keeps their epilogue inside the register budget).
 template <int MODE, int KIND, int EPI>
 struct HasKSplit
 {
-#ifdef CKB_KSPLIT_WITH_D
-    static constexpr bool value = MODE == MODE_GEMM && KIND != KIND_I8;
-#else
     static constexpr bool value = MODE == MODE_GEMM && KIND != KIND_I8 && epi_num_d(EPI) == 0;
-#endif
 };
-
-template <int MODE, int BN, bool KSPLIT = false>
-__device__ __forceinline__ WorkItem decode_work(const KernelParams& P, int unit, int num_units, int slot)
-{
-    WorkItem wi;
-    int tile, slice = 0;
-    wi.kind     = ITEM_TILE;
-    wi.width    = BN;
-    wi.is_slice = false;
-    wi.batch    = 0;
-    wi.tail     = 0;
-    wi.slice    = 0;
-    wi.kb_begin = 0;
-    wi.group    = nullptr;
-    if(KSPLIT && P.ksplit > 1)
-    {
-        if(slot == 1)
-        {
-            wi.kind  = unit < P.ks_rem * P.ksplit ? ITEM_KSLICE : ITEM_NONE;
-            wi.tail  = unit / P.ksplit;
-            wi.slice = unit - wi.tail * P.ksplit;
-            tile     = P.ks_full + wi.tail;
-        }
-        else if(slot == 3)
-        {
-            // the unit that ran slice i of a tail tile also sums column part i of it
-            wi.kind  = unit < P.ks_rem * P.ksplit ? ITEM_REDUCE : ITEM_NONE;
-            wi.tail  = unit / P.ksplit;
-            wi.slice = unit - wi.tail * P.ksplit;
-            tile     = P.ks_full + wi.tail;
-            slice    = wi.slice;
-            wi.width = BN / P.ksplit;
-        }
-        else
-        {
-            tile = unit + (slot == 0 ? 0 : slot == 2 ? 1 : slot - 2) * num_units;
-            if(tile >= P.ks_full)
-                wi.kind = ITEM_NONE;
-        }
-        if(wi.kind == ITEM_NONE)
-            tile = 0;
-    }
-    else
-    {
-        const int w = unit + slot * num_units;
-        if(w >= P.total_work)
-        {
-            wi.kind = ITEM_NONE;
-            tile    = 0;
-        }
-        else if(w < P.split_start)
-            tile = w;
-        else
-        {
-            const int q = w - P.split_start;
-            tile        = P.split_start + q / P.split;
-            slice       = q % P.split;
-            wi.width    = BN / P.split;
-            wi.is_slice = P.split > 1;
-        }
-    }
-    int n_blk;
-    if constexpr(MODE == MODE_GROUPED)
-    {
-        const GroupEntry* G = P.groups + find_group(P.groups, P.group_count, tile);
-        const int local     = tile - G->tile_start;
-        wi.m_blk            = local / G->tiles_n;
-        n_blk               = local % G->tiles_n;
-        wi.num_kb           = G->num_kb;
-        wi.group            = G;
-    }
-    else
-    {
-        if(MODE == MODE_GEMM && P.batch_tiles > 0) // batched GEMM: batch-major tile order
-        {
-            wi.batch = tile / P.batch_tiles;
-            tile -= wi.batch * P.batch_tiles;
-        }
-        wi.m_blk  = tile / P.tiles_n;
-        n_blk     = tile % P.tiles_n;
-        wi.num_kb = P.num_kb;
-    }
-    if(wi.kind == ITEM_KSLICE)
-    {
-        wi.kb_begin   = wi.slice * P.ks_kb;
-        const int rest = P.num_kb - wi.kb_begin;
-        wi.num_kb     = rest < P.ks_kb ? rest : P.ks_kb;
-    }
-    wi.n_start = n_blk * BN + slice * wi.width;
-    return wi;
-}
 
 // One TMA box of a GEMM operand.  The operand maps of a batched GEMM are 3-D (the third coordinate is the
 // batch index); those of a plain GEMM and the per-group maps of MODE_GROUPED are 2-D.
@@ -541,29 +403,14 @@ __device__ __forceinline__ void epilogue_span(uint32_t tmem_addr, const Epilogue
                 uint4 out[2] = {};
                 if(row_ok)
                     epi_compute_vec_i8<EPI>(out, v, ea);
-                if(!st.direct)
-                    stage_and_store<32>(st, out, lane, static_cast<int>(n0), row0);
-                else if(row_ok)
-                {
-                    uint4* e_row = reinterpret_cast<uint4*>(static_cast<int8_t*>(ea.e) + m * ea.lde + n0);
-                    e_row[0]     = out[0];
-                    e_row[1]     = out[1];
-                }
+                stage_and_store<32>(st, out, lane, static_cast<int>(n0), row0);
             }
             else
             {
                 uint4 out[4] = {};
                 if(row_ok)
                     epi_compute_vec_f<EPI, T>(out, v, cur, ea, m, n0);
-                if(!st.direct)
-                    stage_and_store<64>(st, out, lane, static_cast<int>(n0), row0);
-                else if(row_ok)
-                {
-                    uint4* e_row = reinterpret_cast<uint4*>(static_cast<T*>(ea.e) + m * ea.lde + n0);
-#pragma unroll
-                    for(int j = 0; j < 4; ++j)
-                        e_row[j] = out[j];
-                }
+                stage_and_store<64>(st, out, lane, static_cast<int>(n0), row0);
             }
         }
         else if(row_ok)
@@ -576,18 +423,6 @@ __device__ __forceinline__ void epilogue_span(uint32_t tmem_addr, const Epilogue
         if constexpr(PREFETCH_D)
             cur = nxt;
     }
-}
-
-// The reduction epilogue of kernels whose functor reads D tensors, as a function of its own: inlined, its parked
-// slices and D values together push the whole kernel over the register budget (spills in every epilogue path);
-// called, the caller's live registers are saved once per tail tile instead.  Returns the updated segment count.
-template <int EPI, int KIND>
-__device__ __noinline__ uint32_t reduce_epilogue_call(EpilogueArgs ea, StoreStage st, int lane, int64_t m, bool row_ok,
-                                                      int64_t n_begin, int64_t n_end, bool vec_ok,
-                                                      const uint32_t* parked, int ks, int64_t slice_stride)
-{
-    epilogue_span<EPI, KIND, true>(0, ea, st, lane, m, row_ok, n_begin, n_end, vec_ok, parked, ks, slice_stride);
-    return st.count;
 }
 
 // EPI (the fused epilogue functor) is a template parameter: one functor per kernel keeps the
@@ -609,7 +444,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
     constexpr int ATOM_BYTES     = BK_ELEMS * BK_BYTES;
     const bool a_mn              = MODE != MODE_CONV && (P.mn_major & 1) != 0;
     const bool b_mn              = MODE != MODE_CONV && (P.mn_major & 2) != 0;
-    const bool batched           = MODE == MODE_GEMM && P.batch_tiles > 0;
+    const bool batched           = MODE == MODE_GEMM && P.plan.batch_tiles > 0;
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr  = smem_u32(smem_raw);
@@ -701,17 +536,17 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
         const uint32_t bar0 = (CG == 2) ? mapa_shared(full_bar(0), 0) : full_bar(0);
         const int a_per_kb  = a_mn ? BM / BK_ELEMS : 1; // A boxes per k block
         CKB_TR(long long tr_wait = 0; const long long tr_start = clock64();)
-        for(int slot = 0; ok && slot < P.num_slots; ++slot)
+        for(int slot = 0; ok && slot < P.plan.num_slots; ++slot)
         {
-            const WorkItem wi = decode_work<MODE, BN, KSPLIT>(P, unit, num_units, slot);
+            const WorkItem wi = decode_work<MODE, BN, KSPLIT>(P.plan, P.groups, unit, num_units, slot);
             if(wi.kind != ITEM_TILE && wi.kind != ITEM_KSLICE)
                 continue;
             const CUtensorMap* tm_a = &P.tm_a;
             const CUtensorMap* tm_b = wi.is_slice ? &P.tm_b_split : &P.tm_b;
             if constexpr(MODE == MODE_GROUPED)
             {
-                tm_a = &wi.group->tm_a;
-                tm_b = wi.is_slice ? &wi.group->tm_b_split : &wi.group->tm_b;
+                tm_a = &P.groups[wi.group].tm_a;
+                tm_b = wi.is_slice ? &P.groups[wi.group].tm_b_split : &P.groups[wi.group].tm_b;
             }
             // bytes of one k block over the whole CTA group (posted on the leader's barrier)
             const uint32_t sub_bytes = CG * L::A_SUB_BYTES + wi.width * BK_BYTES;
@@ -860,7 +695,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
             for(int s = 0; s < STAGES && s < loads; ++s)
             {
                 const int last_fill = ((loads - 1 - s) / STAGES) * STAGES + s;
-                WaitCtx drain{&misc[2], P.wait_limit_ns, P.status}; // misc[2] stays 0: wait regardless of abort
+                WaitCtx drain{&misc[2], kDrainLimitNs, P.status}; // misc[2] stays 0: wait regardless of abort
                 bounded_wait(full_bar(s), static_cast<uint32_t>(last_fill / STAGES) & 1u, drain, WAIT_DRAIN);
             }
     }
@@ -890,9 +725,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
             const uint32_t idesc_major = (a_mn ? 1u << 15 : 0u) | (b_mn ? 1u << 16 : 0u);
             CKB_TR(long long tr_full = 0, tr_acc = 0, tr_kb = 0, tr_issue = 0, tr_commit = 0;
                    const long long tr_start = clock64();)
-            for(int slot = 0; ok && slot < P.num_slots; ++slot)
+            for(int slot = 0; ok && slot < P.plan.num_slots; ++slot)
             {
-                const WorkItem wi = decode_work<MODE, BN, KSPLIT>(P, unit, num_units, slot);
+                const WorkItem wi = decode_work<MODE, BN, KSPLIT>(P.plan, P.groups, unit, num_units, slot);
                 if(wi.kind != ITEM_TILE && wi.kind != ITEM_KSLICE)
                     continue;
                 const uint32_t idesc     = make_idesc(C_FMT, AB_FMT, TILE_M, static_cast<uint32_t>(wi.width)) | idesc_major;
@@ -983,7 +818,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                     mma_commit_pair(drain_bar);
                 else
                     mma_commit(drain_bar);
-                WaitCtx drain{&misc[2], P.wait_limit_ns, P.status};
+                WaitCtx drain{&misc[2], kDrainLimitNs, P.status};
                 bounded_wait(drain_bar, 0, drain, WAIT_DRAIN);
             }
         }
@@ -1000,13 +835,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
         st.count = 0;
         st.tm_e   = &P.tm_e;
         st.batch  = -1;
-        st.direct = P.store_direct != 0;
         if(MODE != MODE_GROUPED && P.vec_ok != 0 && lane == 0)
             tma_prefetch_desc(&P.tm_e);
         CKB_TR(long long tr_wait = 0; const long long tr_start = clock64();)
-        for(int slot = 0; ok && slot < P.num_slots; ++slot)
+        for(int slot = 0; ok && slot < P.plan.num_slots; ++slot)
         {
-            const WorkItem wi = decode_work<MODE, BN, KSPLIT>(P, unit, num_units, slot);
+            const WorkItem wi = decode_work<MODE, BN, KSPLIT>(P.plan, P.groups, unit, num_units, slot);
             if(wi.kind == ITEM_NONE)
                 continue;
             EpilogueArgs ea   = P.epi;
@@ -1014,7 +848,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
             bool vec_ok = P.vec_ok != 0;
             if constexpr(MODE == MODE_GROUPED)
             {
-                const GroupEntry* G = wi.group;
+                const GroupEntry* G = P.groups + wi.group;
                 Mdim                = G->M;
                 Ndim                = G->N;
                 vec_ok              = G->vec_ok != 0;
@@ -1028,7 +862,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
             }
             if constexpr(MODE == MODE_GEMM)
             {
-                if(P.batch_tiles > 0)
+                if(P.plan.batch_tiles > 0)
                     st.batch = wi.batch; // batched E map: third coordinate
                 if(wi.batch != 0)
                 {
@@ -1055,7 +889,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
             const uint32_t* parked = nullptr;
             if constexpr(KSPLIT)
             {
-                const uint32_t* tail_base = P.ks_partials + static_cast<int64_t>(wi.tail) * P.ksplit * TILE_M * BN;
+                const uint32_t* tail_base = P.ks_partials + static_cast<int64_t>(wi.tail) * P.plan.ksplit * TILE_M * BN;
                 if(wi.kind == ITEM_KSLICE)
                     parked = tail_base + (cta_rank * NUM_EPI_WARPS + half * 4 + quarter) * (32 * (BN / 2));
                 else if(wi.kind == ITEM_REDUCE)
@@ -1073,17 +907,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                 {
                     // every slice of this tail tile is parked once all epilogue warps that ran one have arrived
                     uint32_t* counter     = P.ks_counters + wi.tail;
-                    const uint32_t target = static_cast<uint32_t>(P.ksplit) * NUM_EPI_WARPS * CG;
-                    ok                    = bounded_wait_counter(counter, target, wc);
+                    const uint32_t target = static_cast<uint32_t>(P.plan.ksplit) * NUM_EPI_WARPS * CG;
+                    ok                    = bounded_wait_counter(counter, target + P.ks_wait_extra, wc);
                     ok                    = __all_sync(0xffffffffu, ok);
                     if(!ok)
                         break;
-                    if constexpr(epi_num_d(EPI) > 0)
-                        st.count = reduce_epilogue_call<EPI, KIND>(ea, st, lane, m, row_ok, n_begin, n_end, vec_ok, parked,
-                                                                   P.ksplit, static_cast<int64_t>(TILE_M) * BN);
-                    else
-                        epilogue_span<EPI, KIND, true>(0, ea, st, lane, m, row_ok, n_begin, n_end, vec_ok, parked,
-                                                       P.ksplit, static_cast<int64_t>(TILE_M) * BN);
+                    epilogue_span<EPI, KIND, true>(0, ea, st, lane, m, row_ok, n_begin, n_end, vec_ok, parked,
+                                                   P.plan.ksplit, static_cast<int64_t>(TILE_M) * BN);
                     // the last of the reducing warps leaves the counter at zero for the next launch
                     __syncwarp();
                     if(lane == 0 && atomicAdd(counter, 1u) + 1u == 2u * target)
@@ -1134,21 +964,21 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
             // Ask L2 for the D values of this CTA's next item while its main loop runs.
             if constexpr(KIND != KIND_I8)
             {
-                if(epi_num_d(EPI) > 0 && slot + 1 < P.num_slots)
+                if(epi_num_d(EPI) > 0 && slot + 1 < P.plan.num_slots)
                 {
-                    const WorkItem nx = decode_work<MODE, BN, KSPLIT>(P, unit, num_units, slot + 1);
+                    const WorkItem nx = decode_work<MODE, BN, KSPLIT>(P.plan, P.groups, unit, num_units, slot + 1);
                     if(nx.kind != ITEM_TILE)
                         continue;
                     EpilogueArgs en   = P.epi;
                     int Mn = P.M, Nn = P.N;
                     if constexpr(MODE == MODE_GROUPED)
                     {
-                        en.d0   = nx.group->d0;
-                        en.d1   = nx.group->d1;
-                        en.ldd0 = nx.group->ldd0;
-                        en.ldd1 = nx.group->ldd1;
-                        Mn      = nx.group->M;
-                        Nn      = nx.group->N;
+                        en.d0   = P.groups[nx.group].d0;
+                        en.d1   = P.groups[nx.group].d1;
+                        en.ldd0 = P.groups[nx.group].ldd0;
+                        en.ldd1 = P.groups[nx.group].ldd1;
+                        Mn      = P.groups[nx.group].M;
+                        Nn      = P.groups[nx.group].N;
                     }
                     if constexpr(MODE == MODE_GEMM)
                     {

@@ -19,12 +19,7 @@ template <int BN, int CG, int MODE>
 struct StagesFor
 {
     static constexpr bool conv = MODE == MODE_CONV;
-#if defined(CKB_PAIR_STAGES) && defined(CKB_PAIR_KSUB)
-    // build-time override for pipeline experiments (stages x ksub x 32 KiB must stay below 224 KiB)
-    static constexpr int pair_ksub = conv ? 1 : CKB_PAIR_KSUB, pair_stages = conv ? 6 : CKB_PAIR_STAGES;
-#else
     static constexpr int pair_ksub = conv ? 1 : 2, pair_stages = conv ? 6 : 3;
-#endif
     static constexpr int ksub  = CG == 2 ? pair_ksub : (BN == 256 || conv) ? 1 : 2;
     static constexpr int value = CG == 2 ? pair_stages : BN == 256 ? 4 : BN == 128 ? (conv ? 6 : 3) : (conv ? 8 : 4);
 };

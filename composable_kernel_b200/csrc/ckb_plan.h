@@ -1,0 +1,472 @@
+// Work decomposition of the contraction kernel: which unit (CTA or CTA pair) runs which tile, column slice or
+// K slice in which of its work slots, and the host-side choice of tile shape and tail plan.
+//
+// Plain C++ with no CUDA types: the same text is compiled into the kernel (decode_work runs in every role), into
+// the host side of the library (plan_* run before a launch) and, by g++ alone, into a host-only test that
+// enumerates every (unit, slot) of a plan and checks that each output tile, column range and k range is produced
+// exactly once - the counterpart of the reference's tile-map tests (test/block_to_ctile_map/
+// test_block_to_ctile_map.cpp:205-322) for BlockToCTileMap_M00_N0_M01Adapt (grid/block_to_ctile_map.hpp:112-173).
+#pragma once
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__CUDACC__)
+#define CKB_HD __host__ __device__ __forceinline__
+#else
+#define CKB_HD inline
+#endif
+
+namespace ckb {
+
+enum { MODE_GEMM = 0, MODE_GROUPED = 1, MODE_CONV = 2 };
+
+constexpr int BM = 128; // rows of an output tile per CTA = TMEM lanes
+
+// The work-enumeration part of the kernel parameters.
+struct PlanParams
+{
+    int32_t total_tiles; // T: (128 * cg) x BN tiles over all groups / batches
+    int32_t split_start; // first tile index whose tile is cut into column slices (= T if none)
+    int32_t split;       // column slices per tail tile (1, 2 or 4)
+    int32_t total_work;  // split_start + (T - split_start) * split
+    int32_t tiles_m, tiles_n; // GEMM / CONV: tiles per problem (per batch)
+    int32_t num_kb;      // k blocks per tile (GEMM / CONV)
+    int32_t batch_tiles; // batched GEMM: tiles per batch (0 = not batched)
+    // K-split tail (0 / 1 = off)
+    int32_t ksplit;      // K slices per tail tile
+    int32_t ks_kb;       // k blocks per slice (a multiple of the k blocks per stage)
+    int32_t ks_full;     // tiles that run whole (a multiple of the number of units); tail tiles follow
+    int32_t ks_rem;      // tail tiles
+    int32_t num_slots;   // work slots per unit
+    int32_t m_fastest;   // GEMM / CONV: consecutive tiles walk down a column of tiles instead of along a row
+    int32_t group_count; // MODE_GROUPED
+    int32_t pad_;
+};
+
+// What one work item covers.
+enum { ITEM_NONE = 0, ITEM_TILE = 1, ITEM_KSLICE = 2, ITEM_REDUCE = 3 };
+struct WorkItem
+{
+    int kind;    // ITEM_*: TILE runs all roles; KSLICE is a TILE over part of K whose accumulator is parked;
+                 // REDUCE is epilogue-only
+    int m_blk;   // row tile
+    int n_start; // first output column
+    int width;   // columns of this item (BN, or BN/split for a tail slice)
+    int kb_begin, num_kb; // k blocks [kb_begin, kb_begin + num_kb)
+    int group;   // MODE_GROUPED: index into the group table
+    int batch;   // MODE_GEMM: batch index (0 unless batched)
+    int tail;    // KSLICE / REDUCE: index of the tail tile
+    int slice;   // KSLICE: which K slice; REDUCE: which column part (of width BN / ksplit)
+    bool is_slice; // a column slice of a tail tile
+};
+
+// Finds g with groups[g].tile_start <= tile < groups[g+1].tile_start.
+template <class Group>
+CKB_HD int find_group(const Group* groups, int group_count, int tile)
+{
+    int lo = 0, hi = group_count - 1;
+    while(lo < hi)
+    {
+        const int mid = (lo + hi + 1) >> 1;
+        if(groups[mid].tile_start <= tile)
+            lo = mid;
+        else
+            hi = mid - 1;
+    }
+    return lo;
+}
+
+// Position of tile `local` of a tiles_m x tiles_n problem.  Row order (n fastest) keeps the A row band of
+// consecutive tiles in common and walks through all of B once per `units` tiles; column order (m fastest) does the
+// opposite.  The operand that is walked through again and again is the one that has to stay in L2, so the host
+// picks the order that makes it the smaller one (grouped GEMM: per group).
+CKB_HD void tile_position(int local, int tiles_m, int tiles_n, int m_fastest, int* m_blk, int* n_blk)
+{
+    if(m_fastest)
+    {
+        *n_blk = local / tiles_m;
+        *m_blk = local - *n_blk * tiles_m;
+    }
+    else
+    {
+        *m_blk = local / tiles_n;
+        *n_blk = local - *m_blk * tiles_n;
+    }
+}
+
+// Item of `unit` (CTA or CTA pair) in its work slot `slot`.
+//   plain / column-slice plan: item w = unit + slot * num_units of the list [whole tiles][slices of the tail tiles]
+//   K-split plan             : whole tile, K slice, whole tile, reduction of one column part of the tail tile,
+//                              then the remaining whole tiles (parking and reduction both overlap a main loop)
+// `groups` (MODE_GROUPED) is any array whose elements have tile_start, tiles_m, tiles_n, num_kb and m_fastest.
+template <int MODE, int BN, bool KSPLIT, class Group>
+CKB_HD WorkItem decode_work(const PlanParams& P, const Group* groups, int unit, int num_units, int slot)
+{
+    WorkItem wi;
+    int tile, slice = 0;
+    wi.kind     = ITEM_TILE;
+    wi.width    = BN;
+    wi.is_slice = false;
+    wi.batch    = 0;
+    wi.tail     = 0;
+    wi.slice    = 0;
+    wi.kb_begin = 0;
+    wi.group    = 0;
+    if(KSPLIT && P.ksplit > 1)
+    {
+        if(slot == 1)
+        {
+            wi.kind  = unit < P.ks_rem * P.ksplit ? ITEM_KSLICE : ITEM_NONE;
+            wi.tail  = unit / P.ksplit;
+            wi.slice = unit - wi.tail * P.ksplit;
+            tile     = P.ks_full + wi.tail;
+        }
+        else if(slot == 3)
+        {
+            // the unit that ran slice i of a tail tile also sums column part i of it
+            wi.kind  = unit < P.ks_rem * P.ksplit ? ITEM_REDUCE : ITEM_NONE;
+            wi.tail  = unit / P.ksplit;
+            wi.slice = unit - wi.tail * P.ksplit;
+            tile     = P.ks_full + wi.tail;
+            slice    = wi.slice;
+            wi.width = BN / P.ksplit;
+        }
+        else
+        {
+            tile = unit + (slot == 0 ? 0 : slot == 2 ? 1 : slot - 2) * num_units;
+            if(tile >= P.ks_full)
+                wi.kind = ITEM_NONE;
+        }
+        if(wi.kind == ITEM_NONE)
+            tile = 0;
+    }
+    else
+    {
+        const int w = unit + slot * num_units;
+        if(w >= P.total_work)
+        {
+            wi.kind = ITEM_NONE;
+            tile    = 0;
+        }
+        else if(w < P.split_start)
+            tile = w;
+        else
+        {
+            const int q = w - P.split_start;
+            tile        = P.split_start + q / P.split;
+            slice       = q % P.split;
+            wi.width    = BN / P.split;
+            wi.is_slice = P.split > 1;
+        }
+    }
+    int n_blk;
+    if(MODE == MODE_GROUPED)
+    {
+        wi.group       = find_group(groups, P.group_count, tile);
+        const Group& G = groups[wi.group];
+        tile_position(tile - G.tile_start, G.tiles_m, G.tiles_n, G.m_fastest, &wi.m_blk, &n_blk);
+        wi.num_kb = G.num_kb;
+    }
+    else
+    {
+        if(MODE == MODE_GEMM && P.batch_tiles > 0) // batched GEMM: batch-major tile order
+        {
+            wi.batch = tile / P.batch_tiles;
+            tile -= wi.batch * P.batch_tiles;
+        }
+        tile_position(tile, P.tiles_m, P.tiles_n, P.m_fastest, &wi.m_blk, &n_blk);
+        wi.num_kb = P.num_kb;
+    }
+    if(wi.kind == ITEM_KSLICE)
+    {
+        wi.kb_begin    = wi.slice * P.ks_kb;
+        const int rest = P.num_kb - wi.kb_begin;
+        wi.num_kb      = rest < P.ks_kb ? rest : P.ks_kb;
+    }
+    wi.n_start = n_blk * BN + slice * wi.width;
+    return wi;
+}
+
+// ---------------------------------------------------------------------------------------------- host side
+
+// A tile shape and tail plan the caller asks for instead of the library's own choice (0 = the library decides).
+// This is what distinguishes the instances an instance factory hands out.
+struct TileConfig
+{
+    int bn = 0;        // 64, 128 or 256 accumulator columns
+    int cg = 0;        // 1 = one CTA per 128 x bn tile, 2 = a CTA pair per 256 x 256 tile
+    int no_ksplit = 0; // 1 = never cut tiles along K
+};
+
+inline int pick_bn(int64_t M, int64_t N, int sm_count, int min_bn, int forced)
+{
+    if((forced == 256 || forced == 128 || forced == 64) && forced >= min_bn)
+        return forced;
+    if(N <= 64 && min_bn <= 64)
+        return 64;
+    if(N <= 128)
+        return 128;
+    // Prefer the 256-wide tile (lowest shared-memory traffic per flop) unless it leaves most of the machine idle.
+    const int64_t tiles256 = ((M + BM - 1) / BM) * ((N + 255) / 256);
+    if(tiles256 < sm_count / 2)
+        return 128;
+    return 256;
+}
+
+// CTAs per tile: pairs (256 x 256 tiles, tcgen05 cta_group::2) once the problem fills the machine with
+// 128 x 256 tiles at least once; single CTAs for small problems.
+inline int pick_cg(int64_t tiles_128, int bn, int sm_count, int forced)
+{
+    if(forced == 1 || forced == 2)
+        return bn == 256 ? forced : 1;
+    return (bn == 256 && tiles_128 >= sm_count) ? 2 : 1;
+}
+
+// Column-slice tail: the last, partial wave of tiles is cut into column slices so that it occupies every unit.
+struct WorkPlan
+{
+    int32_t split_start, split, total_work, grid;
+};
+
+// `units` = CTAs (one CTA per tile) or CTA pairs (cg = 2) that run concurrently; min_rows = narrowest B slice
+// (rows) one CTA loads.
+inline WorkPlan plan_work(int64_t total_tiles, int units, int bn, int cg, int min_rows)
+{
+    WorkPlan w;
+    const int64_t G    = units;
+    const int64_t full = (total_tiles / G) * G;
+    const int64_t rem  = total_tiles - full;
+    int split          = 1;
+    if(rem > 0)
+    {
+        // slices of >= 64 columns whose per-CTA share is >= min_rows: K-major 256 -> 4, 128 -> 2, 64 -> 1
+        const int min_width = min_rows * cg > 64 ? min_rows * cg : 64;
+        const int max_split = bn / min_width;
+        while(split * 2 <= max_split && rem * split * 2 <= G)
+            split *= 2;
+    }
+    w.split       = split;
+    w.split_start = static_cast<int32_t>(split > 1 ? full : total_tiles);
+    w.total_work  = static_cast<int32_t>(split > 1 ? full + rem * split : total_tiles);
+    w.grid        = static_cast<int32_t>((w.total_work < G ? w.total_work : G) * cg);
+    return w;
+}
+
+// Cycle estimates per k block of the MMA role, fitted to timings of 1024 x 1024 x K and 512 x 512 x K with and
+// without a K split: 590 for 256 accumulator columns, 340 for 128, 315 for 64 (the narrow ones are bound by the
+// issue rate of the single MMA thread, not by the tensor pipe).
+inline int kb_cycles(int width) { return width >= 256 ? 590 : width >= 128 ? 340 : 315; }
+
+// Whole-problem K split.  A GEMM with few output tiles and a long K leaves most SMs idle whatever the tile shape;
+// cutting every tile's K loop into 2, 4 or 8 slices (the machinery of the K-split tail, with no whole tiles before
+// it) puts 2-8 times as many SMs to work on full-width MMAs.  Parking and summing the slices costs about 9100
+// cycles (5.5 us), most of it the exposed latency of the reduction's loads.
+struct WholeSplit
+{
+    int bn = 0, cg = 0, ksplit = 0;
+};
+
+inline WholeSplit consider_whole_split(int64_t M, int64_t N, int num_kb, int sm_count, int b_min, int64_t est_current)
+{
+    WholeSplit best;
+    int64_t best_est     = est_current - est_current / 8; // has to beat the plan without it by an eighth
+    const int cand[3][2] = {{256, 2}, {256, 1}, {128, 1}};
+    for(const auto& c : cand)
+    {
+        const int bn = c[0], cg = c[1];
+        if(bn / cg < b_min || (cg == 2 && M <= BM)) // a pair tile with one half of its rows empty pays for nothing
+            continue;
+        const int64_t G     = sm_count / cg;
+        const int64_t tiles = ((M + BM * cg - 1) / (BM * cg)) * ((N + bn - 1) / bn);
+        for(int ks = bn / 32; ks >= 2; ks /= 2) // column parts of the reduction are whole 32-column chunks
+        {
+            if(tiles * ks > G)
+                continue;
+            int ks_kb = (num_kb + ks - 1) / ks;
+            ks_kb     = (ks_kb + 1) & ~1;
+            if(ks_kb < 4 || static_cast<int64_t>(ks - 1) * ks_kb >= num_kb)
+                continue;
+            const int64_t est = static_cast<int64_t>(ks_kb) * kb_cycles(bn) + 9100 + (ks > 4 ? 1500 : 0);
+            if(est < best_est)
+            {
+                best_est    = est;
+                best.bn     = bn;
+                best.cg     = cg;
+                best.ksplit = ks;
+            }
+        }
+    }
+    return best;
+}
+
+struct GemmPlanInput
+{
+    int64_t M = 0, N = 0;
+    int num_kb    = 0;
+    int64_t batch = 0;       // 0 = plain GEMM, else the batch count (batch-major tile order)
+    int sm_count  = 0;
+    int b_min     = 32;      // narrowest B slice (rows) one CTA loads
+    bool ks_pays    = false; // 16-bit operands and an epilogue without D tensors (see the K-split notes)
+    bool ks_allowed = false; // scratch may be used (not disabled, not capturing)
+    TileConfig force;
+};
+
+struct GemmPlan
+{
+    int bn = 0, cg = 0;
+    int grid = 0;         // CTAs to launch
+    int b_split_rows = 0; // rows of the B box of a tail slice, per CTA
+    PlanParams pp = {};
+    size_t partial_bytes = 0; // parked accumulators of the K split (0 = no scratch needed)
+};
+
+constexpr int kMaxTailTiles = 1024; // tail-tile counters at the front of the scratch buffer
+
+// Tile shape, CTA grouping and tail plan of one (batched) GEMM.  Returns false when the tile count does not fit.
+inline bool plan_gemm(const GemmPlanInput& in, GemmPlan* out)
+{
+    GemmPlan g;
+    const int64_t nb    = in.batch > 0 ? in.batch : 1;
+    const bool may_ks   = in.ks_pays && in.ks_allowed && !in.force.no_ksplit;
+    int bn              = pick_bn(in.M, in.N, in.sm_count, in.b_min, in.force.bn);
+    int cg              = pick_cg(((in.M + BM - 1) / BM) * ((in.N + bn - 1) / bn) * nb, bn, in.sm_count, in.force.cg);
+    const int num_kb    = in.num_kb;
+    int whole_ksplit    = 0;
+    if(may_ks && in.batch == 0 && in.force.bn == 0 && in.force.cg == 0)
+    {
+        // only where the plan without it runs a single, partly filled wave
+        const int64_t t0 = ((in.M + BM * cg - 1) / (BM * cg)) * ((in.N + bn - 1) / bn);
+        const int64_t G0 = in.sm_count / cg;
+        if(t0 * 2 <= G0)
+        {
+            const WorkPlan w0   = plan_work(t0, static_cast<int>(G0), bn, cg, in.b_min);
+            const WholeSplit ws = consider_whole_split(in.M, in.N, num_kb, in.sm_count, in.b_min,
+                                                       static_cast<int64_t>(num_kb) * kb_cycles(bn / w0.split));
+            if(ws.ksplit >= 2)
+            {
+                bn           = ws.bn;
+                cg           = ws.cg;
+                whole_ksplit = ws.ksplit;
+            }
+        }
+    }
+    const int64_t tiles_n   = (in.N + bn - 1) / bn;
+    const int64_t tiles_m   = (in.M + BM * cg - 1) / (BM * cg);
+    const int64_t all_tiles = tiles_m * tiles_n * nb;
+    if(all_tiles > 0x3FFFFFFFll)
+        return false;
+    const int64_t G   = in.sm_count / cg;
+    WorkPlan plan     = plan_work(all_tiles, static_cast<int>(G), bn, cg, in.b_min);
+    PlanParams& p     = g.pp;
+    const int64_t ful = (all_tiles / G) * G, rem = all_tiles - ful;
+    // K-split tail: with whole waves before it and a tail of at most half the units, cut the tail tiles along K.
+    // A 256-wide tail tile is cut four ways along K where a quarter of the units suffice; with more tail tiles only
+    // two K halves fit, and those beat two 128-column slices only for a long K (parking and reduction cost the same
+    // whatever K is, a column slice costs per k block): measured break-even near 78 k blocks.  The four-way cut
+    // itself needs a K loop long enough to pay for parking and reduction: taken from 40 k blocks on (48 for the
+    // two halves of a 128-wide tile, by the same cost model).
+    if(may_ks && rem > 0 && (ful > 0 || whole_ksplit >= 2) && rem * 2 <= G && rem <= kMaxTailTiles)
+    {
+        int ksplit = whole_ksplit >= 2 ? whole_ksplit
+                     : (G / rem >= 4 && bn >= 256) ? (num_kb >= 40 ? 4 : 0)
+                     : ((bn == 128 && num_kb >= 48) || (bn >= 256 && num_kb >= 80)) ? 2 : 0;
+        int ks_kb  = 0;
+        for(; ksplit >= 2; ksplit /= 2)
+        {
+            ks_kb = (num_kb + ksplit - 1) / ksplit;
+            ks_kb = (ks_kb + 1) & ~1; // slices start on a stage boundary (at most two k blocks per stage)
+            if(ks_kb >= 4 && static_cast<int64_t>(ksplit - 1) * ks_kb < num_kb)
+                break;
+        }
+        if(ksplit >= 2)
+        {
+            g.partial_bytes  = static_cast<size_t>(rem) * ksplit * (BM * cg) * bn * sizeof(uint32_t);
+            p.ksplit         = ksplit;
+            p.ks_kb          = ks_kb;
+            p.ks_full        = static_cast<int32_t>(ful);
+            p.ks_rem         = static_cast<int32_t>(rem);
+            p.num_slots      = static_cast<int32_t>(ful / G + 2 < 4 ? 4 : ful / G + 2);
+            plan.split       = 1;
+            plan.split_start = static_cast<int32_t>(all_tiles);
+            plan.total_work  = static_cast<int32_t>(all_tiles);
+            plan.grid        = static_cast<int32_t>(G * cg);
+        }
+    }
+    if(p.ksplit < 2)
+        p.num_slots = static_cast<int32_t>((plan.total_work + G - 1) / G);
+    p.total_tiles  = static_cast<int32_t>(all_tiles);
+    p.split_start  = plan.split_start;
+    p.split        = plan.split;
+    p.total_work   = plan.total_work;
+    p.tiles_m      = static_cast<int32_t>(tiles_m);
+    p.tiles_n      = static_cast<int32_t>(tiles_n);
+    p.num_kb       = num_kb;
+    p.batch_tiles  = in.batch > 0 ? static_cast<int32_t>(tiles_m * tiles_n) : 0;
+    g.bn           = bn;
+    g.cg           = cg;
+    g.grid         = plan.grid;
+    g.b_split_rows = bn / plan.split / cg;
+    *out           = g;
+    return true;
+}
+
+// One group of a grouped GEMM as the planner sees it; the kernel's table entry carries the same fields.
+struct GroupTiles
+{
+    int32_t tile_start, tiles_m, tiles_n, num_kb, m_fastest;
+};
+
+struct GroupedPlan
+{
+    int bn = 0, cg = 0, grid = 0, b_split_rows = 0;
+    PlanParams pp = {};
+};
+
+// Tile shape and work list of a grouped GEMM: `shapes` holds (M, N, num_kb) per group, `tiles` receives the
+// per-group tile counts, prefix sums and tile order.  Within a group the tile order keeps the smaller operand in
+// L2: with fewer row tiles than column tiles (M_g < N_g) consecutive tiles walk down a column of tiles, so that A_g
+// is the operand every wave reads again while B_g streams through once, and the other way round otherwise.
+inline bool plan_grouped(const int64_t (*shapes)[3], int group_count, int sm_count, int b_min, const TileConfig& force,
+                         GroupTiles* tiles, GroupedPlan* out)
+{
+    int64_t max_n = 0, sum_m = 0;
+    for(int i = 0; i < group_count; ++i)
+    {
+        max_n = max_n > shapes[i][1] ? max_n : shapes[i][1];
+        sum_m += shapes[i][0];
+    }
+    const int bn      = pick_bn(sum_m, max_n, sm_count, b_min, force.bn);
+    int64_t tiles_128 = 0;
+    for(int i = 0; i < group_count; ++i)
+        tiles_128 += ((shapes[i][0] + BM - 1) / BM) * ((shapes[i][1] + bn - 1) / bn);
+    const int cg      = pick_cg(tiles_128, bn, sm_count, force.cg);
+    int64_t all_tiles = 0;
+    for(int i = 0; i < group_count; ++i)
+    {
+        const int64_t tm = (shapes[i][0] + BM * cg - 1) / (BM * cg), tn = (shapes[i][1] + bn - 1) / bn;
+        if(all_tiles + tm * tn > 0x3FFFFFFFll)
+            return false;
+        tiles[i].tile_start = static_cast<int32_t>(all_tiles);
+        tiles[i].tiles_m    = static_cast<int32_t>(tm);
+        tiles[i].tiles_n    = static_cast<int32_t>(tn);
+        tiles[i].num_kb     = static_cast<int32_t>(shapes[i][2]);
+        tiles[i].m_fastest  = tm < tn ? 1 : 0;
+        all_tiles += tm * tn;
+    }
+    const WorkPlan plan = plan_work(all_tiles, sm_count / cg, bn, cg, b_min);
+    GroupedPlan g;
+    g.bn             = bn;
+    g.cg             = cg;
+    g.grid           = plan.grid;
+    g.b_split_rows   = bn / plan.split / cg;
+    g.pp.total_tiles = static_cast<int32_t>(all_tiles);
+    g.pp.split_start = plan.split_start;
+    g.pp.split       = plan.split;
+    g.pp.total_work  = plan.total_work;
+    g.pp.num_slots   = (plan.total_work + plan.grid / cg - 1) / (plan.grid / cg);
+    g.pp.group_count = group_count;
+    *out             = g;
+    return true;
+}
+
+} // namespace ckb

@@ -185,11 +185,13 @@ class DeviceGemmMultipleD(BaseOperator):
     """DeviceGemmMultipleD (device_gemm_multiple_d.hpp:32-53), realised by one sm_100a kernel.
 
     ``dtype`` is CKB_F16, CKB_BF16 or CKB_I8; layouts are the gemm layout tags of
-    device/tensor_layout.hpp:13-25 (A and B in either order, E row-major).
+    device/tensor_layout.hpp:13-25 (A and B in either order, E row-major).  ``tile_config`` is 0 (the library
+    chooses tile shape and tail plan) or ``capi.tile_config(bn, cg, no_ksplit)``: one instance of an instance
+    factory per value.
     """
 
-    def __init__(self, dtype=CKB_F16, a_layout=CKB_ROW_MAJOR, b_layout=CKB_COL_MAJOR):
-        self.dtype, self.a_layout, self.b_layout = dtype, a_layout, b_layout
+    def __init__(self, dtype=CKB_F16, a_layout=CKB_ROW_MAJOR, b_layout=CKB_COL_MAJOR, tile_config=0):
+        self.dtype, self.a_layout, self.b_layout, self.tile_config = dtype, a_layout, b_layout, tile_config
 
     def MakeArgument(self, p_a, p_b, p_ds: Sequence[int], p_e, M, N, K, StrideA, StrideB,
                      StrideDs: Sequence[int], StrideE, a_element_op=None, b_element_op=None,
@@ -197,6 +199,7 @@ class DeviceGemmMultipleD(BaseOperator):
         arg = GemmArgument()
         _fill_gemm_desc(arg.desc, self.dtype, self.a_layout, self.b_layout, p_a, p_b, list(p_ds), p_e,
                         M, N, K, StrideA, StrideB, list(StrideDs), StrideE, cde_element_op)
+        arg.desc.tile_config = self.tile_config
         arg.ab_ops_passthrough = _is_passthrough(a_element_op) and _is_passthrough(b_element_op)
         return arg
 
@@ -308,8 +311,8 @@ class DeviceGroupedGemm(BaseOperator):
     """DeviceGroupedGemm (device_grouped_gemm.hpp:19-44); workspace contract of
     device_grouped_gemm_xdl.hpp:816-819 (caller-allocated device memory)."""
 
-    def __init__(self, dtype=CKB_F16, a_layout=CKB_ROW_MAJOR, b_layout=CKB_COL_MAJOR):
-        self.dtype, self.a_layout, self.b_layout = dtype, a_layout, b_layout
+    def __init__(self, dtype=CKB_F16, a_layout=CKB_ROW_MAJOR, b_layout=CKB_COL_MAJOR, tile_config=0):
+        self.dtype, self.a_layout, self.b_layout, self.tile_config = dtype, a_layout, b_layout, tile_config
 
     def MakeArgument(self, p_a: Sequence[int], p_b: Sequence[int], p_ds: Sequence[Sequence[int]],
                      p_e: Sequence[int], gemm_descs: Sequence[GemmDescHost], a_element_op=None,
@@ -319,6 +322,7 @@ class DeviceGroupedGemm(BaseOperator):
         if not (len(p_a) == n and len(p_b) == n and len(p_e) == n):
             raise RuntimeError("wrong! group_count_ != P_a/b/c.size")
         arg = GroupedGemmArgument(n)
+        arg.desc.tile_config = self.tile_config
         for i, gd in enumerate(gemm_descs):
             ds = list(p_ds[i]) if p_ds else []
             _fill_gemm_desc(arg.group_descs[i], self.dtype, self.a_layout, self.b_layout, p_a[i],
@@ -366,8 +370,8 @@ class DeviceConvFwd(BaseOperator):
     3-D NDHWC/KZYXC/NDHWK, chosen by the length of the spatial vectors (the NumDimSpatial of
     DeviceConvNDFwdXdl..., device_convnd_fwd_xdl_nhwc_kyxc_nhwk.hpp:76).  ``dtype`` is CKB_F16, CKB_BF16 or CKB_I8."""
 
-    def __init__(self, dtype=CKB_F16):
-        self.dtype = dtype
+    def __init__(self, dtype=CKB_F16, tile_config=0):
+        self.dtype, self.tile_config = dtype, tile_config
 
     def MakeArgument(self, p_in, p_wei, p_out, N, K, C, input_spatial_lengths, filter_spatial_lengths,
                      output_spatial_lengths, conv_filter_strides, conv_filter_dilations,
@@ -404,6 +408,7 @@ class DeviceConvFwd(BaseOperator):
             d.pad_h, d.pad_w = lpads
             d.pad_h_right, d.pad_w_right = rpads
         d.dtype = self.dtype
+        d.tile_config = self.tile_config
         d.epilogue = out_element_op.kind
         d.N, d.K, d.C = int(N), int(K), int(C)
         d.p_in = int(p_in) if p_in else None

@@ -116,9 +116,9 @@ bool profile_gemm_typed(bool verify, int init, bool time, int M, int N, int K, i
         c_buf.SetZero();
         const float ms = inv->Run(arg.get(), StreamConfig{nullptr, time});
         if(time)
-            best.offer(op->GetTypeString(), ms, std::size_t(2) * M * N * K, sizeof(T) * (std::size_t(M) * K + std::size_t(K) * N + std::size_t(M) * N));
+            best.offer(op->GetTypeString() + " [" + op->GetBackendString() + "]", ms, std::size_t(2) * M * N * K, sizeof(T) * (std::size_t(M) * K + std::size_t(K) * N + std::size_t(M) * N));
         else
-            best.name = op->GetTypeString();
+            best.name = op->GetTypeString() + " [" + op->GetBackendString() + "]";
         if(verify)
         {
             c_buf.FromDevice(c_dev.mData.data());
@@ -226,10 +226,10 @@ int profile_gemm_add_add_fastgelu(int argc, char* argv[])
         e_buf.SetZero();
         const float ms = op->MakeInvokerPointer()->Run(arg.get(), StreamConfig{nullptr, time});
         if(time)
-            best.offer(op->GetTypeString(), ms, std::size_t(2) * M * N * K,
+            best.offer(op->GetTypeString() + " [" + op->GetBackendString() + "]", ms, std::size_t(2) * M * N * K,
                        2 * (std::size_t(M) * K + std::size_t(K) * N + N + 2 * std::size_t(M) * N));
         else
-            best.name = op->GetTypeString();
+            best.name = op->GetTypeString() + " [" + op->GetBackendString() + "]";
         if(verify)
         {
             e_buf.FromDevice(e_dev.mData.data());
@@ -306,9 +306,9 @@ int profile_grouped_gemm_layout(char* argv[])
         }
         const float ms = op->MakeInvokerPointer()->Run(arg.get(), StreamConfig{nullptr, time});
         if(time)
-            best.offer(op->GetTypeString(), ms, flop, bytes);
+            best.offer(op->GetTypeString() + " [" + op->GetBackendString() + "]", ms, flop, bytes);
         else
-            best.name = op->GetTypeString();
+            best.name = op->GetTypeString() + " [" + op->GetBackendString() + "]";
         if(verify)
             for(std::size_t i = 0; i < G; ++i)
             {
@@ -389,11 +389,11 @@ int profile_conv_fwd_bias_relu(int argc, char* argv[])
         }
         const float ms = op->MakeInvokerPointer()->Run(arg.get(), StreamConfig{nullptr, time});
         if(time)
-            best.offer(op->GetTypeString(), ms, ck::utils::conv::get_flops(p.N_, p.C_, p.K_, p.filter_spatial_lengths_, out_sp),
+            best.offer(op->GetTypeString() + " [" + op->GetBackendString() + "]", ms, ck::utils::conv::get_flops(p.N_, p.C_, p.K_, p.filter_spatial_lengths_, out_sp),
                        ck::utils::conv::get_btype<F16, F16, F16>(p.N_, p.C_, p.K_, p.input_spatial_lengths_,
                                                                  p.filter_spatial_lengths_, out_sp) + 2 * K);
         else
-            best.name = op->GetTypeString();
+            best.name = op->GetTypeString() + " [" + op->GetBackendString() + "]";
         if(verify)
         {
             out_buf.FromDevice(out_d.mData.data());
@@ -461,12 +461,12 @@ int profile_conv_fwd_bias_relu_add(int argc, char* argv[])
         }
         const float ms = op->MakeInvokerPointer()->Run(arg.get(), StreamConfig{nullptr, time});
         if(time)
-            best.offer(op->GetTypeString(), ms, ck::utils::conv::get_flops(p.N_, p.C_, p.K_, p.filter_spatial_lengths_, out_sp),
+            best.offer(op->GetTypeString() + " [" + op->GetBackendString() + "]", ms, ck::utils::conv::get_flops(p.N_, p.C_, p.K_, p.filter_spatial_lengths_, out_sp),
                        ck::utils::conv::get_btype<F16, F16, F16>(p.N_, p.C_, p.K_, p.input_spatial_lengths_,
                                                                  p.filter_spatial_lengths_, out_sp) + 2 * K +
                            2 * resi.mDesc.GetElementSpace());
         else
-            best.name = op->GetTypeString();
+            best.name = op->GetTypeString() + " [" + op->GetBackendString() + "]";
         if(verify)
         {
             out_buf.FromDevice(out_d.mData.data());
@@ -716,11 +716,11 @@ bool profile_convnd_typed(const ck::utils::conv::ConvParams& p, bool verify, int
         }
         const float ms = op->MakeInvokerPointer()->Run(arg.get(), StreamConfig{nullptr, time});
         if(time)
-            best.offer(op->GetTypeString(), ms, conv_util::get_flops(p.N_, p.C_, p.K_, p.filter_spatial_lengths_, out_sp),
+            best.offer(op->GetTypeString() + " [" + op->GetBackendString() + "]", ms, conv_util::get_flops(p.N_, p.C_, p.K_, p.filter_spatial_lengths_, out_sp),
                        conv_util::get_btype<T, T, T>(p.N_, p.C_, p.K_, p.input_spatial_lengths_,
                                                      p.filter_spatial_lengths_, out_sp));
         else
-            best.name = op->GetTypeString();
+            best.name = op->GetTypeString() + " [" + op->GetBackendString() + "]";
         if(verify)
         {
             out_buf.FromDevice(out_d.mData.data());

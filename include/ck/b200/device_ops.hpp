@@ -114,6 +114,20 @@ struct BaseOperator
 {
     virtual bool IsSupportedArgument(const BaseArgument*) { return false; }
     virtual std::string GetTypeString() const { return ""; }
+    // What runs behind the reference-style type string on this backend (not part of the reference interface).
+    virtual std::string GetBackendString() const
+    {
+        if(tile_config_ == 0)
+            return "B200 tcgen05 + TMA, tile shape chosen by the library";
+        const int bn = tile_config_ & 0xFFF, cg = (tile_config_ >> 12) & 0xF;
+        return "B200 tcgen05 + TMA, " + std::to_string(cg == 2 ? 256 : 128) + " x " + std::to_string(bn) + " tile" +
+               (cg == 2 ? " per CTA pair" : "") + (((tile_config_ >> 16) & 1) ? ", no K split" : "");
+    }
+    // Tile configuration this instance asks the library for: 0 = the library's own choice, else a
+    // CKB_TILE_CONFIG(bn, cg, no_ksplit) value (ckb200.h).  MakeArgumentPointer writes it into the argument; an
+    // instance factory hands out one operation object per configuration.
+    void SetTileConfig(int32_t tile_config) { tile_config_ = tile_config; }
+    int32_t GetTileConfig() const { return tile_config_; }
     virtual size_t GetWorkSpaceSize(const BaseArgument*) const { return 0; }
     virtual void SetWorkSpacePointer(BaseArgument* p_arg, void* p_workspace) const
     {
@@ -121,6 +135,9 @@ struct BaseOperator
         p_arg->p_workspace_ = p_workspace;
     }
     virtual ~BaseOperator() {}
+
+    protected:
+    int32_t tile_config_ = 0;
 };
 
 // ---- abstract operations -----------------------------------------------------------------------
@@ -343,6 +360,7 @@ struct GemmArgument : dev::BaseArgument
 {
     ckb_gemm_desc desc{};
     bool host_ok = true; // A/B ops are PassThrough and the epilogue functor has a device twin
+    void set_tile_config(int32_t tc) { desc.tile_config = tc; }
 };
 
 struct GemmInvoker : dev::BaseInvoker
@@ -367,6 +385,7 @@ struct BatchedGemmArgument : dev::BaseArgument
 {
     ckb_batched_gemm_desc desc{};
     bool host_ok = true;
+    void set_tile_config(int32_t tc) { desc.gemm.tile_config = tc; }
 };
 
 struct BatchedGemmInvoker : dev::BaseInvoker
@@ -428,10 +447,13 @@ inline bool gemm_supported(const GemmArgument& a) { return a.host_ok && ckb_gemm
 struct GroupedGemmArgument : dev::BaseArgument
 {
     std::vector<ckb_gemm_desc> groups;
-    bool host_ok = true;
+    bool host_ok        = true;
+    int32_t tile_config = 0;
+    void set_tile_config(int32_t tc) { tile_config = tc; }
     ckb_grouped_gemm_desc view() const
     {
         ckb_grouped_gemm_desc g{};
+        g.tile_config = tile_config;
         g.group_count = static_cast<int32_t>(groups.size());
         g.groups      = groups.data();
         return g;
@@ -471,6 +493,7 @@ struct ConvArgument : dev::BaseArgument
     ckb_conv3d_fwd_desc desc3{}; // 3-D
     bool is_3d   = false;
     bool host_ok = true;
+    void set_tile_config(int32_t tc) { desc.tile_config = desc3.tile_config = tc; }
 };
 
 inline bool conv_supported(const ConvArgument& a);
@@ -553,6 +576,19 @@ ConvArgument make_conv_argument(const void* p_in, const void* p_wei, void* p_out
     return a;
 }
 
+// device_convnd_fwd_xdl_nhwc_kyxc_nhwk.hpp:921-933.  The kernel behind these headers has no such limit (a channel
+// count that TMA cannot read in place goes through a padded copy); the rule is kept so that an instance answers as
+// the reference's instance would, and CK_B200_RELAXED_GEMM_SPECIALIZATION lifts it together with the GEMM rule.
+inline bool vector_widths_accept(index_t C, index_t K, index_t a_vec, index_t b_vec, index_t c_vec)
+{
+#ifdef CK_B200_RELAXED_GEMM_SPECIALIZATION
+    (void)C, (void)K, (void)a_vec, (void)b_vec, (void)c_vec;
+    return true;
+#else
+    return a_vec > 0 && b_vec > 0 && c_vec > 0 && C % a_vec == 0 && C % b_vec == 0 && K % c_vec == 0;
+#endif
+}
+
 // device_convnd_fwd_xdl_nhwc_kyxc_nhwk.hpp:894-919: an instance built for a 1x1 filter specialisation rejects every
 // other geometry (Default and OddC accept all).
 template <dev::ConvolutionForwardSpecialization Spec>
@@ -629,16 +665,18 @@ struct DeviceGemm_Xdl_CShuffle : public DeviceGemm<ALayout, BLayout, CLayout, AD
                                                       AElementwiseOperation a_op, BElementwiseOperation b_op,
                                                       CElementwiseOperation c_op) override
     {
-        return std::make_unique<Argument>(MakeArgument(static_cast<const ADataType*>(p_a),
+        auto arg = std::make_unique<Argument>(MakeArgument(static_cast<const ADataType*>(p_a),
                                                        static_cast<const BDataType*>(p_b), static_cast<CDataType*>(p_c),
                                                        M, N, K, StrideA, StrideB, StrideC, a_op, b_op, c_op));
+        arg->set_tile_config(this->tile_config_);
+        return arg;
     }
     std::unique_ptr<BaseInvoker> MakeInvokerPointer() override { return std::make_unique<Invoker>(); }
     std::string GetTypeString() const override
     {
         std::ostringstream s; // device_gemm_xdl_cshuffle.hpp:655-672
         s << "DeviceGemm_Xdl_CShuffle<" << BlockSize << ", " << MPerBlock << ", " << NPerBlock << ", " << KPerBlock
-          << ", " << AK1 << ", " << BK1 << "> on B200 tcgen05 (tuning parameters ignored)";
+          << ", " << AK1 << ", " << BK1 << ">";
         return s.str();
     }
 };
@@ -678,9 +716,11 @@ struct DeviceGemmXdl : public DeviceGemm<ALayout, BLayout, CLayout, ADataType, B
                                                       AElementwiseOperation a_op, BElementwiseOperation b_op,
                                                       CElementwiseOperation c_op) override
     {
-        return std::make_unique<Argument>(MakeArgument(static_cast<const ADataType*>(p_a),
+        auto arg = std::make_unique<Argument>(MakeArgument(static_cast<const ADataType*>(p_a),
                                                        static_cast<const BDataType*>(p_b), static_cast<CDataType*>(p_c),
                                                        M, N, K, StrideA, StrideB, StrideC, a_op, b_op, c_op));
+        arg->set_tile_config(this->tile_config_);
+        return arg;
     }
     std::unique_ptr<BaseInvoker> MakeInvokerPointer() override { return std::make_unique<Invoker>(); }
     std::string GetTypeString() const override
@@ -688,7 +728,7 @@ struct DeviceGemmXdl : public DeviceGemm<ALayout, BLayout, CLayout, ADataType, B
         std::ostringstream s; // device_gemm_xdl.hpp:522-541
         s << "DeviceGemmXdl<" << BlockSize << ", " << MPerBlock << ", " << NPerBlock << ", " << K0PerBlock << ", " << K1
           << ", " << MPerXDL << ", " << NPerXDL << ", " << MXdlPerWave << ", " << NXdlPerWave
-          << "> on B200 tcgen05 (tuning parameters ignored)";
+          << ">";
         return s.str();
     }
 };
@@ -734,16 +774,18 @@ struct DeviceGemmXdlSplitKCShuffle : public DeviceGemmSplitK<ALayout, BLayout, C
                                                       AElementwiseOperation a_op, BElementwiseOperation b_op,
                                                       CElementwiseOperation c_op, index_t KBatch) override
     {
-        return std::make_unique<Argument>(MakeArgument(static_cast<const ADataType*>(p_a),
+        auto arg = std::make_unique<Argument>(MakeArgument(static_cast<const ADataType*>(p_a),
                                                        static_cast<const BDataType*>(p_b), static_cast<CDataType*>(p_c),
                                                        M, N, K, StrideA, StrideB, StrideC, a_op, b_op, c_op, KBatch));
+        arg->set_tile_config(this->tile_config_);
+        return arg;
     }
     std::unique_ptr<BaseInvoker> MakeInvokerPointer() override { return std::make_unique<Invoker>(); }
     std::string GetTypeString() const override
     {
         std::ostringstream s;
         s << "DeviceGemmXdlSplitKCShuffle<" << BlockSize << ", " << MPerBlock << ", " << NPerBlock << ", " << K0PerBlock
-          << "> on B200 tcgen05 (tuning parameters and KBatch ignored)";
+          << ">";
         return s.str();
     }
 };
@@ -794,16 +836,18 @@ struct DeviceBatchedGemmXdl : public DeviceBatchedGemm<ALayout, BLayout, CLayout
                         index_t BatchStrideC, index_t Batch, AElementwiseOperation a_op, BElementwiseOperation b_op,
                         CElementwiseOperation c_op) override
     {
-        return std::make_unique<Argument>(MakeArgument(
+        auto arg = std::make_unique<Argument>(MakeArgument(
             static_cast<const ADataType*>(p_a), static_cast<const BDataType*>(p_b), static_cast<CDataType*>(p_c), M, N, K,
             StrideA, StrideB, StrideC, BatchStrideA, BatchStrideB, BatchStrideC, Batch, a_op, b_op, c_op));
+        arg->set_tile_config(this->tile_config_);
+        return arg;
     }
     std::unique_ptr<BaseInvoker> MakeInvokerPointer() override { return std::make_unique<Invoker>(); }
     std::string GetTypeString() const override
     {
         std::ostringstream s; // device_batched_gemm_xdl.hpp:625-644
         s << "DeviceBatchedGemmXdl<" << BlockSize << ", " << MPerBlock << ", " << NPerBlock << ", " << K0PerBlock
-          << "> on B200 tcgen05 (tuning parameters ignored)";
+          << ">";
         return s.str();
     }
 };
@@ -850,8 +894,10 @@ struct DeviceGemmMultipleD_Xdl_CShuffle
                         index_t StrideE, AElementwiseOperation a_op, BElementwiseOperation b_op,
                         CDEElementwiseOperation cde_op) override
     {
-        return std::make_unique<Argument>(
+        auto arg = std::make_unique<Argument>(
             MakeArgument(p_a, p_b, p_ds, p_e, M, N, K, StrideA, StrideB, StrideDs, StrideE, a_op, b_op, cde_op));
+        arg->set_tile_config(this->tile_config_);
+        return arg;
     }
     std::unique_ptr<BaseInvoker> MakeInvokerPointer() override { return std::make_unique<Invoker>(); }
     std::string GetTypeString() const override
@@ -859,7 +905,7 @@ struct DeviceGemmMultipleD_Xdl_CShuffle
         std::ostringstream s; // device_gemm_multiple_d_xdl_cshuffle.hpp:735-753
         s << "DeviceGemmMultipleD_Xdl_CShuffle<" << BlockSize << ", " << MPerBlock << ", " << NPerBlock << ", "
           << KPerBlock << ", " << AK1 << ", " << BK1 << ", " << getGemmSpecializationString(GemmSpec)
-          << "> on B200 tcgen05 (tuning parameters ignored)";
+          << ">";
         return s.str();
     }
 };
@@ -930,7 +976,9 @@ struct DeviceGroupedGemmXdl
                         std::vector<GemmDesc>& gemm_descs, AElementwiseOperation a_op, BElementwiseOperation b_op,
                         CDEElementwiseOperation c_op) override
     {
-        return std::make_unique<Argument>(MakeArgument(p_a, p_b, p_ds, p_e, gemm_descs, a_op, b_op, c_op));
+        auto arg = std::make_unique<Argument>(MakeArgument(p_a, p_b, p_ds, p_e, gemm_descs, a_op, b_op, c_op));
+        arg->set_tile_config(this->tile_config_);
+        return arg;
     }
     std::unique_ptr<BaseInvoker> MakeInvokerPointer() override { return std::make_unique<Invoker>(); }
     // device_grouped_gemm_xdl.hpp:816-819: caller-allocated device memory
@@ -943,7 +991,7 @@ struct DeviceGroupedGemmXdl
         std::ostringstream s; // device_grouped_gemm_xdl.hpp:793-814
         s << "DeviceGroupedGemmXdl<" << BlockSize << ", " << MPerBlock << ", " << NPerBlock << ", " << KPerBlock << ", "
           << AK1 << ", " << BK1 << ", " << MPerXDL << ", " << NPerXDL << ", " << MXdlPerWave << ", " << NXdlPerWave
-          << "> on B200 tcgen05 (tuning parameters ignored)";
+          << ">";
         return s.str();
     }
 };
@@ -976,7 +1024,11 @@ struct DeviceConvNDFwdXdl_Input_N_Hi_Wi_C_Weight_K_Y_X_C_Output_N_Ho_Wo_K
         arg.host_ok = arg.host_ok && static_cast<std::size_t>(NumDimSpatial) == input_spatial_lengths.size() &&
                       std::is_same<InDataType, WeiDataType>::value && std::is_same<InDataType, OutDataType>::value &&
                       b200::conv_specialization_accepts<ConvForwardSpecialization>(
-                          filter_spatial_lengths, conv_filter_strides, input_left_pads, input_right_pads);
+                          filter_spatial_lengths, conv_filter_strides, input_left_pads, input_right_pads) &&
+                      // device_convnd_fwd_xdl_nhwc_kyxc_nhwk.hpp:921-933: the instance's vector widths must divide
+                      // C and K - a channel count like C = 3 needs the ScalarPerVector = 1 (OddC) instances
+                      b200::vector_widths_accept(C, K, ABlockTransferSrcScalarPerVector, BBlockTransferSrcScalarPerVector,
+                                                 CThreadTransferDstScalarPerVector);
         return arg;
     }
     static auto MakeInvoker() { return Invoker{}; }
@@ -992,19 +1044,21 @@ struct DeviceConvNDFwdXdl_Input_N_Hi_Wi_C_Weight_K_Y_X_C_Output_N_Ho_Wo_K
                         std::vector<index_t> rpads, InElementwiseOperation in_op, WeiElementwiseOperation wei_op,
                         OutElementwiseOperation out_op) override
     {
-        return std::make_unique<Argument>(MakeArgument(static_cast<const InDataType*>(p_in),
+        auto arg = std::make_unique<Argument>(MakeArgument(static_cast<const InDataType*>(p_in),
                                                        static_cast<const WeiDataType*>(p_wei),
                                                        static_cast<OutDataType*>(p_out), N, K, C, in_sp, filt_sp, out_sp,
                                                        strides, dilations, lpads, rpads, in_op, wei_op, out_op));
+        arg->set_tile_config(this->tile_config_);
+        return arg;
     }
     std::unique_ptr<BaseInvoker> MakeInvokerPointer() override { return std::make_unique<Invoker>(); }
     std::string GetTypeString() const override
     {
         std::ostringstream s;
-        s << "DeviceConv" << NumDimSpatial << "DFwdXdl_Input_N_Hi_Wi_C_Weight_K_Y_X_C_Output_N_Ho_Wo_K<" << BlockSize
+        s << "DeviceConvNDFwdXdl_Input_N_Hi_Wi_C_Weight_K_Y_X_C_Output_N_Ho_Wo_K<" << BlockSize
           << ", " << MPerBlock << ", " << NPerBlock << ", " << K0PerBlock << ", "
           << getConvForwardSpecializationString(ConvForwardSpecialization)
-          << "> on B200 tcgen05 + im2col TMA (tuning parameters ignored)";
+          << ">";
         return s.str();
     }
 };
@@ -1056,10 +1110,12 @@ struct DeviceConv2dFwdXdl_C_Shuffle_Bias_Activation_Input_N_Hi_Wi_C_Weight_K_Y_X
                         std::vector<index_t> rpads, InElementwiseOperation in_op, WeiElementwiseOperation wei_op,
                         OutElementwiseOperation out_op) override
     {
-        return std::make_unique<Argument>(
+        auto arg = std::make_unique<Argument>(
             MakeArgument(static_cast<const InDataType*>(p_in), static_cast<const WeiDataType*>(p_wei),
                          static_cast<OutDataType*>(p_out), static_cast<const OutDataType*>(p_bias), N, K, C, in_sp,
                          filt_sp, out_sp, strides, dilations, lpads, rpads, in_op, wei_op, out_op));
+        arg->set_tile_config(this->tile_config_);
+        return arg;
     }
     std::unique_ptr<BaseInvoker> MakeInvokerPointer() override { return std::make_unique<Invoker>(); }
     std::string GetTypeString() const override
@@ -1067,7 +1123,7 @@ struct DeviceConv2dFwdXdl_C_Shuffle_Bias_Activation_Input_N_Hi_Wi_C_Weight_K_Y_X
         std::ostringstream s;
         s << "DeviceConv2dFwdXdl_C_Shuffle_Bias_Activation_Input_N_Hi_Wi_C_Weight_K_Y_X_C_Output_N_Ho_Wo_K<" << BlockSize
           << ", " << MPerBlock << ", " << NPerBlock << ", " << K0PerBlock
-          << "> on B200 tcgen05 + im2col TMA (tuning parameters ignored)";
+          << ">";
         return s.str();
     }
 };
@@ -1119,11 +1175,13 @@ struct DeviceConv2dFwdXdl_C_Shuffle_Bias_Activation_Add_Input_N_Hi_Wi_C_Weight_K
                         std::vector<index_t> lpads, std::vector<index_t> rpads, InElementwiseOperation in_op,
                         WeiElementwiseOperation wei_op, OutElementwiseOperation out_op) override
     {
-        return std::make_unique<Argument>(
+        auto arg = std::make_unique<Argument>(
             MakeArgument(static_cast<const InDataType*>(p_in), static_cast<const WeiDataType*>(p_wei),
                          static_cast<OutDataType*>(p_out), static_cast<const OutDataType*>(p_bias),
                          static_cast<const OutDataType*>(p_resi), N, K, C, in_sp, filt_sp, out_sp, strides, dilations,
                          lpads, rpads, in_op, wei_op, out_op));
+        arg->set_tile_config(this->tile_config_);
+        return arg;
     }
     std::unique_ptr<BaseInvoker> MakeInvokerPointer() override { return std::make_unique<Invoker>(); }
     std::string GetTypeString() const override
@@ -1131,7 +1189,7 @@ struct DeviceConv2dFwdXdl_C_Shuffle_Bias_Activation_Add_Input_N_Hi_Wi_C_Weight_K
         std::ostringstream s;
         s << "DeviceConv2dFwdXdl_C_Shuffle_Bias_Activation_Add_Input_N_Hi_Wi_C_Weight_K_Y_X_C_Output_N_Ho_Wo_K<"
           << BlockSize << ", " << MPerBlock << ", " << NPerBlock << ", " << K0PerBlock
-          << "> on B200 tcgen05 + im2col TMA (tuning parameters ignored)";
+          << ">";
         return s.str();
     }
 };

@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define CKB_ABI_VERSION 1
+#define CKB_ABI_VERSION 2
 
 /* ---- error codes ------------------------------------------------------- */
 enum {
@@ -100,6 +100,19 @@ enum {
 
 #define CKB_MAX_DS 2
 
+/* ---- tile configuration (field `tile_config` of the descriptors) ------------------------
+ * 0 = the library chooses the tile shape and the plan for the last, partial wave of tiles from
+ * the problem size.  CKB_TILE_CONFIG(bn, cg, no_ksplit) fixes them, which is how an instance
+ * factory (library/include/ck/library/tensor_operation_instance/gpu/gemm.hpp:233-378 hands out
+ * one device operation per tile configuration) exposes several instances of one operation:
+ *   bn        accumulator columns of a tile: 64, 128 or 256 (0 = library's choice)
+ *   cg        CTAs per tile: 1 = 128 x bn tiles, 2 = a CTA pair on a 256 x 256 tile
+ *             (tcgen05 cta_group::2; bn must be 256 or 0); 0 = library's choice
+ *   no_ksplit 1 = never cut tiles along K (keeps a call free of library scratch memory)
+ * A configuration that the problem cannot use (bn below the narrowest tile of the B layout) falls
+ * back to the library's choice for that field. */
+#define CKB_TILE_CONFIG(bn, cg, no_ksplit) ((bn) | ((cg) << 12) | ((no_ksplit) << 16))
+
 /* ---- GEMM: E = epilogue(A*B, D0, D1) ------------------------------------- */
 /* Replaces DeviceGemm::MakeArgumentPointer (device/device_gemm.hpp:26-38) and
  * DeviceGemmMultipleD::MakeArgumentPointer (device/device_gemm_multiple_d.hpp:36-50). */
@@ -111,7 +124,7 @@ typedef struct ckb_gemm_desc {
     int32_t e_layout;            /* E (and every D) is M x N; only CKB_ROW_MAJOR         */
     int32_t epilogue;            /* CKB_EPI_*                                            */
     int32_t n_ds;                /* number of D tensors the epilogue reads (0..2)        */
-    int32_t reserved0;
+    int32_t tile_config;         /* 0 or CKB_TILE_CONFIG(...)                            */
     int64_t M, N, K;
     int64_t lda, ldb, lde;       /* leading dimensions in elements                       */
     int64_t ldd[CKB_MAX_DS];     /* row stride of each D; 0 = one row broadcast over M   */
@@ -134,8 +147,12 @@ int ckb_gemm_supported(const ckb_gemm_desc* desc);
  * Replaces DeviceGemm_Xdl_CShuffle::Invoker::Run (device_gemm_xdl_cshuffle.hpp:456-563).
  *
  * Scratch memory: a 16-bit GEMM whose last wave of tiles is partial may cut those tiles along K, which needs
- * device scratch (4 bytes per accumulator of the tail tiles, at most a few tens of MB).  The library allocates it
- * once per stream on the first such call, grows it on demand and keeps it until ckb_release_scratch.
+ * device scratch.  The library allocates it once per stream on the first such call, sized for the largest plan it
+ * can make (4 KiB + 128 KiB per SM: 19 MB on a B200), so it never grows, and keeps it until ckb_release_scratch.
+ * Operands that TMA cannot read in place (A or B whose base or pitch is not a multiple of 16 bytes - the problems
+ * the reference serves with its ScalarPerVector = 1 instances) are first copied into a temporary with a padded pitch,
+ * allocated and freed on `stream` (cudaMallocAsync / cudaFreeAsync: no device synchronisation); the copy is part of
+ * the call and of its timing.  Such a call cannot be captured into a graph.
  * CUDA graphs: with n_rep = 0 the GEMM, batched-GEMM and convolution launches can be captured into a graph (call
  * the library once on the device outside a capture first); a captured launch never uses the scratch, so a graph
  * may be replayed on any stream.  ckb_grouped_gemm_run copies a table from host memory at every launch; when it is
@@ -167,7 +184,7 @@ int ckb_batched_gemm_run(const ckb_batched_gemm_desc* desc, void* stream, int n_
  * share dtypes, layouts and the epilogue. */
 typedef struct ckb_grouped_gemm_desc {
     int32_t group_count;
-    int32_t reserved0;
+    int32_t tile_config;         /* 0 or CKB_TILE_CONFIG(...); the groups' own fields are ignored */
     const ckb_gemm_desc* groups; /* host array of group_count descriptors */
 } ckb_grouped_gemm_desc;
 
@@ -215,7 +232,9 @@ int ckb_grouped_gemm_run_noalloc(const ckb_grouped_gemm_desc* desc, void* stream
  * (device/device_conv_fwd_bias_activation.hpp:21-38).
  * out[n,ho,wo,k] = epilogue( sum_{y,x,c} in[n, ho*sh + y*dh - ph, wo*sw + x*dw - pw, c]
  *                                        * wei[k,y,x,c],  bias[k] )
- * taps outside the image contribute zero.  All three tensors are packed. */
+ * taps outside the image contribute zero.  All three tensors are packed.  A channel count whose pixel pitch is
+ * not a multiple of 16 bytes (ConvolutionForwardSpecialization::OddC, e.g. C = 3) runs through a zero-padded
+ * stream-ordered copy of input and weights, like the unaligned GEMM operands above. */
 typedef struct ckb_conv2d_fwd_desc {
     int32_t dtype;               /* CKB_F16 / CKB_BF16 / CKB_I8 (in, wei, out, bias)     */
     int32_t epilogue;            /* PASSTHROUGH, RELU, ADD_RELU (bias), ADD_HARDSWISH (bias),
@@ -228,7 +247,7 @@ typedef struct ckb_conv2d_fwd_desc {
     int32_t dilation_h, dilation_w;
     int32_t pad_h, pad_w;            /* left pads  */
     int32_t pad_h_right, pad_w_right;
-    int32_t reserved0;
+    int32_t tile_config;         /* 0 or CKB_TILE_CONFIG(...)                            */
     const void* p_in;
     const void* p_wei;
     void* p_out;
@@ -258,7 +277,7 @@ typedef struct ckb_conv3d_fwd_desc {
     int32_t dilation_d, dilation_h, dilation_w;
     int32_t pad_d, pad_h, pad_w;     /* left pads */
     int32_t pad_d_right, pad_h_right, pad_w_right;
-    int32_t reserved0;
+    int32_t tile_config;         /* 0 or CKB_TILE_CONFIG(...)                            */
     const void* p_in;
     const void* p_wei;
     void* p_out;

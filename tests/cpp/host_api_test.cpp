@@ -215,8 +215,11 @@ static void test_traits_and_support()
     GemmSpec<dev::GemmSpecialization::KPadding> k_padded;
     EXPECT(k_padded.IsSupportedArgument(k_padded.MakeArgument(pa, pb, pc, 512, 256, 72, 72, 72, 256, {}, {}, {})));
     EXPECT(!k_padded.IsSupportedArgument(k_padded.MakeArgument(pa, pb, pc, 500, 256, 72, 72, 72, 256, {}, {}, {})));
-    // strides that TMA cannot address are refused whatever the specialisation
-    auto bad = padded.MakeArgument(pa, pb, pc, 100, 40, 70, 70, 70, 40, {}, {}, {});
+    // a pitch that TMA cannot address in place is served through a padded copy (the reference's ScalarPerVector = 1 case)
+    auto odd = padded.MakeArgument(pa, pb, pc, 100, 40, 70, 70, 70, 40, {}, {}, {});
+    EXPECT(padded.IsSupportedArgument(odd));
+    // a leading dimension shorter than the row is refused whatever the specialisation
+    auto bad = padded.MakeArgument(pa, pb, pc, 100, 40, 72, 64, 72, 40, {}, {}, {});
     EXPECT(!padded.IsSupportedArgument(bad));
     bool threw = false;
     try
@@ -228,7 +231,8 @@ static void test_traits_and_support()
         threw = std::string(e.what()).find("GridwiseGemm has invalid setting") != std::string::npos;
     }
     EXPECT(threw); // device_gemm_xdl_cshuffle.hpp:475-481
-    EXPECT(gemm.GetTypeString().find("DeviceGemm_Xdl_CShuffle<256, 256, 128, 32, 8, 8>") == 0);
+    EXPECT(gemm.GetTypeString() == "DeviceGemm_Xdl_CShuffle<256, 256, 128, 32, 8, 8>"); // device_gemm_xdl_cshuffle.hpp:655-672
+    EXPECT(gemm.GetBackendString().find("B200") == 0);
 
     Gemm<Col, Col, F16, ew::PassThrough> gemm_km; // A column-major (km_nk): lda counts M
     auto km = gemm_km.MakeArgument(pa, pb, pc, 256, 256, 128, 256, 128, 256, {}, {}, {});
@@ -332,7 +336,17 @@ static void test_instance_factory()
     {
         using Op = dev::DeviceGemm<Row, Col, Row, ck::half_t, ck::half_t, ck::half_t, PT, PT, PT>;
         auto ops = inst::DeviceOperationInstanceFactory<Op>::GetInstances();
-        EXPECT(ops.size() == 1);
+        EXPECT(ops.size() == 6); // the library's own choice + five pinned tile configurations
+        EXPECT(ops[0]->GetTileConfig() == 0 && ops[1]->GetTileConfig() == CKB_TILE_CONFIG(256, 2, 0));
+        EXPECT(ops[1]->GetTypeString() == "DeviceGemm_Xdl_CShuffle<320, 256, 256, 64, 8, 8>");
+        EXPECT(ops[4]->GetTypeString() == "DeviceGemm_Xdl_CShuffle<320, 128, 64, 64, 8, 8>");
+        EXPECT(ops[5]->GetBackendString().find("no K split") != std::string::npos);
+        for(auto& op : ops)
+        {
+            auto a = op->MakeArgumentPointer(pa, pa, pc, 256, 256, 64, 64, 64, 256, {}, {}, {});
+            EXPECT(op->IsSupportedArgument(a.get()));
+            EXPECT(dynamic_cast<ck::b200::GemmArgument*>(a.get())->desc.tile_config == op->GetTileConfig());
+        }
         auto arg = ops[0]->MakeArgumentPointer(pa, pa, pc, 256, 256, 64, 64, 64, 256, {}, {}, {});
         EXPECT(ops[0]->IsSupportedArgument(arg.get()));
         EXPECT(ops[0]->GetTypeString().find("DeviceGemm_Xdl_CShuffle") != std::string::npos);
@@ -361,7 +375,7 @@ static void test_instance_factory()
         using Op = dev::DeviceGemmMultipleD<Row, Col, Row, ck::half_t, ck::half_t, inst::F16_F16_TUPLE, ck::half_t, PT, PT,
                                             inst::AddAddFastGelu>;
         auto ops = inst::DeviceOperationInstanceFactory<Op>::GetInstances();
-        EXPECT(ops.size() == 1);
+        EXPECT(ops.size() == 6);
         auto arg = ops[0]->MakeArgumentPointer(pa, pa, std::array<const void*, 2>{pa, pa}, pc, 256, 256, 64, 64, 64,
                                                std::array<ck::index_t, 2>{0, 256}, 256, {}, {}, {});
         EXPECT(ops[0]->IsSupportedArgument(arg.get()));
@@ -369,13 +383,16 @@ static void test_instance_factory()
     {
         using Op = dev::DeviceGroupedGemm<Row, Col, Row, ck::half_t, ck::half_t, inst::EMPTY_TUPLE, ck::half_t, PT, PT, PT>;
         auto ops = inst::DeviceOperationInstanceFactory<Op>::GetInstances();
-        EXPECT(ops.size() == 1);
+        EXPECT(ops.size() == 6);
         std::vector<const void*> as{pa, pa}, bs{pa, pa};
         std::vector<void*> cs{pc, pc};
         std::vector<std::array<const void*, 0>> ds(2);
         std::vector<dev::GemmDesc> descs{{256, 128, 64, 64, 64, 128, {}}, {512, 256, 128, 128, 128, 256, {}}};
         auto arg = ops[0]->MakeArgumentPointer(as, bs, ds, cs, descs, {}, {}, {});
         EXPECT(ops[0]->GetWorkSpaceSize(arg.get()) > 0);
+        auto arg3 = ops[3]->MakeArgumentPointer(as, bs, ds, cs, descs, {}, {}, {});
+        EXPECT(ops[3]->IsSupportedArgument(arg3.get()));
+        EXPECT(dynamic_cast<ck::b200::GroupedGemmArgument*>(arg3.get())->view().tile_config == CKB_TILE_CONFIG(128, 1, 0));
     }
 }
 
@@ -473,7 +490,10 @@ static void test_convnd_host_side()
     auto mismatch = Conv3d::MakeArgument(pa, pa, pc, 4, 256, 64, {28, 28}, {3, 3}, {14, 14}, {2, 2}, {2, 2}, {2, 2},
                                          {2, 2}, {}, {}, {});
     EXPECT(!Conv3d::IsSupportedArgument(mismatch)); // a 2-D problem handed to the 3-D instance
-    EXPECT(Conv3d{}.GetTypeString().find("DeviceConv3DFwdXdl") == 0);
+    EXPECT(Conv3d{}.GetTypeString().find("DeviceConvNDFwdXdl_Input_N_Hi_Wi_C_Weight_K_Y_X_C_Output_N_Ho_Wo_K<") == 0);
+    // device_convnd_fwd_xdl_nhwc_kyxc_nhwk.hpp:921-933: C = 3 needs an instance whose vector widths divide it
+    auto c3 = Conv1d::MakeArgument(pa, pa, pc, 4, 256, 3, {71}, {3}, {36}, {2}, {2}, {2}, {2}, {}, {}, {});
+    EXPECT(!Conv1d::IsSupportedArgument(c3));
 }
 
 int main()

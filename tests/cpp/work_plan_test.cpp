@@ -1,0 +1,299 @@
+// Host-only test of the kernel's work decomposition (composable_kernel_b200/csrc/ckb_plan.h): for a sweep of
+// problem sizes, SM counts, tile configurations, batch counts and group tables, every (unit, slot) of the plan is
+// decoded exactly as the kernel's roles decode it, and the test asserts that
+//   - every 32-column chunk of every output tile is written exactly once (by a whole tile, a column slice or a
+//     reduction part), with valid tile indices;
+//   - under a K split every tail tile's k blocks are covered exactly once by its slices, each slice starts on a
+//     stage boundary, the unit that runs slice i reduces column part i, every unit of the launch is needed at the
+//     same time only up to the number of units, and the parked partials fit the fixed scratch size;
+//   - the grouped table's prefix sums, per-group tile order and binary search agree.
+// It is the counterpart of the reference's tile-map tests (test/block_to_ctile_map/test_block_to_ctile_map.cpp:205-322).
+// Build: g++ -std=c++17 -I composable_kernel_b200/csrc tests/cpp/work_plan_test.cpp
+#include <array>
+#include <cstdio>
+#include <cstdlib>
+#include <map>
+#include <random>
+#include <tuple>
+#include <vector>
+
+#include "ckb_plan.h"
+
+using namespace ckb;
+
+static long g_checks = 0, g_plans = 0, g_ksplit_plans = 0, g_slice_plans = 0;
+
+#define REQUIRE(cond, ...)                                \
+    do                                                    \
+    {                                                     \
+        ++g_checks;                                       \
+        if(!(cond))                                       \
+        {                                                 \
+            std::printf("FAILED %s:%d: %s\n  ", __FILE__, __LINE__, #cond); \
+            std::printf(__VA_ARGS__);                     \
+            std::printf("\n");                            \
+            std::exit(1);                                 \
+        }                                                 \
+    } while(0)
+
+struct Coverage
+{
+    // key: (group or batch, m_blk, first column of a 32-column chunk) -> times written
+    std::map<std::tuple<int, int, int>, int> out;
+    // key: tail tile -> per k block, times accumulated
+    std::map<int, std::vector<int>> tail_k;
+    std::map<int, std::vector<int>> tail_slices; // tail -> slice ids seen
+};
+
+template <int MODE, int BN, bool KSPLIT>
+static void walk(const PlanParams& P, const GroupTiles* groups, int cg, int grid, Coverage& cov)
+{
+    const int num_units = grid / cg;
+    for(int unit = 0; unit < num_units; ++unit)
+        for(int slot = 0; slot < P.num_slots; ++slot)
+        {
+            const WorkItem wi = decode_work<MODE, BN, KSPLIT>(P, groups, unit, num_units, slot);
+            if(wi.kind == ITEM_NONE)
+                continue;
+            const int scope = MODE == MODE_GROUPED ? wi.group : wi.batch;
+            const int tiles_m = MODE == MODE_GROUPED ? groups[wi.group].tiles_m : P.tiles_m;
+            const int tiles_n = MODE == MODE_GROUPED ? groups[wi.group].tiles_n : P.tiles_n;
+            REQUIRE(wi.m_blk >= 0 && wi.m_blk < tiles_m, "m_blk %d of %d", wi.m_blk, tiles_m);
+            REQUIRE(wi.n_start >= 0 && wi.n_start + wi.width <= tiles_n * BN, "columns [%d, %d) of %d", wi.n_start,
+                    wi.n_start + wi.width, tiles_n * BN);
+            REQUIRE(wi.width >= 32 && wi.width % 32 == 0 && wi.n_start % 32 == 0, "width %d start %d", wi.width, wi.n_start);
+            if(wi.kind == ITEM_TILE || wi.kind == ITEM_REDUCE)
+                for(int c = wi.n_start; c < wi.n_start + wi.width; c += 32)
+                    ++cov.out[{scope, wi.m_blk, c}];
+            if(wi.kind == ITEM_TILE)
+            {
+                const int want_kb = MODE == MODE_GROUPED ? groups[wi.group].num_kb : P.num_kb;
+                REQUIRE(wi.kb_begin == 0 && wi.num_kb == want_kb, "whole tile covers k blocks [%d, +%d) of %d", wi.kb_begin,
+                        wi.num_kb, want_kb);
+                if(wi.is_slice)
+                    REQUIRE(wi.width == BN / P.split && wi.width >= 64, "slice width %d", wi.width);
+            }
+            if(wi.kind == ITEM_KSLICE)
+            {
+                REQUIRE(KSPLIT && slot == 1, "K slice outside slot 1");
+                REQUIRE(wi.tail >= 0 && wi.tail < P.ks_rem && wi.slice < P.ksplit, "tail %d slice %d", wi.tail, wi.slice);
+                REQUIRE(wi.width == BN && wi.n_start % BN == 0, "a K slice covers the whole tile width");
+                REQUIRE(wi.kb_begin % 2 == 0 && wi.num_kb >= 1, "slice [%d, +%d)", wi.kb_begin, wi.num_kb);
+                REQUIRE(unit == wi.tail * P.ksplit + wi.slice, "slice owner");
+                auto& v = cov.tail_k[wi.tail];
+                v.resize(P.num_kb, 0);
+                for(int k = wi.kb_begin; k < wi.kb_begin + wi.num_kb; ++k)
+                {
+                    REQUIRE(k < P.num_kb, "k block %d of %d", k, P.num_kb);
+                    ++v[k];
+                }
+                cov.tail_slices[wi.tail].push_back(wi.slice);
+            }
+            if(wi.kind == ITEM_REDUCE)
+            {
+                REQUIRE(KSPLIT && slot == 3, "reduction outside slot 3");
+                REQUIRE(unit == wi.tail * P.ksplit + wi.slice, "the unit that ran slice i reduces part i");
+                REQUIRE(wi.width == BN / P.ksplit && wi.width >= 32, "reduction part width %d", wi.width);
+            }
+        }
+}
+
+template <int MODE, bool KSPLIT>
+static void walk_bn(int bn, const PlanParams& P, const GroupTiles* groups, int cg, int grid, Coverage& cov)
+{
+    if(bn == 256)
+        walk<MODE, 256, KSPLIT>(P, groups, cg, grid, cov);
+    else if(bn == 128)
+        walk<MODE, 128, KSPLIT>(P, groups, cg, grid, cov);
+    else if(bn == 64)
+        walk<MODE, 64, KSPLIT>(P, groups, cg, grid, cov);
+    else
+        REQUIRE(false, "tile width %d", bn);
+}
+
+static void check_gemm_plan(const GemmPlanInput& in)
+{
+    GemmPlan gp;
+    REQUIRE(plan_gemm(in, &gp), "plan_gemm refused M=%lld N=%lld", (long long)in.M, (long long)in.N);
+    ++g_plans;
+    const PlanParams& P = gp.pp;
+    const int cg = gp.cg, bn = gp.bn, units = in.sm_count / cg;
+    REQUIRE(cg == 1 || (cg == 2 && bn == 256), "cg %d bn %d", cg, bn);
+    REQUIRE(gp.grid % cg == 0 && gp.grid >= cg && gp.grid <= units * cg, "grid %d", gp.grid);
+    REQUIRE(bn / cg >= in.b_min || bn == 64, "B rows per CTA %d below the minimum %d", bn / cg, in.b_min);
+    const int64_t nb = in.batch > 0 ? in.batch : 1;
+    REQUIRE(P.tiles_m == (in.M + BM * cg - 1) / (BM * cg) && P.tiles_n == (in.N + bn - 1) / bn, "tile counts");
+    REQUIRE(P.total_tiles == static_cast<int64_t>(P.tiles_m) * P.tiles_n * nb, "total tiles");
+    if(P.ksplit >= 2)
+    {
+        ++g_ksplit_plans;
+        REQUIRE(in.ks_pays && in.ks_allowed && !in.force.no_ksplit, "K split where it is not allowed");
+        REQUIRE(gp.grid == units * cg, "a K-split launch uses every unit");
+        REQUIRE(P.ks_full % units == 0 && P.ks_full + P.ks_rem == P.total_tiles, "whole tiles %d + tail %d", P.ks_full, P.ks_rem);
+        REQUIRE(P.ks_rem * P.ksplit <= units, "slices %d x %d beyond the %d units", P.ks_rem, P.ksplit, units);
+        REQUIRE(P.ks_rem <= kMaxTailTiles, "tail tiles beyond the counters");
+        REQUIRE(P.ks_kb % 2 == 0 && P.ks_kb * (P.ksplit - 1) < P.num_kb && P.ks_kb * P.ksplit >= P.num_kb, "slice length");
+        REQUIRE(bn / P.ksplit >= 32, "reduction part narrower than a chunk");
+        REQUIRE(gp.partial_bytes == static_cast<size_t>(P.ks_rem) * P.ksplit * BM * cg * bn * 4, "parked bytes");
+        REQUIRE(gp.partial_bytes <= static_cast<size_t>(in.sm_count) * BM * 256 * 4, "parked bytes beyond the fixed scratch");
+        REQUIRE(P.num_slots >= 4 && P.num_slots == (P.ks_full / units + 2 < 4 ? 4 : P.ks_full / units + 2), "slots");
+    }
+    else
+    {
+        REQUIRE(gp.partial_bytes == 0, "scratch without a K split");
+        if(P.split > 1)
+        {
+            ++g_slice_plans;
+            REQUIRE(P.split_start % units == 0 && (P.total_tiles - P.split_start) * P.split <= units, "slice tail");
+            REQUIRE(gp.b_split_rows == bn / P.split / cg && gp.b_split_rows * cg >= 64 && gp.b_split_rows >= in.b_min,
+                    "rows of a slice's B box: %d", gp.b_split_rows);
+        }
+        REQUIRE(P.num_slots == (P.total_work + units - 1) / units, "slots");
+    }
+    Coverage cov;
+    if(in.ks_pays)
+        walk_bn<MODE_GEMM, true>(bn, P, static_cast<const GroupTiles*>(nullptr), cg, gp.grid, cov);
+    else
+        walk_bn<MODE_GEMM, false>(bn, P, static_cast<const GroupTiles*>(nullptr), cg, gp.grid, cov);
+    // every chunk of every tile exactly once
+    REQUIRE(static_cast<int64_t>(cov.out.size()) == static_cast<int64_t>(P.total_tiles) * (bn / 32), "chunks written: %zu of %lld",
+            cov.out.size(), (long long)P.total_tiles * (bn / 32));
+    for(const auto& kv : cov.out)
+        REQUIRE(kv.second == 1, "chunk (%d, %d, %d) written %d times", std::get<0>(kv.first), std::get<1>(kv.first),
+                std::get<2>(kv.first), kv.second);
+    if(P.ksplit >= 2)
+    {
+        REQUIRE(static_cast<int>(cov.tail_k.size()) == P.ks_rem, "tail tiles with slices");
+        for(const auto& kv : cov.tail_k)
+            for(int k = 0; k < P.num_kb; ++k)
+                REQUIRE(kv.second[k] == 1, "tail %d k block %d accumulated %d times", kv.first, k, kv.second[k]);
+        for(const auto& kv : cov.tail_slices)
+            REQUIRE(static_cast<int>(kv.second.size()) == P.ksplit, "tail %d has %zu slices", kv.first, kv.second.size());
+    }
+}
+
+static void check_grouped_plan(const std::vector<std::array<int64_t, 3>>& shapes, int sm_count, int b_min, TileConfig force)
+{
+    std::vector<GroupTiles> tiles(shapes.size());
+    GroupedPlan gp;
+    REQUIRE(plan_grouped(reinterpret_cast<const int64_t(*)[3]>(shapes.data()), static_cast<int>(shapes.size()), sm_count, b_min,
+                         force, tiles.data(), &gp),
+            "plan_grouped refused");
+    ++g_plans;
+    const int cg = gp.cg, bn = gp.bn;
+    int64_t sum = 0;
+    for(size_t i = 0; i < shapes.size(); ++i)
+    {
+        REQUIRE(tiles[i].tile_start == sum, "prefix sum of group %zu", i);
+        REQUIRE(tiles[i].tiles_m == (shapes[i][0] + BM * cg - 1) / (BM * cg) && tiles[i].tiles_n == (shapes[i][1] + bn - 1) / bn,
+                "tile counts of group %zu", i);
+        REQUIRE(tiles[i].m_fastest == (tiles[i].tiles_m < tiles[i].tiles_n ? 1 : 0), "tile order of group %zu", i);
+        sum += static_cast<int64_t>(tiles[i].tiles_m) * tiles[i].tiles_n;
+        for(int t = tiles[i].tile_start; t < sum; ++t)
+            REQUIRE(find_group(tiles.data(), static_cast<int>(tiles.size()), t) == static_cast<int>(i), "find_group(%d)", t);
+    }
+    REQUIRE(gp.pp.total_tiles == sum && gp.pp.group_count == static_cast<int>(shapes.size()), "totals");
+    Coverage cov;
+    walk_bn<MODE_GROUPED, false>(bn, gp.pp, tiles.data(), cg, gp.grid, cov);
+    REQUIRE(static_cast<int64_t>(cov.out.size()) == sum * (bn / 32), "chunks written: %zu of %lld", cov.out.size(),
+            (long long)sum * (bn / 32));
+    for(const auto& kv : cov.out)
+        REQUIRE(kv.second == 1, "group %d chunk (%d, %d) written %d times", std::get<0>(kv.first), std::get<1>(kv.first),
+                std::get<2>(kv.first), kv.second);
+}
+
+int main()
+{
+    // tile order: both orders enumerate every position once
+    for(int tm : {1, 3, 16})
+        for(int tn : {1, 2, 16})
+            for(int order : {0, 1})
+            {
+                std::map<std::pair<int, int>, int> seen;
+                for(int t = 0; t < tm * tn; ++t)
+                {
+                    int m, n;
+                    tile_position(t, tm, tn, order, &m, &n);
+                    REQUIRE(m >= 0 && m < tm && n >= 0 && n < tn, "position");
+                    ++seen[{m, n}];
+                }
+                REQUIRE(static_cast<int>(seen.size()) == tm * tn, "order %d visits every tile", order);
+            }
+
+    const int64_t sizes[] = {1, 100, 128, 129, 256, 300, 768, 1000, 2048, 2560, 3328, 3840, 4096, 4864, 8192};
+    const int kbs[]       = {1, 3, 4, 16, 27, 32, 40, 47, 48, 64, 80, 128, 256};
+    const int sms[]       = {148, 132, 16, 2};
+    for(int sm : sms)
+        for(int64_t M : sizes)
+            for(int64_t N : sizes)
+                for(int kb : kbs)
+                    for(int pays = 0; pays < 2; ++pays)
+                    {
+                        GemmPlanInput in;
+                        in.M = M, in.N = N, in.num_kb = kb, in.sm_count = sm, in.b_min = 32;
+                        in.ks_pays = pays != 0, in.ks_allowed = true;
+                        check_gemm_plan(in);
+                        if(kb == 40 || kb == 80)
+                        {
+                            in.ks_allowed = false; // a capturing stream / no scratch
+                            check_gemm_plan(in);
+                            in.ks_allowed = true;
+                            in.b_min      = 64; // N-major B
+                            check_gemm_plan(in);
+                            for(int bn : {64, 128, 256})
+                                for(int cgf : {0, 1, 2})
+                                    for(int nks : {0, 1})
+                                    {
+                                        in.force.bn = bn, in.force.cg = cgf, in.force.no_ksplit = nks;
+                                        check_gemm_plan(in);
+                                    }
+                            in.force = TileConfig{};
+                            in.b_min = 32;
+                            for(int64_t batch : {2, 3, 40})
+                            {
+                                in.batch = batch;
+                                check_gemm_plan(in);
+                            }
+                        }
+                    }
+    // the five benchmark shapes on a B200
+    {
+        GemmPlanInput in;
+        in.sm_count = 148, in.b_min = 32, in.ks_allowed = true;
+        in.M = 3840, in.N = 4096, in.num_kb = 64, in.ks_pays = true;
+        check_gemm_plan(in);
+        GemmPlan gp;
+        plan_gemm(in, &gp);
+        REQUIRE(gp.bn == 256 && gp.cg == 2 && gp.pp.ksplit == 4 && gp.pp.ks_rem == 18 && gp.pp.ks_full == 222, "fp16 GEMM plan");
+        in.num_kb = 32, in.ks_pays = false;
+        check_gemm_plan(in);
+        plan_gemm(in, &gp);
+        REQUIRE(gp.pp.ksplit == 0 && gp.pp.split == 4 && gp.pp.split_start == 222, "int8 GEMM plan");
+        in.M = 128 * 36 * 36, in.N = 256, in.num_kb = 27, in.b_min = 64;
+        check_gemm_plan(in);
+    }
+    // grouped tables
+    std::mt19937 rng(1234);
+    for(int rep = 0; rep < 300; ++rep)
+    {
+        std::vector<std::array<int64_t, 3>> shapes(1 + rng() % 24);
+        for(auto& s : shapes)
+            s = {static_cast<int64_t>(1 + rng() % 4200), static_cast<int64_t>(1 + rng() % 4200), static_cast<int64_t>(1 + rng() % 70)};
+        for(int sm : {148, 64})
+        {
+            check_grouped_plan(shapes, sm, 32, TileConfig{});
+            TileConfig f;
+            f.bn = 128;
+            check_grouped_plan(shapes, sm, 64, f);
+        }
+    }
+    {
+        std::vector<std::array<int64_t, 3>> shapes(64);
+        for(int g = 0; g < 64; ++g)
+            shapes[g] = {256 * (1 + g % 16), 4096, 64};
+        check_grouped_plan(shapes, 148, 32, TileConfig{});
+    }
+    std::printf("work plan checks passed: %ld plans (%ld with a K split, %ld with column slices), %ld assertions\n", g_plans,
+                g_ksplit_plans, g_slice_plans, g_checks);
+    return 0;
+}

@@ -30,7 +30,7 @@ def test_library_exports_every_declared_symbol():
     for n in names:
         assert hasattr(L, n), f"{n} declared in ckb200.h but not exported"
         assert n in capi.SYMBOLS, f"{n} has no ctypes prototype"
-    assert L.ckb_abi_version() == 1
+    assert L.ckb_abi_version() == capi.CKB_ABI_VERSION == 2
 
 
 def test_struct_layout_matches_header():
@@ -70,10 +70,24 @@ def test_gemm_supported_rules():
     op = ck.DeviceGemm()
     ok = op.MakeArgument(0x1000, 0x2000, 0x3000, 3840, 4096, 4096, 4096, 4096, 4096)
     assert op.IsSupportedArgument(ok)
-    # ragged sizes are fine (TMA zero-fills), as long as rows are 16-byte pitched
+    # ragged sizes are fine (TMA zero-fills); a pitch or base that is not a multiple of 16 bytes is served through a
+    # padded copy by the plain GEMM and refused by the batched and grouped entry points
     assert op.IsSupportedArgument(op.MakeArgument(0x1000, 0x2000, 0x3000, 100, 37, 72, 72, 72, 37))
-    assert not op.IsSupportedArgument(op.MakeArgument(0x1000, 0x2000, 0x3000, 100, 37, 70, 70, 70, 37))
+    assert op.IsSupportedArgument(op.MakeArgument(0x1000, 0x2000, 0x3000, 100, 37, 70, 70, 70, 37))
+    bg = ck.DeviceBatchedGemm()
+    assert not bg.IsSupportedArgument(bg.MakeArgument(0x1000, 0x2000, 0x3000, 100, 37, 70, 70, 70, 37, 7000, 2590, 3700, 2))
     assert "16 bytes" in capi.last_error()
+    gg = ck.DeviceGroupedGemm()
+    assert not gg.IsSupportedArgument(gg.MakeArgument([0x1000], [0x2000], [], [0x3000],
+                                                      [ck.GemmDescHost(100, 37, 70, 70, 70, 37)]))
+    # tile configurations: a pinned tile shape is part of the descriptor; malformed values are refused
+    for tc in (capi.tile_config(256, 2), capi.tile_config(256, 1), capi.tile_config(128, 1), capi.tile_config(64, 1),
+               capi.tile_config(256, 2, 1), capi.tile_config(0, 0, 1)):
+        pinned = ck.DeviceGemm(tile_config=tc)
+        assert pinned.IsSupportedArgument(pinned.MakeArgument(0x1000, 0x2000, 0x3000, 512, 512, 512, 512, 512, 512))
+    for tc in (capi.tile_config(96, 1), capi.tile_config(128, 2), capi.tile_config(256, 3), -1, 1 << 20):
+        pinned = ck.DeviceGemm(tile_config=tc)
+        assert not pinned.IsSupportedArgument(pinned.MakeArgument(0x1000, 0x2000, 0x3000, 512, 512, 512, 512, 512, 512))
     assert not op.IsSupportedArgument(op.MakeArgument(0x1000, 0x2000, 0x3000, 0, 8, 8, 8, 8, 8))
     # non-PassThrough A/B element ops cannot be applied by TMA
     assert not op.IsSupportedArgument(op.MakeArgument(0x1000, 0x2000, 0x3000, 8, 8, 8, 8, 8, 8, ck.Scale(2.0)))
@@ -95,7 +109,7 @@ def test_gemm_supported_rules():
     assert i8.IsSupportedArgument(i8.MakeArgument(0x1000, 0x2000, 0x3000, 3840, 4096, 4096, 4096, 4096, 4096,
                                                   None, None, ck.RequantReluRequant(0.03, 1.0)))
     # Run on an unsupported argument throws like the reference (device_gemm_xdl_cshuffle.hpp:475-481)
-    bad = op.MakeArgument(0x1000, 0x2000, 0x3000, 100, 37, 70, 70, 70, 37)
+    bad = op.MakeArgument(0x1000, 0x2000, 0x3000, 100, 37, 72, 64, 72, 37)  # lda < K
     with pytest.raises(RuntimeError, match="invalid setting"):
         op.MakeInvoker().Run(bad)
 
@@ -124,5 +138,6 @@ def test_conv_validation():
                                         None, None, ck.AddRelu(), p_bias=0x4000)
     assert conv.IsSupportedArgument(mk())
     assert not conv.IsSupportedArgument(mk(out=(35, 36)))      # inconsistent geometry
-    assert not conv.IsSupportedArgument(mk(C=12))               # pixel pitch not 16-byte
+    assert conv.IsSupportedArgument(mk(C=12))                   # pixel pitch not 16-byte: served through a padded copy
+    assert conv.IsSupportedArgument(mk(C=3))                    # the reference's OddC case
     assert not conv.IsSupportedArgument(mk(s=(9, 9), out=(8, 8)))  # stride beyond the TMA limit

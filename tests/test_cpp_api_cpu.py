@@ -24,6 +24,21 @@ def test_host_api_checks_pass():
     assert "all host API checks passed" in run.stdout
 
 
+def test_work_plan_covers_every_tile_exactly_once():
+    """Host-only sweep over the kernel's work decomposition (tile order, column-slice tail, K-split plans, batched
+    and grouped tile tables), compiled by g++ alone from the header the kernel itself includes."""
+    out_dir = os.path.join(ROOT, "tests", "cpp", "bin")
+    os.makedirs(out_dir, exist_ok=True)
+    exe = os.path.join(out_dir, "work_plan_test")
+    cmd = ["g++", "-std=c++17", "-O2", "-I", os.path.join(ROOT, "composable_kernel_b200", "csrc"),
+           os.path.join(ROOT, "tests", "cpp", "work_plan_test.cpp"), "-o", exe]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr[-3000:]
+    run = subprocess.run([exe], capture_output=True, text=True, timeout=600)
+    assert run.returncode == 0, run.stdout[-3000:]
+    assert "work plan checks passed" in run.stdout
+
+
 def test_example_drivers_build():
     res = subprocess.run(["make", "-C", os.path.join(ROOT, "examples"), "-j4"], capture_output=True, text=True)
     assert res.returncode == 0, res.stderr[-3000:]

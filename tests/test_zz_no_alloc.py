@@ -4,7 +4,10 @@ its group table lives in a fixed array inside the library instead of a caller-pr
 
 The entry point is called through the C ABI twice in a row, with different group sets, and each
 result must equal - bit for bit, the kernel is the same - what the workspace-taking entry point
-ckb_grouped_gemm_run writes for the same descriptors.  The second call is smaller than the first,
+ckb_grouped_gemm_run writes for the same descriptors, and must agree with the CPU oracle group by
+group (the reference's check_err rule), so that a fault shared by both entry points cannot hide.
+Device memory is watched at the driver level (cudaMemGetInfo): torch's own counters only see
+torch's caching allocator, not a cudaMalloc made inside the library.  The second call is smaller than the first,
 so entries left in the shared table by the first call must not leak into it.  The file name sorts
 last so that a run that stops at the first failure has already run every other test; the test
 needs no state from the others and passes alone in a fresh process."""
@@ -16,6 +19,7 @@ import torch
 
 import composable_kernel_b200 as ck
 from composable_kernel_b200 import capi
+from tests import helpers as H
 
 pytestmark = pytest.mark.gpu
 
@@ -45,17 +49,28 @@ def _run_both(shapes, seed, with_bias):
     op.SetWorkSpacePointer(arg, ws.data_ptr())
     assert op.IsSupportedArgument(arg), capi.last_error()
     op.MakeInvoker().Run(arg)
-    # new entry point: no workspace, nothing allocated by the call
+    # new entry point: no workspace, nothing allocated by the call.  The first call on a device loads the module
+    # and looks up the table's address; the call after it is the one whose device memory is watched.
     arg2 = bind(E_new)
-    before = torch.cuda.memory_allocated()
     capi.check(capi.lib().ckb_grouped_gemm_run_noalloc(ctypes.byref(arg2.desc), None))
     torch.cuda.synchronize()
-    assert torch.cuda.memory_allocated() == before
+    for e in E_new:
+        e.fill_(float("nan"))
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    capi.check(capi.lib().ckb_grouped_gemm_run_noalloc(ctypes.byref(arg2.desc), None))
+    torch.cuda.synchronize()
+    free_after = torch.cuda.mem_get_info()[0]
+    assert free_after >= free_before, f"the call took {free_before - free_after} bytes of device memory"
     assert ck.device_status() == 0
-    for e_new, e_ref in zip(E_new, E_ref):
+    A, B, bias = keep
+    fn = ck.AddRelu() if with_bias else ck.PassThrough()
+    for g, (e_new, e_ref) in enumerate(zip(E_new, E_ref)):
         a, b = e_new.cpu().numpy(), e_ref.cpu().numpy()
         assert np.isfinite(b.astype(np.float32)).all()
         np.testing.assert_array_equal(a.view(np.uint16), b.view(np.uint16))
+        ref = H.oracle_gemm(A[g].cpu().numpy(), B[g].cpu().numpy(), fn, bias[g].cpu().numpy() if with_bias else None)
+        H.assert_close(a, ref)
 
 
 def test_noalloc_matches_workspace_entry_point_on_two_calls_in_a_row(cuda_device):
