@@ -163,9 +163,10 @@ def test_conv2d_fwd_int8_bit_exact(cuda_device, case):
         np.testing.assert_array_equal(out, ref)
 
 
-def test_conv2d_fwd_int8_needs_16_channel_pitch(cuda_device):
-    conv = ck.DeviceConvFwd(capi.CKB_I8)
-    arg = conv.MakeArgument(0x1000, 0x2000, 0x3000, 2, 32, 24, (8, 8), (3, 3), (8, 8), (1, 1), (1, 1), (1, 1), (1, 1),
-                            None, None, ck.PassThrough())
-    assert not conv.IsSupportedArgument(arg)
-    assert "multiple of 16" in capi.last_error()
+def test_conv2d_fwd_int8_odd_channel_pitch_runs_through_the_padded_copy(cuda_device):
+    """24 int8 channels are a 24-byte pixel pitch, which TMA cannot read in place."""
+    rng = np.random.default_rng(77)
+    inp = rng.integers(-5, 6, (2, 8, 8, 24)).astype(np.int8)
+    wei = rng.integers(-5, 6, (32, 3, 3, 24)).astype(np.int8)
+    out = run_conv_i8(inp, wei, (1, 1), (1, 1), (1, 1), ck.PassThrough())
+    np.testing.assert_array_equal(out, oracle.conv2d_fwd(inp, wei, (1, 1), (1, 1), (1, 1)))

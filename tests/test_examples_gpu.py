@@ -70,7 +70,7 @@ def test_grouped_gemm_bias_example(examples_built):
 def test_convnd_fwd_example(examples_built):
     # verify init time nd N K C <filter> <input> <strides> <dilations> <left pads> <right pads>
     out = run_example("convnd_fwd_xdl_fp16", 1, 1, 1, 1, 4, 64, 32, 3, 71, 2, 1, 1, 1)
-    assert "Perf:" in out and "DeviceConv1DFwdXdl" in out
+    assert "Perf:" in out and "DeviceConvNDFwdXdl" in out
     run_example("convnd_fwd_xdl_fp16", 1, 2, 0, 2, 4, 64, 64, 3, 3, 17, 19, 2, 1, 1, 2, 1, 2, 1, 2)
     run_example("convnd_fwd_xdl_fp16", 1, 1, 0, 3, 2, 32, 16, 3, 3, 3, 9, 10, 11, 1, 2, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1)
     # the int8 instance list of the same example (int32 accumulation, bit-exact)
@@ -81,7 +81,7 @@ def test_convnd_fwd_example(examples_built):
 def test_client_examples_walk_the_instance_factory(examples_built):
     """Client-style programs: device-operation interface + instance list only, best instance re-run at the end."""
     out = run_example("client_gemm", 512, 768, 256, 256, 256, 768)
-    assert "found 1 instances" in out and "Best Perf:" in out and out.rstrip().endswith("Done")
+    assert "found 6 instances" in out and "Best Perf:" in out and out.rstrip().endswith("Done")
     out = run_example("client_gemm_add_add_fastgelu", 512, 768, 256, 256, 256, 0, 768, 768)
     assert "Best Perf:" in out and "DeviceGemmMultipleD_Xdl_CShuffle" in out and out.rstrip().endswith("Done")
 
@@ -122,7 +122,7 @@ def test_conv_examples(examples_built):
     # N K C Y X Hi Wi Sy Sx Dy Dx LeftPy LeftPx RightPy RightPx
     geom = (4, 64, 64, 3, 3, 17, 17, 2, 2, 1, 1, 1, 1, 1, 1)
     out = run_example("conv2d_fwd_xdl_bias_relu", 1, 2, 1, 1, *geom)
-    assert "im2col TMA" in out
+    assert "DeviceConv2dFwdXdl_C_Shuffle_Bias_Activation_Input_N_Hi_Wi_C_Weight_K_Y_X_C_Output_N_Ho_Wo_K<" in out
     run_example("conv2d_fwd_xdl_bias_relu", 1, 1, 0, 0, *geom)  # plain convolution, integer init
     out = run_example("conv2d_fwd_xdl_bias_relu", 1, 2, 1, 2, *geom)  # bias + ReLU + residual add (example 07)
     assert "Bias_Activation_Add" in out
@@ -166,12 +166,12 @@ def test_profiler_driver_convnd(examples_built):
     the reference's device tests, verified against the N-D ReferenceConvFwd of the compat headers."""
     # conv_fwd dtype layout verify init log time nd N K C <filter> <input> <strides> <dilations> <lpads> <rpads>
     out = run_example("ck_profiler", "conv_fwd", 1, 1, 1, 1, 0, 1, 1, 4, 256, 64, 3, 71, 2, 2, 2, 2)
-    assert "Best Perf for conv_fwd" in out and "DeviceConv1DFwdXdl" in out
+    assert "Best Perf for conv_fwd" in out and "DeviceConvNDFwdXdl" in out
     out = run_example("ck_profiler", "conv_fwd", 3, 1, 1, 1, 0, 1, 2, 4, 64, 64, 3, 3, 17, 17, 2, 2, 1, 1, 1, 1, 1, 1)
-    assert "DeviceConv2DFwdXdl" in out
+    assert "DeviceConvNDFwdXdl" in out
     out = run_example("ck_profiler", "conv_fwd", 1, 1, 1, 1, 0, 1, 3, 2, 64, 32, 3, 3, 3, 10, 10, 10, 1, 1, 1, 2, 2, 2,
                       2, 2, 2, 2, 2, 2)
-    assert "Best Perf for conv_fwd" in out and "DeviceConv3DFwdXdl" in out
+    assert "Best Perf for conv_fwd" in out and "DeviceConvNDFwdXdl" in out
 
 
 def test_profiler_driver_batched_gemm(examples_built):

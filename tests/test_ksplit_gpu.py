@@ -26,6 +26,7 @@ def run(a, bt, op=None, dtype=capi.CKB_F16, stream=None, reps=1, out=None):
     g = ck.DeviceGemm(dtype)
     arg = g.MakeArgument(da.data_ptr(), db.data_ptr(), e.data_ptr(), M, N, K, K, K, N, None, None, op or ck.PassThrough())
     assert g.IsSupportedArgument(arg), capi.last_error()
+    torch.cuda.synchronize()  # inputs and the zeroed output are in place before a launch on another stream
     for _ in range(reps):
         g.MakeInvoker().Run(arg, ck.StreamConfig(stream, False))
     torch.cuda.synchronize()
@@ -88,6 +89,39 @@ def test_ksplit_bf16(cuda_device):
     bt = oracle.to_bf16(rng.integers(-5, 6, (N, K)).astype(np.float32))
     out = run(a, bt, dtype=capi.CKB_BF16)
     np.testing.assert_array_equal(out, oracle.gemm(a, bt.T))
+
+
+def test_first_ksplit_launch_of_a_fresh_scratch_on_a_side_stream(cuda_device):
+    """The scratch of a stream is allocated, and its counters zeroed, by the first K-split launch on that stream; the
+    zeroing has to be ordered before that launch on the stream itself - a torch side stream is non-blocking, so work on
+    the legacy default stream is not."""
+    capi.check(capi.lib().ckb_release_scratch(None, 1))  # every stream starts without scratch
+    rng = np.random.default_rng(19)
+    M, N, K = 2048, 2560, 2560
+    a, bt = ints(rng, (M, K)), ints(rng, (N, K))
+    ref = oracle.gemm(a, bt.T)
+    for _ in range(3):
+        st = torch.cuda.Stream()
+        out = run(a, bt, stream=st.cuda_stream, reps=2)
+        np.testing.assert_array_equal(out, ref)
+        capi.check(capi.lib().ckb_release_scratch(st.cuda_stream, 0))
+
+
+@pytest.mark.parametrize("cfg", [(256, 2, 0), (256, 1, 0), (128, 1, 0), (64, 1, 0), (256, 2, 1), (0, 0, 1)])
+def test_pinned_tile_configurations_bit_exact(cuda_device, cfg):
+    """The tile configurations an instance factory hands out (CKB_TILE_CONFIG): same results from every one."""
+    rng = np.random.default_rng(23)
+    M, N, K = 2048, 2560, 2560
+    a, bt = ints(rng, (M, K)), ints(rng, (N, K))
+    da, db = torch.from_numpy(a).cuda(), torch.from_numpy(bt).cuda()
+    e = torch.zeros((M, N), dtype=torch.float16, device="cuda")
+    g = ck.DeviceGemm(capi.CKB_F16, tile_config=capi.tile_config(*cfg))
+    arg = g.MakeArgument(da.data_ptr(), db.data_ptr(), e.data_ptr(), M, N, K, K, K, N)
+    assert g.IsSupportedArgument(arg), capi.last_error()
+    g.MakeInvoker().Run(arg)
+    torch.cuda.synchronize()
+    assert ck.device_status() == 0
+    np.testing.assert_array_equal(e.cpu().numpy(), oracle.gemm(a, bt.T))
 
 
 def test_ksplit_on_two_streams_at_once(cuda_device):
