@@ -28,9 +28,10 @@ CKB_NOALLOC_MAX_GROUPS = 256
 CKB_ABI_VERSION = 2
 
 
-def tile_config(bn: int = 0, cg: int = 0, no_ksplit: int = 0) -> int:
-    """CKB_TILE_CONFIG(bn, cg, no_ksplit) of include/ckb200.h; 0 = the library's own choice."""
-    return bn | (cg << 12) | (no_ksplit << 16)
+def tile_config(bn: int = 0, cg: int = 0, no_ksplit: int = 0, kbatch: int = 0) -> int:
+    """CKB_TILE_CONFIG(bn, cg, no_ksplit) / CKB_TILE_CONFIG_KBATCH(bn, cg, kbatch) of include/ckb200.h;
+    0 = the library's own choice."""
+    return bn | (cg << 12) | (no_ksplit << 16) | (kbatch << 20)
 
 EPI_NUM_D = {CKB_EPI_ADD: 1, CKB_EPI_ADD_RELU_F16: 1, CKB_EPI_BILINEAR: 1, CKB_EPI_ADD_RELU: 1,
              CKB_EPI_ADD_HARDSWISH: 1, CKB_EPI_ADD_ADD_FASTGELU: 2, CKB_EPI_ADD_RELU_ADD: 2}
@@ -104,6 +105,7 @@ class Conv3dFwdDesc(Structure):
 SYMBOLS = {
     "ckb_abi_version": (c_int, []),
     "ckb_last_error": (c_char_p, []),
+    "ckb_last_plan": (c_char_p, []),
     "ckb_launch_count": (c_uint64, []),
     "ckb_device_info": (c_int, [c_char_p, c_size_t, POINTER(c_int), POINTER(c_int), POINTER(c_int)]),
     "ckb_device_status": (c_int, [POINTER(c_uint32)]),
@@ -157,6 +159,11 @@ def lib() -> ctypes.CDLL:
 
 def last_error() -> str:
     return (lib().ckb_last_error() or b"").decode()
+
+
+def last_plan() -> str:
+    """Plan of the calling thread's last launch, e.g. 'gemm tile=128x256 cg=1 grid=144 ... cluster_k=8 ...'."""
+    return (lib().ckb_last_plan() or b"").decode()
 
 
 def check(rc: int) -> None:

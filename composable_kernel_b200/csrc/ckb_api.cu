@@ -23,6 +23,7 @@ namespace {
 using namespace ckb;
 
 thread_local std::string t_last_error;
+thread_local char t_last_plan[200] = "";
 std::atomic<uint64_t> g_launches{0};
 
 // Device status word read by the kernels through KernelParams::status.
@@ -95,6 +96,7 @@ struct DeviceInfo
     int cc_major = 0, cc_minor = 0;
     uint32_t* status = nullptr;
     bool ready       = false;
+    int cluster_cap[3] = {-1, -1, -1}; // clusters of 2 / 4 / 8 CTAs resident at once (-1: not asked yet)
     std::map<cudaStream_t, Scratch> scratch;
 };
 DeviceInfo g_dev[64];
@@ -216,9 +218,12 @@ uint32_t test_kslice_wait_extra()
 // CKB_FORCE_BN / CKB_FORCE_CG / CKB_NO_SPLITK (read at every call), else all zero = the library decides.
 int check_tile_config(int32_t tc)
 {
-    const int bn = tc & 0xFFF, cg = (tc >> 12) & 0xF, rest = tc >> 17;
-    if(tc < 0 || rest != 0 || !(bn == 0 || bn == 64 || bn == 128 || bn == 256) || cg > 2)
-        return fail(CKB_ERR_INVALID, "tile_config 0x%x is not a CKB_TILE_CONFIG(bn, cg, no_ksplit) value", tc);
+    const int bn = tc & 0xFFF, cg = (tc >> 12) & 0xF, kbatch = (tc >> 20) & 0xFF, rest = (tc >> 17) & 0x7, top = tc >> 28;
+    if(tc < 0 || rest != 0 || top != 0 || !(bn == 0 || bn == 64 || bn == 128 || bn == 256) || cg > 2 ||
+       !(kbatch == 0 || kbatch == 1 || kbatch == 2 || kbatch == 4 || kbatch == 8))
+        return fail(CKB_ERR_INVALID, "tile_config 0x%x is not a CKB_TILE_CONFIG / CKB_TILE_CONFIG_KBATCH value", tc);
+    if(kbatch >= 2 && cg == 2)
+        return fail(CKB_ERR_UNSUPPORTED, "a K batch runs on single-CTA tiles (cg = 1)");
     if(cg == 2 && bn != 256 && bn != 0)
         return fail(CKB_ERR_UNSUPPORTED, "a CTA pair (cg = 2) works on 256-wide tiles only");
     return CKB_OK;
@@ -232,6 +237,12 @@ TileConfig tile_config_of(int32_t tc)
         t.bn        = tc & 0xFFF;
         t.cg        = (tc >> 12) & 0xF;
         t.no_ksplit = (tc >> 16) & 1;
+        t.kbatch    = (tc >> 20) & 0xFF;
+        if(t.kbatch == 1) // one K batch = no split
+        {
+            t.kbatch    = 0;
+            t.no_ksplit = 1;
+        }
         return t;
     }
     const char* s = getenv("CKB_FORCE_BN");
@@ -478,6 +489,14 @@ unsigned long long* trace_buffer()
 #endif
 }
 
+// Remembers what the calling thread's last launch looked like (ckb_last_plan).
+void note_plan(const char* what, int bn, int cg, int grid, const PlanParams& pp, int copies)
+{
+    snprintf(t_last_plan, sizeof(t_last_plan),
+             "%s tile=%dx%d cg=%d grid=%d tiles=%d col_split=%d ksplit=%d cluster_k=%d slots=%d copies=%d", what,
+             BM * cg, bn, cg, grid, pp.total_tiles, pp.split, pp.ksplit, pp.cluster_k ? pp.ksplit : 0, pp.num_slots, copies);
+}
+
 // Work that has to run on the stream before the contraction kernel of the same call: pitch-fixing copies of
 // operands that TMA cannot read in place (see repack_pitch_kernel).  Part of every timed repetition.
 struct Repack
@@ -599,6 +618,7 @@ bool tma_readable(const void* p, int64_t ld, int eb) { return aligned16(p) && (l
 } // namespace
 
 namespace ckb {
+extern template cudaError_t cluster_capacity<MODE_GEMM, KIND_F16, CKB_EPI_PASSTHROUGH>(int, int*);
 #define CKB_INST(M, K, E) extern template cudaError_t launch_epi<M, K, E>(int, int, const KernelParams&, int, cudaStream_t);
 #include "ckb_instances.def"
 #undef CKB_INST
@@ -636,6 +656,8 @@ int ckb_trace_read(unsigned long long* host, int words)
 #endif
 
 const char* ckb_last_error(void) { return t_last_error.c_str(); }
+
+const char* ckb_last_plan(void) { return t_last_plan; }
 
 uint64_t ckb_launch_count(void) { return g_launches.load(); }
 
@@ -824,6 +846,26 @@ static int gemm_run_impl(const ckb_gemm_desc* d_in, const BatchInfo& bi, void* s
     // more energy than the narrow MMAs it removes) - those keep the column slices.
     in.ks_pays    = d->ab_dtype != CKB_I8 && d->n_ds == 0;
     in.ks_allowed = !capturing;
+    in.cluster_ok = true;
+    {
+        // asked once per device: how many clusters of 2 / 4 / 8 CTAs fit at the same time
+        std::lock_guard<std::mutex> lock(g_dev_mutex);
+        for(int i = 0; i < 3; ++i)
+        {
+            if(dev->cluster_cap[i] < 0)
+            {
+                int n = 0;
+                if(cluster_capacity<MODE_GEMM, KIND_F16, CKB_EPI_PASSTHROUGH>(2 << i, &n) != cudaSuccess)
+                {
+                    cudaGetLastError();
+                    n = 0;
+                }
+                const int limit    = dev->sm_count / (2 << i); // a CKB_SM_LIMIT partition shrinks it further
+                dev->cluster_cap[i] = n < limit ? n : limit;
+            }
+            in.cluster_cap[i] = dev->cluster_cap[i];
+        }
+    }
     GemmPlan gp;
     if(!plan_gemm(in, &gp))
         return fail(CKB_ERR_UNSUPPORTED, "too many tiles");
@@ -877,6 +919,12 @@ static int gemm_run_impl(const ckb_gemm_desc* d_in, const BatchInfo& bi, void* s
     LaunchFn fn     = find_launch(MODE_GEMM, kind_of(d->ab_dtype), d->epilogue);
     if(!fn)
         return fail(CKB_ERR_UNSUPPORTED, "no kernel instance for epilogue %d", d->epilogue);
+    note_plan("gemm", bn, cg, gp.grid, p.plan, n_pre);
+    {
+        const size_t n = strlen(t_last_plan);
+        snprintf(t_last_plan + n, sizeof(t_last_plan) - n, " cluster_cap=%d/%d/%d", in.cluster_cap[0], in.cluster_cap[1],
+                 in.cluster_cap[2]);
+    }
     return run_timed(fn, bn, cg, p, gp.grid, stream, n_rep, avg_ms, pre, n_pre);
 }
 
@@ -1111,6 +1159,7 @@ int ckb_grouped_gemm_run(const ckb_grouped_gemm_desc* g, void* workspace, size_t
     LaunchFn fn = find_launch(MODE_GROUPED, kind_of(g->groups[0].ab_dtype), g->groups[0].epilogue);
     if(!fn)
         return fail(CKB_ERR_UNSUPPORTED, "no kernel instance for epilogue %d", g->groups[0].epilogue);
+    note_plan("grouped", gp.plan.bn, gp.plan.cg, gp.plan.grid, p.plan, 0);
     return run_timed(fn, gp.plan.bn, gp.plan.cg, p, gp.plan.grid, stream, n_rep, avg_ms);
 }
 
@@ -1474,6 +1523,7 @@ static int run_conv(const ConvProblem& c_in, void* stream_, int n_rep, float* av
     LaunchFn fn = find_launch(MODE_CONV, kind_of(c.dtype), c.epilogue);
     if(!fn)
         return fail(CKB_ERR_UNSUPPORTED, "no kernel instance for epilogue %d", c.epilogue);
+    note_plan("conv", bn, cg, gp.grid, p.plan, n_pre);
     return run_timed(fn, bn, cg, p, gp.grid, stream, n_rep, avg_ms, pre, n_pre);
 }
 

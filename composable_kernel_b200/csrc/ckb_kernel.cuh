@@ -425,13 +425,170 @@ __device__ __forceinline__ void epilogue_span(uint32_t tmem_addr, const Epilogue
     }
 }
 
+// ---- cluster K split: accumulators through shared memory, summed over distributed shared memory ----------------
+// Layout of a CTA's raw accumulator tile in its own shared memory (the pipeline stages, free once the main loop is
+// done): [quad of 4 columns][row] of 16 bytes, so that a warp (32 consecutive rows) writes and reads 512 contiguous
+// bytes per instruction.
+__device__ __forceinline__ uint32_t partial_offset(int quad, int row) { return static_cast<uint32_t>(quad * BM + row) * 16u; }
+
+// One epilogue warp moves `ncols` (a multiple of 32) accumulator columns of its 32 rows from tensor memory to the tile.
+__device__ __forceinline__ void stash_span(uint32_t tmem_addr, uint32_t partial_base, int row, int col_begin, int ncols)
+{
+    for(int c = 0; c < ncols / 32; ++c)
+    {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem_addr + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for(int q = 0; q < 8; ++q)
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(partial_base +
+                                                                          partial_offset((col_begin + c * 32) / 4 + q, row)),
+                         "r"(v[4 * q]), "r"(v[4 * q + 1]), "r"(v[4 * q + 2]), "r"(v[4 * q + 3])
+                         : "memory");
+    }
+}
+
+__device__ __forceinline__ uint4 ld_cluster_v4(uint32_t cluster_addr)
+{
+    uint4 v;
+    asm volatile("ld.shared::cluster.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "r"(cluster_addr)
+                 : "memory");
+    return v;
+}
+
+// CTA `rank` of a cluster of KS CTAs sums column part `rank` (BN / KS columns) of the tile over the accumulators
+// of all CTAs of the cluster, in slice order (deterministic), applies the epilogue and writes E.  `t` = 0 .. 255
+// indexes the epilogue threads; consecutive threads take consecutive rows of one 16-column segment.  The reads
+// over distributed shared memory are latency bound: 16 of them (8 for two slices) are in flight per thread.
+template <int EPI, int KIND, int BN, int KS>
+__device__ __forceinline__ void cluster_reduce_epilogue(const KernelParams& P, const WorkItem& wi, uint32_t partial_base,
+                                                        int rank, int t)
+{
+    using T            = typename std::conditional<KIND == KIND_BF16, __nv_bfloat16, __half>::type;
+    constexpr int ND   = (KIND == KIND_I8) ? 0 : epi_num_d(EPI);
+    constexpr int PW   = BN / KS;           // columns of this CTA's part
+    constexpr int SEGS = PW >> 4;           // 16-column segments per row
+    constexpr int QG   = KS == 8 ? 2 : 4;   // quads of 4 columns whose slices are fetched together
+    static_assert(PW >= 16 && PW % 16 == 0, "column parts are whole 16-column segments");
+    const EpilogueArgs& ea = P.epi;
+    uint32_t peer[KS];
+#pragma unroll
+    for(int s = 0; s < KS; ++s)
+        peer[s] = mapa_shared(partial_base, static_cast<uint32_t>(s));
+    for(int i = t; i < BM * SEGS; i += 32 * NUM_EPI_WARPS)
+    {
+        const int seg = i >> 7, row = i & (BM - 1);
+        const int col0 = rank * PW + seg * 16; // first column inside the tile
+        const int64_t m = static_cast<int64_t>(wi.m_blk) * BM + row, n0 = static_cast<int64_t>(wi.n_start) + col0;
+        uint32_t v[16];
+#pragma unroll
+        for(int g = 0; g < 4 / QG; ++g)
+        {
+            uint4 part[QG][KS];
+#pragma unroll
+            for(int q = 0; q < QG; ++q)
+#pragma unroll
+                for(int s = 0; s < KS; ++s)
+                    part[q][s] = ld_cluster_v4(peer[s] + partial_offset((col0 >> 2) + g * QG + q, row));
+#pragma unroll
+            for(int q = 0; q < QG; ++q)
+            {
+                uint4 a = part[q][0];
+#pragma unroll
+                for(int s = 1; s < KS; ++s)
+                {
+                    if constexpr(KIND == KIND_I8)
+                    {
+                        a.x += part[q][s].x, a.y += part[q][s].y, a.z += part[q][s].z, a.w += part[q][s].w;
+                    }
+                    else
+                    {
+                        a.x = __float_as_uint(__uint_as_float(a.x) + __uint_as_float(part[q][s].x));
+                        a.y = __float_as_uint(__uint_as_float(a.y) + __uint_as_float(part[q][s].y));
+                        a.z = __float_as_uint(__uint_as_float(a.z) + __uint_as_float(part[q][s].z));
+                        a.w = __float_as_uint(__uint_as_float(a.w) + __uint_as_float(part[q][s].w));
+                    }
+                }
+                const int j = (g * QG + q) * 4;
+                v[j] = a.x, v[j + 1] = a.y, v[j + 2] = a.z, v[j + 3] = a.w;
+            }
+        }
+        if(m >= P.M || n0 >= P.N)
+            continue;
+        const bool full = P.vec_ok != 0 && n0 + 16 <= P.N;
+        if constexpr(KIND == KIND_I8)
+        {
+            int8_t* e_row = static_cast<int8_t*>(ea.e) + m * ea.lde + n0;
+            if(full)
+            {
+                uint32_t w[4];
+#pragma unroll
+                for(int k = 0; k < 4; ++k)
+                {
+                    uint32_t packed = 0;
+#pragma unroll
+                    for(int j = 0; j < 4; ++j)
+                        packed |= (static_cast<uint32_t>(epi_apply_i8<EPI>(static_cast<int32_t>(v[4 * k + j]), ea.p)) & 0xFFu)
+                                  << (8 * j);
+                    w[k] = packed;
+                }
+                *reinterpret_cast<uint4*>(e_row) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            else
+            {
+#pragma unroll
+                for(int j = 0; j < 16; ++j)
+                    if(n0 + j < P.N)
+                        e_row[j] = static_cast<int8_t>(epi_apply_i8<EPI>(static_cast<int32_t>(v[j]), ea.p));
+            }
+        }
+        else
+        {
+            T* e_row        = static_cast<T*>(ea.e) + m * ea.lde + n0;
+            const T* d0_row = ND >= 1 ? static_cast<const T*>(ea.d0) + m * ea.ldd0 + n0 : nullptr;
+            const T* d1_row = ND >= 2 ? static_cast<const T*>(ea.d1) + m * ea.ldd1 + n0 : nullptr;
+            alignas(16) T out[16];
+#pragma unroll
+            for(int j = 0; j < 16; ++j)
+            {
+                T a = from_f32<T>(0.0f), b = from_f32<T>(0.0f);
+                if(n0 + j < P.N)
+                {
+                    if constexpr(ND >= 1)
+                        a = d0_row[j];
+                    if constexpr(ND >= 2)
+                        b = d1_row[j];
+                }
+                out[j] = epi_apply_f<EPI, T>(__uint_as_float(v[j]), a, b, ea.p);
+            }
+            if(full)
+            {
+                reinterpret_cast<uint4*>(e_row)[0] = reinterpret_cast<const uint4*>(out)[0];
+                reinterpret_cast<uint4*>(e_row)[1] = reinterpret_cast<const uint4*>(out)[1];
+            }
+            else
+            {
+#pragma unroll
+                for(int j = 0; j < 16; ++j)
+                    if(n0 + j < P.N)
+                        e_row[j] = out[j];
+            }
+        }
+    }
+}
+
 // EPI (the fused epilogue functor) is a template parameter: one functor per kernel keeps the
 // epilogue warps inside the 168-register budget that ten warps per SM leave.
-template <int MODE, int KIND, int EPI, int BN, int STAGES, int CG, int KSUB>
+// CK = true: the cluster K split (MODE_GEMM, one CTA per tile): see decode_cluster_k in ckb_plan.h.
+template <int MODE, int KIND, int EPI, int BN, int STAGES, int CG, int KSUB, bool CK = false>
 __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __grid_constant__ KernelParams P)
 {
+    static_assert(!CK || (MODE == MODE_GEMM && CG == 1), "the cluster K split runs plain GEMM tiles on single CTAs");
     using L = SmemLayout<BN, STAGES, CG, KSUB>;
-    constexpr bool KSPLIT = HasKSplit<MODE, KIND, EPI>::value;
+    static_assert(!CK || BN * BM * 4 <= STAGES * L::STAGE_BYTES, "the raw accumulator tile must fit in the stages");
+    constexpr bool KSPLIT = HasKSplit<MODE, KIND, EPI>::value && !CK;
     constexpr int TILE_M  = BM * CG;
     constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
     constexpr int UMMA_K_BYTES   = 32; // 16 x 16-bit or 32 x 8-bit
@@ -467,6 +624,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
     const bool is_leader    = cta_rank == 0;
     const int unit          = (CG == 2) ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
     const int num_units     = (CG == 2) ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+    // CK: this CTA's K slice = its rank in the cluster, the cluster's tile = its index
+    const int ck_rank = CK ? static_cast<int>(cluster_ctarank()) : 0;
+    auto work_item    = [&](int slot) -> WorkItem {
+        if constexpr(CK)
+            return decode_cluster_k<BN>(P.plan, static_cast<int>(blockIdx.x) / P.plan.ksplit, ck_rank);
+        else
+            return decode_work<MODE, BN, KSPLIT>(P.plan, P.groups, unit, num_units, slot);
+    };
 
     if(threadIdx.x == 0)
     {
@@ -538,7 +703,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
         CKB_TR(long long tr_wait = 0; const long long tr_start = clock64();)
         for(int slot = 0; ok && slot < P.plan.num_slots; ++slot)
         {
-            const WorkItem wi = decode_work<MODE, BN, KSPLIT>(P.plan, P.groups, unit, num_units, slot);
+            const WorkItem wi = work_item(slot);
             if(wi.kind != ITEM_TILE && wi.kind != ITEM_KSLICE)
                 continue;
             const CUtensorMap* tm_a = &P.tm_a;
@@ -727,7 +892,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                    const long long tr_start = clock64();)
             for(int slot = 0; ok && slot < P.plan.num_slots; ++slot)
             {
-                const WorkItem wi = decode_work<MODE, BN, KSPLIT>(P.plan, P.groups, unit, num_units, slot);
+                const WorkItem wi = work_item(slot);
                 if(wi.kind != ITEM_TILE && wi.kind != ITEM_KSLICE)
                     continue;
                 const uint32_t idesc     = make_idesc(C_FMT, AB_FMT, TILE_M, static_cast<uint32_t>(wi.width)) | idesc_major;
@@ -840,7 +1005,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
         CKB_TR(long long tr_wait = 0; const long long tr_start = clock64();)
         for(int slot = 0; ok && slot < P.plan.num_slots; ++slot)
         {
-            const WorkItem wi = decode_work<MODE, BN, KSPLIT>(P.plan, P.groups, unit, num_units, slot);
+            const WorkItem wi = work_item(slot);
             if(wi.kind == ITEM_NONE)
                 continue;
             EpilogueArgs ea   = P.epi;
@@ -933,7 +1098,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
             tc_fence_after_sync();
             const uint32_t tmem_addr =
                 tmem_base + acc * BN + half * span + (static_cast<uint32_t>(quarter * 32) << 16);
-            if(KSPLIT && wi.kind == ITEM_KSLICE)
+            if constexpr(CK)
+                stash_span(tmem_addr, base_addr, quarter * 32 + lane, half * span, span);
+            else if(KSPLIT && wi.kind == ITEM_KSLICE)
                 park_span(tmem_addr, const_cast<uint32_t*>(parked) + static_cast<int64_t>(wi.slice) * TILE_M * BN, span, lane);
             else
                 epilogue_span<EPI, KIND>(tmem_addr, ea, st, lane, m, row_ok, n_begin, n_end, vec_ok);
@@ -948,6 +1115,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                     mbar_arrive(tmem_empty_bar(acc));
             }
 
+            if constexpr(CK)
+                continue; // summed after the cluster barrier below
             if constexpr(KSPLIT)
             {
                 if(wi.kind == ITEM_KSLICE)
@@ -966,7 +1135,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
             {
                 if(epi_num_d(EPI) > 0 && slot + 1 < P.plan.num_slots)
                 {
-                    const WorkItem nx = decode_work<MODE, BN, KSPLIT>(P.plan, P.groups, unit, num_units, slot + 1);
+                    const WorkItem nx = work_item(slot + 1);
                     if(nx.kind != ITEM_TILE)
                         continue;
                     EpilogueArgs en   = P.epi;
@@ -1011,10 +1180,31 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
         })
     }
 
+    if constexpr(CK)
+    {
+        // Every CTA of the cluster has its accumulator in shared memory (release / acquire at cluster scope); then
+        // each sums its column part over all of them.  A CTA that gave up on a wait still takes part in both
+        // barriers; its part is skipped and the status word tells the host.
+        cluster_sync_all();
+        if(warp >= 2 && misc[1] == 0)
+        {
+            const WorkItem wi = work_item(0);
+            const int t       = static_cast<int>(threadIdx.x) - 64;
+            if constexpr(BN >= 128)
+                if(P.plan.ksplit == 8)
+                    cluster_reduce_epilogue<EPI, KIND, BN, 8>(P, wi, base_addr, ck_rank, t);
+            if(P.plan.ksplit == 4)
+                cluster_reduce_epilogue<EPI, KIND, BN, 4>(P, wi, base_addr, ck_rank, t);
+            else if(P.plan.ksplit == 2)
+                cluster_reduce_epilogue<EPI, KIND, BN, 2>(P, wi, base_addr, ck_rank, t);
+        }
+    }
+
     // ---------------------------------------------------------------------- common exit
     tc_fence_before_sync();
-    if constexpr(CG == 2)
-        cluster_sync_all(); // the leader's MMAs read the peer's shared memory until the very end
+    if constexpr(CG == 2 || CK)
+        cluster_sync_all(); // CG = 2: the leader's MMAs read the peer's shared memory until the very end;
+                            // CK: the other CTAs of the cluster read this one's accumulator tile
     else
         __syncthreads();
     tc_fence_after_sync();

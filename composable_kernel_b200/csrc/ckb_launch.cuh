@@ -13,6 +13,7 @@ namespace ckb {
 // main loop once the tiles are large.
 //   one CTA per tile : BN 256 -> 4 stages x 1 x 48 KiB, BN 128 -> 3 x 2 x 32 KiB, BN 64 -> 4 x 2 x 24 KiB
 //   CTA pair per tile: BN 256 -> 3 stages x 2 x 32 KiB per CTA (256 x 256 tile per pair)
+// The cluster K-split instances use the single-CTA shapes; their raw accumulator tile (BN x 512 bytes) reuses the stages.
 // The implicit-GEMM convolution keeps one k block per stage: two were slower with a single-thread producer and no
 // faster with the warp-wide one, and six shallow stages ride out the longer latency of the im2col copies.
 template <int BN, int CG, int MODE>
@@ -34,14 +35,15 @@ inline bool programmatic_launch_enabled()
     return on;
 }
 
-template <int MODE, int KIND, int EPI, int BN, int CG>
+// CK: the cluster K-split instance of the tile shape (a cluster of p.plan.ksplit CTAs per tile).
+template <int MODE, int KIND, int EPI, int BN, int CG, bool CK = false>
 cudaError_t launch_one(const KernelParams& p, int grid, cudaStream_t stream)
 {
     constexpr int STAGES = StagesFor<BN, CG, MODE>::value;
     constexpr int KSUB   = StagesFor<BN, CG, MODE>::ksub;
     constexpr int SMEM   = SmemLayout<BN, STAGES, CG, KSUB>::DYN_BYTES;
     static_assert(SMEM <= 227 * 1024, "pipeline does not fit in shared memory");
-    auto kern            = contraction_kernel<MODE, KIND, EPI, BN, STAGES, CG, KSUB>;
+    auto kern            = contraction_kernel<MODE, KIND, EPI, BN, STAGES, CG, KSUB, CK>;
     static bool attr_done[64] = {};
     int dev                   = 0;
     cudaError_t err           = cudaGetDevice(&dev);
@@ -62,10 +64,10 @@ cudaError_t launch_one(const KernelParams& p, int grid, cudaStream_t stream)
     cfg.stream             = stream;
     cudaLaunchAttribute attr[2];
     int n_attr = 0;
-    if constexpr(CG == 2)
+    if constexpr(CG == 2 || CK)
     {
         attr[n_attr].id               = cudaLaunchAttributeClusterDimension;
-        attr[n_attr].val.clusterDim.x = CG;
+        attr[n_attr].val.clusterDim.x = CK ? p.plan.ksplit : CG;
         attr[n_attr].val.clusterDim.y = 1;
         attr[n_attr].val.clusterDim.z = 1;
         ++n_attr;
@@ -87,6 +89,24 @@ cudaError_t launch_one(const KernelParams& p, int grid, cudaStream_t stream)
 template <int MODE, int KIND, int EPI>
 cudaError_t launch_epi(int bn, int cg, const KernelParams& p, int grid, cudaStream_t stream)
 {
+    if(p.plan.cluster_k != 0)
+    {
+        if constexpr(MODE == MODE_GEMM)
+        {
+            const int ks = p.plan.ksplit;
+            if(cg != 1 || !(ks == 2 || ks == 4 || ks == 8) || grid % ks != 0)
+                return cudaErrorInvalidValue;
+            switch(bn)
+            {
+            case 256: return launch_one<MODE, KIND, EPI, 256, 1, true>(p, grid, stream);
+            case 128: return launch_one<MODE, KIND, EPI, 128, 1, true>(p, grid, stream);
+            case 64: return launch_one<MODE, KIND, EPI, 64, 1, true>(p, grid, stream);
+            default: return cudaErrorInvalidValue;
+            }
+        }
+        else
+            return cudaErrorInvalidValue;
+    }
     if(cg == 2 && bn == 256)
         return launch_one<MODE, KIND, EPI, 256, 2>(p, grid, stream);
     if(cg != 1)
@@ -98,6 +118,34 @@ cudaError_t launch_epi(int bn, int cg, const KernelParams& p, int grid, cudaStre
     case 64: return launch_one<MODE, KIND, EPI, 64, 1>(p, grid, stream);
     default: return cudaErrorInvalidValue;
     }
+}
+
+// How many clusters of `ks` CTAs of the cluster K-split kernel (256-wide tile; the narrower ones use the same
+// shared memory per CTA) the device holds at once: clusters are placed inside one GPC each, so this is less than
+// SMs / ks and depends on how many SMs each GPC of the part has.
+template <int MODE, int KIND, int EPI>
+cudaError_t cluster_capacity(int ks, int* clusters)
+{
+    constexpr int BN = 256, CG = 1;
+    constexpr int STAGES = StagesFor<BN, CG, MODE>::value;
+    constexpr int KSUB   = StagesFor<BN, CG, MODE>::ksub;
+    constexpr int SMEM   = SmemLayout<BN, STAGES, CG, KSUB>::DYN_BYTES;
+    auto kern            = contraction_kernel<MODE, KIND, EPI, BN, STAGES, CG, KSUB, true>;
+    cudaError_t err      = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if(err != cudaSuccess)
+        return err;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim            = dim3(ks * 64, 1, 1);
+    cfg.blockDim           = dim3(NUM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes   = SMEM;
+    cudaLaunchAttribute attr[1];
+    attr[0].id               = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = ks;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs                = attr;
+    cfg.numAttrs             = 1;
+    return cudaOccupancyMaxActiveClusters(clusters, kern, &cfg);
 }
 
 typedef cudaError_t (*LaunchFn)(int, int, const KernelParams&, int, cudaStream_t);

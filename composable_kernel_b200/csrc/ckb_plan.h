@@ -40,7 +40,7 @@ struct PlanParams
     int32_t num_slots;   // work slots per unit
     int32_t m_fastest;   // GEMM / CONV: consecutive tiles walk down a column of tiles instead of along a row
     int32_t group_count; // MODE_GROUPED
-    int32_t pad_;
+    int32_t cluster_k;   // 1: cluster K split - CTA r of cluster t runs K slice r of tile t (see decode_cluster_k)
 };
 
 // What one work item covers.
@@ -187,6 +187,37 @@ CKB_HD WorkItem decode_work(const PlanParams& P, const Group* groups, int unit, 
     return wi;
 }
 
+// Cluster K split (GEMMs with few tiles and a long K): a thread-block cluster of `ksplit` CTAs works on ONE
+// 128 x BN tile, CTA r accumulating K slice r; the slices are summed through distributed shared memory (CTA r
+// reads column part r of every CTA's accumulator, in slice order) and CTA r writes that part of E.  Clusters are
+// independent of one another: nothing waits across clusters and no global scratch is involved.
+// Item of the CTA with cluster rank `rank` in cluster `cluster` (= tile index).
+template <int BN>
+CKB_HD WorkItem decode_cluster_k(const PlanParams& P, int cluster, int rank)
+{
+    WorkItem wi;
+    wi.kind     = ITEM_KSLICE;
+    wi.width    = BN;
+    wi.is_slice = false;
+    wi.group    = 0;
+    wi.batch    = 0;
+    wi.tail     = cluster;
+    wi.slice    = rank;
+    int tile    = cluster;
+    if(P.batch_tiles > 0)
+    {
+        wi.batch = tile / P.batch_tiles;
+        tile -= wi.batch * P.batch_tiles;
+    }
+    int n_blk;
+    tile_position(tile, P.tiles_m, P.tiles_n, P.m_fastest, &wi.m_blk, &n_blk);
+    wi.kb_begin    = rank * P.ks_kb;
+    const int rest = P.num_kb - wi.kb_begin;
+    wi.num_kb      = rest < P.ks_kb ? rest : P.ks_kb;
+    wi.n_start     = n_blk * BN;
+    return wi;
+}
+
 // ---------------------------------------------------------------------------------------------- host side
 
 // A tile shape and tail plan the caller asks for instead of the library's own choice (0 = the library decides).
@@ -196,6 +227,8 @@ struct TileConfig
     int bn = 0;        // 64, 128 or 256 accumulator columns
     int cg = 0;        // 1 = one CTA per 128 x bn tile, 2 = a CTA pair per 256 x 256 tile
     int no_ksplit = 0; // 1 = never cut tiles along K
+    int kbatch    = 0; // 2, 4 or 8: cut every tile's K loop into that many slices on a cluster (KBatch of the
+                       // reference's split-K operation, device_gemm_splitk.hpp:23-42); 0 = the library decides
 };
 
 inline int pick_bn(int64_t M, int64_t N, int sm_count, int min_bn, int forced)
@@ -264,9 +297,33 @@ inline int kb_cycles(int width) { return width >= 256 ? 590 : width >= 128 ? 340
 struct WholeSplit
 {
     int bn = 0, cg = 0, ksplit = 0;
+    bool cluster = false; // slices summed through distributed shared memory instead of the L2 scratch
 };
 
-inline WholeSplit consider_whole_split(int64_t M, int64_t N, int num_kb, int sm_count, int b_min, int64_t est_current)
+// Cost model of the K-split plans (SM cycles), fitted to timings on a B200 of 256 x 256 x 16384, 512 x 512 x 8192,
+// 768 x 768 x 4096, 1024 x 1024 x 8192, 128 x 4096 x 8192 and 128 x 8192 x 4096 with every slice count pinned:
+//   through the L2 scratch (park, counter wait, reload): about 9100 cycles on top of the slice's main loop;
+//   inside a cluster: the slice's main loop at 340 cycles per k block for 128-wide tiles and 500 for 256-wide ones
+//   (one CTA per tile pulls a 48 KiB stage per k block through L2), plus accumulator -> shared memory, cluster
+//   barrier and the reads over distributed shared memory: about 6000 cycles for a 128-wide tile, 12500 for a
+//   256-wide one (the reads are latency bound and grow with the tile).
+constexpr int kParkedReduceCycles = 9100;
+inline int cluster_kb_cycles(int bn) { return bn >= 256 ? 500 : bn >= 128 ? 340 : 315; }
+inline int cluster_reduce_cycles(int bn) { return bn >= 256 ? 12500 : bn >= 128 ? 6000 : 4500; }
+
+// k blocks per slice of a `ks`-way cut (even, so that slices start on a stage boundary); 0 when a slice would be
+// empty or shorter than two k blocks.
+inline int slice_kb(int num_kb, int ks)
+{
+    int kb = (num_kb + ks - 1) / ks;
+    kb     = (kb + 1) & ~1;
+    return (kb >= 2 && static_cast<int64_t>(ks - 1) * kb < num_kb) ? kb : 0;
+}
+
+// `parked` / `cluster`: which of the two ways of summing the slices the caller may use (the parked one needs the
+// scratch buffer and 16-bit operands with a D-less epilogue; the cluster one works for every kernel).
+inline WholeSplit consider_whole_split(int64_t M, int64_t N, int num_kb, int sm_count, int b_min, int64_t est_current,
+                                       bool parked, bool cluster, const int* cluster_cap)
 {
     WholeSplit best;
     int64_t best_est     = est_current - est_current / 8; // has to beat the plan without it by an eighth
@@ -278,21 +335,32 @@ inline WholeSplit consider_whole_split(int64_t M, int64_t N, int num_kb, int sm_
             continue;
         const int64_t G     = sm_count / cg;
         const int64_t tiles = ((M + BM * cg - 1) / (BM * cg)) * ((N + bn - 1) / bn);
-        for(int ks = bn / 32; ks >= 2; ks /= 2) // column parts of the reduction are whole 32-column chunks
+        for(int ks = 8; ks >= 2; ks /= 2)
         {
             if(tiles * ks > G)
                 continue;
-            int ks_kb = (num_kb + ks - 1) / ks;
-            ks_kb     = (ks_kb + 1) & ~1;
-            if(ks_kb < 4 || static_cast<int64_t>(ks - 1) * ks_kb >= num_kb)
+            const int ks_kb = slice_kb(num_kb, ks);
+            if(ks_kb < 4)
                 continue;
-            const int64_t est = static_cast<int64_t>(ks_kb) * kb_cycles(bn) + 9100 + (ks > 4 ? 1500 : 0);
-            if(est < best_est)
+            for(int way = 0; way < 2; ++way)
             {
-                best_est    = est;
-                best.bn     = bn;
-                best.cg     = cg;
-                best.ksplit = ks;
+                const bool by_cluster = way == 1;
+                // parked: column parts of whole 32-column chunks; cluster: one CTA per tile, parts of >= 16 columns,
+                // every cluster resident at once (clusters live inside one GPC each, so fewer fit than SMs / ks)
+                if(by_cluster ? !(cluster && cg == 1 && bn / ks >= 16 && tiles <= cluster_cap[ks == 2 ? 0 : ks == 4 ? 1 : 2])
+                              : !(parked && bn / ks >= 32))
+                    continue;
+                const int64_t est = by_cluster ? static_cast<int64_t>(ks_kb) * cluster_kb_cycles(bn) + cluster_reduce_cycles(bn)
+                                               : static_cast<int64_t>(ks_kb) * kb_cycles(bn) + kParkedReduceCycles +
+                                                     (ks > 4 ? 1500 : 0);
+                if(est < best_est)
+                {
+                    best_est     = est;
+                    best.bn      = bn;
+                    best.cg      = cg;
+                    best.ksplit  = ks;
+                    best.cluster = by_cluster;
+                }
             }
         }
     }
@@ -308,6 +376,8 @@ struct GemmPlanInput
     int b_min     = 32;      // narrowest B slice (rows) one CTA loads
     bool ks_pays    = false; // 16-bit operands and an epilogue without D tensors (see the K-split notes)
     bool ks_allowed = false; // scratch may be used (not disabled, not capturing)
+    bool cluster_ok = false; // the kernel family has cluster K-split instances (plain GEMM)
+    int cluster_cap[3] = {0, 0, 0}; // clusters of 2 / 4 / 8 CTAs the device holds at once
     TileConfig force;
 };
 
@@ -316,6 +386,7 @@ struct GemmPlan
     int bn = 0, cg = 0;
     int grid = 0;         // CTAs to launch
     int b_split_rows = 0; // rows of the B box of a tail slice, per CTA
+    int cluster = 1;      // CTAs per cluster besides the pairing: the slice count of a cluster K split, else 1
     PlanParams pp = {};
     size_t partial_bytes = 0; // parked accumulators of the K split (0 = no scratch needed)
 };
@@ -332,7 +403,21 @@ inline bool plan_gemm(const GemmPlanInput& in, GemmPlan* out)
     int cg              = pick_cg(((in.M + BM - 1) / BM) * ((in.N + bn - 1) / bn) * nb, bn, in.sm_count, in.force.cg);
     const int num_kb    = in.num_kb;
     int whole_ksplit    = 0;
-    if(may_ks && in.batch == 0 && in.force.bn == 0 && in.force.cg == 0)
+    bool by_cluster     = false;
+    const bool may_cluster = in.cluster_ok && !in.force.no_ksplit && in.batch == 0;
+    if((in.force.kbatch == 2 || in.force.kbatch == 4 || in.force.kbatch == 8) && may_cluster && in.force.cg != 2)
+    {
+        // the caller names the slice count: one CTA per tile, a cluster of kbatch CTAs per tile
+        // (several waves of clusters are fine - clusters do not wait for one another - but one must fit)
+        const int cap = in.cluster_cap[in.force.kbatch == 2 ? 0 : in.force.kbatch == 4 ? 1 : 2];
+        if(slice_kb(num_kb, in.force.kbatch) >= 2 && bn / in.force.kbatch >= 16 && cap >= 1)
+        {
+            cg           = 1;
+            whole_ksplit = in.force.kbatch;
+            by_cluster   = true;
+        }
+    }
+    else if((may_ks || may_cluster) && in.batch == 0 && in.force.bn == 0 && in.force.cg == 0)
     {
         // only where the plan without it runs a single, partly filled wave
         const int64_t t0 = ((in.M + BM * cg - 1) / (BM * cg)) * ((in.N + bn - 1) / bn);
@@ -341,14 +426,41 @@ inline bool plan_gemm(const GemmPlanInput& in, GemmPlan* out)
         {
             const WorkPlan w0   = plan_work(t0, static_cast<int>(G0), bn, cg, in.b_min);
             const WholeSplit ws = consider_whole_split(in.M, in.N, num_kb, in.sm_count, in.b_min,
-                                                       static_cast<int64_t>(num_kb) * kb_cycles(bn / w0.split));
+                                                       static_cast<int64_t>(num_kb) * kb_cycles(bn / w0.split), may_ks,
+                                                       may_cluster, in.cluster_cap);
             if(ws.ksplit >= 2)
             {
                 bn           = ws.bn;
                 cg           = ws.cg;
                 whole_ksplit = ws.ksplit;
+                by_cluster   = ws.cluster;
             }
         }
+    }
+    if(by_cluster)
+    {
+        const int64_t tn = (in.N + bn - 1) / bn, tm = (in.M + BM - 1) / BM;
+        if(tm * tn * whole_ksplit > 0x3FFFFFFFll)
+            return false;
+        PlanParams& p = g.pp;
+        p.total_tiles = static_cast<int32_t>(tm * tn);
+        p.split_start = p.total_tiles;
+        p.split       = 1;
+        p.total_work  = p.total_tiles;
+        p.tiles_m     = static_cast<int32_t>(tm);
+        p.tiles_n     = static_cast<int32_t>(tn);
+        p.num_kb      = num_kb;
+        p.ksplit      = whole_ksplit;
+        p.ks_kb       = slice_kb(num_kb, whole_ksplit);
+        p.num_slots   = 1;
+        p.cluster_k   = 1;
+        g.bn           = bn;
+        g.cg           = 1;
+        g.cluster      = whole_ksplit;
+        g.grid         = static_cast<int>(tm * tn * whole_ksplit);
+        g.b_split_rows = bn;
+        *out           = g;
+        return true;
     }
     const int64_t tiles_n   = (in.N + bn - 1) / bn;
     const int64_t tiles_m   = (in.M + BM * cg - 1) / (BM * cg);

@@ -112,6 +112,12 @@ enum {
  * A configuration that the problem cannot use (bn below the narrowest tile of the B layout) falls
  * back to the library's choice for that field. */
 #define CKB_TILE_CONFIG(bn, cg, no_ksplit) ((bn) | ((cg) << 12) | ((no_ksplit) << 16))
+/* The same with a K batch: kbatch = 2, 4 or 8 cuts the K loop of every tile into that many slices, each run by one
+ * CTA of a thread-block cluster and summed through distributed shared memory in slice order (plain GEMM only; the
+ * KBatch of DeviceGemmSplitK, device/device_gemm_splitk.hpp:23-42, with the result written once instead of added
+ * atomically).  kbatch = 1 means no split; a count the problem cannot use (slices shorter than two k blocks of
+ * 128 bytes, column parts narrower than 16) falls back to the library's choice. */
+#define CKB_TILE_CONFIG_KBATCH(bn, cg, kbatch) ((bn) | ((cg) << 12) | ((kbatch) << 20))
 
 /* ---- GEMM: E = epilogue(A*B, D0, D1) ------------------------------------- */
 /* Replaces DeviceGemm::MakeArgumentPointer (device/device_gemm.hpp:26-38) and
@@ -304,6 +310,10 @@ int ckb_release_scratch(void* stream, int all_streams);
 /* ---- diagnostics ------------------------------------------------------------- */
 /* Message of the last failing call made by this thread ("" if none). */
 const char* ckb_last_error(void);
+/* One line describing the launch plan of the calling thread's last *_run call: tile shape, CTAs per tile, grid,
+ * column slices or K slices of the last wave, cluster K split, pitch-fixing copies and, for a GEMM, how many
+ * clusters of 2 / 4 / 8 CTAs the device holds at once ("" before the first call). */
+const char* ckb_last_plan(void);
 /* Device name / SM count of the current device (device_utility/device_prop.hpp:12-52). */
 int ckb_device_info(char* name, size_t name_bytes, int* sm_count, int* cc_major, int* cc_minor);
 /* Number of kernel launches issued by this library in this process. */

@@ -111,11 +111,64 @@ static void walk_bn(int bn, const PlanParams& P, const GroupTiles* groups, int c
         REQUIRE(false, "tile width %d", bn);
 }
 
+// Cluster K split: cluster c works on tile c, CTA r of the cluster on K slice r; the column parts of the reduction
+// (BN / ksplit columns each, one per CTA) are whole 16-column segments.
+template <int BN>
+static void walk_clusters(const GemmPlanInput& in, const GemmPlan& gp)
+{
+    const PlanParams& P = gp.pp;
+    const int ks = P.ksplit;
+    REQUIRE(gp.cg == 1 && gp.cluster == ks && (ks == 2 || ks == 4 || ks == 8), "cluster of %d", gp.cluster);
+    REQUIRE(gp.grid == P.total_tiles * ks && P.num_slots == 1 && gp.partial_bytes == 0, "cluster grid");
+    REQUIRE(BN / ks >= 16 && (BN / ks) % 16 == 0, "column part of %d columns", BN / ks);
+    REQUIRE(P.ks_kb % 2 == 0 && P.ks_kb * (ks - 1) < P.num_kb && P.ks_kb * ks >= P.num_kb, "slice length %d", P.ks_kb);
+    if(in.force.kbatch == 0)
+        REQUIRE(P.total_tiles <= in.cluster_cap[ks == 2 ? 0 : ks == 4 ? 1 : 2], "%d clusters of %d beyond the capacity",
+                P.total_tiles, ks);
+    std::map<std::pair<int, int>, int> tiles_seen;
+    for(int c = 0; c < P.total_tiles; ++c)
+    {
+        std::vector<int> k_seen(P.num_kb, 0);
+        for(int r = 0; r < ks; ++r)
+        {
+            const WorkItem wi = decode_cluster_k<BN>(P, c, r);
+            REQUIRE(wi.kind == ITEM_KSLICE && wi.slice == r && wi.width == BN, "item of cluster %d rank %d", c, r);
+            REQUIRE(wi.m_blk >= 0 && wi.m_blk < P.tiles_m && wi.n_start % BN == 0 && wi.n_start / BN < P.tiles_n, "tile position");
+            REQUIRE(wi.num_kb >= 1 && wi.kb_begin % 2 == 0, "slice [%d, +%d)", wi.kb_begin, wi.num_kb);
+            for(int k = wi.kb_begin; k < wi.kb_begin + wi.num_kb; ++k)
+            {
+                REQUIRE(k < P.num_kb, "k block %d", k);
+                ++k_seen[k];
+            }
+            if(r == 0)
+                ++tiles_seen[{wi.m_blk, wi.n_start}];
+        }
+        for(int k = 0; k < P.num_kb; ++k)
+            REQUIRE(k_seen[k] == 1, "cluster %d k block %d accumulated %d times", c, k, k_seen[k]);
+    }
+    REQUIRE(static_cast<int>(tiles_seen.size()) == P.total_tiles, "every tile has one cluster");
+}
+
+static long g_cluster_plans = 0;
+
 static void check_gemm_plan(const GemmPlanInput& in)
 {
     GemmPlan gp;
     REQUIRE(plan_gemm(in, &gp), "plan_gemm refused M=%lld N=%lld", (long long)in.M, (long long)in.N);
     ++g_plans;
+    if(gp.pp.cluster_k)
+    {
+        ++g_cluster_plans;
+        REQUIRE(in.cluster_ok && !in.force.no_ksplit && in.batch == 0, "cluster plan where it is not allowed");
+        REQUIRE(gp.pp.tiles_m == (in.M + BM - 1) / BM && gp.pp.tiles_n == (in.N + gp.bn - 1) / gp.bn, "tile counts");
+        if(gp.bn == 256)
+            walk_clusters<256>(in, gp);
+        else if(gp.bn == 128)
+            walk_clusters<128>(in, gp);
+        else
+            walk_clusters<64>(in, gp);
+        return;
+    }
     const PlanParams& P = gp.pp;
     const int cg = gp.cg, bn = gp.bn, units = in.sm_count / cg;
     REQUIRE(cg == 1 || (cg == 2 && bn == 256), "cg %d bn %d", cg, bn);
@@ -233,6 +286,23 @@ int main()
                         in.M = M, in.N = N, in.num_kb = kb, in.sm_count = sm, in.b_min = 32;
                         in.ks_pays = pays != 0, in.ks_allowed = true;
                         check_gemm_plan(in);
+                        if(M <= 1024 && N <= 4096)
+                        {
+                            // cluster K split: the library's choice under two capacities, and every named K batch
+                            GemmPlanInput c = in;
+                            c.cluster_ok = true;
+                            c.cluster_cap[0] = 70, c.cluster_cap[1] = 33, c.cluster_cap[2] = 13;
+                            check_gemm_plan(c);
+                            c.cluster_cap[0] = 8, c.cluster_cap[1] = 4, c.cluster_cap[2] = 0;
+                            check_gemm_plan(c);
+                            for(int kbatch : {2, 4, 8})
+                                for(int bn : {0, 64, 128, 256})
+                                {
+                                    c.force = TileConfig{};
+                                    c.force.kbatch = kbatch, c.force.bn = bn;
+                                    check_gemm_plan(c);
+                                }
+                        }
                         if(kb == 40 || kb == 80)
                         {
                             in.ks_allowed = false; // a capturing stream / no scratch
@@ -293,7 +363,8 @@ int main()
             shapes[g] = {256 * (1 + g % 16), 4096, 64};
         check_grouped_plan(shapes, 148, 32, TileConfig{});
     }
-    std::printf("work plan checks passed: %ld plans (%ld with a K split, %ld with column slices), %ld assertions\n", g_plans,
-                g_ksplit_plans, g_slice_plans, g_checks);
+    REQUIRE(g_cluster_plans > 1000 && g_ksplit_plans > 1000 && g_slice_plans > 1000, "the sweep reaches every kind of plan");
+    std::printf("work plan checks passed: %ld plans (%ld with a K split through the scratch, %ld with a cluster K split, %ld "
+                "with column slices), %ld assertions\n", g_plans, g_ksplit_plans, g_cluster_plans, g_slice_plans, g_checks);
     return 0;
 }
