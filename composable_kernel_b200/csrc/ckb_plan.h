@@ -302,14 +302,15 @@ struct WholeSplit
 
 // Cost model of the K-split plans (SM cycles), fitted to timings on a B200 of 256 x 256 x 16384, 512 x 512 x 8192,
 // 768 x 768 x 4096, 1024 x 1024 x 8192, 128 x 4096 x 8192 and 128 x 8192 x 4096 with every slice count pinned:
-//   through the L2 scratch (park, counter wait, reload): about 9100 cycles on top of the slice's main loop;
+//   through the L2 scratch (park, counter wait, reload): about 11000 cycles on top of the slice's main loop when
+//   most of the machine takes part;
 //   inside a cluster: the slice's main loop at 340 cycles per k block for 128-wide tiles and 500 for 256-wide ones
 //   (one CTA per tile pulls a 48 KiB stage per k block through L2), plus accumulator -> shared memory, cluster
-//   barrier and the reads over distributed shared memory: about 6000 cycles for a 128-wide tile, 12500 for a
+//   barrier and the reads over distributed shared memory: about 4500 cycles for a 128-wide tile, 10000 for a
 //   256-wide one (the reads are latency bound and grow with the tile).
-constexpr int kParkedReduceCycles = 9100;
+constexpr int kParkedReduceCycles = 11000;
 inline int cluster_kb_cycles(int bn) { return bn >= 256 ? 500 : bn >= 128 ? 340 : 315; }
-inline int cluster_reduce_cycles(int bn) { return bn >= 256 ? 12500 : bn >= 128 ? 6000 : 4500; }
+inline int cluster_reduce_cycles(int bn) { return bn >= 256 ? 10000 : bn >= 128 ? 4500 : 4000; }
 
 // k blocks per slice of a `ks`-way cut (even, so that slices start on a stage boundary); 0 when a slice would be
 // empty or shorter than two k blocks.

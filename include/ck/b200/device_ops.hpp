@@ -734,8 +734,8 @@ struct DeviceGemmXdl : public DeviceGemm<ALayout, BLayout, CLayout, ADataType, B
 };
 
 // device_gemm_xdl_splitk_c_shuffle.hpp:23-60.  KBatch is the reference's tuning knob for how many ways the K loop
-// is cut (partial sums added atomically into a zero-initialised C); here the result is written once and the library
-// decides by itself where cutting K pays (the tail wave), so the value only has to be >= 1.
+// is cut (partial sums added atomically into a zero-initialised C); here KBatch = 2, 4 or 8 becomes the slice count
+// of the cluster K split and the result is written once, in a fixed summation order.
 template <typename ADataType, typename BDataType, typename CDataType, typename AccDataType, typename ALayout,
           typename BLayout, typename CLayout, typename AElementwiseOperation, typename BElementwiseOperation,
           typename CElementwiseOperation, GemmSpecialization GemmSpec, index_t BlockSize, index_t MPerBlock,
@@ -761,6 +761,11 @@ struct DeviceGemmXdlSplitKCShuffle : public DeviceGemmSplitK<ALayout, BLayout, C
         // device_gemm_xdl_splitk_c_shuffle.hpp pads K to a multiple of KBatch * K0PerBlock * K1 whatever the
         // specialisation; M and N follow the usual rule
         arg.host_ok = arg.host_ok && KBatch >= 1 && b200::specialization_accepts<GemmSpec, MPerBlock, NPerBlock, 1>(M, N, K);
+        // KBatch = 1: no split; 2, 4 or 8: that many K slices on a thread-block cluster, summed in slice order and
+        // written once (the reference adds the slices atomically into a zero-initialised C); any other count leaves
+        // the choice to the library
+        if(KBatch == 1 || KBatch == 2 || KBatch == 4 || KBatch == 8)
+            arg.desc.tile_config = CKB_TILE_CONFIG_KBATCH(0, 0, static_cast<int32_t>(KBatch));
         return arg;
     }
     static auto MakeInvoker() { return Invoker{}; }
@@ -777,7 +782,8 @@ struct DeviceGemmXdlSplitKCShuffle : public DeviceGemmSplitK<ALayout, BLayout, C
         auto arg = std::make_unique<Argument>(MakeArgument(static_cast<const ADataType*>(p_a),
                                                        static_cast<const BDataType*>(p_b), static_cast<CDataType*>(p_c),
                                                        M, N, K, StrideA, StrideB, StrideC, a_op, b_op, c_op, KBatch));
-        arg->set_tile_config(this->tile_config_);
+        if(this->tile_config_ != 0)
+            arg->set_tile_config(this->tile_config_);
         return arg;
     }
     std::unique_ptr<BaseInvoker> MakeInvokerPointer() override { return std::make_unique<Invoker>(); }

@@ -27,7 +27,7 @@ from oracle import ck_oracle as oracle
 
 torch.cuda.set_device(0)
 rng = np.random.default_rng(6)
-M, N, K = 256, 256, 16384          # few tiles, long K: every tile is cut along K (whole-problem split)
+M, N, K = 2048, 2560, 2560         # 80 pair tiles on 74 pairs: the 6 tail tiles are cut along K, parked and summed
 a = rng.integers(-5, 6, (M, K)).astype(np.float16)
 bt = rng.integers(-5, 6, (N, K)).astype(np.float16)
 da, db = torch.from_numpy(a).cuda(), torch.from_numpy(bt).cuda()
@@ -43,6 +43,7 @@ def status():
 
 # 1. a normal launch under the short limit: nothing expires
 g.MakeInvoker().Run(arg)
+assert "ksplit=4" in capi.last_plan() and "cluster_k=0" in capi.last_plan(), capi.last_plan()
 rc, w = status()
 assert (rc, w) == (capi.CKB_OK, 0), (rc, w)
 assert (e.cpu().numpy() == ref).all()
