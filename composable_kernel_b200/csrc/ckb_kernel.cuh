@@ -7,6 +7,7 @@
 //                             M|N positions x the k rows.  One lane per box, one warp-wide copy.
 //   warp 1     MMA issuer   : one thread issues tcgen05.mma (128 x width x 16|32) into one of two
 //                             TMEM accumulators (2 x BN columns) and commits to mbarriers
+//   warp 10    (convolution only) issues the weight copies, warp 0 then only the im2col copies
 //   warps 2-9  epilogue     : tcgen05.ld the finished accumulator (two warps per TMEM lane
 //                             quarter, each half of the columns), apply the fused epilogue with
 //                             the D values prefetched one segment ahead, write each 32 x 32 segment
@@ -80,6 +81,14 @@ enum { KIND_F16 = 0, KIND_BF16 = 1, KIND_I8 = 2 };
 constexpr int BK_BYTES      = 128; // bytes of K per stage row = one swizzle span
 constexpr int NUM_EPI_WARPS = 8;
 constexpr int NUM_THREADS   = 64 + 32 * NUM_EPI_WARPS;
+// The convolution runs one warp more: its weight copies are issued by a warp of their own, so that they do not
+// queue behind the im2col copy of the same stage in the producer warp (an im2col copy blocks its issuer for about
+// 450 cycles; +2.3 % on the N128 C192 71x71 K256 3x3 stride-2 problem, same box, interleaved runs).
+template <int MODE>
+constexpr int threads_for()
+{
+    return MODE == MODE_CONV ? NUM_THREADS + 32 : NUM_THREADS;
+}
 
 // Device status word (KernelParams::status points at it): 0 = fine; otherwise
 // (code << 24) | (block & 0xFFFFFF) of the first wait that gave up.
@@ -583,7 +592,7 @@ __device__ __forceinline__ void cluster_reduce_epilogue(const KernelParams& P, c
 // epilogue warps inside the 168-register budget that ten warps per SM leave.
 // CK = true: the cluster K split (MODE_GEMM, one CTA per tile): see decode_cluster_k in ckb_plan.h.
 template <int MODE, int KIND, int EPI, int BN, int STAGES, int CG, int KSUB, bool CK = false>
-__global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __grid_constant__ KernelParams P)
+__global__ void __launch_bounds__(threads_for<MODE>(), 1) contraction_kernel(const __grid_constant__ KernelParams P)
 {
     static_assert(!CK || (MODE == MODE_GEMM && CG == 1), "the cluster K split runs plain GEMM tiles on single CTAs");
     using L = SmemLayout<BN, STAGES, CG, KSUB>;
@@ -677,8 +686,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
 
     WaitCtx wc{&misc[1], P.wait_limit_ns, P.status};
 
-    if(warp == 0)
+    constexpr bool SPLITP = MODE == MODE_CONV; // convolution: warp 0 issues the im2col copies, the last warp the weights
+    if(warp == 0 || (SPLITP && warp == 2 + NUM_EPI_WARPS))
     {
+        const bool does_b = !SPLITP || warp != 0;
+        const bool does_a = !SPLITP || warp == 0;
         // ------------------------------------------------------------------ TMA producer
         // One lane per TMA box of a stage: the lanes compute their destinations and coordinates side by
         // side and the whole stage is issued by one warp-wide copy instruction (two for the convolution,
@@ -797,9 +809,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
                 const int nsub      = (wi.num_kb - kb < KSUB) ? wi.num_kb - kb : KSUB;
                 const uint32_t dst  = base_addr + stage * L::STAGE_BYTES + box_off;
                 const uint32_t bar  = bar0 + 8u * stage;
-                if(is_leader && lane == 0)
+                if(is_leader && lane == 0 && does_a) // the bytes of both warps' copies are counted on this barrier
                     mbar_arrive_expect_tx(full_bar(stage), sub_bytes * nsub);
-                if(lane_on && box_j < nsub)
+                if(lane_on && box_j < nsub && (is_b ? does_b : does_a))
                 {
                     if constexpr(MODE == MODE_CONV)
                     {
@@ -856,7 +868,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
         // stage used.  The leader's barriers count the bytes of both CTAs, and the pair leaves together
         // (cluster sync at the exit).  Fill number f (0-based) goes to stage f % STAGES with phase
         // (f / STAGES) & 1.
-        if(is_leader && lane == 0)
+        if(is_leader && lane == 0 && warp == 0)
             for(int s = 0; s < STAGES && s < loads; ++s)
             {
                 const int last_fill = ((loads - 1 - s) / STAGES) * STAGES + s;
@@ -988,7 +1000,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) contraction_kernel(const __gri
             }
         }
     }
-    else
+    else if(warp < 2 + NUM_EPI_WARPS)
     {
         // ------------------------------------------------------------------ epilogue warps
         const int quarter = warp & 3;        // TMEM lane quarter this warp may read

@@ -59,7 +59,7 @@ cudaError_t launch_one(const KernelParams& p, int grid, cudaStream_t stream)
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim            = dim3(grid, 1, 1); // CG = 2: a multiple of the cluster size
-    cfg.blockDim           = dim3(NUM_THREADS, 1, 1);
+    cfg.blockDim           = dim3(threads_for<MODE>(), 1, 1);
     cfg.dynamicSmemBytes   = SMEM;
     cfg.stream             = stream;
     cudaLaunchAttribute attr[2];
@@ -136,7 +136,7 @@ cudaError_t cluster_capacity(int ks, int* clusters)
         return err;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim            = dim3(ks * 64, 1, 1);
-    cfg.blockDim           = dim3(NUM_THREADS, 1, 1);
+    cfg.blockDim           = dim3(threads_for<MODE>(), 1, 1);
     cfg.dynamicSmemBytes   = SMEM;
     cudaLaunchAttribute attr[1];
     attr[0].id               = cudaLaunchAttributeClusterDimension;
