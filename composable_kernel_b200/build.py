@@ -37,7 +37,7 @@ def sources():
 
 
 def _headers():
-    hs = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".def"))]
+    hs = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".def", ".h"))]
     hs.append(os.path.join(HERE, "..", "include", "ckb200.h"))
     return hs
 

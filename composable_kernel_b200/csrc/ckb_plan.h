@@ -306,11 +306,11 @@ struct WholeSplit
 //   most of the machine takes part;
 //   inside a cluster: the slice's main loop at 340 cycles per k block for 128-wide tiles and 500 for 256-wide ones
 //   (one CTA per tile pulls a 48 KiB stage per k block through L2), plus accumulator -> shared memory, cluster
-//   barrier and the reads over distributed shared memory: about 4500 cycles for a 128-wide tile, 10000 for a
-//   256-wide one (the reads are latency bound and grow with the tile).
+//   barrier and the reads over distributed shared memory: about 2500 cycles for a 64-wide tile, 4500 for a 128-wide
+//   one, 10000 for a 256-wide one (the reads are latency bound and grow with the tile).
 constexpr int kParkedReduceCycles = 11000;
-inline int cluster_kb_cycles(int bn) { return bn >= 256 ? 500 : bn >= 128 ? 340 : 315; }
-inline int cluster_reduce_cycles(int bn) { return bn >= 256 ? 10000 : bn >= 128 ? 4500 : 4000; }
+inline int cluster_kb_cycles(int bn) { return bn >= 256 ? 500 : bn >= 128 ? 340 : 330; }
+inline int cluster_reduce_cycles(int bn) { return bn >= 256 ? 10000 : bn >= 128 ? 4500 : 2500; }
 
 // k blocks per slice of a `ks`-way cut (even, so that slices start on a stage boundary); 0 when a slice would be
 // empty or shorter than two k blocks.
@@ -328,11 +328,13 @@ inline WholeSplit consider_whole_split(int64_t M, int64_t N, int num_kb, int sm_
 {
     WholeSplit best;
     int64_t best_est     = est_current - est_current / 8; // has to beat the plan without it by an eighth
-    const int cand[3][2] = {{256, 2}, {256, 1}, {128, 1}};
+    const int cand[4][2] = {{256, 2}, {256, 1}, {128, 1}, {64, 1}};
     for(const auto& c : cand)
     {
         const int bn = c[0], cg = c[1];
         if(bn / cg < b_min || (cg == 2 && M <= BM)) // a pair tile with one half of its rows empty pays for nothing
+            continue;
+        if(bn == 64 && !cluster) // 64-wide tiles only as cluster tiles (their reduction is the cheapest)
             continue;
         const int64_t G     = sm_count / cg;
         const int64_t tiles = ((M + BM * cg - 1) / (BM * cg)) * ((N + bn - 1) / bn);
@@ -349,7 +351,7 @@ inline WholeSplit consider_whole_split(int64_t M, int64_t N, int num_kb, int sm_
                 // parked: column parts of whole 32-column chunks; cluster: one CTA per tile, parts of >= 16 columns,
                 // every cluster resident at once (clusters live inside one GPC each, so fewer fit than SMs / ks)
                 if(by_cluster ? !(cluster && cg == 1 && bn / ks >= 16 && tiles <= cluster_cap[ks == 2 ? 0 : ks == 4 ? 1 : 2])
-                              : !(parked && bn / ks >= 32))
+                              : !(parked && bn >= 128 && bn / ks >= 32))
                     continue;
                 const int64_t est = by_cluster ? static_cast<int64_t>(ks_kb) * cluster_kb_cycles(bn) + cluster_reduce_cycles(bn)
                                                : static_cast<int64_t>(ks_kb) * kb_cycles(bn) + kParkedReduceCycles +
