@@ -15,7 +15,9 @@ pytestmark = pytest.mark.gpu
 ROW, COL = capi.CKB_ROW_MAJOR, capi.CKB_COL_MAJOR
 
 
-def draw_case(rng, big):
+def draw_case(rng, big, wide=False):
+    """wide: also draw what the plain cases leave at their defaults - any K, leading dimensions that are not multiples
+    of 16 bytes (the padded-copy path), a pinned tile configuration or a named K batch, and long K with few tiles."""
     dtype = [capi.CKB_F16, capi.CKB_BF16, capi.CKB_I8][rng.integers(0, 3)]
     per16 = 16 if dtype == capi.CKB_I8 else 8
     if big:
@@ -24,9 +26,15 @@ def draw_case(rng, big):
     else:
         M, N = int(rng.integers(1, 700)), int(rng.integers(1, 700))
         K = int(rng.integers(1, 40)) * 16
+    if wide:
+        K = int(rng.integers(1, 3000)) if rng.integers(0, 2) else int(rng.integers(64, 160)) * 64
+        if K > 3000:
+            M, N = int(rng.integers(1, 600)), int(rng.integers(1, 600))
     a_layout, b_layout = [ROW, COL][rng.integers(0, 2)], [ROW, COL][rng.integers(0, 2)]
     # leading dimensions: the contiguous extent rounded up to 16 bytes, sometimes padded further
     def ld(extent):
+        if wide and rng.integers(0, 2):
+            return extent + int(rng.integers(0, 2 * per16))  # any pitch
         return (extent + per16 - 1) // per16 * per16 + per16 * int(rng.integers(0, 3))
     lda = ld(K if a_layout == ROW else M)
     ldb = ld(K if b_layout == COL else N)
@@ -36,11 +44,16 @@ def draw_case(rng, big):
             rng.integers(0, 4)]
     else:
         op = [ck.PassThrough(), ck.Relu(), ck.Scale(0.5), ck.FastGelu()][rng.integers(0, 4)]
-    return dtype, M, N, K, a_layout, b_layout, lda, ldb, lde, op
+    tile = 0
+    if wide:
+        tile = [0, capi.tile_config(256, 2), capi.tile_config(256, 1), capi.tile_config(128, 1), capi.tile_config(64, 1),
+                capi.tile_config(256, 2, 1), capi.tile_config(kbatch=2), capi.tile_config(kbatch=4), capi.tile_config(kbatch=8),
+                capi.tile_config(128, 1, kbatch=4), capi.tile_config(64, 1, kbatch=2)][rng.integers(0, 11)]
+    return dtype, M, N, K, a_layout, b_layout, lda, ldb, lde, op, tile
 
 
 def run_case(rng, case):
-    dtype, M, N, K, a_layout, b_layout, lda, ldb, lde, op = case
+    dtype, M, N, K, a_layout, b_layout, lda, ldb, lde, op, tile = case
     if dtype == capi.CKB_I8:
         a, b = rng.integers(-5, 6, (M, K)).astype(np.int8), rng.integers(-5, 6, (K, N)).astype(np.int8)
     else:
@@ -59,7 +72,7 @@ def run_case(rng, case):
     da, db = image(a, a_layout == COL, lda), image(b, b_layout == COL, ldb)
     tdt = {capi.CKB_I8: torch.int8, capi.CKB_F16: torch.float16, capi.CKB_BF16: torch.int16}[dtype]
     e = torch.zeros((M, lde), dtype=tdt, device="cuda")
-    gemm = ck.DeviceGemm(dtype, a_layout, b_layout)
+    gemm = ck.DeviceGemm(dtype, a_layout, b_layout, tile_config=tile)
     arg = gemm.MakeArgument(da.data_ptr(), db.data_ptr(), e.data_ptr(), M, N, K, lda, ldb, lde, None, None, op)
     assert gemm.IsSupportedArgument(arg), capi.last_error()
     gemm.MakeInvoker().Run(arg)
@@ -70,7 +83,7 @@ def run_case(rng, case):
     ref = oracle.gemm(a, b, op.kind, op.params)
     exact = dtype == capi.CKB_I8 or op.kind in (capi.CKB_EPI_PASSTHROUGH, capi.CKB_EPI_RELU)
     if exact:
-        np.testing.assert_array_equal(out, ref, err_msg=str(case[:9]))
+        np.testing.assert_array_equal(out, ref, err_msg=str(case[:9]) + " " + capi.last_plan())
     elif dtype == capi.CKB_BF16:
         o, r = oracle.from_bf16(out), oracle.from_bf16(ref)
         assert np.all(np.abs(o - r) <= np.abs(r) * 2.0 ** -7 + 1e-3), case[:9]
@@ -91,7 +104,13 @@ def test_random_large_gemm(cuda_device, seed):
     run_case(rng, draw_case(rng, big=True))
 
 
-@pytest.mark.parametrize("seed", range(30))
+@pytest.mark.parametrize("seed", range(80))
+def test_random_gemm_any_pitch_tile_configuration_and_k_batch(cuda_device, seed):
+    rng = np.random.default_rng(7000 + seed)
+    run_case(rng, draw_case(rng, big=seed % 8 == 0, wide=True))
+
+
+@pytest.mark.parametrize("seed", range(45))
 def test_random_convolution(cuda_device, seed):
     """Random 1-D / 2-D / 3-D channels-last convolutions (f16 / bf16 / int8), PassThrough, integer inputs: bit exact."""
     rng = np.random.default_rng(9000 + seed)
@@ -99,6 +118,8 @@ def test_random_convolution(cuda_device, seed):
     dtype = [capi.CKB_F16, capi.CKB_BF16, capi.CKB_I8][rng.integers(0, 3)]
     cmul = 16 if dtype == capi.CKB_I8 else 8
     N, C, K = int(rng.integers(1, 5)), cmul * int(rng.integers(1, 14)), int(rng.integers(1, 70))
+    if seed % 3 == 0:
+        C = int(rng.integers(1, 100))  # any channel count: the zero-padded copy of input and weights
     filt = [int(rng.integers(1, 4)) for _ in range(nd)]
     dil = [int(rng.integers(1, 4)) for _ in range(nd)]
     stride = [int(rng.integers(1, 4)) for _ in range(nd)]
