@@ -73,6 +73,38 @@ def test_gemm_and_conv_replay_from_a_graph(cuda_device):
         np.testing.assert_array_equal(out.cpu().numpy(), oracle.conv2d_fwd(inp, wei, (2, 2), (1, 1), (1, 1)))
 
 
+def test_cluster_k_split_replays_from_a_graph(cuda_device):
+    """A GEMM with few tiles and a long K runs as thread-block clusters whose K slices are summed through distributed
+    shared memory: no scratch, no counters, so the captured launch takes the same plan as the eager one."""
+    rng = np.random.default_rng(79)
+    M, N, K = 256, 384, 8192
+    a, bt = _ints(rng, (M, K)), _ints(rng, (N, K))
+    da, db = torch.from_numpy(a).cuda(), torch.from_numpy(bt).cuda()
+    e = torch.zeros((M, N), dtype=torch.float16, device="cuda")
+    gemm = ck.DeviceGemm(capi.CKB_F16)
+    arg = gemm.MakeArgument(da.data_ptr(), db.data_ptr(), e.data_ptr(), M, N, K, K, K, N)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        gemm.MakeInvoker().Run(arg, ck.StreamConfig(side.cuda_stream, False))
+    eager_plan = capi.last_plan()
+    side.synchronize()
+    assert "cluster_k=0" not in eager_plan, eager_plan
+    np.testing.assert_array_equal(e.cpu().numpy(), oracle.gemm(a, bt.T))
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        gemm.MakeInvoker().Run(arg, ck.StreamConfig(torch.cuda.current_stream().cuda_stream, False))
+    assert capi.last_plan() == eager_plan
+    for rep in range(2):
+        a, bt = _ints(rng, (M, K)), _ints(rng, (N, K))
+        da.copy_(torch.from_numpy(a))
+        db.copy_(torch.from_numpy(bt))
+        e.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert ck.device_status() == 0
+        np.testing.assert_array_equal(e.cpu().numpy(), oracle.gemm(a, bt.T))
+
+
 def test_grouped_gemm_replays_from_a_graph_and_noalloc_refuses_capture(cuda_device):
     rng = np.random.default_rng(78)
     shapes = [(256, 128, 64), (200, 264, 136), (512, 384, 256)]
