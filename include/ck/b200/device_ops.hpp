@@ -1100,7 +1100,10 @@ struct DeviceConv2dFwdXdl_C_Shuffle_Bias_Activation_Input_N_Hi_Wi_C_Weight_K_Y_X
         arg.host_ok = arg.host_ok && OutGlobalMemoryDataOperation == InMemoryDataOperationEnum::Set &&
                       std::is_same<InDataType, WeiDataType>::value && std::is_same<InDataType, OutDataType>::value &&
                       b200::conv_specialization_accepts<ConvForwardSpecialization>(
-                          filter_spatial_lengths, conv_filter_strides, input_left_pads, input_right_pads);
+                          filter_spatial_lengths, conv_filter_strides, input_left_pads, input_right_pads) &&
+                      // device_conv2d_fwd_xdl_c_shuffle_bias_activation_nhwc_kyxc_nhwk.hpp:793-806
+                      b200::vector_widths_accept(C, K, ABlockTransferSrcScalarPerVector, BBlockTransferSrcScalarPerVector,
+                                                 CBlockTransferScalarPerVector);
         return arg;
     }
     static auto MakeInvoker() { return Invoker{}; }
@@ -1165,7 +1168,9 @@ struct DeviceConv2dFwdXdl_C_Shuffle_Bias_Activation_Add_Input_N_Hi_Wi_C_Weight_K
         arg.host_ok = arg.host_ok && std::is_same<InDataType, WeiDataType>::value &&
                       std::is_same<InDataType, OutDataType>::value &&
                       b200::conv_specialization_accepts<ConvForwardSpecialization>(
-                          filter_spatial_lengths, conv_filter_strides, input_left_pads, input_right_pads);
+                          filter_spatial_lengths, conv_filter_strides, input_left_pads, input_right_pads) &&
+                      b200::vector_widths_accept(C, K, ABlockTransferSrcScalarPerVector, BBlockTransferSrcScalarPerVector,
+                                                 CBlockTransferScalarPerVector);
         return arg;
     }
     static auto MakeInvoker() { return Invoker{}; }
