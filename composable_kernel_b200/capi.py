@@ -28,10 +28,10 @@ CKB_NOALLOC_MAX_GROUPS = 256
 CKB_ABI_VERSION = 2
 
 
-def tile_config(bn: int = 0, cg: int = 0, no_ksplit: int = 0, kbatch: int = 0) -> int:
-    """CKB_TILE_CONFIG(bn, cg, no_ksplit) / CKB_TILE_CONFIG_KBATCH(bn, cg, kbatch) of include/ckb200.h;
-    0 = the library's own choice."""
-    return bn | (cg << 12) | (no_ksplit << 16) | (kbatch << 20)
+def tile_config(bn: int = 0, cg: int = 0, no_ksplit: int = 0, kbatch: int = 0, balanced: int = 0) -> int:
+    """CKB_TILE_CONFIG(bn, cg, no_ksplit) / CKB_TILE_CONFIG_KBATCH(bn, cg, kbatch) / CKB_TILE_CONFIG_BALANCED(bn, cg)
+    of include/ckb200.h; 0 = the library's own choice."""
+    return bn | (cg << 12) | (no_ksplit << 16) | (balanced << 17) | (kbatch << 20)
 
 EPI_NUM_D = {CKB_EPI_ADD: 1, CKB_EPI_ADD_RELU_F16: 1, CKB_EPI_BILINEAR: 1, CKB_EPI_ADD_RELU: 1,
              CKB_EPI_ADD_HARDSWISH: 1, CKB_EPI_ADD_ADD_FASTGELU: 2, CKB_EPI_ADD_RELU_ADD: 2}

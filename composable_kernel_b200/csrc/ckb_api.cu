@@ -218,12 +218,15 @@ uint32_t test_kslice_wait_extra()
 // CKB_FORCE_BN / CKB_FORCE_CG / CKB_NO_SPLITK (read at every call), else all zero = the library decides.
 int check_tile_config(int32_t tc)
 {
-    const int bn = tc & 0xFFF, cg = (tc >> 12) & 0xF, kbatch = (tc >> 20) & 0xFF, rest = (tc >> 17) & 0x7, top = tc >> 28;
+    const int bn = tc & 0xFFF, cg = (tc >> 12) & 0xF, kbatch = (tc >> 20) & 0xFF, rest = (tc >> 18) & 0x3, top = tc >> 28;
+    const int balanced = (tc >> 17) & 1, no_ksplit = (tc >> 16) & 1;
     if(tc < 0 || rest != 0 || top != 0 || !(bn == 0 || bn == 64 || bn == 128 || bn == 256) || cg > 2 ||
        !(kbatch == 0 || kbatch == 1 || kbatch == 2 || kbatch == 4 || kbatch == 8))
         return fail(CKB_ERR_INVALID, "tile_config 0x%x is not a CKB_TILE_CONFIG / CKB_TILE_CONFIG_KBATCH value", tc);
     if(kbatch >= 2 && cg == 2)
         return fail(CKB_ERR_UNSUPPORTED, "a K batch runs on single-CTA tiles (cg = 1)");
+    if(balanced && (no_ksplit || kbatch != 0))
+        return fail(CKB_ERR_INVALID, "balanced K ranges exclude a K batch and the no-K-split flag");
     if(cg == 2 && bn != 256 && bn != 0)
         return fail(CKB_ERR_UNSUPPORTED, "a CTA pair (cg = 2) works on 256-wide tiles only");
     return CKB_OK;
@@ -237,6 +240,7 @@ TileConfig tile_config_of(int32_t tc)
         t.bn        = tc & 0xFFF;
         t.cg        = (tc >> 12) & 0xF;
         t.no_ksplit = (tc >> 16) & 1;
+        t.stream_k  = (tc >> 17) & 1;
         t.kbatch    = (tc >> 20) & 0xFF;
         if(t.kbatch == 1) // one K batch = no split
         {
@@ -493,8 +497,9 @@ unsigned long long* trace_buffer()
 void note_plan(const char* what, int bn, int cg, int grid, const PlanParams& pp, int copies)
 {
     snprintf(t_last_plan, sizeof(t_last_plan),
-             "%s tile=%dx%d cg=%d grid=%d tiles=%d col_split=%d ksplit=%d cluster_k=%d slots=%d copies=%d", what,
-             BM * cg, bn, cg, grid, pp.total_tiles, pp.split, pp.ksplit, pp.cluster_k ? pp.ksplit : 0, pp.num_slots, copies);
+             "%s tile=%dx%d cg=%d grid=%d tiles=%d col_split=%d ksplit=%d cluster_k=%d balanced=%d slots=%d copies=%d", what,
+             BM * cg, bn, cg, grid, pp.total_tiles, pp.split, pp.ksplit, pp.cluster_k ? pp.ksplit : 0,
+             pp.stream_k ? pp.ks_kb : 0, pp.num_slots, copies);
 }
 
 // Work that has to run on the stream before the contraction kernel of the same call: pitch-fixing copies of
@@ -871,7 +876,7 @@ static int gemm_run_impl(const ckb_gemm_desc* d_in, const BatchInfo& bi, void* s
         return fail(CKB_ERR_UNSUPPORTED, "too many tiles");
     KernelParams p;
     memset(&p, 0, sizeof(p));
-    if(gp.pp.ksplit >= 2)
+    if(gp.pp.ksplit >= 2 || gp.pp.stream_k != 0)
     {
         // the K split needs scratch; without it the column-slice plan stands
         void* sc = scratch_for(dev, stream, gp.partial_bytes);

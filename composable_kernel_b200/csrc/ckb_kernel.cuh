@@ -68,6 +68,8 @@
 //   [4] MMA: cycles in its loop                       [5] first epilogue warp: cycles waiting for the MMA
 //   [6] first epilogue warp: cycles in its loop       [7] k blocks issued by the MMA role
 //   [8] MMA: cycles issuing tcgen05.mma               [9] MMA: cycles issuing tcgen05.commit
+//   first epilogue warp, K-split plans: [10] cycles waiting on a tile counter, [11] cycles in fix-up epilogues,
+//   [12] cycles parking accumulators
 #ifdef CKB_TRACE
 #define CKB_TR(...) __VA_ARGS__
 #else
@@ -363,9 +365,39 @@ __device__ __forceinline__ void reduce_chunk(uint32_t (&v)[32], const uint32_t* 
     }
 }
 
+// Balanced K ranges: adds chunk `c` of this lane's row of `n` parked accumulators (parking slots `block`,
+// `block + stride`, ...: increasing k) to the accumulator values just read from tensor memory.
+template <int KIND>
+__device__ __forceinline__ void fixup_chunk(uint32_t (&v)[32], const uint32_t* block, int c, int lane, int n, int64_t stride)
+{
+    auto add = [](uint32_t a, uint32_t b) {
+        if constexpr(KIND == KIND_I8)
+            return a + b;
+        else
+            return __float_as_uint(__uint_as_float(a) + __uint_as_float(b));
+    };
+    // eight loads of 16 bytes per thread in flight; two accumulators at a time would not fit the register budget
+    for(int s = 0; s < n; ++s)
+    {
+        const uint4* src = reinterpret_cast<const uint4*>(block + s * stride) + lane + c * 8 * 32;
+        uint4 t[8];
+#pragma unroll
+        for(int q = 0; q < 8; ++q)
+            t[q] = __ldcg(src + q * 32);
+#pragma unroll
+        for(int q = 0; q < 8; ++q)
+        {
+            v[4 * q]     = add(v[4 * q], t[q].x);
+            v[4 * q + 1] = add(v[4 * q + 1], t[q].y);
+            v[4 * q + 2] = add(v[4 * q + 2], t[q].z);
+            v[4 * q + 3] = add(v[4 * q + 3], t[q].w);
+        }
+    }
+}
+
 // REDUCE = true: the accumulator comes from the parked K slices (`parked` = this warp's block in slice 0)
-// instead of tensor memory.
-template <int EPI, int KIND, bool REDUCE = false>
+// instead of tensor memory.  FIX = true: `ks` parked accumulators are added to the one in tensor memory.
+template <int EPI, int KIND, bool REDUCE = false, bool FIX = false>
 __device__ __forceinline__ void epilogue_span(uint32_t tmem_addr, const EpilogueArgs& ea, StoreStage& st, int lane,
                                               int64_t m, bool row_ok, int64_t n_begin, int64_t n_end, bool vec_ok,
                                               const uint32_t* parked = nullptr, int ks = 0, int64_t slice_stride = 0)
@@ -403,6 +435,8 @@ __device__ __forceinline__ void epilogue_span(uint32_t tmem_addr, const Epilogue
         {
             tmem_ld_32x32b_x32(tmem_addr + c * 32, v);
             tmem_ld_wait();
+            if constexpr(FIX)
+                fixup_chunk<KIND>(v, parked, c, lane, ks, slice_stride);
         }
         if(vec_ok && ncols == 32) // warp-uniform: a whole segment leaves through the staged TMA store
         {
@@ -1014,7 +1048,7 @@ __global__ void __launch_bounds__(threads_for<MODE>(), 1) contraction_kernel(con
         st.batch  = -1;
         if(MODE != MODE_GROUPED && P.vec_ok != 0 && lane == 0)
             tma_prefetch_desc(&P.tm_e);
-        CKB_TR(long long tr_wait = 0; const long long tr_start = clock64();)
+        CKB_TR(long long tr_wait = 0, tr_ctr = 0, tr_fix = 0, tr_park = 0; const long long tr_start = clock64();)
         for(int slot = 0; ok && slot < P.plan.num_slots; ++slot)
         {
             const WorkItem wi = work_item(slot);
@@ -1066,8 +1100,10 @@ __global__ void __launch_bounds__(threads_for<MODE>(), 1) contraction_kernel(con
             const uint32_t* parked = nullptr;
             if constexpr(KSPLIT)
             {
-                const uint32_t* tail_base = P.ks_partials + static_cast<int64_t>(wi.tail) * P.plan.ksplit * TILE_M * BN;
-                if(wi.kind == ITEM_KSLICE)
+                // (balanced K ranges: [parking slot = unit][CTA of the pair][epilogue warp][...], wi.slice = 0)
+                const int per_tail        = P.plan.stream_k != 0 ? 1 : P.plan.ksplit;
+                const uint32_t* tail_base = P.ks_partials + static_cast<int64_t>(wi.tail) * per_tail * TILE_M * BN;
+                if(wi.kind == ITEM_KSLICE || wi.fix > 0)
                     parked = tail_base + (cta_rank * NUM_EPI_WARPS + half * 4 + quarter) * (32 * (BN / 2));
                 else if(wi.kind == ITEM_REDUCE)
                 {
@@ -1083,7 +1119,7 @@ __global__ void __launch_bounds__(threads_for<MODE>(), 1) contraction_kernel(con
                 if(wi.kind == ITEM_REDUCE)
                 {
                     // every slice of this tail tile is parked once all epilogue warps that ran one have arrived
-                    uint32_t* counter     = P.ks_counters + wi.tail;
+                    uint32_t* counter     = P.ks_counters + wi.ctr;
                     const uint32_t target = static_cast<uint32_t>(P.plan.ksplit) * NUM_EPI_WARPS * CG;
                     ok                    = bounded_wait_counter(counter, target + P.ks_wait_extra, wc);
                     ok                    = __all_sync(0xffffffffu, ok);
@@ -1113,7 +1149,34 @@ __global__ void __launch_bounds__(threads_for<MODE>(), 1) contraction_kernel(con
             if constexpr(CK)
                 stash_span(tmem_addr, base_addr, quarter * 32 + lane, half * span, span);
             else if(KSPLIT && wi.kind == ITEM_KSLICE)
+            {
+                CKB_TR(const long long trp0 = clock64();)
                 park_span(tmem_addr, const_cast<uint32_t*>(parked) + static_cast<int64_t>(wi.slice) * TILE_M * BN, span, lane);
+                CKB_TR(tr_park += clock64() - trp0;)
+            }
+            else if(KSPLIT && wi.fix > 0)
+            {
+                // the rest of this tile's K range was parked by the next `fix` units as the first item of their runs
+                if constexpr(KSPLIT)
+                {
+                    uint32_t* counter     = P.ks_counters + wi.ctr;
+                    const uint32_t target = static_cast<uint32_t>(wi.fix) * NUM_EPI_WARPS * CG;
+                    CKB_TR(const long long trc0 = clock64();)
+                    ok                    = bounded_wait_counter(counter, target, wc);
+                    ok                    = __all_sync(0xffffffffu, ok);
+                    CKB_TR(const long long trc1 = clock64(); tr_ctr += trc1 - trc0;)
+                    if(ok)
+                    {
+                        epilogue_span<EPI, KIND, false, true>(tmem_addr, ea, st, lane, m, row_ok, n_begin, n_end, vec_ok,
+                                                              parked, wi.fix, static_cast<int64_t>(TILE_M) * BN);
+                        CKB_TR(tr_fix += clock64() - trc1;)
+                        // the last of this tile's warps (both CTAs of a pair) leaves the counter at zero
+                        __syncwarp();
+                        if(lane == 0 && atomicAdd(counter, 1u) + 1u == target + NUM_EPI_WARPS * CG)
+                            atomicExch(counter, 0u);
+                    }
+                }
+            }
             else
                 epilogue_span<EPI, KIND>(tmem_addr, ea, st, lane, m, row_ok, n_begin, n_end, vec_ok);
             // Release the accumulator: all of this warp's tcgen05.ld have completed.
@@ -1137,7 +1200,7 @@ __global__ void __launch_bounds__(threads_for<MODE>(), 1) contraction_kernel(con
                     __threadfence();
                     __syncwarp();
                     if(lane == 0)
-                        atomicAdd(P.ks_counters + wi.tail, 1u);
+                        atomicAdd(P.ks_counters + wi.ctr, 1u);
                     continue;
                 }
             }
@@ -1189,6 +1252,9 @@ __global__ void __launch_bounds__(threads_for<MODE>(), 1) contraction_kernel(con
         CKB_TR(if(P.trace && warp == 2 && lane == 0) {
             P.trace[blockIdx.x * 16 + 5] = tr_wait;
             P.trace[blockIdx.x * 16 + 6] = clock64() - tr_start;
+            P.trace[blockIdx.x * 16 + 10] = tr_ctr;
+            P.trace[blockIdx.x * 16 + 11] = tr_fix;
+            P.trace[blockIdx.x * 16 + 12] = tr_park;
         })
     }
 

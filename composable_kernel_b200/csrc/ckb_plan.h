@@ -41,6 +41,8 @@ struct PlanParams
     int32_t m_fastest;   // GEMM / CONV: consecutive tiles walk down a column of tiles instead of along a row
     int32_t group_count; // MODE_GROUPED
     int32_t cluster_k;   // 1: cluster K split - CTA r of cluster t runs K slice r of tile t (see decode_cluster_k)
+    int32_t stream_k;    // 1: balanced K ranges - the k blocks of the last ks_rem tiles are dealt out evenly, ks_kb per
+                         //    unit, across tile boundaries (ksplit stays 0; see decode_work)
 };
 
 // What one work item covers.
@@ -48,15 +50,19 @@ enum { ITEM_NONE = 0, ITEM_TILE = 1, ITEM_KSLICE = 2, ITEM_REDUCE = 3 };
 struct WorkItem
 {
     int kind;    // ITEM_*: TILE runs all roles; KSLICE is a TILE over part of K whose accumulator is parked;
-                 // REDUCE is epilogue-only
+                 // REDUCE is epilogue-only.  A TILE with fix > 0 covers k blocks [0, num_kb) of its tile only and
+                 // adds the parked accumulators of the `fix` units that ran the rest before its epilogue
     int m_blk;   // row tile
     int n_start; // first output column
     int width;   // columns of this item (BN, or BN/split for a tail slice)
     int kb_begin, num_kb; // k blocks [kb_begin, kb_begin + num_kb)
     int group;   // MODE_GROUPED: index into the group table
     int batch;   // MODE_GEMM: batch index (0 unless batched)
-    int tail;    // KSLICE / REDUCE: index of the tail tile
+    int tail;    // KSLICE / REDUCE: index of the tail tile.  Balanced K ranges: the parking slot - of this unit
+                 // (KSLICE) or of the first unit whose accumulator is added (TILE with fix > 0)
     int slice;   // KSLICE: which K slice; REDUCE: which column part (of width BN / ksplit)
+    int fix;     // TILE: parked accumulators to add (slots tail, tail + 1, ...), in k order
+    int ctr;     // index of the counter the item's tile is announced on
     bool is_slice; // a column slice of a tail tile
 };
 
@@ -98,6 +104,13 @@ CKB_HD void tile_position(int local, int tiles_m, int tiles_n, int m_fastest, in
 //   plain / column-slice plan: item w = unit + slot * num_units of the list [whole tiles][slices of the tail tiles]
 //   K-split plan             : whole tile, K slice, whole tile, reduction of one column part of the tail tile,
 //                              then the remaining whole tiles (parking and reduction both overlap a main loop)
+//   balanced K ranges        : the k blocks of the last ks_rem tiles, laid end to end, are dealt out in runs of
+//                              ks_kb per unit.  A unit's run starts inside a tile (that part is parked in the
+//                              unit's own slot of the scratch: slot 0 of the schedule), may cover whole tiles and
+//                              ends with the head [0, n) of a tile, whose other parts the following one or two
+//                              units parked long before; the head's epilogue adds them.  The ks_full whole tiles
+//                              before that region run between the parked part and the rest of the run.  Nothing
+//                              that is waited for ever waits itself: parked parts are always a unit's first item.
 // `groups` (MODE_GROUPED) is any array whose elements have tile_start, tiles_m, tiles_n, num_kb and m_fastest.
 template <int MODE, int BN, bool KSPLIT, class Group>
 CKB_HD WorkItem decode_work(const PlanParams& P, const Group* groups, int unit, int num_units, int slot)
@@ -112,13 +125,55 @@ CKB_HD WorkItem decode_work(const PlanParams& P, const Group* groups, int unit, 
     wi.slice    = 0;
     wi.kb_begin = 0;
     wi.group    = 0;
-    if(KSPLIT && P.ksplit > 1)
+    wi.fix      = 0;
+    wi.ctr      = 0;
+    int run_kb  = -1; // balanced K ranges: k blocks of this item (else taken from the tile)
+    if(KSPLIT && P.stream_k != 0)
+    {
+        const int dp = P.ks_full / num_units; // whole tiles per unit ahead of the balanced region
+        const int j  = slot == 0 ? 0 : slot - dp; // index of the item inside this unit's run (<= 0: a whole tile)
+        if(slot != 0 && j <= 0)
+            tile = unit + (slot - 1) * num_units;
+        else
+        {
+            const int total = P.ks_rem * P.num_kb;
+            const int lo    = unit * P.ks_kb;
+            const int hi    = lo + P.ks_kb < total ? lo + P.ks_kb : total;
+            const int st    = (lo < total ? lo / P.num_kb : 0) + j; // tile of the balanced region
+            const int t_lo  = st * P.num_kb;
+            if(lo >= total || t_lo >= hi)
+            {
+                wi.kind = ITEM_NONE;
+                tile    = 0;
+            }
+            else
+            {
+                tile          = P.ks_full + st;
+                wi.kb_begin   = j == 0 ? lo - t_lo : 0;
+                const int end = hi - t_lo < P.num_kb ? hi - t_lo : P.num_kb;
+                run_kb        = end - wi.kb_begin;
+                wi.ctr        = st;
+                if(wi.kb_begin > 0)
+                {
+                    wi.kind = ITEM_KSLICE;
+                    wi.tail = unit;
+                }
+                else if(end < P.num_kb)
+                {
+                    wi.fix  = (t_lo + P.num_kb - hi + P.ks_kb - 1) / P.ks_kb;
+                    wi.tail = unit + 1;
+                }
+            }
+        }
+    }
+    else if(KSPLIT && P.ksplit > 1)
     {
         if(slot == 1)
         {
             wi.kind  = unit < P.ks_rem * P.ksplit ? ITEM_KSLICE : ITEM_NONE;
             wi.tail  = unit / P.ksplit;
             wi.slice = unit - wi.tail * P.ksplit;
+            wi.ctr   = wi.tail;
             tile     = P.ks_full + wi.tail;
         }
         else if(slot == 3)
@@ -127,6 +182,7 @@ CKB_HD WorkItem decode_work(const PlanParams& P, const Group* groups, int unit, 
             wi.kind  = unit < P.ks_rem * P.ksplit ? ITEM_REDUCE : ITEM_NONE;
             wi.tail  = unit / P.ksplit;
             wi.slice = unit - wi.tail * P.ksplit;
+            wi.ctr   = wi.tail;
             tile     = P.ks_full + wi.tail;
             slice    = wi.slice;
             wi.width = BN / P.ksplit;
@@ -177,7 +233,9 @@ CKB_HD WorkItem decode_work(const PlanParams& P, const Group* groups, int unit, 
         tile_position(tile, P.tiles_m, P.tiles_n, P.m_fastest, &wi.m_blk, &n_blk);
         wi.num_kb = P.num_kb;
     }
-    if(wi.kind == ITEM_KSLICE)
+    if(run_kb >= 0)
+        wi.num_kb = run_kb;
+    else if(wi.kind == ITEM_KSLICE)
     {
         wi.kb_begin    = wi.slice * P.ks_kb;
         const int rest = P.num_kb - wi.kb_begin;
@@ -201,6 +259,8 @@ CKB_HD WorkItem decode_cluster_k(const PlanParams& P, int cluster, int rank)
     wi.is_slice = false;
     wi.group    = 0;
     wi.batch    = 0;
+    wi.fix      = 0;
+    wi.ctr      = 0;
     wi.tail     = cluster;
     wi.slice    = rank;
     int tile    = cluster;
@@ -229,6 +289,7 @@ struct TileConfig
     int no_ksplit = 0; // 1 = never cut tiles along K
     int kbatch    = 0; // 2, 4 or 8: cut every tile's K loop into that many slices on a cluster (KBatch of the
                        // reference's split-K operation, device_gemm_splitk.hpp:23-42); 0 = the library decides
+    int stream_k  = 0; // 1 = balanced K ranges wherever the kernel family has them, whatever the cost model says
 };
 
 inline int pick_bn(int64_t M, int64_t N, int sm_count, int min_bn, int forced)
@@ -396,6 +457,50 @@ struct GemmPlan
 
 constexpr int kMaxTailTiles = 1024; // tail-tile counters at the front of the scratch buffer
 
+// Balanced K ranges (see decode_work): the k blocks of the tiles are laid end to end and dealt out evenly.  The
+// library takes the plan by itself only for one partly filled wave of 256-wide tiles with a long K, by this cost
+// model in SM cycles, fitted to timings of 1280 x 2048 x K (K = 4096 ... 16384) on a B200:
+//   one CTA per 128 x 256 tile, tiles <= SMs        558 per k block + 5600
+//   balanced, one CTA per tile, every SM loading     729 per k block + 17700
+//   balanced, CTA pairs on 256 x 256 tiles           606 per k block + 22200
+// With every SM loading a k block costs more, and the last epilogue of a unit grows by the wait for the unit that
+// parks last and by the parked accumulators it reads back from L2.  The units' K ranges are out of step, so an
+// operand panel is fetched once per tile that uses it instead of once per wave: beyond what stays in L2 the plan
+// loses (512 x 8192 x 16384 with one CTA per tile: four times the DRAM traffic, 184 us against 104).
+constexpr int kBalancedGainPct = 93; // taken when its estimate is at most this share of the plain plan's
+inline int64_t est_plain_wave(int num_kb, int cg) { return static_cast<int64_t>(num_kb) * (cg == 2 ? 480 : 558) + 5600; }
+inline int64_t est_balanced(int64_t run_kb, int cg) { return cg == 2 ? run_kb * 606 + 22200 : run_kb * 729 + 17700; }
+inline int64_t balanced_operand_limit(int cg) { return cg == 2 ? (128ll << 20) : (64ll << 20); }
+inline int64_t balanced_run_kb(int64_t tiles, int num_kb, int64_t units)
+{
+    const int64_t w = (tiles * num_kb + units - 1) / units;
+    return (w + 1) & ~int64_t(1);
+}
+
+// CTAs per tile (1 or 2) of the balanced plan the library would take for a problem whose plain plan is one partly
+// filled wave of 256-wide tiles with `cg_now` CTAs per tile; 0 = keep the plain plan.
+inline int consider_balanced(int64_t M, int64_t N, int num_kb, int sm_count, int b_min, int cg_now, int cg_forced)
+{
+    const int64_t est_now = est_plain_wave(num_kb, cg_now);
+    int best              = 0;
+    int64_t best_est      = est_now * kBalancedGainPct / 100;
+    for(int cg = 2; cg >= 1; --cg)
+    {
+        if((cg_forced != 0 && cg_forced != cg) || 256 / cg < b_min || (cg == 2 && M <= BM))
+            continue;
+        const int64_t G = sm_count / cg, T = ((M + BM * cg - 1) / (BM * cg)) * ((N + 255) / 256);
+        if(T >= G || T * 2 <= G || (M + N) * static_cast<int64_t>(num_kb) * 128 > balanced_operand_limit(cg))
+            continue;
+        const int64_t est = est_balanced(balanced_run_kb(T, num_kb, G), cg);
+        if(est <= best_est)
+        {
+            best_est = est;
+            best     = cg;
+        }
+    }
+    return best;
+}
+
 // Tile shape, CTA grouping and tail plan of one (batched) GEMM.  Returns false when the tile count does not fit.
 inline bool plan_gemm(const GemmPlanInput& in, GemmPlan* out)
 {
@@ -405,6 +510,16 @@ inline bool plan_gemm(const GemmPlanInput& in, GemmPlan* out)
     int bn              = pick_bn(in.M, in.N, in.sm_count, in.b_min, in.force.bn);
     int cg              = pick_cg(((in.M + BM - 1) / BM) * ((in.N + bn - 1) / bn) * nb, bn, in.sm_count, in.force.cg);
     const int num_kb    = in.num_kb;
+    {
+        // One partly filled wave of 128 x 256 tiles over a problem that is narrow in M or N (at most 512): few tiles
+        // share each panel of the large operand, so it streams from DRAM nearly once per tile; a CTA pair loads half
+        // as much of B per CTA and was 3-12 % faster there (512 x 8192 x 4096: 26.9 against 29.9 us, 512 x 8192 x
+        // 16384: 88.6 against 101; square-ish problems of the same tile count lose 4 % with pairs).
+        const int64_t tm = (in.M + BM - 1) / BM, t128 = tm * ((in.N + 255) / 256) * nb;
+        if(in.force.cg == 0 && bn == 256 && cg == 1 && t128 < in.sm_count && t128 * 2 > in.sm_count && tm % 2 == 0 &&
+           (in.M <= 512 || in.N <= 512) && in.b_min <= 128)
+            cg = 2;
+    }
     int whole_ksplit    = 0;
     bool by_cluster     = false;
     const bool may_cluster = in.cluster_ok && !in.force.no_ksplit && in.batch == 0;
@@ -437,6 +552,20 @@ inline bool plan_gemm(const GemmPlanInput& in, GemmPlan* out)
                 cg           = ws.cg;
                 whole_ksplit = ws.ksplit;
                 by_cluster   = ws.cluster;
+            }
+        }
+    }
+    bool balanced = false;
+    if(may_ks && whole_ksplit < 2 && in.batch == 0 && in.force.bn == 0 && bn == 256 && num_kb >= 8)
+    {
+        const int64_t t_now = ((in.M + BM * cg - 1) / (BM * cg)) * ((in.N + bn - 1) / bn);
+        if(t_now < in.sm_count / cg)
+        {
+            const int cg_bal = consider_balanced(in.M, in.N, num_kb, in.sm_count, in.b_min, cg, in.force.cg);
+            if(cg_bal != 0)
+            {
+                cg       = cg_bal;
+                balanced = true;
             }
         }
     }
@@ -507,7 +636,28 @@ inline bool plan_gemm(const GemmPlanInput& in, GemmPlan* out)
             plan.grid        = static_cast<int32_t>(G * cg);
         }
     }
-    if(p.ksplit < 2)
+    // Balanced K ranges: by the library's own choice (above) or because the caller asks for them - then also with
+    // whole waves before the region, which takes in the last full wave so that every run covers at least a tile.
+    if(may_ks && p.ksplit < 2 && whole_ksplit < 2 && in.batch == 0 && bn >= 128 && rem > 0 && all_tiles * 2 > G && num_kb >= 8 &&
+       (balanced || in.force.stream_k != 0))
+    {
+        const int64_t D = all_tiles < 2 * G ? 0 : ful - G, R = all_tiles - D;
+        const int64_t W = balanced_run_kb(R, num_kb, G);
+        if(R <= kMaxTailTiles && W * 2 >= num_kb)
+        {
+            g.partial_bytes  = static_cast<size_t>(G) * (BM * cg) * bn * sizeof(uint32_t); // one parking slot per unit
+            p.stream_k       = 1;
+            p.ks_kb          = static_cast<int32_t>(W);
+            p.ks_full        = static_cast<int32_t>(D);
+            p.ks_rem         = static_cast<int32_t>(R);
+            p.num_slots      = static_cast<int32_t>(D / G + 1 + (W - 1 + num_kb - 1) / num_kb);
+            plan.split       = 1;
+            plan.split_start = static_cast<int32_t>(all_tiles);
+            plan.total_work  = static_cast<int32_t>(all_tiles);
+            plan.grid        = static_cast<int32_t>(G * cg);
+        }
+    }
+    if(p.ksplit < 2 && p.stream_k == 0)
         p.num_slots = static_cast<int32_t>((plan.total_work + G - 1) / G);
     p.total_tiles  = static_cast<int32_t>(all_tiles);
     p.split_start  = plan.split_start;

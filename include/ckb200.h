@@ -118,6 +118,12 @@ enum {
  * atomically).  kbatch = 1 means no split; a count the problem cannot use (slices shorter than two k blocks of
  * 128 bytes, column parts narrower than 16) falls back to the library's choice. */
 #define CKB_TILE_CONFIG_KBATCH(bn, cg, kbatch) ((bn) | ((cg) << 12) | ((kbatch) << 20))
+/* The same with balanced K ranges: the k blocks of the tiles of the last one or two waves are laid end to end and
+ * dealt out evenly over the CTAs (or CTA pairs), across tile boundaries; a CTA whose run ends inside a tile adds
+ * the accumulators that the CTAs running the rest of that tile parked in the library's scratch, in k order
+ * (16-bit GEMMs whose epilogue reads no D tensor, tiles of 128 or 256 columns; elsewhere the field falls back to
+ * the library's choice).  The library also takes this plan by itself where its cost estimate says so. */
+#define CKB_TILE_CONFIG_BALANCED(bn, cg) ((bn) | ((cg) << 12) | (1 << 17))
 
 /* ---- GEMM: E = epilogue(A*B, D0, D1) ------------------------------------- */
 /* Replaces DeviceGemm::MakeArgumentPointer (device/device_gemm.hpp:26-38) and

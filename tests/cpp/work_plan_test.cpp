@@ -6,6 +6,10 @@
 //   - under a K split every tail tile's k blocks are covered exactly once by its slices, each slice starts on a
 //     stage boundary, the unit that runs slice i reduces column part i, every unit of the launch is needed at the
 //     same time only up to the number of units, and the parked partials fit the fixed scratch size;
+//   - under balanced K ranges every unit's run is ks_kb k blocks of the region laid end to end, a part that is parked
+//     is the first item of its unit and lies in the unit's own parking slot, every tile that is not run whole has
+//     exactly one head [0, n) whose `fix` count and first slot name exactly the units that parked the rest, in k
+//     order, and all k blocks of the tile are covered once;
 //   - the grouped table's prefix sums, per-group tile order and binary search agree.
 // It is the counterpart of the reference's tile-map tests (test/block_to_ctile_map/test_block_to_ctile_map.cpp:205-322).
 // Build: g++ -std=c++17 -I composable_kernel_b200/csrc tests/cpp/work_plan_test.cpp
@@ -21,7 +25,7 @@
 
 using namespace ckb;
 
-static long g_checks = 0, g_plans = 0, g_ksplit_plans = 0, g_slice_plans = 0;
+static long g_checks = 0, g_plans = 0, g_ksplit_plans = 0, g_slice_plans = 0, g_balanced_plans = 0;
 
 #define REQUIRE(cond, ...)                                \
     do                                                    \
@@ -43,6 +47,11 @@ struct Coverage
     // key: tail tile -> per k block, times accumulated
     std::map<int, std::vector<int>> tail_k;
     std::map<int, std::vector<int>> tail_slices; // tail -> slice ids seen
+    // balanced K ranges: tile of the region -> (first parking slot, count) named by its head; -> units that parked, with
+    // the first k block of each part
+    std::map<int, std::pair<int, int>> head_fix;
+    std::map<int, std::vector<std::pair<int, int>>> parked_by;
+    std::map<int, int> unit_kb; // unit -> k blocks of the region it runs
 };
 
 template <int MODE, int BN, bool KSPLIT>
@@ -65,9 +74,40 @@ static void walk(const PlanParams& P, const GroupTiles* groups, int cg, int grid
             if(wi.kind == ITEM_TILE || wi.kind == ITEM_REDUCE)
                 for(int c = wi.n_start; c < wi.n_start + wi.width; c += 32)
                     ++cov.out[{scope, wi.m_blk, c}];
+            if(KSPLIT && P.stream_k != 0 && (wi.kind == ITEM_KSLICE || wi.fix > 0 || (slot == 0 || slot > P.ks_full / num_units)))
+            {
+                // an item of the balanced region
+                REQUIRE(wi.kind == ITEM_TILE || wi.kind == ITEM_KSLICE, "kind %d in a balanced run", wi.kind);
+                REQUIRE(wi.ctr >= 0 && wi.ctr < P.ks_rem && wi.width == BN && !wi.is_slice, "tile %d of the region", wi.ctr);
+                REQUIRE(wi.num_kb >= 1 && wi.kb_begin >= 0 && wi.kb_begin + wi.num_kb <= P.num_kb, "k range [%d, +%d)", wi.kb_begin, wi.num_kb);
+                auto& v = cov.tail_k[wi.ctr];
+                v.resize(P.num_kb, 0);
+                for(int k = wi.kb_begin; k < wi.kb_begin + wi.num_kb; ++k)
+                    ++v[k];
+                cov.unit_kb[unit] += wi.num_kb;
+                if(wi.kind == ITEM_KSLICE)
+                {
+                    REQUIRE(slot == 0 && wi.tail == unit && wi.kb_begin > 0 && wi.slice == 0 && wi.fix == 0, "a parked part is a unit's first item, in its own slot");
+                    cov.parked_by[wi.ctr].push_back({unit, wi.kb_begin});
+                }
+                else
+                {
+                    REQUIRE(wi.kb_begin == 0, "a head starts at k block 0");
+                    if(wi.num_kb < P.num_kb)
+                    {
+                        REQUIRE(wi.fix >= 1 && wi.tail == unit + 1, "head of %d k blocks names %d parts from slot %d", wi.num_kb, wi.fix, wi.tail);
+                        REQUIRE(cov.head_fix.count(wi.ctr) == 0, "two heads for tile %d", wi.ctr);
+                        cov.head_fix[wi.ctr] = {wi.tail, wi.fix};
+                    }
+                    else
+                        REQUIRE(wi.fix == 0, "a whole tile adds nothing");
+                }
+                continue;
+            }
             if(wi.kind == ITEM_TILE)
             {
                 const int want_kb = MODE == MODE_GROUPED ? groups[wi.group].num_kb : P.num_kb;
+                REQUIRE(wi.fix == 0, "fix-up outside a balanced plan");
                 REQUIRE(wi.kb_begin == 0 && wi.num_kb == want_kb, "whole tile covers k blocks [%d, +%d) of %d", wi.kb_begin,
                         wi.num_kb, want_kb);
                 if(wi.is_slice)
@@ -177,7 +217,18 @@ static void check_gemm_plan(const GemmPlanInput& in)
     const int64_t nb = in.batch > 0 ? in.batch : 1;
     REQUIRE(P.tiles_m == (in.M + BM * cg - 1) / (BM * cg) && P.tiles_n == (in.N + bn - 1) / bn, "tile counts");
     REQUIRE(P.total_tiles == static_cast<int64_t>(P.tiles_m) * P.tiles_n * nb, "total tiles");
-    if(P.ksplit >= 2)
+    if(P.stream_k != 0)
+    {
+        ++g_balanced_plans;
+        REQUIRE(in.ks_pays && in.ks_allowed && !in.force.no_ksplit && in.batch == 0 && P.ksplit == 0 && P.split == 1, "balanced plan where it is not allowed");
+        REQUIRE(gp.grid == units * cg && bn >= 128, "a balanced launch uses every unit");
+        REQUIRE(P.ks_full % units == 0 && P.ks_full + P.ks_rem == P.total_tiles && P.ks_rem <= kMaxTailTiles, "whole tiles %d + region %d", P.ks_full, P.ks_rem);
+        REQUIRE(P.ks_kb % 2 == 0 && static_cast<int64_t>(P.ks_kb) * units >= static_cast<int64_t>(P.ks_rem) * P.num_kb &&
+                    static_cast<int64_t>(P.ks_kb - 2) * units < static_cast<int64_t>(P.ks_rem) * P.num_kb, "run length %d", P.ks_kb);
+        REQUIRE(gp.partial_bytes == static_cast<size_t>(units) * BM * cg * bn * 4, "one parking slot per unit");
+        REQUIRE(gp.partial_bytes <= static_cast<size_t>(in.sm_count) * BM * 256 * 4, "parked bytes beyond the fixed scratch");
+    }
+    else if(P.ksplit >= 2)
     {
         ++g_ksplit_plans;
         REQUIRE(in.ks_pays && in.ks_allowed && !in.force.no_ksplit, "K split where it is not allowed");
@@ -214,7 +265,28 @@ static void check_gemm_plan(const GemmPlanInput& in)
     for(const auto& kv : cov.out)
         REQUIRE(kv.second == 1, "chunk (%d, %d, %d) written %d times", std::get<0>(kv.first), std::get<1>(kv.first),
                 std::get<2>(kv.first), kv.second);
-    if(P.ksplit >= 2)
+    if(P.stream_k != 0)
+    {
+        REQUIRE(static_cast<int>(cov.tail_k.size()) == P.ks_rem, "tiles of the balanced region");
+        for(const auto& kv : cov.tail_k)
+            for(int k = 0; k < P.num_kb; ++k)
+                REQUIRE(kv.second[k] == 1, "tile %d k block %d accumulated %d times", kv.first, k, kv.second[k]);
+        for(const auto& kv : cov.unit_kb)
+            REQUIRE(kv.second <= P.ks_kb, "unit %d runs %d k blocks", kv.first, kv.second);
+        REQUIRE(cov.parked_by.size() == cov.head_fix.size(), "every tile with parked parts has a head that adds them");
+        for(const auto& kv : cov.head_fix)
+        {
+            const auto& parts = cov.parked_by[kv.first];
+            REQUIRE(static_cast<int>(parts.size()) == kv.second.second, "tile %d: %zu parts parked, head adds %d", kv.first, parts.size(), kv.second.second);
+            for(size_t i = 0; i < parts.size(); ++i)
+            {
+                REQUIRE(parts[i].first == kv.second.first + static_cast<int>(i), "tile %d: part %zu parked by unit %d", kv.first, i, parts[i].first);
+                if(i > 0)
+                    REQUIRE(parts[i].second > parts[i - 1].second, "parts in k order");
+            }
+        }
+    }
+    else if(P.ksplit >= 2)
     {
         REQUIRE(static_cast<int>(cov.tail_k.size()) == P.ks_rem, "tail tiles with slices");
         for(const auto& kv : cov.tail_k)
@@ -319,6 +391,13 @@ int main()
                                     }
                             in.force = TileConfig{};
                             in.b_min = 32;
+                            for(int bn : {0, 128, 256}) // balanced K ranges wherever they apply
+                                for(int cgf : {0, 1, 2})
+                                {
+                                    in.force.bn = bn, in.force.cg = cgf, in.force.stream_k = 1;
+                                    check_gemm_plan(in);
+                                }
+                            in.force = TileConfig{};
                             for(int64_t batch : {2, 3, 40})
                             {
                                 in.batch = batch;
@@ -342,6 +421,26 @@ int main()
         in.M = 128 * 36 * 36, in.N = 256, in.num_kb = 27, in.b_min = 64;
         check_gemm_plan(in);
     }
+    // one half-filled wave: balanced K ranges on CTA pairs for a long K, the plain plan for a short one or for
+    // operands that would not stay in L2
+    {
+        GemmPlanInput in;
+        in.sm_count = 148, in.b_min = 32, in.ks_allowed = true, in.ks_pays = true;
+        in.M = 1280, in.N = 2048, in.num_kb = 128;
+        GemmPlan gp;
+        plan_gemm(in, &gp);
+        REQUIRE(gp.pp.stream_k == 1 && gp.cg == 2 && gp.bn == 256 && gp.pp.ks_kb == 70 && gp.pp.ks_full == 0 && gp.pp.ks_rem == 40,
+                "1280 x 2048 x 8192: balanced, run %d", gp.pp.ks_kb);
+        in.num_kb = 64;
+        plan_gemm(in, &gp);
+        REQUIRE(gp.pp.stream_k == 0 && gp.cg == 1, "1280 x 2048 x 4096: plain");
+        in.M = 512, in.N = 8192, in.num_kb = 256;
+        plan_gemm(in, &gp);
+        REQUIRE(gp.pp.stream_k == 0, "512 x 8192 x 16384: operands beyond L2, plain");
+        in.M = 1280, in.N = 2048, in.num_kb = 128, in.ks_pays = false;
+        plan_gemm(in, &gp);
+        REQUIRE(gp.pp.stream_k == 0, "no balanced plan for kernels without the scratch path");
+    }
     // grouped tables
     std::mt19937 rng(1234);
     for(int rep = 0; rep < 300; ++rep)
@@ -363,8 +462,10 @@ int main()
             shapes[g] = {256 * (1 + g % 16), 4096, 64};
         check_grouped_plan(shapes, 148, 32, TileConfig{});
     }
-    REQUIRE(g_cluster_plans > 1000 && g_ksplit_plans > 1000 && g_slice_plans > 1000, "the sweep reaches every kind of plan");
-    std::printf("work plan checks passed: %ld plans (%ld with a K split through the scratch, %ld with a cluster K split, %ld "
-                "with column slices), %ld assertions\n", g_plans, g_ksplit_plans, g_cluster_plans, g_slice_plans, g_checks);
+    REQUIRE(g_cluster_plans > 1000 && g_ksplit_plans > 1000 && g_slice_plans > 1000 && g_balanced_plans > 1000,
+            "the sweep reaches every kind of plan");
+    std::printf("work plan checks passed: %ld plans (%ld with a K split through the scratch, %ld with balanced K ranges, %ld "
+                "with a cluster K split, %ld with column slices), %ld assertions\n", g_plans, g_ksplit_plans, g_balanced_plans,
+                g_cluster_plans, g_slice_plans, g_checks);
     return 0;
 }

@@ -193,6 +193,16 @@ def test_op_instance_run_engine_conv(examples_built, nd):
     assert "SUCCESS" in out and "PASSED" in out and "Perf:" in out
 
 
+def test_odd_channel_conv_and_odd_pitch_gemm_through_the_device_ops(examples_built):
+    """The reference's odd-channel problem (test/convnd_fwd/conv2d_fwd.cpp:110-111: C = 3) through an instance whose
+    operand loads are one element wide, and a K = 1001, lda = ldb = 1001 GEMM through the MNKPadding instances of the
+    factory: both verified by the example's CPU reference operator."""
+    out = run_example("convnd_fwd_instance_engine", 2, "oddc")
+    assert "SUCCESS" in out and "PASSED" in out and "Perf:" in out
+    out = run_example("ck_profiler", "gemm", 1, 1, 1, 1, 0, 1, 515, 333, 1001, 1001, 1001, 333)
+    assert "Best Perf for gemm" in out
+
+
 def test_profiler_driver_bilinear_and_splitk(examples_built):
     """gemm_bilinear (profile_gemm_bilinear.cpp:29-43) and gemm_splitk (profile_gemm_splitk.cpp:29-42)."""
     out = run_example("ck_profiler", "gemm_bilinear", 1, 1, 1, 2, 0, 1, 384, 512, 256, 256, 256, 512, 512, 0.5, 1.5)
