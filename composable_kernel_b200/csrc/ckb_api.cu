@@ -151,7 +151,10 @@ bool stream_is_capturing(cudaStream_t stream)
     return st != cudaStreamCaptureStatusNone;
 }
 
-constexpr size_t kScratchCounterBytes = kMaxTailTiles * sizeof(uint32_t); // tail-tile counters at the front
+// Front of the scratch buffer: the tail-tile counters, then the flags of the balanced K ranges (one per parking
+// slot x CTA x epilogue warp = 8 per SM); 16 KiB hold both for up to 384 SMs.
+constexpr size_t kScratchCounterBytes = 16 * 1024;
+static_assert(kScratchCounterBytes >= kMaxTailTiles * sizeof(uint32_t) + 384 * 8 * sizeof(uint32_t), "counter area");
 
 // Scratch of `stream` for the K-split plans; nullptr when the device has no memory left for it or the stream is
 // capturing (the caller then keeps a plan that needs none).  Every K-split plan parks at most one accumulator tile
@@ -883,6 +886,7 @@ static int gemm_run_impl(const ckb_gemm_desc* d_in, const BatchInfo& bi, void* s
         if(sc)
         {
             p.ks_counters   = static_cast<uint32_t*>(sc);
+            p.ks_flags      = p.ks_counters + kMaxTailTiles;
             p.ks_partials   = reinterpret_cast<uint32_t*>(static_cast<char*>(sc) + kScratchCounterBytes);
             p.ks_wait_extra = test_kslice_wait_extra();
         }

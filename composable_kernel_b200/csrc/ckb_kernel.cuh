@@ -160,6 +160,8 @@ struct KernelParams
     int64_t batch_stride_e, batch_stride_d0, batch_stride_d1; // elements between batches of E / D0 / D1
     uint32_t* ks_partials; // [tail tile][slice][TILE_M rows][BN columns] raw 32-bit accumulators
     uint32_t* ks_counters; // one per tail tile, zero between launches
+    uint32_t* ks_flags;    // balanced K ranges: one per (parking slot, CTA of the pair, epilogue warp), set by the
+                           // warp that parked its block, cleared by the one warp that reads it back
     uint32_t ks_wait_extra; // test hook: added to the arrival count a reduction waits for, so that the wait runs out
     uint32_t pad_;
     ConvGeom conv;
@@ -293,7 +295,10 @@ __device__ __forceinline__ bool bounded_wait_counter(const uint32_t* counter, ui
 // out as [chunk of 32 columns][quad q of 4 columns][lane] of 16 bytes (lane = row), 512 contiguous bytes per
 // instruction, instead of 32 row pieces a row pitch apart.
 // Slice side: one warp parks `ncols` (a multiple of 32) raw accumulator columns of its 32 rows.
-__device__ __forceinline__ void park_span(uint32_t tmem_addr, uint32_t* block, int ncols, int lane)
+// With `flag` (balanced K ranges) the block is published to the one warp that will add it back: stores -> fence ->
+// flag (a fence per chunk, so that the reader could start on chunk 0 while chunk 1 is parked, was tried: the fences
+// made parking three times as slow).
+__device__ __forceinline__ void park_span(uint32_t tmem_addr, uint32_t* block, int ncols, int lane, uint32_t* flag = nullptr)
 {
     uint4* dst = reinterpret_cast<uint4*>(block) + lane;
     for(int c = 0; c < ncols / 32; ++c)
@@ -304,6 +309,13 @@ __device__ __forceinline__ void park_span(uint32_t tmem_addr, uint32_t* block, i
 #pragma unroll
         for(int q = 0; q < 8; ++q)
             __stcg(dst + (c * 8 + q) * 32, make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]));
+    }
+    if(flag)
+    {
+        __threadfence();
+        __syncwarp();
+        if(lane == 0)
+            atomicExch(flag, 1u);
     }
 }
 
@@ -365,10 +377,21 @@ __device__ __forceinline__ void reduce_chunk(uint32_t (&v)[32], const uint32_t* 
     }
 }
 
-// Balanced K ranges: adds chunk `c` of this lane's row of `n` parked accumulators (parking slots `block`,
-// `block + stride`, ...: increasing k) to the accumulator values just read from tensor memory.
+// Balanced K ranges: waits until the warp with this warp's rows and columns in another unit has parked its block.
+// The flag is cleared for the next launch (this warp is its only reader).  Returns false when the wait gave up.
+__device__ __forceinline__ bool wait_parked(uint32_t* flag, int lane, const WaitCtx& wc)
+{
+    bool ok = bounded_wait_counter(flag, 1u, wc);
+    ok      = __all_sync(0xffffffffu, ok);
+    if(ok && lane == 0)
+        __stcg(flag, 0u);
+    return ok;
+}
+
+// Adds chunk `c` of this lane's row of a parked accumulator (`block`: the block of the warp that parked it) to the
+// accumulator values in `v`.
 template <int KIND>
-__device__ __forceinline__ void fixup_chunk(uint32_t (&v)[32], const uint32_t* block, int c, int lane, int n, int64_t stride)
+__device__ __forceinline__ void fixup_chunk(uint32_t (&v)[32], const uint32_t* block, int c, int lane)
 {
     auto add = [](uint32_t a, uint32_t b) {
         if constexpr(KIND == KIND_I8)
@@ -376,31 +399,51 @@ __device__ __forceinline__ void fixup_chunk(uint32_t (&v)[32], const uint32_t* b
         else
             return __float_as_uint(__uint_as_float(a) + __uint_as_float(b));
     };
-    // eight loads of 16 bytes per thread in flight; two accumulators at a time would not fit the register budget
-    for(int s = 0; s < n; ++s)
+    // eight loads of 16 bytes per thread in flight; two chunks at a time would not fit the register budget
+    const uint4* src = reinterpret_cast<const uint4*>(block) + lane + c * 8 * 32;
+    uint4 t[8];
+#pragma unroll
+    for(int q = 0; q < 8; ++q)
+        t[q] = __ldcg(src + q * 32);
+#pragma unroll
+    for(int q = 0; q < 8; ++q)
     {
-        const uint4* src = reinterpret_cast<const uint4*>(block + s * stride) + lane + c * 8 * 32;
-        uint4 t[8];
-#pragma unroll
-        for(int q = 0; q < 8; ++q)
-            t[q] = __ldcg(src + q * 32);
-#pragma unroll
-        for(int q = 0; q < 8; ++q)
-        {
-            v[4 * q]     = add(v[4 * q], t[q].x);
-            v[4 * q + 1] = add(v[4 * q + 1], t[q].y);
-            v[4 * q + 2] = add(v[4 * q + 2], t[q].z);
-            v[4 * q + 3] = add(v[4 * q + 3], t[q].w);
-        }
+        v[4 * q]     = add(v[4 * q], t[q].x);
+        v[4 * q + 1] = add(v[4 * q + 1], t[q].y);
+        v[4 * q + 2] = add(v[4 * q + 2], t[q].z);
+        v[4 * q + 3] = add(v[4 * q + 3], t[q].w);
     }
 }
 
+// Balanced K ranges, tiles in three parts: while the main loop of the head still runs, its epilogue warps copy the
+// accumulator that the unit after next parked (the tile's last part, parked early) into the free half of the tensor
+// memory, so that the final epilogue reads only one parked accumulator from L2.
+__device__ __forceinline__ void prefetch_parked(uint32_t tmem_addr, const uint32_t* block, int ncols, int lane)
+{
+    for(int c = 0; c < ncols / 32; ++c)
+    {
+        const uint4* src = reinterpret_cast<const uint4*>(block) + lane + c * 8 * 32;
+        uint32_t v[32];
+#pragma unroll
+        for(int q = 0; q < 8; ++q)
+        {
+            const uint4 t = __ldcg(src + q * 32);
+            v[4 * q] = t.x, v[4 * q + 1] = t.y, v[4 * q + 2] = t.z, v[4 * q + 3] = t.w;
+        }
+        tmem_st_32x32b_x32(tmem_addr + c * 32, v);
+    }
+    tmem_st_wait();
+}
+
 // REDUCE = true: the accumulator comes from the parked K slices (`parked` = this warp's block in slice 0)
-// instead of tensor memory.  FIX = true: `ks` parked accumulators are added to the one in tensor memory.
+// instead of tensor memory.  FIX = true (balanced K ranges): the parked accumulator `parked` and then a second one -
+// prefetched into tensor memory at `tmem_pre` (`has_pre`), or still in L2 (`parked2`) - are added, in this order, to
+// the one at `tmem_addr`.
 template <int EPI, int KIND, bool REDUCE = false, bool FIX = false>
 __device__ __forceinline__ void epilogue_span(uint32_t tmem_addr, const EpilogueArgs& ea, StoreStage& st, int lane,
                                               int64_t m, bool row_ok, int64_t n_begin, int64_t n_end, bool vec_ok,
-                                              const uint32_t* parked = nullptr, int ks = 0, int64_t slice_stride = 0)
+                                              const uint32_t* parked = nullptr, int ks = 0, int64_t slice_stride = 0,
+                                              bool has_pre = false, uint32_t tmem_pre = 0, const uint32_t* parked2 = nullptr)
 {
     using T          = typename std::conditional<KIND == KIND_BF16, __nv_bfloat16, __half>::type;
     constexpr int ND = (KIND == KIND_I8) ? 0 : epi_num_d(EPI);
@@ -436,7 +479,20 @@ __device__ __forceinline__ void epilogue_span(uint32_t tmem_addr, const Epilogue
             tmem_ld_32x32b_x32(tmem_addr + c * 32, v);
             tmem_ld_wait();
             if constexpr(FIX)
-                fixup_chunk<KIND>(v, parked, c, lane, ks, slice_stride);
+            {
+                fixup_chunk<KIND>(v, parked, c, lane);
+                if(parked2 != nullptr)
+                    fixup_chunk<KIND>(v, parked2, c, lane);
+                else if(has_pre)
+                {
+                    uint32_t w[32];
+                    tmem_ld_32x32b_x32(tmem_pre + c * 32, w);
+                    tmem_ld_wait();
+#pragma unroll
+                    for(int i = 0; i < 32; ++i)
+                        v[i] = (KIND == KIND_I8) ? v[i] + w[i] : __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(w[i]));
+                }
+            }
         }
         if(vec_ok && ncols == 32) // warp-uniform: a whole segment leaves through the staged TMA store
         {
@@ -1098,6 +1154,7 @@ __global__ void __launch_bounds__(threads_for<MODE>(), 1) contraction_kernel(con
             // K-split tail: this warp's block of the tail tile in slice 0 of the scratch buffer
             // ([tail tile][slice][CTA of the pair][epilogue warp][32 rows x span columns])
             const uint32_t* parked = nullptr;
+            uint32_t* fix_flags    = nullptr;
             if constexpr(KSPLIT)
             {
                 // (balanced K ranges: [parking slot = unit][CTA of the pair][epilogue warp][...], wi.slice = 0)
@@ -1105,7 +1162,9 @@ __global__ void __launch_bounds__(threads_for<MODE>(), 1) contraction_kernel(con
                 const uint32_t* tail_base = P.ks_partials + static_cast<int64_t>(wi.tail) * per_tail * TILE_M * BN;
                 if(wi.kind == ITEM_KSLICE || wi.fix > 0)
                     parked = tail_base + (cta_rank * NUM_EPI_WARPS + half * 4 + quarter) * (32 * (BN / 2));
-                else if(wi.kind == ITEM_REDUCE)
+                if(P.plan.stream_k != 0) // the flag of this warp's block in parking slot wi.tail
+                    fix_flags = P.ks_flags + (wi.tail * CG + cta_rank) * NUM_EPI_WARPS + half * 4 + quarter;
+                if(wi.kind == ITEM_REDUCE)
                 {
                     // chunks of 32 columns: the tile has BN / 32, each parking warp holds BN / 64 of them
                     const int id0 = (wi.slice * wi.width + half * span) / 32; // first chunk this warp sums
@@ -1137,6 +1196,34 @@ __global__ void __launch_bounds__(threads_for<MODE>(), 1) contraction_kernel(con
             const int acc            = iter & 1;
             const uint32_t acc_phase = (iter >> 1) & 1;
             ++iter;
+            uint32_t tmem_pre       = 0;
+            bool has_pre            = false;
+            const uint32_t* parked2 = nullptr; // the second parked part, where it cannot be prefetched
+            if constexpr(KSPLIT)
+            {
+                if(wi.fix >= 2)
+                {
+                    // A tile in three parts.  The part of the unit after next is the tile's last: parked early.  If
+                    // this head is the last item of its unit, the other accumulator buffer is free (this warp has
+                    // drained its part of it) and takes that part while the head's main loop still runs.
+                    CKB_TR(const long long trq0 = clock64();)
+                    ok = wait_parked(fix_flags + CG * NUM_EPI_WARPS, lane, wc);
+                    if(!ok)
+                        break;
+                    bool last_item = true;
+                    for(int later = slot + 1; last_item && later < P.plan.num_slots; ++later)
+                        last_item = work_item(later).kind == ITEM_NONE;
+                    if(last_item)
+                    {
+                        has_pre  = true;
+                        tmem_pre = tmem_base + (acc ^ 1) * BN + half * span + (static_cast<uint32_t>(quarter * 32) << 16);
+                        prefetch_parked(tmem_pre, parked + static_cast<int64_t>(TILE_M) * BN, span, lane);
+                    }
+                    else
+                        parked2 = parked + static_cast<int64_t>(TILE_M) * BN; // whole tiles follow: both buffers are in use
+                    CKB_TR(tr_ctr += clock64() - trq0;)
+                }
+            }
             CKB_TR(const long long tr0 = clock64();)
             ok = bounded_wait(tmem_full_bar(acc), acc_phase, wc, WAIT_TMEM_FULL);
             CKB_TR(tr_wait += clock64() - tr0;)
@@ -1151,30 +1238,24 @@ __global__ void __launch_bounds__(threads_for<MODE>(), 1) contraction_kernel(con
             else if(KSPLIT && wi.kind == ITEM_KSLICE)
             {
                 CKB_TR(const long long trp0 = clock64();)
-                park_span(tmem_addr, const_cast<uint32_t*>(parked) + static_cast<int64_t>(wi.slice) * TILE_M * BN, span, lane);
+                park_span(tmem_addr, const_cast<uint32_t*>(parked) + static_cast<int64_t>(wi.slice) * TILE_M * BN, span, lane,
+                          fix_flags);
                 CKB_TR(tr_park += clock64() - trp0;)
             }
             else if(KSPLIT && wi.fix > 0)
             {
-                // the rest of this tile's K range was parked by the next `fix` units as the first item of their runs
+                // the rest of this tile's K range was parked by the next `fix` units as the first item of their runs:
+                // the next unit's part is read back from L2 here, the part of the unit after next (if any) is
+                // already in tensor memory
                 if constexpr(KSPLIT)
                 {
-                    uint32_t* counter     = P.ks_counters + wi.ctr;
-                    const uint32_t target = static_cast<uint32_t>(wi.fix) * NUM_EPI_WARPS * CG;
                     CKB_TR(const long long trc0 = clock64();)
-                    ok                    = bounded_wait_counter(counter, target, wc);
-                    ok                    = __all_sync(0xffffffffu, ok);
+                    ok = wait_parked(fix_flags, lane, wc);
                     CKB_TR(const long long trc1 = clock64(); tr_ctr += trc1 - trc0;)
                     if(ok)
-                    {
-                        epilogue_span<EPI, KIND, false, true>(tmem_addr, ea, st, lane, m, row_ok, n_begin, n_end, vec_ok,
-                                                              parked, wi.fix, static_cast<int64_t>(TILE_M) * BN);
-                        CKB_TR(tr_fix += clock64() - trc1;)
-                        // the last of this tile's warps (both CTAs of a pair) leaves the counter at zero
-                        __syncwarp();
-                        if(lane == 0 && atomicAdd(counter, 1u) + 1u == target + NUM_EPI_WARPS * CG)
-                            atomicExch(counter, 0u);
-                    }
+                        epilogue_span<EPI, KIND, false, true>(tmem_addr, ea, st, lane, m, row_ok, n_begin, n_end, vec_ok, parked,
+                                                              0, 0, has_pre, tmem_pre, parked2);
+                    CKB_TR(tr_fix += clock64() - trc1;)
                 }
             }
             else
@@ -1194,6 +1275,8 @@ __global__ void __launch_bounds__(threads_for<MODE>(), 1) contraction_kernel(con
                 continue; // summed after the cluster barrier below
             if constexpr(KSPLIT)
             {
+                if(wi.kind == ITEM_KSLICE && P.plan.stream_k != 0)
+                    continue; // published chunk by chunk
                 if(wi.kind == ITEM_KSLICE)
                 {
                     // publish the parked slice: stores -> fence -> one arrival per warp

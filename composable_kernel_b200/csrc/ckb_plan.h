@@ -458,18 +458,23 @@ struct GemmPlan
 constexpr int kMaxTailTiles = 1024; // tail-tile counters at the front of the scratch buffer
 
 // Balanced K ranges (see decode_work): the k blocks of the tiles are laid end to end and dealt out evenly.  The
-// library takes the plan by itself only for one partly filled wave of 256-wide tiles with a long K, by this cost
-// model in SM cycles, fitted to timings of 1280 x 2048 x K (K = 4096 ... 16384) on a B200:
-//   one CTA per 128 x 256 tile, tiles <= SMs        558 per k block + 5600
-//   balanced, one CTA per tile, every SM loading     729 per k block + 17700
-//   balanced, CTA pairs on 256 x 256 tiles           606 per k block + 22200
-// With every SM loading a k block costs more, and the last epilogue of a unit grows by the wait for the unit that
-// parks last and by the parked accumulators it reads back from L2.  The units' K ranges are out of step, so an
-// operand panel is fetched once per tile that uses it instead of once per wave: beyond what stays in L2 the plan
-// loses (512 x 8192 x 16384 with one CTA per tile: four times the DRAM traffic, 184 us against 104).
+// library takes the plan by itself only for one partly filled wave of 256-wide tiles, by this cost model in SM
+// cycles, fitted to timings of 1280 x 2048 x K (K = 4096 ... 8192; 80 tiles of 128 x 256) on a B200:
+//   one CTA per 128 x 256 tile, tiles <= SMs        572 per k block +  5300
+//   CTA pairs on 256 x 256 tiles, tiles <= pairs     516 per k block + 10500
+//   balanced, one CTA per tile, every SM loading     644 per k block + 19000
+//   balanced, CTA pairs                              509 per k block + 24100
+// The fixed cost of the balanced plans is the end of the launch: a unit whose whole run is the middle of a tile
+// parks its accumulator when everyone else is done (stores, fence, flag: 6000 cycles), and the unit with the head of
+// that tile then reads it back (3600) before its epilogue.  The units' K ranges are out of step, so an operand panel
+// is fetched once per tile that uses it instead of once per wave: beyond what stays in L2 the plan loses
+// (512 x 8192 x 16384 with one CTA per tile: four times the DRAM traffic, 184 us against 104).
 constexpr int kBalancedGainPct = 93; // taken when its estimate is at most this share of the plain plan's
-inline int64_t est_plain_wave(int num_kb, int cg) { return static_cast<int64_t>(num_kb) * (cg == 2 ? 480 : 558) + 5600; }
-inline int64_t est_balanced(int64_t run_kb, int cg) { return cg == 2 ? run_kb * 606 + 22200 : run_kb * 729 + 17700; }
+inline int64_t est_plain_wave(int num_kb, int cg)
+{
+    return cg == 2 ? static_cast<int64_t>(num_kb) * 516 + 10500 : static_cast<int64_t>(num_kb) * 572 + 5300;
+}
+inline int64_t est_balanced(int64_t run_kb, int cg) { return cg == 2 ? run_kb * 509 + 24100 : run_kb * 644 + 19000; }
 inline int64_t balanced_operand_limit(int cg) { return cg == 2 ? (128ll << 20) : (64ll << 20); }
 inline int64_t balanced_run_kb(int64_t tiles, int num_kb, int64_t units)
 {
