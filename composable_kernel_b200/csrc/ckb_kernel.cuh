@@ -524,14 +524,51 @@ __device__ __forceinline__ void epilogue_span(uint32_t tmem_addr, const Epilogue
     }
 }
 
-// ---- cluster K split: accumulators through shared memory, summed over distributed shared memory ----------------
-// Layout of a CTA's raw accumulator tile in its own shared memory (the pipeline stages, free once the main loop is
-// done): [quad of 4 columns][row] of 16 bytes, so that a warp (32 consecutive rows) writes and reads 512 contiguous
-// bytes per instruction.
+// ---- cluster K split: accumulators summed over distributed shared memory ------------------------------------------
+// CTA r of the cluster sums column part r (BN / KS columns) of the tile.  Two ways of getting the slices there, both
+// through the pipeline stages, which are free once every main loop of the cluster is over:
+//   push  every CTA sends each quad of 4 columns of its raw accumulator straight to the CTA that owns the quad's part
+//         (`st.shared::cluster`, fire and forget), into the slot of its own K slice there: [slice = sending CTA][quad
+//         of the part][row] of 16 bytes.  Barrier before (the stages of the peers must be free), barrier after (release
+//         / acquire), then each CTA finds all slices of its part in its own shared memory.
+//   pull  every CTA keeps its accumulator at home ([quad][row] over all BN columns), one barrier, and CTA r reads its
+//         part from every peer with `ld.shared::cluster` (latency bound: 16 reads in flight per thread); a barrier at
+//         the exit keeps the shared memory alive until the peers have read it.
+// Same box, 128 x 128 x 8192 with 8 CTAs per tile: 10.2 us pull, 9.6 push; 768 x 768 x 4096, 2 x 64-wide: 12.3 / 11.95;
+// 1024 x 1024 x 8192, 4 x 256-wide: 19.1 / 20.25 (96 KiB of remote stores per CTA with the whole machine at it).  Push
+// is used for clusters of 8 and for 64-wide tiles, pull for 2 and 4 CTAs on 128- and 256-wide tiles.
+// In both a warp (32 consecutive rows) moves 512 contiguous bytes per instruction.
+__device__ __forceinline__ bool cluster_push(int bn, int ks) { return ks == 8 || bn == 64; }
+__device__ __forceinline__ uint32_t part_slot_bytes(int pw) { return static_cast<uint32_t>(pw) * (BM * 4u); }
 __device__ __forceinline__ uint32_t partial_offset(int quad, int row) { return static_cast<uint32_t>(quad * BM + row) * 16u; }
 
-// One epilogue warp moves `ncols` (a multiple of 32) accumulator columns of its 32 rows from tensor memory to the tile.
-__device__ __forceinline__ void stash_span(uint32_t tmem_addr, uint32_t partial_base, int row, int col_begin, int ncols)
+// One epilogue warp sends `ncols` (a multiple of 32) accumulator columns of its 32 rows from tensor memory to their
+// owners.  `pw_shift` = log2 of the part width in columns (>= 4).
+__device__ __forceinline__ void stash_span(uint32_t tmem_addr, uint32_t partial_base, int my_rank, int pw_shift, int row,
+                                           int col_begin, int ncols)
+{
+    const uint32_t slot = partial_base + static_cast<uint32_t>(my_rank) * part_slot_bytes(1 << pw_shift);
+    for(int c = 0; c < ncols / 32; ++c)
+    {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem_addr + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for(int q = 0; q < 8; ++q)
+        {
+            const int col      = col_begin + c * 32 + q * 4;
+            const int owner    = col >> pw_shift;
+            const int quad     = (col - (owner << pw_shift)) >> 2;
+            const uint32_t dst = mapa_shared(slot + partial_offset(quad, row), static_cast<uint32_t>(owner));
+            asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v[4 * q]), "r"(v[4 * q + 1]),
+                         "r"(v[4 * q + 2]), "r"(v[4 * q + 3])
+                         : "memory");
+        }
+    }
+}
+
+// pull: one epilogue warp moves `ncols` (a multiple of 32) accumulator columns of its 32 rows to this CTA's own tile
+__device__ __forceinline__ void stash_span_local(uint32_t tmem_addr, uint32_t partial_base, int row, int col_begin, int ncols)
 {
     for(int c = 0; c < ncols / 32; ++c)
     {
@@ -557,11 +594,17 @@ __device__ __forceinline__ uint4 ld_cluster_v4(uint32_t cluster_addr)
     return v;
 }
 
-// CTA `rank` of a cluster of KS CTAs sums column part `rank` (BN / KS columns) of the tile over the accumulators
-// of all CTAs of the cluster, in slice order (deterministic), applies the epilogue and writes E.  `t` = 0 .. 255
-// indexes the epilogue threads; consecutive threads take consecutive rows of one 16-column segment.  The reads
-// over distributed shared memory are latency bound: 16 of them (8 for two slices) are in flight per thread.
-template <int EPI, int KIND, int BN, int KS>
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+
+// CTA `rank` of a cluster of KS CTAs sums column part `rank` (BN / KS columns) of the tile over the slices that all
+// CTAs of the cluster sent it, in slice order (deterministic), applies the epilogue and writes E.  `t` = 0 .. 255
+// indexes the epilogue threads; consecutive threads take consecutive rows of one 16-column segment.
+template <int EPI, int KIND, int BN, int KS, bool PUSH>
 __device__ __forceinline__ void cluster_reduce_epilogue(const KernelParams& P, const WorkItem& wi, uint32_t partial_base,
                                                         int rank, int t)
 {
@@ -575,7 +618,7 @@ __device__ __forceinline__ void cluster_reduce_epilogue(const KernelParams& P, c
     uint32_t peer[KS];
 #pragma unroll
     for(int s = 0; s < KS; ++s)
-        peer[s] = mapa_shared(partial_base, static_cast<uint32_t>(s));
+        peer[s] = PUSH ? 0u : mapa_shared(partial_base, static_cast<uint32_t>(s));
     for(int i = t; i < BM * SEGS; i += 32 * NUM_EPI_WARPS)
     {
         const int seg = i >> 7, row = i & (BM - 1);
@@ -590,7 +633,12 @@ __device__ __forceinline__ void cluster_reduce_epilogue(const KernelParams& P, c
             for(int q = 0; q < QG; ++q)
 #pragma unroll
                 for(int s = 0; s < KS; ++s)
-                    part[q][s] = ld_cluster_v4(peer[s] + partial_offset((col0 >> 2) + g * QG + q, row));
+                {
+                    if constexpr(PUSH)
+                        part[q][s] = ld_shared_v4(partial_base + s * part_slot_bytes(PW) + partial_offset(seg * 4 + g * QG + q, row));
+                    else
+                        part[q][s] = ld_cluster_v4(peer[s] + partial_offset((col0 >> 2) + g * QG + q, row));
+                }
 #pragma unroll
             for(int q = 0; q < QG; ++q)
             {
@@ -1234,7 +1282,10 @@ __global__ void __launch_bounds__(threads_for<MODE>(), 1) contraction_kernel(con
             const uint32_t tmem_addr =
                 tmem_base + acc * BN + half * span + (static_cast<uint32_t>(quarter * 32) << 16);
             if constexpr(CK)
-                stash_span(tmem_addr, base_addr, quarter * 32 + lane, half * span, span);
+            {
+                // the accumulator leaves after the cluster barrier below: the pipeline stages it goes to, in this
+                // CTA and in its peers, are in use until every main loop of the cluster is over
+            }
             else if(KSPLIT && wi.kind == ITEM_KSLICE)
             {
                 CKB_TR(const long long trp0 = clock64();)
@@ -1341,33 +1392,52 @@ __global__ void __launch_bounds__(threads_for<MODE>(), 1) contraction_kernel(con
         })
     }
 
+    bool ck_pull = false;
     if constexpr(CK)
     {
-        // Every CTA of the cluster has its accumulator in shared memory (release / acquire at cluster scope); then
-        // each sums its column part over all of them.  A CTA that gave up on a wait still takes part in both
-        // barriers; its part is skipped and the status word tells the host.
-        cluster_sync_all();
-        if(warp >= 2 && misc[1] == 0)
+        // A CTA that gave up on a wait still takes part in every barrier; it hands over nothing, the sums that miss
+        // its slice are wrong, and the status word tells the host.
+        const bool push = cluster_push(BN, P.plan.ksplit);
+        ck_pull         = !push;
+        const bool epi  = warp >= 2 && warp < 2 + NUM_EPI_WARPS && misc[1] == 0;
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
+        constexpr int span = BN / 2;
+        const uint32_t tmem_addr = tmem_base + half * span + (static_cast<uint32_t>(quarter * 32) << 16);
+        if(push)
+        {
+            // First barrier: the main loop of every CTA of the cluster is over (the epilogue warps get here only
+            // once their accumulator is complete), so the pipeline stages are free everywhere.
+            cluster_sync_all();
+            if(epi)
+            {
+                tc_fence_after_sync();
+                stash_span(tmem_addr, base_addr, ck_rank, 31 - __clz(BN / P.plan.ksplit), quarter * 32 + lane, half * span, span);
+            }
+        }
+        else if(epi)
+            stash_span_local(tmem_addr, base_addr, quarter * 32 + lane, half * span, span);
+        cluster_sync_all(); // every slice is where it will be read (release / acquire at cluster scope)
+        if(warp >= 2 && warp < 2 + NUM_EPI_WARPS && misc[1] == 0)
         {
             const WorkItem wi = work_item(0);
             const int t       = static_cast<int>(threadIdx.x) - 64;
             if constexpr(BN >= 128)
                 if(P.plan.ksplit == 8)
-                    cluster_reduce_epilogue<EPI, KIND, BN, 8>(P, wi, base_addr, ck_rank, t);
+                    cluster_reduce_epilogue<EPI, KIND, BN, 8, true>(P, wi, base_addr, ck_rank, t);
             if(P.plan.ksplit == 4)
-                cluster_reduce_epilogue<EPI, KIND, BN, 4>(P, wi, base_addr, ck_rank, t);
+                cluster_reduce_epilogue<EPI, KIND, BN, 4, BN == 64>(P, wi, base_addr, ck_rank, t);
             else if(P.plan.ksplit == 2)
-                cluster_reduce_epilogue<EPI, KIND, BN, 2>(P, wi, base_addr, ck_rank, t);
+                cluster_reduce_epilogue<EPI, KIND, BN, 2, BN == 64>(P, wi, base_addr, ck_rank, t);
         }
     }
 
     // ---------------------------------------------------------------------- common exit
     tc_fence_before_sync();
-    if constexpr(CG == 2 || CK)
+    if(CG == 2 || ck_pull)
         cluster_sync_all(); // CG = 2: the leader's MMAs read the peer's shared memory until the very end;
-                            // CK: the other CTAs of the cluster read this one's accumulator tile
+                            // CK, pull: the other CTAs of the cluster read this one's accumulator tile
     else
-        __syncthreads();
+        __syncthreads();    // (CK, push: nothing touches a peer's shared memory after the second barrier)
     tc_fence_after_sync();
     if(warp == 1)
     {

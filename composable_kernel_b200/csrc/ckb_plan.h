@@ -367,11 +367,11 @@ struct WholeSplit
 //   most of the machine takes part;
 //   inside a cluster: the slice's main loop at 340 cycles per k block for 128-wide tiles and 500 for 256-wide ones
 //   (one CTA per tile pulls a 48 KiB stage per k block through L2), plus accumulator -> shared memory, cluster
-//   barrier and the reads over distributed shared memory: about 2500 cycles for a 64-wide tile, 4500 for a 128-wide
+//   barrier and the hand-over through distributed shared memory: about 1800 cycles for a 64-wide tile, 4500 for a 128-wide
 //   one, 10000 for a 256-wide one (the reads are latency bound and grow with the tile).
 constexpr int kParkedReduceCycles = 11000;
 inline int cluster_kb_cycles(int bn) { return bn >= 256 ? 500 : bn >= 128 ? 340 : 330; }
-inline int cluster_reduce_cycles(int bn) { return bn >= 256 ? 10000 : bn >= 128 ? 4500 : 2500; }
+inline int cluster_reduce_cycles(int bn) { return bn >= 256 ? 10000 : bn >= 128 ? 4500 : 1800; }
 
 // k blocks per slice of a `ks`-way cut (even, so that slices start on a stage boundary); 0 when a slice would be
 // empty or shorter than two k blocks.
