@@ -104,6 +104,23 @@ def test_random_large_gemm(cuda_device, seed):
     run_case(rng, draw_case(rng, big=True))
 
 
+@pytest.mark.parametrize("seed", range(24))
+def test_random_gemm_around_one_wave_of_tiles(cuda_device, seed):
+    """Half a wave to two waves of 128 x 256 / 256 x 256 tiles, where the plan for the partial wave matters: the
+    library's choice, balanced K ranges on single CTAs and on pairs, pinned tiles, no K split - bit for bit."""
+    rng = np.random.default_rng(9000 + seed)
+    M = int(rng.choice([640, 768, 1024, 1280, 1408, 1536, 1792, 2048, 2304])) - int(rng.choice([0, 0, 1, 17, 100]))
+    N = int(rng.choice([1024, 1536, 2048, 2560, 3072, 4096])) - int(rng.choice([0, 0, 8, 24, 200]))
+    K = int(rng.choice([1024, 2048, 2368, 4096])) - int(rng.choice([0, 0, 8, 64]))
+    tile = [0, capi.tile_config(256, 1, balanced=1), capi.tile_config(256, 2, balanced=1), capi.tile_config(128, 1, balanced=1),
+            capi.tile_config(256, 2), capi.tile_config(256, 1), capi.tile_config(no_ksplit=1), 0][rng.integers(0, 8)]
+    dtype = [capi.CKB_F16, capi.CKB_BF16][rng.integers(0, 2)]
+    op = [ck.PassThrough(), ck.Relu()][rng.integers(0, 2)]
+    per16 = 8
+    ld = lambda extent: (extent + per16 - 1) // per16 * per16
+    run_case(rng, (dtype, M, N, K, ROW, COL, ld(K), ld(K), ld(N), op, tile))
+
+
 @pytest.mark.parametrize("seed", range(80))
 def test_random_gemm_any_pitch_tile_configuration_and_k_batch(cuda_device, seed):
     rng = np.random.default_rng(7000 + seed)
