@@ -379,9 +379,9 @@ __device__ __forceinline__ void reduce_chunk(uint32_t (&v)[32], const uint32_t* 
 
 // Balanced K ranges: waits until the warp with this warp's rows and columns in another unit has parked its block.
 // The flag is cleared for the next launch (this warp is its only reader).  Returns false when the wait gave up.
-__device__ __forceinline__ bool wait_parked(uint32_t* flag, int lane, const WaitCtx& wc)
+__device__ __forceinline__ bool wait_parked(uint32_t* flag, int lane, const WaitCtx& wc, uint32_t extra)
 {
-    bool ok = bounded_wait_counter(flag, 1u, wc);
+    bool ok = bounded_wait_counter(flag, 1u + extra, wc); // extra: test hook, a value the flag never takes
     ok      = __all_sync(0xffffffffu, ok);
     if(ok && lane == 0)
         __stcg(flag, 0u);
@@ -1255,7 +1255,7 @@ __global__ void __launch_bounds__(threads_for<MODE>(), 1) contraction_kernel(con
                     // this head is the last item of its unit, the other accumulator buffer is free (this warp has
                     // drained its part of it) and takes that part while the head's main loop still runs.
                     CKB_TR(const long long trq0 = clock64();)
-                    ok = wait_parked(fix_flags + CG * NUM_EPI_WARPS, lane, wc);
+                    ok = wait_parked(fix_flags + CG * NUM_EPI_WARPS, lane, wc, P.ks_wait_extra);
                     if(!ok)
                         break;
                     bool last_item = true;
@@ -1301,7 +1301,7 @@ __global__ void __launch_bounds__(threads_for<MODE>(), 1) contraction_kernel(con
                 if constexpr(KSPLIT)
                 {
                     CKB_TR(const long long trc0 = clock64();)
-                    ok = wait_parked(fix_flags, lane, wc);
+                    ok = wait_parked(fix_flags, lane, wc, P.ks_wait_extra);
                     CKB_TR(const long long trc1 = clock64(); tr_ctr += trc1 - trc0;)
                     if(ok)
                         epilogue_span<EPI, KIND, false, true>(tmem_addr, ea, st, lane, m, row_ok, n_begin, n_end, vec_ok, parked,

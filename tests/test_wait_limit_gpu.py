@@ -1,7 +1,7 @@
 """GPU test of the kernel's give-up path: a bounded wait that runs out.
 
-Every wait inside the kernel (mbarriers, the arrival counters of the K-split reduction) is a polling loop with a time
-limit; when it expires the waiting thread records a code in the device status word, the roles of its CTA drain and
+Every wait inside the kernel (mbarriers, the arrival counters of the K-split reduction, the flags of the balanced K
+ranges) is a polling loop with a time limit; when it expires the waiting thread records a code in the device status word, the roles of its CTA drain and
 the kernel returns, so that the context stays usable.  Here a test hook makes the reductions of a K-split GEMM wait
 for one arrival more than will ever come (CKB_TEST_KSLICE_WAIT_EXTRA=1) under a limit of a few milliseconds
 (CKB_WAIT_LIMIT_MS): every copy and MMA of the launch completes normally, only that wait gives up.  Nothing faults,
@@ -67,6 +67,30 @@ for _ in range(2):
     g.MakeInvoker().Run(arg)
     rc, w = status()
     assert (rc, w) == (capi.CKB_OK, 0), (rc, w)
+    assert (e.cpu().numpy() == ref).all()
+
+# 4. the same for the flag waits of the balanced K ranges (pinned: 40 pair tiles dealt out over 74 pairs)
+M, N, K = 1280, 2048, 2048
+a = rng.integers(-5, 6, (M, K)).astype(np.float16)
+bt = rng.integers(-5, 6, (N, K)).astype(np.float16)
+da, db = torch.from_numpy(a).cuda(), torch.from_numpy(bt).cuda()
+e = torch.zeros((M, N), dtype=torch.float16, device="cuda")
+g = ck.DeviceGemm(capi.CKB_F16, tile_config=capi.tile_config(256, 2, balanced=1))
+arg = g.MakeArgument(da.data_ptr(), db.data_ptr(), e.data_ptr(), M, N, K, K, K, N)
+ref = oracle.gemm(a, bt.T)
+g.MakeInvoker().Run(arg)
+assert "balanced=0" not in capi.last_plan(), capi.last_plan()
+assert status() == (capi.CKB_OK, 0)
+assert (e.cpu().numpy() == ref).all()
+os.environ["CKB_TEST_KSLICE_WAIT_EXTRA"] = "1"
+g.MakeInvoker().Run(arg)
+rc, w = status()
+assert rc == capi.CKB_ERR_DEVICE and w >> 24 == 6, (rc, hex(w))
+del os.environ["CKB_TEST_KSLICE_WAIT_EXTRA"]
+for _ in range(2):                               # flags were cleared: bit exact again
+    e.zero_()
+    g.MakeInvoker().Run(arg)
+    assert status() == (capi.CKB_OK, 0)
     assert (e.cpu().numpy() == ref).all()
 print("wait-limit case passed")
 '''
