@@ -83,11 +83,12 @@ def test_gemm_supported_rules():
     # tile configurations: a pinned tile shape is part of the descriptor; malformed values are refused
     for tc in (capi.tile_config(256, 2), capi.tile_config(256, 1), capi.tile_config(128, 1), capi.tile_config(64, 1),
                capi.tile_config(256, 2, 1), capi.tile_config(0, 0, 1), capi.tile_config(kbatch=1), capi.tile_config(kbatch=4),
-               capi.tile_config(128, 1, kbatch=8)):
+               capi.tile_config(128, 1, kbatch=8), capi.tile_config(256, 2, balanced=1), capi.tile_config(balanced=1)):
         pinned = ck.DeviceGemm(tile_config=tc)
         assert pinned.IsSupportedArgument(pinned.MakeArgument(0x1000, 0x2000, 0x3000, 512, 512, 512, 512, 512, 512))
     for tc in (capi.tile_config(96, 1), capi.tile_config(128, 2), capi.tile_config(256, 3), -1, 1 << 28,
-               capi.tile_config(kbatch=3), capi.tile_config(256, 2, kbatch=4)):
+               capi.tile_config(kbatch=3), capi.tile_config(256, 2, kbatch=4), capi.tile_config(256, 1, kbatch=2, balanced=1),
+               capi.tile_config(no_ksplit=1, balanced=1), 1 << 18):
         pinned = ck.DeviceGemm(tile_config=tc)
         assert not pinned.IsSupportedArgument(pinned.MakeArgument(0x1000, 0x2000, 0x3000, 512, 512, 512, 512, 512, 512))
     assert not op.IsSupportedArgument(op.MakeArgument(0x1000, 0x2000, 0x3000, 0, 8, 8, 8, 8, 8))
