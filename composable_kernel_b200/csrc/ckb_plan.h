@@ -648,7 +648,7 @@ inline bool plan_gemm(const GemmPlanInput& in, GemmPlan* out)
     {
         const int64_t D = all_tiles < 2 * G ? 0 : ful - G, R = all_tiles - D;
         const int64_t W = balanced_run_kb(R, num_kb, G);
-        if(R <= kMaxTailTiles && W * 2 >= num_kb)
+        if(R <= kMaxTailTiles && W * 2 >= num_kb && R * num_kb < (1ll << 30)) // (unit, k block) positions are 32-bit
         {
             g.partial_bytes  = static_cast<size_t>(G) * (BM * cg) * bn * sizeof(uint32_t); // one parking slot per unit
             p.stream_k       = 1;
