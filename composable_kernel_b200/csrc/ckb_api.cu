@@ -854,6 +854,7 @@ static int gemm_run_impl(const ckb_gemm_desc* d_in, const BatchInfo& bi, void* s
     // more energy than the narrow MMAs it removes) - those keep the column slices.
     in.ks_pays    = d->ab_dtype != CKB_I8 && d->n_ds == 0;
     in.ks_allowed = !capturing;
+    in.bal_ok     = bi.batch == 0; // balanced K ranges: every plain GEMM (instances of their own where ks_pays is false)
     in.cluster_ok = true;
     {
         // asked once per device: how many clusters of 2 / 4 / 8 CTAs fit at the same time

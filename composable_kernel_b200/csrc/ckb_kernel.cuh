@@ -228,13 +228,21 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, cons
     }
 }
 
-// Kernel instances that carry the K-split tail: 16-bit GEMMs whose epilogue reads no D tensor (the host enables
-// it only for those; leaving the code out of the others keeps their epilogue inside the register budget).
+// Kernel instances that carry the K-split tail and the whole-problem split through the scratch: 16-bit GEMMs whose
+// epilogue reads no D tensor (the host enables them only for those; the reduction holds four parked slices in
+// registers next to the epilogue's state, and leaving it out of the others keeps their epilogue inside the register
+// budget).
 template <int MODE, int KIND, int EPI>
 struct HasKSplit
 {
     static constexpr bool value = MODE == MODE_GEMM && KIND != KIND_I8 && epi_num_d(EPI) == 0;
 };
+// Kernel variants (last template argument of the kernel).  The balanced K ranges need parking and a fix-up loop;
+// the D-less 16-bit GEMM kernels carry them anyway (they share the parking with the K-split tail), for the other
+// plain GEMMs - fused D epilogues, int8 - they are compiled into instances of their own, so that the kernels that
+// run the whole-tile plans keep their register budget (with the loops compiled in, the Add + Add + FastGelu kernel
+// spilled and lost 2.3 %, the int8 one 0.9 %).
+enum { VARIANT_PLAIN = 0, VARIANT_CLUSTER_K = 1, VARIANT_BALANCED = 2 };
 
 // One TMA box of a GEMM operand.  The operand maps of a batched GEMM are 3-D (the third coordinate is the
 // batch index); those of a plain GEMM and the per-group maps of MODE_GROUPED are 2-D.
@@ -435,15 +443,42 @@ __device__ __forceinline__ void prefetch_parked(uint32_t tmem_addr, const uint32
     tmem_st_wait();
 }
 
+// Balanced K ranges, the head of a tile: adds the accumulators that other units parked to the one in tensor memory
+// at `tmem_addr` and writes the sum back, 32 columns at a time: first the block `parked` of the next unit, then the
+// part of the unit after next - prefetched into tensor memory at `tmem_pre` (`has_pre`) or still in L2 (`parked2`).
+// In k order whatever the timing, so the result does not depend on it.  The normal epilogue runs afterwards.
+template <int KIND>
+__device__ __forceinline__ void fixup_span(uint32_t tmem_addr, const uint32_t* parked, const uint32_t* parked2, bool has_pre,
+                                           uint32_t tmem_pre, int ncols, int lane)
+{
+    for(int c = 0; c < ncols / 32; ++c)
+    {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(tmem_addr + c * 32, v);
+        tmem_ld_wait();
+        fixup_chunk<KIND>(v, parked, c, lane);
+        if(parked2 != nullptr)
+            fixup_chunk<KIND>(v, parked2, c, lane);
+        else if(has_pre)
+        {
+            uint32_t w[32];
+            tmem_ld_32x32b_x32(tmem_pre + c * 32, w);
+            tmem_ld_wait();
+#pragma unroll
+            for(int i = 0; i < 32; ++i)
+                v[i] = (KIND == KIND_I8) ? v[i] + w[i] : __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(w[i]));
+        }
+        tmem_st_32x32b_x32(tmem_addr + c * 32, v);
+    }
+    tmem_st_wait();
+}
+
 // REDUCE = true: the accumulator comes from the parked K slices (`parked` = this warp's block in slice 0)
-// instead of tensor memory.  FIX = true (balanced K ranges): the parked accumulator `parked` and then a second one -
-// prefetched into tensor memory at `tmem_pre` (`has_pre`), or still in L2 (`parked2`) - are added, in this order, to
-// the one at `tmem_addr`.
-template <int EPI, int KIND, bool REDUCE = false, bool FIX = false>
+// instead of tensor memory.
+template <int EPI, int KIND, bool REDUCE = false>
 __device__ __forceinline__ void epilogue_span(uint32_t tmem_addr, const EpilogueArgs& ea, StoreStage& st, int lane,
                                               int64_t m, bool row_ok, int64_t n_begin, int64_t n_end, bool vec_ok,
-                                              const uint32_t* parked = nullptr, int ks = 0, int64_t slice_stride = 0,
-                                              bool has_pre = false, uint32_t tmem_pre = 0, const uint32_t* parked2 = nullptr)
+                                              const uint32_t* parked = nullptr, int ks = 0, int64_t slice_stride = 0)
 {
     using T          = typename std::conditional<KIND == KIND_BF16, __nv_bfloat16, __half>::type;
     constexpr int ND = (KIND == KIND_I8) ? 0 : epi_num_d(EPI);
@@ -478,21 +513,6 @@ __device__ __forceinline__ void epilogue_span(uint32_t tmem_addr, const Epilogue
         {
             tmem_ld_32x32b_x32(tmem_addr + c * 32, v);
             tmem_ld_wait();
-            if constexpr(FIX)
-            {
-                fixup_chunk<KIND>(v, parked, c, lane);
-                if(parked2 != nullptr)
-                    fixup_chunk<KIND>(v, parked2, c, lane);
-                else if(has_pre)
-                {
-                    uint32_t w[32];
-                    tmem_ld_32x32b_x32(tmem_pre + c * 32, w);
-                    tmem_ld_wait();
-#pragma unroll
-                    for(int i = 0; i < 32; ++i)
-                        v[i] = (KIND == KIND_I8) ? v[i] + w[i] : __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(w[i]));
-                }
-            }
         }
         if(vec_ok && ncols == 32) // warp-uniform: a whole segment leaves through the staged TMA store
         {
@@ -728,14 +748,19 @@ __device__ __forceinline__ void cluster_reduce_epilogue(const KernelParams& P, c
 
 // EPI (the fused epilogue functor) is a template parameter: one functor per kernel keeps the
 // epilogue warps inside the 168-register budget that ten warps per SM leave.
-// CK = true: the cluster K split (MODE_GEMM, one CTA per tile): see decode_cluster_k in ckb_plan.h.
-template <int MODE, int KIND, int EPI, int BN, int STAGES, int CG, int KSUB, bool CK = false>
+// VARIANT_CLUSTER_K: the cluster K split (MODE_GEMM, one CTA per tile): see decode_cluster_k in ckb_plan.h.
+// VARIANT_BALANCED: see the enumeration.
+template <int MODE, int KIND, int EPI, int BN, int STAGES, int CG, int KSUB, int VARIANT = VARIANT_PLAIN>
 __global__ void __launch_bounds__(threads_for<MODE>(), 1) contraction_kernel(const __grid_constant__ KernelParams P)
 {
+    constexpr bool CK = VARIANT == VARIANT_CLUSTER_K;
     static_assert(!CK || (MODE == MODE_GEMM && CG == 1), "the cluster K split runs plain GEMM tiles on single CTAs");
+    static_assert(VARIANT != VARIANT_BALANCED || MODE == MODE_GEMM, "balanced K ranges are a plan of the plain GEMM");
     using L = SmemLayout<BN, STAGES, CG, KSUB>;
     static_assert(!CK || BN * BM * 4 <= STAGES * L::STAGE_BYTES, "the raw accumulator tile must fit in the stages");
-    constexpr bool KSPLIT = HasKSplit<MODE, KIND, EPI>::value && !CK;
+    constexpr bool KSPLIT = HasKSplit<MODE, KIND, EPI>::value && !CK;   // K-split tail / whole split through the scratch
+    constexpr bool BAL    = MODE == MODE_GEMM && !CK && (HasKSplit<MODE, KIND, EPI>::value || VARIANT == VARIANT_BALANCED);
+    constexpr bool PARK   = KSPLIT || BAL;                              // either: accumulators are parked
     constexpr int TILE_M  = BM * CG;
     constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
     constexpr int UMMA_K_BYTES   = 32; // 16 x 16-bit or 32 x 8-bit
@@ -777,7 +802,7 @@ __global__ void __launch_bounds__(threads_for<MODE>(), 1) contraction_kernel(con
         if constexpr(CK)
             return decode_cluster_k<BN>(P.plan, static_cast<int>(blockIdx.x) / P.plan.ksplit, ck_rank);
         else
-            return decode_work<MODE, BN, KSPLIT>(P.plan, P.groups, unit, num_units, slot);
+            return decode_work<MODE, BN, PARK>(P.plan, P.groups, unit, num_units, slot);
     };
 
     if(threadIdx.x == 0)
@@ -1203,7 +1228,7 @@ __global__ void __launch_bounds__(threads_for<MODE>(), 1) contraction_kernel(con
             // ([tail tile][slice][CTA of the pair][epilogue warp][32 rows x span columns])
             const uint32_t* parked = nullptr;
             uint32_t* fix_flags    = nullptr;
-            if constexpr(KSPLIT)
+            if constexpr(PARK)
             {
                 // (balanced K ranges: [parking slot = unit][CTA of the pair][epilogue warp][...], wi.slice = 0)
                 const int per_tail        = P.plan.stream_k != 0 ? 1 : P.plan.ksplit;
@@ -1212,7 +1237,7 @@ __global__ void __launch_bounds__(threads_for<MODE>(), 1) contraction_kernel(con
                     parked = tail_base + (cta_rank * NUM_EPI_WARPS + half * 4 + quarter) * (32 * (BN / 2));
                 if(P.plan.stream_k != 0) // the flag of this warp's block in parking slot wi.tail
                     fix_flags = P.ks_flags + (wi.tail * CG + cta_rank) * NUM_EPI_WARPS + half * 4 + quarter;
-                if(wi.kind == ITEM_REDUCE)
+                if(KSPLIT && wi.kind == ITEM_REDUCE)
                 {
                     // chunks of 32 columns: the tile has BN / 32, each parking warp holds BN / 64 of them
                     const int id0 = (wi.slice * wi.width + half * span) / 32; // first chunk this warp sums
@@ -1247,7 +1272,7 @@ __global__ void __launch_bounds__(threads_for<MODE>(), 1) contraction_kernel(con
             uint32_t tmem_pre       = 0;
             bool has_pre            = false;
             const uint32_t* parked2 = nullptr; // the second parked part, where it cannot be prefetched
-            if constexpr(KSPLIT)
+            if constexpr(BAL)
             {
                 if(wi.fix >= 2)
                 {
@@ -1286,26 +1311,28 @@ __global__ void __launch_bounds__(threads_for<MODE>(), 1) contraction_kernel(con
                 // the accumulator leaves after the cluster barrier below: the pipeline stages it goes to, in this
                 // CTA and in its peers, are in use until every main loop of the cluster is over
             }
-            else if(KSPLIT && wi.kind == ITEM_KSLICE)
+            else if(PARK && wi.kind == ITEM_KSLICE)
             {
                 CKB_TR(const long long trp0 = clock64();)
                 park_span(tmem_addr, const_cast<uint32_t*>(parked) + static_cast<int64_t>(wi.slice) * TILE_M * BN, span, lane,
                           fix_flags);
                 CKB_TR(tr_park += clock64() - trp0;)
             }
-            else if(KSPLIT && wi.fix > 0)
+            else if(BAL && wi.fix > 0)
             {
                 // the rest of this tile's K range was parked by the next `fix` units as the first item of their runs:
                 // the next unit's part is read back from L2 here, the part of the unit after next (if any) is
-                // already in tensor memory
-                if constexpr(KSPLIT)
+                // already in tensor memory; the sum goes back into the accumulator and the epilogue runs as usual
+                if constexpr(BAL)
                 {
                     CKB_TR(const long long trc0 = clock64();)
                     ok = wait_parked(fix_flags, lane, wc, P.ks_wait_extra);
                     CKB_TR(const long long trc1 = clock64(); tr_ctr += trc1 - trc0;)
                     if(ok)
-                        epilogue_span<EPI, KIND, false, true>(tmem_addr, ea, st, lane, m, row_ok, n_begin, n_end, vec_ok, parked,
-                                                              0, 0, has_pre, tmem_pre, parked2);
+                    {
+                        fixup_span<KIND>(tmem_addr, parked, parked2, has_pre, tmem_pre, span, lane);
+                        epilogue_span<EPI, KIND>(tmem_addr, ea, st, lane, m, row_ok, n_begin, n_end, vec_ok);
+                    }
                     CKB_TR(tr_fix += clock64() - trc1;)
                 }
             }
@@ -1324,11 +1351,11 @@ __global__ void __launch_bounds__(threads_for<MODE>(), 1) contraction_kernel(con
 
             if constexpr(CK)
                 continue; // summed after the cluster barrier below
-            if constexpr(KSPLIT)
+            if constexpr(PARK)
             {
                 if(wi.kind == ITEM_KSLICE && P.plan.stream_k != 0)
-                    continue; // published chunk by chunk
-                if(wi.kind == ITEM_KSLICE)
+                    continue; // published by its flag
+                if(KSPLIT && wi.kind == ITEM_KSLICE)
                 {
                     // publish the parked slice: stores -> fence -> one arrival per warp
                     __threadfence();

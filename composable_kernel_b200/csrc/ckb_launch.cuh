@@ -35,15 +35,18 @@ inline bool programmatic_launch_enabled()
     return on;
 }
 
-// CK: the cluster K-split instance of the tile shape (a cluster of p.plan.ksplit CTAs per tile).
-template <int MODE, int KIND, int EPI, int BN, int CG, bool CK = false>
+// VARIANT_CLUSTER_K: the cluster K-split instance of the tile shape (a cluster of p.plan.ksplit CTAs per tile);
+// VARIANT_BALANCED: the instance with the parking and fix-up loops of the balanced K ranges, for kernel families
+// whose plain instance does not carry them.
+template <int MODE, int KIND, int EPI, int BN, int CG, int VARIANT = VARIANT_PLAIN>
 cudaError_t launch_one(const KernelParams& p, int grid, cudaStream_t stream)
 {
+    constexpr bool CK    = VARIANT == VARIANT_CLUSTER_K;
     constexpr int STAGES = StagesFor<BN, CG, MODE>::value;
     constexpr int KSUB   = StagesFor<BN, CG, MODE>::ksub;
     constexpr int SMEM   = SmemLayout<BN, STAGES, CG, KSUB>::DYN_BYTES;
     static_assert(SMEM <= 227 * 1024, "pipeline does not fit in shared memory");
-    auto kern            = contraction_kernel<MODE, KIND, EPI, BN, STAGES, CG, KSUB, CK>;
+    auto kern            = contraction_kernel<MODE, KIND, EPI, BN, STAGES, CG, KSUB, VARIANT>;
     static bool attr_done[64] = {};
     int dev                   = 0;
     cudaError_t err           = cudaGetDevice(&dev);
@@ -98,14 +101,27 @@ cudaError_t launch_epi(int bn, int cg, const KernelParams& p, int grid, cudaStre
                 return cudaErrorInvalidValue;
             switch(bn)
             {
-            case 256: return launch_one<MODE, KIND, EPI, 256, 1, true>(p, grid, stream);
-            case 128: return launch_one<MODE, KIND, EPI, 128, 1, true>(p, grid, stream);
-            case 64: return launch_one<MODE, KIND, EPI, 64, 1, true>(p, grid, stream);
+            case 256: return launch_one<MODE, KIND, EPI, 256, 1, VARIANT_CLUSTER_K>(p, grid, stream);
+            case 128: return launch_one<MODE, KIND, EPI, 128, 1, VARIANT_CLUSTER_K>(p, grid, stream);
+            case 64: return launch_one<MODE, KIND, EPI, 64, 1, VARIANT_CLUSTER_K>(p, grid, stream);
             default: return cudaErrorInvalidValue;
             }
         }
         else
             return cudaErrorInvalidValue;
+    }
+    if(p.plan.stream_k != 0)
+    {
+        if constexpr(MODE != MODE_GEMM)
+            return cudaErrorInvalidValue;
+        else if constexpr(!HasKSplit<MODE, KIND, EPI>::value)
+        {
+            // balanced K ranges for a kernel family whose plain instances do not carry them: 256-wide tiles only
+            if(bn != 256 || (cg != 1 && cg != 2))
+                return cudaErrorInvalidValue;
+            return cg == 2 ? launch_one<MODE, KIND, EPI, 256, 2, VARIANT_BALANCED>(p, grid, stream)
+                           : launch_one<MODE, KIND, EPI, 256, 1, VARIANT_BALANCED>(p, grid, stream);
+        }
     }
     if(cg == 2 && bn == 256)
         return launch_one<MODE, KIND, EPI, 256, 2>(p, grid, stream);
@@ -130,7 +146,7 @@ cudaError_t cluster_capacity(int ks, int* clusters)
     constexpr int STAGES = StagesFor<BN, CG, MODE>::value;
     constexpr int KSUB   = StagesFor<BN, CG, MODE>::ksub;
     constexpr int SMEM   = SmemLayout<BN, STAGES, CG, KSUB>::DYN_BYTES;
-    auto kern            = contraction_kernel<MODE, KIND, EPI, BN, STAGES, CG, KSUB, true>;
+    auto kern            = contraction_kernel<MODE, KIND, EPI, BN, STAGES, CG, KSUB, VARIANT_CLUSTER_K>;
     cudaError_t err      = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if(err != cudaSuccess)
         return err;

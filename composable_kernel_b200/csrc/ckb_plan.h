@@ -440,6 +440,8 @@ struct GemmPlanInput
     int b_min     = 32;      // narrowest B slice (rows) one CTA loads
     bool ks_pays    = false; // 16-bit operands and an epilogue without D tensors (see the K-split notes)
     bool ks_allowed = false; // scratch may be used (not disabled, not capturing)
+    bool bal_ok     = false; // the kernel family has instances with the balanced K ranges for 256-wide tiles (every
+                             // plain GEMM; families with ks_pays carry them in all their instances)
     bool cluster_ok = false; // the kernel family has cluster K-split instances (plain GEMM)
     int cluster_cap[3] = {0, 0, 0}; // clusters of 2 / 4 / 8 CTAs the device holds at once
     TileConfig force;
@@ -560,8 +562,9 @@ inline bool plan_gemm(const GemmPlanInput& in, GemmPlan* out)
             }
         }
     }
-    bool balanced = false;
-    if(may_ks && whole_ksplit < 2 && in.batch == 0 && in.force.bn == 0 && bn == 256 && num_kb >= 8)
+    const bool may_bal = (in.ks_pays || in.bal_ok) && in.ks_allowed && !in.force.no_ksplit;
+    bool balanced      = false;
+    if(may_bal && whole_ksplit < 2 && in.batch == 0 && in.force.bn == 0 && bn == 256 && num_kb >= 8)
     {
         const int64_t t_now = ((in.M + BM * cg - 1) / (BM * cg)) * ((in.N + bn - 1) / bn);
         if(t_now < in.sm_count / cg)
@@ -643,8 +646,8 @@ inline bool plan_gemm(const GemmPlanInput& in, GemmPlan* out)
     }
     // Balanced K ranges: by the library's own choice (above) or because the caller asks for them - then also with
     // whole waves before the region, which takes in the last full wave so that every run covers at least a tile.
-    if(may_ks && p.ksplit < 2 && whole_ksplit < 2 && in.batch == 0 && bn >= 128 && rem > 0 && all_tiles * 2 > G && num_kb >= 8 &&
-       (balanced || in.force.stream_k != 0))
+    if(may_bal && p.ksplit < 2 && whole_ksplit < 2 && in.batch == 0 && (in.ks_pays ? bn >= 128 : bn == 256) && rem > 0 &&
+       all_tiles * 2 > G && num_kb >= 8 && (balanced || in.force.stream_k != 0))
     {
         const int64_t D = all_tiles < 2 * G ? 0 : ful - G, R = all_tiles - D;
         const int64_t W = balanced_run_kb(R, num_kb, G);

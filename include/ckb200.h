@@ -121,8 +121,9 @@ enum {
 /* The same with balanced K ranges: the k blocks of the tiles of the last one or two waves are laid end to end and
  * dealt out evenly over the CTAs (or CTA pairs), across tile boundaries; a CTA whose run ends inside a tile adds
  * the accumulators that the CTAs running the rest of that tile parked in the library's scratch, in k order
- * (16-bit GEMMs whose epilogue reads no D tensor, tiles of 128 or 256 columns; elsewhere the field falls back to
- * the library's choice).  The library also takes this plan by itself where its cost estimate says so. */
+ * (plain, non-batched GEMMs: 16-bit GEMMs whose epilogue reads no D tensor on tiles of 128 or 256 columns, int8 and
+ * D-reading epilogues on 256-wide tiles; elsewhere the field falls back to the library's choice).  The library also
+ * takes this plan by itself where its cost estimate says so. */
 #define CKB_TILE_CONFIG_BALANCED(bn, cg) ((bn) | ((cg) << 12) | (1 << 17))
 
 /* ---- GEMM: E = epilogue(A*B, D0, D1) ------------------------------------- */

@@ -220,8 +220,9 @@ static void check_gemm_plan(const GemmPlanInput& in)
     if(P.stream_k != 0)
     {
         ++g_balanced_plans;
-        REQUIRE(in.ks_pays && in.ks_allowed && !in.force.no_ksplit && in.batch == 0 && P.ksplit == 0 && P.split == 1, "balanced plan where it is not allowed");
-        REQUIRE(gp.grid == units * cg && bn >= 128, "a balanced launch uses every unit");
+        REQUIRE((in.ks_pays || in.bal_ok) && in.ks_allowed && !in.force.no_ksplit && in.batch == 0 && P.ksplit == 0 && P.split == 1,
+                "balanced plan where it is not allowed");
+        REQUIRE(gp.grid == units * cg && (in.ks_pays ? bn >= 128 : bn == 256), "a balanced launch uses every unit");
         REQUIRE(P.ks_full % units == 0 && P.ks_full + P.ks_rem == P.total_tiles && P.ks_rem <= kMaxTailTiles, "whole tiles %d + region %d", P.ks_full, P.ks_rem);
         REQUIRE(P.ks_kb % 2 == 0 && static_cast<int64_t>(P.ks_kb) * units >= static_cast<int64_t>(P.ks_rem) * P.num_kb &&
                     static_cast<int64_t>(P.ks_kb - 2) * units < static_cast<int64_t>(P.ks_rem) * P.num_kb, "run length %d", P.ks_kb);
@@ -255,7 +256,7 @@ static void check_gemm_plan(const GemmPlanInput& in)
         REQUIRE(P.num_slots == (P.total_work + units - 1) / units, "slots");
     }
     Coverage cov;
-    if(in.ks_pays)
+    if(in.ks_pays || in.bal_ok)
         walk_bn<MODE_GEMM, true>(bn, P, static_cast<const GroupTiles*>(nullptr), cg, gp.grid, cov);
     else
         walk_bn<MODE_GEMM, false>(bn, P, static_cast<const GroupTiles*>(nullptr), cg, gp.grid, cov);
@@ -398,6 +399,18 @@ int main()
                                     check_gemm_plan(in);
                                 }
                             in.force = TileConfig{};
+                            if(!in.ks_pays) // families with balanced instances only: the library's choice and the pinned plan
+                            {
+                                in.bal_ok = true;
+                                check_gemm_plan(in);
+                                for(int cgf : {0, 1, 2})
+                                {
+                                    in.force.cg = cgf, in.force.stream_k = 1;
+                                    check_gemm_plan(in);
+                                }
+                                in.force  = TileConfig{};
+                                in.bal_ok = false;
+                            }
                             for(int64_t batch : {2, 3, 40})
                             {
                                 in.batch = batch;
@@ -440,6 +453,9 @@ int main()
         in.M = 1280, in.N = 2048, in.num_kb = 128, in.ks_pays = false;
         plan_gemm(in, &gp);
         REQUIRE(gp.pp.stream_k == 0, "no balanced plan for kernels without the scratch path");
+        in.bal_ok = true; // fused epilogues, int8: instances of their own
+        plan_gemm(in, &gp);
+        REQUIRE(gp.pp.stream_k == 1 && gp.cg == 2 && gp.bn == 256 && gp.pp.ks_kb == 70, "balanced instances of the other families");
     }
     // grouped tables
     std::mt19937 rng(1234);

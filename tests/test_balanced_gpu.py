@@ -97,15 +97,65 @@ def test_balanced_real_inputs_relu_and_bf16(cuda_device):
     np.testing.assert_array_equal(out, oracle.gemm(a16, b16.T))
 
 
-def test_balanced_flag_falls_back_where_the_kernel_family_has_no_scratch_path(cuda_device):
-    """int8 and D-reading epilogues keep their plans; the flag is not an error."""
+@pytest.mark.parametrize("cg", [1, 2])
+def test_balanced_int8_requantisation_bit_exact(cuda_device, cg):
+    """int8 GEMMs run the balanced plan in kernel instances of their own (256-wide tiles)."""
+    rng = np.random.default_rng(9 + cg)
+    M, N, K = 1280, 2048, 4096
+    a = rng.integers(-5, 6, (M, K)).astype(np.int8)
+    bt = rng.integers(-5, 6, (N, K)).astype(np.int8)
+    da, db = torch.from_numpy(a).cuda(), torch.from_numpy(bt).cuda()
+    e = torch.zeros((M, N), dtype=torch.int8, device="cuda")
+    fn = ck.RequantReluRequantRne(0.03, 14.0)
+    g = ck.DeviceGemm(capi.CKB_I8, tile_config=capi.tile_config(256, cg, balanced=1))
+    arg = g.MakeArgument(da.data_ptr(), db.data_ptr(), e.data_ptr(), M, N, K, K, K, N, None, None, fn)
+    assert g.IsSupportedArgument(arg), capi.last_error()
+    for _ in range(2):
+        g.MakeInvoker().Run(arg)
+    plan = capi.last_plan()
+    torch.cuda.synchronize()
+    assert ck.device_status() == 0
+    assert balanced_run_length(plan) > 0, plan
+    np.testing.assert_array_equal(e.cpu().numpy(), oracle.gemm(a, bt.T, fn.kind, fn.params))
+
+
+@pytest.mark.parametrize("cg", [1, 2])
+def test_balanced_with_fused_d_epilogue(cuda_device, cg):
+    """Add + Add + FastGelu (a bias row and a residual) on top of balanced K ranges: the parked parts are summed into
+    the accumulator in tensor memory, then the usual epilogue reads D0 and D1."""
+    rng = np.random.default_rng(21 + cg)
+    M, N, K = 1280 - 3, 2048, 2048
+    a = rng.uniform(-1, 1, (M, K)).astype(np.float16)
+    bt = rng.uniform(-1, 1, (N, K)).astype(np.float16)
+    d0 = rng.uniform(-1, 1, (N,)).astype(np.float16)
+    d1 = rng.uniform(-1, 1, (M, N)).astype(np.float16)
+    da, db, dd0, dd1 = (torch.from_numpy(x).cuda() for x in (a, bt, d0, d1))
+    e = torch.zeros((M, N), dtype=torch.float16, device="cuda")
+    op = ck.DeviceGemmMultipleD(tile_config=capi.tile_config(256, cg, balanced=1))
+    arg = op.MakeArgument(da.data_ptr(), db.data_ptr(), [dd0.data_ptr(), dd1.data_ptr()], e.data_ptr(), M, N, K,
+                          K, K, [0, N], N, None, None, ck.AddAddFastGelu())
+    assert op.IsSupportedArgument(arg), capi.last_error()
+    for _ in range(2):
+        op.MakeInvoker().Run(arg)
+    plan = capi.last_plan()
+    torch.cuda.synchronize()
+    assert ck.device_status() == 0
+    assert balanced_run_length(plan) > 0, plan
+    ref = oracle.gemm(a, bt.T, oracle.EPI_ADD_ADD_FASTGELU, None, np.broadcast_to(d0, (M, N)), d1)
+    bad, err = oracle.check_err(e.cpu().numpy(), ref)
+    assert bad == 0, (bad, err)
+
+
+def test_balanced_flag_falls_back_on_narrow_tiles_of_the_other_families(cuda_device):
+    """The balanced instances of int8 and D-reading kernels exist for 256-wide tiles; a pinned 128-wide tile keeps
+    its plan and the flag is not an error."""
     rng = np.random.default_rng(9)
     a = rng.integers(-5, 6, (1280, 1024)).astype(np.int8)
-    bt = rng.integers(-5, 6, (2048, 1024)).astype(np.int8)
+    bt = rng.integers(-5, 6, (1536, 1024)).astype(np.int8)
     da, db = torch.from_numpy(a).cuda(), torch.from_numpy(bt).cuda()
-    e = torch.zeros((1280, 2048), dtype=torch.int8, device="cuda")
-    g = ck.DeviceGemm(capi.CKB_I8, tile_config=capi.tile_config(256, 1, balanced=1))
-    arg = g.MakeArgument(da.data_ptr(), db.data_ptr(), e.data_ptr(), 1280, 2048, 1024, 1024, 1024, 2048)
+    e = torch.zeros((1280, 1536), dtype=torch.int8, device="cuda")
+    g = ck.DeviceGemm(capi.CKB_I8, tile_config=capi.tile_config(128, 1, balanced=1))
+    arg = g.MakeArgument(da.data_ptr(), db.data_ptr(), e.data_ptr(), 1280, 1536, 1024, 1024, 1024, 1536)
     assert g.IsSupportedArgument(arg), capi.last_error()
     g.MakeInvoker().Run(arg)
     torch.cuda.synchronize()
